@@ -1,0 +1,247 @@
+"""Regenerates the golden fixtures in this directory from the reference's own eager (CPU) lanes.
+
+Run from the repository root in a container that has the reference checked out:
+
+    python tests/golden/make_golden.py [--reference /path/to/entropack-checkout]
+
+The reference ships no golden vectors, so its eager lanes are the executable specification: every
+fixture holds a seeded input and the exact buffers / outputs the reference produced for it. The
+fixtures are what travels; the reference itself is never needed to run the tests.
+
+DFloat11 encode in the reference needs the third-party ``dahuffman`` package, which is not
+installed. A stand-in module exposing the four members the reference touches
+(``HuffmanCodec.from_frequencies``, ``get_code_table``, ``_table``, ``_eof``) is installed into
+``sys.modules``; its code table comes from the oracle's own Huffman builder, so codeword values are
+ours while every downstream byte (LUTs, bitstream, metadata) is produced by reference code.
+"""
+import argparse
+import sys
+import types
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+
+import oracle  # noqa: E402
+
+
+def install_huffman_stand_in():
+    class _EOF:
+        def __repr__(self):
+            return "_EOF"
+
+    eof = _EOF()
+
+    class HuffmanCodec:
+        def __init__(self, table):
+            self._table = table
+            self._eof = eof
+
+        @classmethod
+        def from_frequencies(cls, frequencies):
+            counts = np.zeros(256, dtype=np.int64)
+            for symbol, count in frequencies.items():
+                counts[int(symbol)] = int(count)
+            code_len, code_val = oracle.dfloat11_code(counts)
+            order = sorted((int(code_len[s]), int(code_val[s]), s) for s in range(257) if code_len[s] > 0)
+            table = {}
+            for bits, value, symbol in order:
+                table[eof if symbol == 256 else symbol] = (bits, value)
+            return cls(table)
+
+        def get_code_table(self):
+            return self._table
+
+    module = types.ModuleType("dahuffman")
+    module.HuffmanCodec = HuffmanCodec
+    sys.modules["dahuffman"] = module
+
+
+def as_numpy(buffers: dict) -> dict:
+    out = {}
+    for key, value in buffers.items():
+        tensor = value.detach().cpu().contiguous()
+        if tensor.dtype == torch.bfloat16:
+            tensor = tensor.view(torch.int16)
+        out[key] = tensor.numpy()
+    return out
+
+
+def raw_bytes(tensor: torch.Tensor) -> np.ndarray:
+    return tensor.detach().contiguous().reshape(-1).view(torch.uint8).numpy().copy()
+
+
+def tile_ans_cases():
+    g = torch.Generator().manual_seed(1234)
+    randn = lambda *shape: torch.randn(*shape, generator=g)  # noqa: E731
+    cases = {}
+    base = randn(96, 130) * 0.02
+    cases["bf16"] = (base.to(torch.bfloat16), {})
+    cases["fp16"] = (base.to(torch.float16), {})
+    cases["fp32"] = (base.clone(), {})
+    x = randn(75, 129)
+    cases["fp8_e4m3"] = ((x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn), {})
+    cases["int8"] = ((randn(64, 200) * 20).round().clamp(-127, 127).to(torch.int8), {})
+    cases["int32_small"] = ((randn(5000) * 40).round().to(torch.int32), {})
+    cases["uint8_noise"] = (torch.randint(0, 256, (9000,), generator=g, dtype=torch.uint8), {})
+    cases["int16_const_lane_pb12"] = (torch.randint(0, 200, (7001,), generator=g, dtype=torch.int16), {"probability_bits": 12})
+    cases["bf16_ragged_tile100"] = ((randn(1237) * 0.02).to(torch.bfloat16), {"tile_elements": 100, "probability_bits": 10})
+    cases["fp32_tile33"] = (randn(700) * 0.02, {"tile_elements": 33})
+    cases["int8_single"] = (torch.tensor([5], dtype=torch.int8), {})
+    cases["fp16_31"] = ((randn(31) * 0.02).to(torch.float16), {"tile_elements": 64})
+    cases["int64_mixed"] = ((randn(3000) * 1000).round().to(torch.int64), {})
+    big = randn(256, 1024)
+    cases["bf16_large"] = ((big * 0.02).to(torch.bfloat16), {})
+    cases["fp8_e4m3_large"] = ((big * (448.0 / big.abs().max())).to(torch.float8_e4m3fn), {})
+    return cases
+
+
+def make_tile_ans(ep, out_dir: Path):
+    for name, (tensor, options) in tile_ans_cases().items():
+        config = ep.TileANSConfig(execution_backend="eager", **options)
+        compressed = ep.compress(tensor, config)
+        assert compressed.compress_method == "tile_ans", (name, compressed.header)
+        restored = ep.decompress(compressed, config)
+        assert torch.equal(restored.view(torch.uint8), tensor.view(torch.uint8)), name
+        record = {f"buf_{k}": v for k, v in as_numpy(compressed.buffers).items()}
+        record["input_bytes"] = raw_bytes(tensor)
+        record["itemsize"] = np.array(tensor.element_size())
+        record["dtype"] = np.array(str(tensor.dtype).removeprefix("torch."))
+        record["shape"] = np.array(tensor.shape, dtype=np.int64)
+        record["tile_elements_arg"] = np.array(options.get("tile_elements", 0))
+        record["probability_bits_arg"] = np.array(options.get("probability_bits", 0))
+        if tensor.numel() < 50000:
+            record["blob"] = compressed.entropack_quant_state.numpy()
+        np.savez_compressed(out_dir / f"tile_ans_{name}.npz", **record)
+        print(f"tile_ans {name}: {compressed.actual_bpp:.3f} bpp, pb={int(compressed.buffers['layout'][1])}, "
+              f"modes={compressed.buffers['lane_modes'].tolist()}")
+
+
+def lattice_weight(rows, cols, seed, outlier_rows=0):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(rows, cols, generator=g) * 0.02
+    if outlier_rows:
+        picks = torch.randperm(rows, generator=g)[:outlier_rows]
+        w[picks] = torch.distributions.StudentT(3.0).sample((outlier_rows, cols)).to(torch.float32) * 0.02
+    return w
+
+
+def make_lattice(ep, out_dir: Path):
+    from entropack.schemes.lattice_rans import eager, rans
+
+    torch.manual_seed(99)  # StudentT sampling uses the global generator
+    cases = {
+        "bf16_2p3": (lattice_weight(64, 256, 5, 1).to(torch.bfloat16), 2.3, {}),
+        "bf16_3p5": (lattice_weight(64, 256, 5, 1).to(torch.bfloat16), 3.5, {}),
+        "bf16_4p0": (lattice_weight(64, 256, 5, 1).to(torch.bfloat16), 4.0, {}),
+        "bf16_6p0": (lattice_weight(64, 256, 5, 1).to(torch.bfloat16), 6.0, {}),
+        "bf16_4p0_pad": (lattice_weight(50, 203, 6).to(torch.bfloat16), 4.0, {"tile_elements": 2000}),
+        "bf16_subsample": (lattice_weight(300, 64, 7).to(torch.bfloat16), 4.0, {"scale_search_max_vectors": 800}),
+        "fp16_4p0": (lattice_weight(40, 128, 8).to(torch.float16), 4.0, {}),
+        "fp32_5p0": (lattice_weight(40, 128, 9), 5.0, {}),
+        "bf16_9p0_pb12": (lattice_weight(32, 128, 10).to(torch.bfloat16), 9.0, {}),
+        "bf16_6p0_outliers": (lattice_weight(128, 512, 12, 6).to(torch.bfloat16), 6.0, {}),
+        "bf16_10p5_wide": (lattice_weight(64, 512, 13, 4).to(torch.bfloat16), 10.5, {}),
+    }
+    w = lattice_weight(48, 128, 11)
+    scale = (w.abs().amax(dim=1) / 448.0).clamp(min=torch.finfo(torch.float32).eps)
+    cases["fp8_codes_5p0"] = ((w / scale.unsqueeze(1)).clamp(-448, 448).to(torch.float8_e4m3fn), 5.0, {})
+    cases["int8_codes_5p0"] = ((w / (w.abs().amax(dim=1, keepdim=True) / 127)).round().clamp(-127, 127).to(torch.int8), 5.0, {})
+    for name, (tensor, bpp, options) in cases.items():
+        config = ep.EntroPackLossyConfig(target_bpp=bpp, execution_backend="eager", **options)
+        compressed = ep.compress(tensor, config)
+        assert compressed.compress_method == "lattice_rans", (name, compressed.header)
+        restored = ep.decompress(compressed, config)
+        record = {f"buf_{k}": v for k, v in as_numpy(compressed.buffers).items()}
+        record["input_bytes"] = raw_bytes(tensor)
+        record["decoded_bytes"] = raw_bytes(restored)
+        record["dtype"] = np.array(str(tensor.dtype).removeprefix("torch."))
+        record["shape"] = np.array(tensor.shape, dtype=np.int64)
+        record["target_bpp"] = np.array(bpp)
+        record["actual_bpp"] = np.array(compressed.actual_bpp)
+        record["options"] = np.array(repr(options))
+        record["blob"] = compressed.entropack_quant_state.numpy()
+        rel = ((restored.float() - tensor.float()).norm() / tensor.float().norm()).item()
+        record["rel_l2"] = np.array(rel)
+        np.savez_compressed(out_dir / f"lattice_{name}.npz", **record)
+        print(f"lattice {name}: target {bpp} actual {compressed.actual_bpp:.4f} rel_l2 {rel:.4f} "
+              f"pb={int(compressed.buffers['layout'][1])} alpha_max={int(compressed.buffers['stream_meta'][:, 3].max())}")
+
+    # Sub-function pins: quantiser, normaliser, size model, stream encoder.
+    g = torch.Generator().manual_seed(4321)
+    y = torch.randn(4000, 8, generator=g) * 1.7
+    y[:500] = (torch.randint(-6, 7, (500, 8), generator=g).float() * 0.5)      # exact ties on the half-integer grid
+    y[500:700] = (torch.randint(-8, 9, (200, 8), generator=g).float() * 0.25)
+    point = eager.nearest_e8(y)
+    c, z0_6, m = eager.point_to_fields(point)
+    counts_list, freq_list = [], []
+    rng = np.random.default_rng(7)
+    for trial in range(60):
+        alphabet = int(rng.integers(1, 300))
+        table_bits = int(rng.integers(9, 13))
+        if trial % 3 == 0:
+            counts = rng.integers(0, 5, alphabet)
+        elif trial % 3 == 1:
+            counts = (rng.pareto(1.2, alphabet) * 50).astype(np.int64)
+        else:
+            counts = rng.integers(0, 100000, alphabet)
+        counts = counts.astype(np.int64)
+        if counts.sum() == 0:
+            counts[0] = 3
+        counts_list.append(np.concatenate([[table_bits, alphabet], counts]))
+        freq_list.append(rans.normalize_freq(counts, 1 << table_bits).astype(np.int64))
+    c_np, z_np, m_np = c.numpy(), z0_6.numpy(), m.numpy()
+    stats = eager._stream_stats(eager._coord_streams(c_np, z_np, m_np))
+    coded = [rans.coded_bytes(stats[0], stats[1], pb, te) for pb, te in ((11, 16384), (9, 4096), (12, 288))]
+    payload, states, offsets, meta, freq_tables = eager._encode_streams(c_np, z_np, m_np, 11, 2000)
+    np.savez_compressed(
+        out_dir / "lattice_units.npz", y=y.numpy(), c=c_np.astype(np.int32), z0_6=z_np.astype(np.int32),
+        m=m_np.astype(np.int32), normalize_inputs=np.concatenate(counts_list), normalize_outputs=np.concatenate(freq_list),
+        coded_bytes=np.array(coded), coded_args=np.array([[11, 16384], [9, 4096], [12, 288]]),
+        enc_payload=payload.astype(np.uint16), enc_states=states.astype(np.uint32), enc_offsets=offsets.astype(np.uint32),
+        enc_meta=meta.astype(np.int32), enc_freq=freq_tables.astype(np.uint16),
+    )
+    print("lattice units: coded_bytes", coded)
+
+
+def make_dfloat11(ep, out_dir: Path):
+    g = torch.Generator().manual_seed(77)
+    cases = {
+        "normal": (torch.randn(120, 173, generator=g) * 0.02).to(torch.bfloat16),
+        "wide": (torch.randn(30000, generator=g) * torch.exp(torch.randn(30000, generator=g) * 6)).to(torch.bfloat16),
+        "tiny": (torch.randn(7, generator=g)).to(torch.bfloat16),
+        "constant": torch.full((5000,), 0.5, dtype=torch.bfloat16),
+    }
+    for name, tensor in cases.items():
+        config = ep.DFloat11Config(execution_backend="eager")
+        compressed = ep.compress(tensor, config)
+        assert compressed.compress_method == "dfloat11", (name, compressed.header)
+        restored = ep.decompress(compressed, config)
+        assert torch.equal(restored.view(torch.int16), tensor.view(torch.int16)), name
+        record = {f"buf_{k}": v for k, v in as_numpy(compressed.buffers).items()}
+        record["input_bits"] = tensor.reshape(-1).view(torch.int16).numpy().view(np.uint16)
+        record["shape"] = np.array(tensor.shape, dtype=np.int64)
+        record["blob"] = compressed.entropack_quant_state.numpy()
+        np.savez_compressed(out_dir / f"dfloat11_{name}.npz", **record)
+        print(f"dfloat11 {name}: {compressed.actual_bpp:.3f} bpp, luts {tuple(compressed.buffers['luts'].shape)}")
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--reference", default="/root/reference")
+    args = parser.parse_args()
+    sys.path.insert(0, args.reference)
+    install_huffman_stand_in()
+    import entropack as ep
+
+    make_tile_ans(ep, HERE)
+    make_lattice(ep, HERE)
+    make_dfloat11(ep, HERE)
+
+
+if __name__ == "__main__":
+    main()
