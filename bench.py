@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the compression hot path: lossless Tile-ANS decode throughput.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+Workload ("c2_tile_ans_decode"): the four 8192 x 8192 tensors of the lossless benchmark config --
+fp8 e4m3 (N(0,1) scaled to amax 448), int8 (round(N(0,20^2)) clipped to +-127), fp16 and fp32
+(N(0,0.02^2)) -- seeded synthetic data, compressed once at set-up. One step decodes all four
+containers. Bytes per step = container bytes (header excluded) read once + dense bytes written once.
+
+  value      device-resident throughput: containers already in HBM, K steps timed with CUDA events
+             (one region per step, a 512 MB L2 flush between steps outside the timed regions).
+  e2e        the same decode through the public API starting from pinned HOST blobs: host->device
+             copy of each blob, decode, device->host copy of each dense result, all inside the timed
+             region.
+  roofline   per-launch CUDA-event timing of the decode kernel (the only kernel in the step):
+             algorithmic bytes / average launch time against the measured HBM copy bandwidth.
+  cpu_baseline / --impl reference
+             the CPU oracle (a C port of the reference's eager lane, OpenMP over tiles) decoding a
+             quarter-height sample of the same four tensors on the host cores.
+
+With N > 1 (torchrun, one rank per GPU) every rank decodes its own copy of the workload (weak
+scaling, no collective on the data path); the time is the max over ranks.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+KINDS = ("fp8_e4m3", "int8", "fp16", "fp32")
+SEEDS = {"fp8_e4m3": 1, "int8": 2, "fp16": 3, "fp32": 4}
+ROWS, COLS = 8192, 8192
+METRIC = "decode GB/s/GPU (HBM frac)"
+
+
+def make_tensor(kind: str, rows: int, cols: int, device) -> torch.Tensor:
+    generator = torch.Generator(device=device).manual_seed(SEEDS[kind])
+    x = torch.randn(rows, cols, generator=generator, device=device)
+    if kind == "fp8_e4m3":
+        return (x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn)
+    if kind == "int8":
+        return (x * 20).round().clamp(-127, 127).to(torch.int8)
+    if kind == "fp16":
+        return (x * 0.02).to(torch.float16)
+    return x * 0.02
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed regions run."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.lines: list[str] = []
+        self.process = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._drain, daemon=True)
+        self.thread.start()
+
+    def _drain(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(clocks)[len(clocks) // 2:] if clocks else []
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max_clock, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port on host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_workload(sample_rows: int):
+    import oracle
+
+    oracle.build()
+    work = []
+    for kind in KINDS:
+        tensor = make_tensor(kind, sample_rows, COLS, "cpu")
+        raw = tensor.view(torch.uint8).numpy().reshape(-1)
+        buffers = oracle.tile_ans_encode(raw, tensor.element_size(), 8192)
+        nbytes = sum(int(np.asarray(v).nbytes) for v in buffers.values()) + raw.nbytes
+        work.append((buffers, raw, nbytes))
+    return oracle, work
+
+
+def time_cpu(steps: int, warmup: int, sample_rows: int) -> dict:
+    oracle, work = cpu_workload(sample_rows)
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    total_bytes = sum(nbytes for _, _, nbytes in work)
+    for _ in range(warmup):
+        for buffers, _, _ in work:
+            oracle.tile_ans_decode(buffers)
+    begin = time.perf_counter()
+    for _ in range(steps):
+        for buffers, raw, _ in work:
+            out = oracle.tile_ans_decode(buffers)
+    elapsed = time.perf_counter() - begin
+    assert np.array_equal(out, work[-1][1])
+    return {
+        "value": total_bytes * steps / elapsed / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+        "sample": f"rows 0..{sample_rows - 1} of each of the four 8192x8192 tensors ({sample_rows}x{COLS} per dtype), "
+                  f"{steps} passes, OpenMP over tiles",
+        "ms_per_step": elapsed / steps * 1e3, "bytes_per_step": total_bytes,
+    }
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    result = time_cpu(args.steps, args.warmup, sample_rows=2048)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": result["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "c2_tile_ans_decode", "tensors": list(KINDS), "shape": [ROWS, COLS],
+                   "note": "reference is Python; its eager lane is timed through the C oracle port on host cores"},
+        "cpu_baseline": {k: result[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": result["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------
+# B200 arm
+# ------------------------------------------------------------------------------------------------
+def run_b200(args) -> None:
+    import entropack_b200 as ep
+    from entropack_b200 import _native
+    from entropack_b200.schemes.tile_ans import b200 as lane
+    from entropack_b200.schemes.tile_ans.format import TileBuffers, parse_layout_cached
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    distributed = world > 1
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    config = ep.TileANSConfig()
+    containers, launches, dense_bytes, stored_bytes = [], [], 0, 0
+    lib = _native.load()
+    stream = torch.cuda.current_stream(device)
+    for kind in KINDS:
+        tensor = make_tensor(kind, ROWS, COLS, device)
+        container = ep.compress(tensor, config)
+        assert container.compress_method == "tile_ans"
+        check = ep.decompress(container, config)
+        assert torch.equal(check.view(torch.uint8), tensor.view(torch.uint8)), f"{kind}: round trip is not bit-exact"
+        del check
+        buffers = TileBuffers(**container.buffers)
+        tile_elements, prob_bits, lanes, elements = parse_layout_cached(buffers.layout)
+        modes = np.ascontiguousarray(buffers.lane_modes.cpu().numpy())
+        output = torch.empty(elements * lanes, dtype=torch.uint8, device=device)
+        arguments = (
+            buffers.payload.data_ptr(), buffers.payload.numel(), buffers.offsets.data_ptr(), buffers.states.data_ptr(),
+            buffers.decode_tables.data_ptr(), modes.ctypes.data, output.data_ptr(), elements, tile_elements, prob_bits, lanes,
+            None, stream.cuda_stream)
+        launches.append((kind, arguments, modes, output, tensor))
+        containers.append(container)
+        dense_bytes += elements * lanes
+        stored_bytes += container.storage_nbytes(include_header=False)
+    bytes_per_step = dense_bytes + stored_bytes
+    per_kind_bytes = [c.storage_nbytes(include_header=False) + c.numel() * c.element_size() for c in containers]
+
+    flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=device)
+
+    def step():
+        for _, arguments, *_ in launches:
+            status = lib.ep_tile_ans_decode(*arguments)
+            if status != 0:
+                _native.check(status, "tile_ans decode")
+
+    def barrier():
+        if distributed:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(device)
+    for kind, _, _, output, tensor in launches:
+        assert torch.equal(output, tensor.view(torch.uint8).reshape(-1)), f"{kind}: decode differs from the source"
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    for index in range(args.steps):
+        flush.zero_()
+        starts[index].record(stream)
+        step()
+        stops[index].record(stream)
+    barrier()
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    total_ms = float(sum(step_ms))
+
+    # per-launch timing of the decode kernel for the roofline
+    kernel_ms = [0.0] * len(launches)
+    for _ in range(args.steps):
+        flush.zero_()
+        for index, (_, arguments, *_rest) in enumerate(launches):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            lib.ep_tile_ans_decode(*arguments)
+            end.record(stream)
+            end.synchronize()
+            kernel_ms[index] += begin.elapsed_time(end)
+    kernel_ms = [v / args.steps for v in kernel_ms]
+
+    # end to end through the public API from pinned host blobs
+    host_blobs = [c.entropack_quant_state.cpu().pin_memory() for c in containers]
+    host_outputs = [torch.empty(c.numel() * c.element_size(), dtype=torch.uint8).pin_memory() for c in containers]
+    h2d_bytes = sum(b.numel() for b in host_blobs)
+    d2h_bytes = sum(o.numel() for o in host_outputs)
+
+    def e2e_step():
+        for blob, host_output in zip(host_blobs, host_outputs):
+            container = ep.CompressedTensor.unpack(blob).to(device, non_blocking=True)
+            dense = ep.decompress(container, config)
+            host_output.copy_(dense.view(torch.uint8).reshape(-1), non_blocking=True)
+        torch.cuda.synchronize(device)
+
+    for _ in range(2):
+        e2e_step()
+    e2e_steps = max(2, min(args.steps, 5))
+    barrier()
+    e2e_begin = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_seconds = time.perf_counter() - e2e_begin
+    clocks = sampler.stop() if rank == 0 else None
+    assert torch.equal(host_outputs[0], launches[0][4].view(torch.uint8).reshape(-1).cpu())
+
+    if distributed:
+        times = torch.tensor([total_ms, e2e_seconds], dtype=torch.float64, device=device)
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        total_ms, e2e_seconds = float(times[0]), float(times[1])
+    if rank != 0:
+        if distributed:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    ms_per_step = total_ms / args.steps
+    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    kernel_seconds = sum(kernel_ms) * 1e-3
+    achieved = bytes_per_step / kernel_seconds / 1e9
+    cpu = time_cpu(steps=3, warmup=1, sample_rows=2048)
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+        "data": "synthetic",
+        "config": {"workload": "c2_tile_ans_decode", "tensors": list(KINDS), "shape": [ROWS, COLS],
+                   "bytes_per_step": bytes_per_step, "stored_bpp": {k: round(c.actual_bpp, 4) for k, c in zip(KINDS, containers)},
+                   "l2": "inputs larger than L2, plus a 512 MB flush between timed steps", "per_gpu_GBps": value / world,
+                   "hbm_frac_of_" + peak_kind: value / world / peak},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_kind, "traffic": None, "kernel": "tile_ans_decode_kernel",
+                     "per_launch_ms": dict(zip(KINDS, kernel_ms)),
+                     "per_launch_GBps": {k: b / (ms * 1e-3) / 1e9 for k, b, ms in zip(KINDS, per_kind_bytes, kernel_ms)}},
+        "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": world * bytes_per_step * e2e_steps / e2e_seconds / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
+        "gpu_launches": len(launches) * args.steps,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if distributed:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

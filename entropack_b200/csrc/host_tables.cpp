@@ -1,0 +1,205 @@
+// Host-side pieces of the C ABI: status strings, CUDA error capture, and the Tile-ANS table planner
+// (histogram -> probability_bits, lane modes, frequencies, cdfs, decode tables).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <queue>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "../../include/entropack_b200.h"
+
+namespace ep {
+
+static thread_local std::string g_last_cuda_error;
+
+int record_cuda_error(cudaError_t error, const char* where) {
+  g_last_cuda_error = std::string(where ? where : "?") + ": " + cudaGetErrorName(error) + " (" + cudaGetErrorString(error) + ")";
+  return EP_ERR_CUDA;
+}
+
+namespace {
+
+constexpr int kStatesPerTile = 32;
+
+// Largest-remainder allocation of `table_size` slots to the symbols of a histogram: every present
+// symbol gets at least one slot, leftovers go to the largest fractional parts, ties to the smaller
+// symbol; an overshoot (from the clamp to one) is taken back from the smallest fractional parts among
+// symbols still above one. Same results as normalize_counts, entropack/schemes/tile_ans/eager.py:16-48.
+int normalize(const uint64_t* counts, int symbols, int table_size, uint16_t* frequencies) {
+  uint64_t total = 0;
+  for (int s = 0; s < symbols; ++s) total += counts[s];
+  if (total == 0) return EP_ERR_NORMALIZE;
+  std::vector<double> target(symbols);
+  std::vector<int64_t> freq(symbols);
+  const double ratio = static_cast<double>(table_size) / static_cast<double>(total);
+  int64_t sum = 0;
+  for (int s = 0; s < symbols; ++s) {
+    target[s] = static_cast<double>(counts[s]) * ratio;
+    freq[s] = static_cast<int64_t>(std::floor(target[s]));
+    if (counts[s] != 0 && freq[s] < 1) freq[s] = 1;
+    sum += freq[s];
+  }
+  int64_t difference = table_size - sum;
+  using Item = std::pair<double, int>;
+  std::priority_queue<Item, std::vector<Item>, std::greater<Item>> queue;
+  if (difference > 0) {
+    for (int s = 0; s < symbols; ++s) if (counts[s] != 0) queue.emplace(-(target[s] - static_cast<double>(freq[s])), s);
+    for (; difference > 0; --difference) {
+      Item item = queue.top();
+      queue.pop();
+      freq[item.second] += 1;
+      queue.emplace(item.first + 1.0, item.second);
+    }
+  } else if (difference < 0) {
+    for (int s = 0; s < symbols; ++s) {
+      if (counts[s] != 0 && freq[s] > 1) queue.emplace(target[s] - static_cast<double>(freq[s]), s);
+    }
+    for (; difference < 0; ++difference) {
+      if (queue.empty()) return EP_ERR_NORMALIZE;
+      Item item = queue.top();
+      queue.pop();
+      freq[item.second] -= 1;
+      if (freq[item.second] > 1) queue.emplace(item.first + 1.0, item.second);
+    }
+  }
+  for (int s = 0; s < symbols; ++s) frequencies[s] = static_cast<uint16_t>(freq[s]);
+  return EP_OK;
+}
+
+double coded_bits(const uint64_t* counts, const uint16_t* frequencies, int prob_bits) {
+  double bits = 0.0;
+  for (int s = 0; s < 256; ++s) {
+    if (counts[s]) bits += static_cast<double>(counts[s]) * (prob_bits - std::log2(static_cast<double>(frequencies[s])));
+  }
+  return bits;
+}
+
+// A lane is stored raw when coding it would not pay: estimated bits per symbol at or above
+// min(threshold, 8 - 32*32/tile_elements) (the per-tile state overhead). With `frequencies` the
+// estimate is the cross entropy under the quantised table, otherwise the plain entropy.
+void choose_modes(const uint64_t* histograms, int lanes, double threshold, int64_t tile_elements, const uint16_t* frequencies,
+                  int prob_bits, uint8_t* modes) {
+  const double effective = std::min(threshold, 8.0 - static_cast<double>(kStatesPerTile * 32) / static_cast<double>(tile_elements));
+  for (int lane = 0; lane < lanes; ++lane) {
+    const uint64_t* counts = histograms + lane * 256;
+    uint64_t total = 0;
+    for (int s = 0; s < 256; ++s) total += counts[s];
+    double bits_per_symbol;
+    if (frequencies == nullptr) {
+      double h = 0.0;
+      for (int s = 0; s < 256; ++s) {
+        if (counts[s]) {
+          const double p = static_cast<double>(counts[s]) / static_cast<double>(total);
+          h += p * std::log2(p);
+        }
+      }
+      bits_per_symbol = -h;
+    } else {
+      bits_per_symbol = coded_bits(counts, frequencies + lane * 256, prob_bits) / static_cast<double>(total);
+    }
+    modes[lane] = bits_per_symbol >= effective ? 1 : 0;
+  }
+}
+
+}  // namespace
+}  // namespace ep
+
+extern "C" const char* ep_status_string(int status) {
+  switch (status) {
+    case EP_OK: return "ok";
+    case EP_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case EP_ERR_UNSUPPORTED: return "unsupported configuration";
+    case EP_ERR_CUDA: return "CUDA runtime error";
+    case EP_ERR_NORMALIZE: return "unable to normalize rANS frequencies";
+    case EP_ERR_ALPHABET: return "alphabet exceeds the rANS table";
+    case EP_ERR_TOO_LARGE: return "tensor too large for this entry point";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int ep_abi_version(void) { return 1; }
+
+extern "C" const char* ep_last_cuda_error(void) { return ep::g_last_cuda_error.c_str(); }
+
+extern "C" int ep_tile_ans_plan(const uint64_t* histograms_host, int num_lanes, int64_t tile_elements,
+                                double raw_lane_threshold, int prob_bits_in, int* prob_bits_out, uint16_t* frequencies_host,
+                                uint16_t* cdfs_host, uint32_t* decode_tables_host, uint8_t* lane_modes_host) {
+  using namespace ep;
+  if (!histograms_host || !prob_bits_out || !frequencies_host || !cdfs_host || !decode_tables_host || !lane_modes_host) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (num_lanes < 1 || num_lanes > 8 || tile_elements <= 0 || raw_lane_threshold < 0.0 || raw_lane_threshold > 8.0) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (prob_bits_in != 0 && (prob_bits_in < 9 || prob_bits_in > 12)) return EP_ERR_INVALID_ARGUMENT;
+  uint64_t num_elements = 0;
+  for (int s = 0; s < 256; ++s) num_elements += histograms_host[s];
+  if (num_elements == 0) return EP_ERR_INVALID_ARGUMENT;
+
+  int prob_bits = prob_bits_in;
+  if (prob_bits_in != 0) {
+    for (int lane = 0; lane < num_lanes; ++lane) {
+      const int rc = normalize(histograms_host + lane * 256, 256, 1 << prob_bits, frequencies_host + lane * 256);
+      if (rc != EP_OK) return rc;
+    }
+    choose_modes(histograms_host, num_lanes, raw_lane_threshold, tile_elements, nullptr, 0, lane_modes_host);
+  } else {
+    // Price every table size; take the smallest one within 0.15 % of the original size of the cheapest.
+    const int64_t n = static_cast<int64_t>(num_elements);
+    const int64_t tiles = (n + tile_elements - 1) / tile_elements;
+    const int64_t raw_words = (n / tile_elements) * ((tile_elements + 1) / 2) + ((n % tile_elements) + 1) / 2;
+    uint8_t plain[8];
+    choose_modes(histograms_host, num_lanes, raw_lane_threshold, tile_elements, nullptr, 0, plain);
+    const bool all_raw = std::all_of(plain, plain + num_lanes, [](uint8_t m) { return m == 1; });
+    const int variants = all_raw ? 1 : 4;
+    std::vector<uint16_t> freq(static_cast<size_t>(4) * num_lanes * 256);
+    uint8_t modes[4][8];
+    double bytes[4];
+    for (int v = 0; v < variants; ++v) {
+      const int pb = 9 + v;
+      uint16_t* f = freq.data() + static_cast<size_t>(v) * num_lanes * 256;
+      for (int lane = 0; lane < num_lanes; ++lane) {
+        const int rc = normalize(histograms_host + lane * 256, 256, 1 << pb, f + lane * 256);
+        if (rc != EP_OK) return rc;
+      }
+      choose_modes(histograms_host, num_lanes, raw_lane_threshold, tile_elements, f, pb, modes[v]);
+      double estimate = static_cast<double>((tiles * num_lanes + 1) * 4 + static_cast<int64_t>(num_lanes) * (4 << pb) + num_lanes + 40);
+      for (int lane = 0; lane < num_lanes; ++lane) {
+        if (modes[v][lane] == 1) {
+          estimate += static_cast<double>(raw_words * 2);
+        } else {
+          estimate += coded_bits(histograms_host + lane * 256, f + lane * 256, pb) / 8.0;
+          estimate += static_cast<double>(tiles * kStatesPerTile * 4);
+        }
+      }
+      bytes[v] = estimate;
+    }
+    const double best = *std::min_element(bytes, bytes + variants);
+    const double tolerance = static_cast<double>(n) * num_lanes * 0.0015;
+    int chosen = 0;
+    while (bytes[chosen] > best + tolerance) ++chosen;
+    prob_bits = 9 + chosen;
+    std::memcpy(frequencies_host, freq.data() + static_cast<size_t>(chosen) * num_lanes * 256, sizeof(uint16_t) * num_lanes * 256);
+    std::memcpy(lane_modes_host, modes[chosen], num_lanes);
+  }
+  *prob_bits_out = prob_bits;
+  const uint32_t table_size = 1u << prob_bits;
+  for (int lane = 0; lane < num_lanes; ++lane) {
+    uint32_t running = 0;
+    for (uint32_t symbol = 0; symbol < 256; ++symbol) {
+      const uint32_t f = frequencies_host[lane * 256 + symbol];
+      cdfs_host[lane * 256 + symbol] = static_cast<uint16_t>(running);
+      if (running + f > table_size) return EP_ERR_NORMALIZE;
+      const uint32_t entry = (running << 20) | ((f & 0xFFFu) << 8) | symbol;
+      std::fill(decode_tables_host + static_cast<size_t>(lane) * table_size + running,
+                decode_tables_host + static_cast<size_t>(lane) * table_size + running + f, entry);
+      running += f;
+    }
+    if (running != table_size) return EP_ERR_NORMALIZE;
+  }
+  return EP_OK;
+}

@@ -1,0 +1,517 @@
+// Tile-ANS (lossless byte-lane rANS) kernels for sm_100a and their C entry points.
+//
+// Format (entropack/schemes/tile_ans/format.py:58-64, eager.py:176-307): the tensor's elements are
+// split into byte lanes; each lane is cut into tiles of `tile_elements` symbols; a (lane, tile)
+// stream is either raw bytes or a 32-way interleaved rANS stream of 16-bit words that the decoder
+// consumes back to front. Stream index = lane * tiles + tile.
+//
+// Decode: one warp owns one tile across ALL byte lanes, so every element is rebuilt in registers and
+// leaves with a single whole-element store (32 consecutive elements per warp store), whatever the
+// lane pattern. Coded lanes keep one rANS state per thread and look symbols up in a shared-memory
+// table that is re-packed at staging time to hold `slot - cdf` directly.
+//
+// Encode: one warp owns one tile across all byte lanes as well, so the input is read once as whole
+// elements. Division by the symbol frequency uses a per-symbol 32-bit reciprocal with one correction.
+#include "ep_common.cuh"
+
+namespace ep {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxLanes = 8;
+
+struct LaneSetup {
+  uint32_t raw_mask;            // bit b set: byte lane b is stored raw
+  uint8_t ans_rank[kMaxLanes];  // rank of byte lane b among the coded lanes
+  int ans_lanes;
+};
+
+struct DecodeParams {
+  const uint16_t* payload;
+  int64_t payload_words;
+  const uint32_t* offsets;
+  const uint32_t* states;
+  const uint32_t* tables;
+  void* output;
+  int64_t num_elements;
+  int64_t tile_elements;
+  int64_t tiles;
+  int prob_bits;
+  LaneSetup lanes;
+  int* error;
+};
+
+template <int BYTES> struct Element;
+template <> struct Element<1> { using type = uint8_t; };
+template <> struct Element<2> { using type = uint16_t; };
+template <> struct Element<4> { using type = uint32_t; };
+template <> struct Element<8> { using type = uint64_t; };
+
+// Shared table entry: symbol | frequency << 8 | (slot - cdf) << 20. A frequency field of 0 can only
+// mean "the whole table" (one symbol, 4096 slots): such a lane decodes to a constant and never reads.
+template <int NLANES>
+__global__ void __launch_bounds__(kThreads) tile_ans_decode_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint32_t shared_tables[];
+  __shared__ int constant_symbol[kMaxLanes];
+  using element_t = typename Element<NLANES>::type;
+
+  const uint32_t table_size = 1u << p.prob_bits;
+  if (threadIdx.x < kMaxLanes) constant_symbol[threadIdx.x] = -1;
+  __syncthreads();
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    if ((p.lanes.raw_mask >> b) & 1u) continue;
+    const uint32_t* source = p.tables + static_cast<size_t>(b) * table_size;
+    uint32_t* staged = shared_tables + static_cast<size_t>(p.lanes.ans_rank[b]) * table_size;
+    for (uint32_t slot = threadIdx.x; slot < table_size; slot += kThreads) {
+      const uint32_t entry = source[slot];
+      if (((entry >> 8) & 0xFFFu) == 0u && slot == 0u) constant_symbol[b] = static_cast<int>(entry & 0xFFu);
+      staged[slot] = (entry & 0xFFFFFu) | ((slot - (entry >> 20)) << 20);
+    }
+  }
+  __syncthreads();
+
+  const int64_t tile = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (tile >= p.tiles) return;
+  const uint32_t lane = lane_id();
+  const uint32_t mask_ge = lanemask_ge();
+  const uint32_t slot_mask = table_size - 1u;
+  const int64_t tile_begin = tile * p.tile_elements;
+  const int count = static_cast<int>(min(p.tile_elements, p.num_elements - tile_begin));
+
+  const uint8_t* raw_bytes[NLANES];
+  const uint16_t* words[NLANES];
+  const uint32_t* table[NLANES];
+  int position[NLANES];
+  uint32_t state[NLANES];
+  int constant[NLANES];
+  int failure = 0;
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    const int64_t stream = static_cast<int64_t>(b) * p.tiles + tile;
+    const uint32_t begin = p.offsets[stream];
+    const uint32_t end = p.offsets[stream + 1];
+    if (end < begin || static_cast<int64_t>(end) > p.payload_words) failure = EP_STREAM_BAD_OFFSETS;
+    raw_bytes[b] = reinterpret_cast<const uint8_t*>(p.payload + begin);
+    words[b] = p.payload + begin;
+    position[b] = static_cast<int>(end - begin);
+    table[b] = shared_tables;
+    state[b] = kStateMin;
+    constant[b] = constant_symbol[b];
+    if ((p.lanes.raw_mask >> b) & 1u) {
+      if (!failure && end - begin != static_cast<uint32_t>((count + 1) >> 1)) failure = EP_STREAM_BAD_RAW_LENGTH;
+    } else {
+      const int rank = p.lanes.ans_rank[b];
+      table[b] = shared_tables + static_cast<size_t>(rank) * table_size;
+      state[b] = p.states[(static_cast<int64_t>(rank) * p.tiles + tile) * kNumStates + lane];
+    }
+  }
+  if (failure) {
+    if (lane == 0) report(p.error, failure);
+    return;
+  }
+
+  element_t* out = static_cast<element_t*>(p.output) + tile_begin;
+  // Groups of 32 symbols run back to front; a partial group at the tile's end comes first.
+  int offset = count - (count & 31);
+  bool valid = lane < static_cast<uint32_t>(count & 31);
+  if ((count & 31) == 0) {
+    offset -= 32;
+    valid = true;
+  }
+  for (; offset >= 0; offset -= 32, valid = true) {
+    element_t value = 0;
+#pragma unroll
+    for (int b = 0; b < NLANES; ++b) {
+      uint32_t byte = 0;
+      if ((p.lanes.raw_mask >> b) & 1u) {
+        if (valid) byte = raw_bytes[b][offset + lane];
+      } else if (constant[b] >= 0) {
+        byte = static_cast<uint32_t>(constant[b]);
+      } else {
+        if (valid) {
+          const uint32_t x = state[b];
+          const uint32_t slot = x & slot_mask;
+          const uint32_t entry = table[b][slot];
+          byte = entry & 0xFFu;
+          state[b] = ((entry >> 8) & 0xFFFu) * (x >> p.prob_bits) + (entry >> 20);
+        }
+        renormalize(valid, state[b], words[b], position[b], mask_ge);
+      }
+      value |= static_cast<element_t>(static_cast<element_t>(byte) << (8 * b));
+    }
+    if (valid) out[offset + lane] = value;
+  }
+
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    if (((p.lanes.raw_mask >> b) & 1u) || constant[b] >= 0) continue;
+    const bool dirty = __any_sync(0xFFFFFFFFu, state[b] != kStateMin);
+    if (position[b] < 0) failure = EP_STREAM_UNDERRUN;
+    else if (position[b] != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
+  }
+  if (failure && lane == 0) report(p.error, failure);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Histogram: one private 256-bin table per (warp, byte lane) in shared memory, folded per block.
+// ------------------------------------------------------------------------------------------------
+template <int NLANES>
+__global__ void __launch_bounds__(kThreads) tile_ans_histogram_kernel(const uint8_t* __restrict__ input, int64_t num_elements,
+                                                                      unsigned long long* __restrict__ histograms) {
+  using element_t = typename Element<NLANES>::type;
+  // 8 lanes x 8 copies would pass the 48 KB static limit, so wide elements share a copy per warp pair
+  constexpr int kCopies = NLANES == 8 ? kWarps / 2 : kWarps;
+  __shared__ uint32_t bins[kCopies][NLANES][256];
+  uint32_t* flat = &bins[0][0][0];
+  for (int i = threadIdx.x; i < kCopies * NLANES * 256; i += kThreads) flat[i] = 0;
+  __syncthreads();
+  const int warp = (threadIdx.x >> 5) % kCopies;
+  const element_t* elements = reinterpret_cast<const element_t*>(input);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t e = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; e < num_elements; e += stride) {
+    const element_t value = elements[e];
+#pragma unroll
+    for (int b = 0; b < NLANES; ++b) atomicAdd(&bins[warp][b][(value >> (8 * b)) & 0xFF], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < NLANES * 256; i += kThreads) {
+    uint32_t sum = 0;
+#pragma unroll
+    for (int w = 0; w < kCopies; ++w) sum += flat[w * NLANES * 256 + i];
+    if (sum) atomicAdd(histograms + i, static_cast<unsigned long long>(sum));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Encode
+// ------------------------------------------------------------------------------------------------
+struct EncodeParams {
+  const void* input;
+  int64_t num_elements;
+  int64_t tile_elements;
+  int64_t tiles;
+  int prob_bits;
+  const uint16_t* frequencies;  // [lanes][256]
+  const uint16_t* cdfs;         // [lanes][256]
+  LaneSetup lanes;
+  uint16_t* scratch;            // [lanes * tiles][tile_elements]
+  uint32_t* word_counts;        // [lanes * tiles]
+  uint32_t* states;             // [ans_lanes * tiles][32]
+};
+
+// Per coded lane and symbol: .x = frequency | cdf << 16, .y = floor(2^32 / frequency) (frequency 1
+// is stored as 0xFFFFFFFF; the correction step below absorbs the off-by-one either way).
+template <int NLANES>
+__global__ void __launch_bounds__(kThreads) tile_ans_encode_kernel(const EncodeParams p) {
+  using element_t = typename Element<NLANES>::type;
+  __shared__ uint2 symbol_table[NLANES][256];
+  for (int i = threadIdx.x; i < NLANES * 256; i += kThreads) {
+    const uint32_t f = p.frequencies[i];
+    const uint32_t c = p.cdfs[i];
+    const uint32_t reciprocal = f > 1u ? static_cast<uint32_t>(0x100000000ull / f) : 0xFFFFFFFFu;
+    (&symbol_table[0][0])[i] = make_uint2(f | (c << 16), reciprocal);
+  }
+  __syncthreads();
+
+  const int64_t tile = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (tile >= p.tiles) return;
+  const uint32_t lane = lane_id();
+  const uint32_t mask_lt = lanemask_lt();
+  const int64_t tile_begin = tile * p.tile_elements;
+  const int count = static_cast<int>(min(p.tile_elements, p.num_elements - tile_begin));
+  const element_t* in = static_cast<const element_t*>(p.input) + tile_begin;
+  const uint32_t emit_shift = 31 - p.prob_bits;
+
+  uint16_t* slot[NLANES];
+  uint32_t state[NLANES];
+  uint32_t emitted[NLANES];
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    slot[b] = p.scratch + (static_cast<int64_t>(b) * p.tiles + tile) * p.tile_elements;
+    state[b] = kStateMin;
+    emitted[b] = 0;
+  }
+
+  for (int base = 0; base < count; base += 32) {
+    const bool valid = base + static_cast<int>(lane) < count;
+    const element_t value = valid ? in[base + lane] : element_t(0);
+#pragma unroll
+    for (int b = 0; b < NLANES; ++b) {
+      const uint32_t symbol = static_cast<uint32_t>(value >> (8 * b)) & 0xFFu;
+      if ((p.lanes.raw_mask >> b) & 1u) {
+        // a raw stream is the lane's bytes in element order (two per little-endian word)
+        if (valid) reinterpret_cast<uint8_t*>(slot[b])[base + lane] = static_cast<uint8_t>(symbol);
+        continue;
+      }
+      const uint2 info = symbol_table[b][symbol];
+      const uint32_t f = info.x & 0xFFFFu;
+      uint32_t x = state[b];
+      const bool emit = valid && x >= (f << emit_shift);
+      const uint32_t vote = __ballot_sync(0xFFFFFFFFu, emit);
+      if (emit) {
+        slot[b][emitted[b] + __popc(vote & mask_lt)] = static_cast<uint16_t>(x);
+        x >>= 16;
+      }
+      emitted[b] += __popc(vote);
+      if (valid) {
+        uint32_t q = __umulhi(x, info.y);
+        uint32_t r = x - q * f;
+        if (r >= f) {
+          r -= f;
+          q += 1;
+        }
+        state[b] = (q << p.prob_bits) + r + (info.x >> 16);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    const int64_t stream = static_cast<int64_t>(b) * p.tiles + tile;
+    if ((p.lanes.raw_mask >> b) & 1u) {
+      if (lane == 0) {
+        if (count & 1) reinterpret_cast<uint8_t*>(slot[b])[count] = 0;
+        p.word_counts[stream] = static_cast<uint32_t>((count + 1) >> 1);
+      }
+    } else {
+      p.states[(static_cast<int64_t>(p.lanes.ans_rank[b]) * p.tiles + tile) * kNumStates + lane] = state[b];
+      if (lane == 0) p.word_counts[stream] = emitted[b];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Exclusive scan of u32 counts (single block, sequential over 1024-wide chunks) and stream gather.
+// ------------------------------------------------------------------------------------------------
+constexpr int kScanThreads = 1024;
+
+__global__ void __launch_bounds__(kScanThreads) exclusive_scan_u32_kernel(const uint32_t* __restrict__ counts, int64_t count,
+                                                                          uint32_t* __restrict__ offsets,
+                                                                          unsigned long long* __restrict__ total) {
+  __shared__ unsigned long long warp_sums[32];
+  __shared__ unsigned long long carry_shared;
+  const uint32_t lane = lane_id();
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_shared = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < count; base += kScanThreads) {
+    const int64_t index = base + threadIdx.x;
+    const unsigned long long own = index < count ? counts[index] : 0ull;
+    unsigned long long inclusive = own;
+#pragma unroll
+    for (int step = 1; step < 32; step <<= 1) {
+      const unsigned long long below = __shfl_up_sync(0xFFFFFFFFu, inclusive, step);
+      if (lane >= static_cast<uint32_t>(step)) inclusive += below;
+    }
+    if (lane == 31) warp_sums[warp] = inclusive;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long sum = warp_sums[lane];
+#pragma unroll
+      for (int step = 1; step < 32; step <<= 1) {
+        const unsigned long long below = __shfl_up_sync(0xFFFFFFFFu, sum, step);
+        if (lane >= static_cast<uint32_t>(step)) sum += below;
+      }
+      warp_sums[lane] = sum;
+    }
+    __syncthreads();
+    const unsigned long long carry = carry_shared;
+    const unsigned long long before = carry + (warp > 0 ? warp_sums[warp - 1] : 0ull) + inclusive - own;
+    if (index < count) offsets[index] = static_cast<uint32_t>(before);
+    __syncthreads();
+    if (threadIdx.x == kScanThreads - 1) carry_shared = carry + warp_sums[31];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    offsets[count] = static_cast<uint32_t>(carry_shared);
+    total[0] = carry_shared;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) compact_streams_kernel(const uint16_t* __restrict__ scratch,
+                                                                   const uint32_t* __restrict__ offsets,
+                                                                   uint16_t* __restrict__ payload, int64_t slot_words,
+                                                                   int64_t streams) {
+  for (int64_t stream = blockIdx.x; stream < streams; stream += gridDim.x) {
+    const uint32_t begin = offsets[stream];
+    const uint32_t words = offsets[stream + 1] - begin;
+    const uint16_t* source = scratch + stream * slot_words;
+    uint16_t* target = payload + begin;
+    // 32-bit body between 4-byte-aligned ends; the slot base is 4-byte aligned when slot_words is even
+    const uint32_t head = (begin & 1u) && words ? 1u : 0u;
+    if (head && threadIdx.x == 0) target[0] = source[0];
+    if ((slot_words & 1) == 0 && head == 0) {
+      const uint32_t pairs = words >> 1;
+      const uint32_t* source32 = reinterpret_cast<const uint32_t*>(source);
+      uint32_t* target32 = reinterpret_cast<uint32_t*>(target);
+      for (uint32_t i = threadIdx.x; i < pairs; i += kThreads) target32[i] = source32[i];
+      if ((words & 1u) && threadIdx.x == 0) target[words - 1] = source[words - 1];
+    } else {
+      for (uint32_t i = head + threadIdx.x; i < words; i += kThreads) target[i] = source[i];
+    }
+  }
+}
+
+int make_lane_setup(const uint8_t* lane_modes_host, int num_lanes, LaneSetup* setup) {
+  if (lane_modes_host == nullptr) return EP_ERR_INVALID_ARGUMENT;
+  if (num_lanes != 1 && num_lanes != 2 && num_lanes != 4 && num_lanes != 8) return EP_ERR_UNSUPPORTED;
+  setup->raw_mask = 0;
+  setup->ans_lanes = 0;
+  for (int b = 0; b < kMaxLanes; ++b) setup->ans_rank[b] = 0;
+  for (int b = 0; b < num_lanes; ++b) {
+    if (lane_modes_host[b] > 1) return EP_ERR_INVALID_ARGUMENT;
+    if (lane_modes_host[b] == 1) {
+      setup->raw_mask |= 1u << b;
+    } else {
+      setup->ans_rank[b] = static_cast<uint8_t>(setup->ans_lanes++);
+    }
+  }
+  return EP_OK;
+}
+
+template <typename Kernel>
+int allow_shared(Kernel kernel, size_t bytes) {
+  if (bytes > 48 * 1024) {
+    EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+  }
+  return EP_OK;
+}
+
+}  // namespace
+}  // namespace ep
+
+using namespace ep;
+
+extern "C" int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                  const uint32_t* states_dev, const uint32_t* decode_tables_dev,
+                                  const uint8_t* lane_modes_host, void* output_dev, int64_t num_elements,
+                                  int64_t tile_elements, int prob_bits, int num_lanes, int* error_dev, ep_stream_t stream) {
+  if (num_elements <= 0 || tile_elements <= 0 || tile_elements > 0x7FFFFFFF || prob_bits < 9 || prob_bits > 12 ||
+      payload_words < 0 || offsets_dev == nullptr || output_dev == nullptr) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  DecodeParams p;
+  const int status = make_lane_setup(lane_modes_host, num_lanes, &p.lanes);
+  if (status != EP_OK) return status;
+  if (p.lanes.ans_lanes > 0 && (states_dev == nullptr || decode_tables_dev == nullptr)) return EP_ERR_INVALID_ARGUMENT;
+  if (payload_words > 0 && payload_dev == nullptr) return EP_ERR_INVALID_ARGUMENT;
+  p.payload = payload_dev;
+  p.payload_words = payload_words;
+  p.offsets = offsets_dev;
+  p.states = states_dev;
+  p.tables = decode_tables_dev;
+  p.output = output_dev;
+  p.num_elements = num_elements;
+  p.tile_elements = tile_elements;
+  p.tiles = (num_elements + tile_elements - 1) / tile_elements;
+  p.prob_bits = prob_bits;
+  p.error = error_dev;
+  const int64_t blocks = (p.tiles + kWarps - 1) / kWarps;
+  if (blocks > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
+  const size_t shared = static_cast<size_t>(p.lanes.ans_lanes) * sizeof(uint32_t) << prob_bits;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>(blocks));
+  switch (num_lanes) {
+    case 1: {
+      const int rc = allow_shared(tile_ans_decode_kernel<1>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<1><<<grid, kThreads, shared, s>>>(p);
+      break;
+    }
+    case 2: {
+      const int rc = allow_shared(tile_ans_decode_kernel<2>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<2><<<grid, kThreads, shared, s>>>(p);
+      break;
+    }
+    case 4: {
+      const int rc = allow_shared(tile_ans_decode_kernel<4>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<4><<<grid, kThreads, shared, s>>>(p);
+      break;
+    }
+    default: {
+      const int rc = allow_shared(tile_ans_decode_kernel<8>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<8><<<grid, kThreads, shared, s>>>(p);
+      break;
+    }
+  }
+  return check_launch("tile_ans_decode_kernel");
+}
+
+extern "C" int ep_tile_ans_histogram(const void* input_dev, int64_t num_elements, int num_lanes, uint64_t* histograms_dev,
+                                     ep_stream_t stream) {
+  if (input_dev == nullptr || histograms_dev == nullptr || num_elements <= 0) return EP_ERR_INVALID_ARGUMENT;
+  if (num_lanes != 1 && num_lanes != 2 && num_lanes != 4 && num_lanes != 8) return EP_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EP_CUDA_CHECK(cudaMemsetAsync(histograms_dev, 0, sizeof(uint64_t) * 256 * num_lanes, s));
+  const int64_t wanted = (num_elements + kThreads - 1) / kThreads;
+  const int per_sm = num_lanes >= 8 ? 3 : (num_lanes == 4 ? 6 : 8);
+  const unsigned blocks = static_cast<unsigned>(wanted < kSmCount * per_sm ? wanted : kSmCount * per_sm);
+  auto* out = reinterpret_cast<unsigned long long*>(histograms_dev);
+  const auto* in = static_cast<const uint8_t*>(input_dev);
+  switch (num_lanes) {
+    case 1: tile_ans_histogram_kernel<1><<<blocks, kThreads, 0, s>>>(in, num_elements, out); break;
+    case 2: tile_ans_histogram_kernel<2><<<blocks, kThreads, 0, s>>>(in, num_elements, out); break;
+    case 4: tile_ans_histogram_kernel<4><<<blocks, kThreads, 0, s>>>(in, num_elements, out); break;
+    default: tile_ans_histogram_kernel<8><<<blocks, kThreads, 0, s>>>(in, num_elements, out); break;
+  }
+  return check_launch("tile_ans_histogram_kernel");
+}
+
+extern "C" int ep_tile_ans_encode(const void* input_dev, int64_t num_elements, int num_lanes, int64_t tile_elements,
+                                  int prob_bits, const uint16_t* frequencies_dev, const uint16_t* cdfs_dev,
+                                  const uint8_t* lane_modes_host, uint16_t* scratch_dev, uint32_t* word_counts_dev,
+                                  uint32_t* states_dev, ep_stream_t stream) {
+  if (input_dev == nullptr || num_elements <= 0 || tile_elements <= 0 || tile_elements > 0x7FFFFFFF || prob_bits < 9 ||
+      prob_bits > 12 || frequencies_dev == nullptr || cdfs_dev == nullptr || scratch_dev == nullptr ||
+      word_counts_dev == nullptr) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  EncodeParams p;
+  const int status = make_lane_setup(lane_modes_host, num_lanes, &p.lanes);
+  if (status != EP_OK) return status;
+  if (p.lanes.ans_lanes > 0 && states_dev == nullptr) return EP_ERR_INVALID_ARGUMENT;
+  p.input = input_dev;
+  p.num_elements = num_elements;
+  p.tile_elements = tile_elements;
+  p.tiles = (num_elements + tile_elements - 1) / tile_elements;
+  p.prob_bits = prob_bits;
+  p.frequencies = frequencies_dev;
+  p.cdfs = cdfs_dev;
+  p.scratch = scratch_dev;
+  p.word_counts = word_counts_dev;
+  p.states = states_dev;
+  const int64_t blocks = (p.tiles + kWarps - 1) / kWarps;
+  if (blocks > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>(blocks));
+  switch (num_lanes) {
+    case 1: tile_ans_encode_kernel<1><<<grid, kThreads, 0, s>>>(p); break;
+    case 2: tile_ans_encode_kernel<2><<<grid, kThreads, 0, s>>>(p); break;
+    case 4: tile_ans_encode_kernel<4><<<grid, kThreads, 0, s>>>(p); break;
+    default: tile_ans_encode_kernel<8><<<grid, kThreads, 0, s>>>(p); break;
+  }
+  return check_launch("tile_ans_encode_kernel");
+}
+
+extern "C" int ep_exclusive_scan_u32(const uint32_t* counts_dev, int64_t count, uint32_t* offsets_dev, uint64_t* total_dev,
+                                     ep_stream_t stream) {
+  if (counts_dev == nullptr || offsets_dev == nullptr || total_dev == nullptr || count < 0) return EP_ERR_INVALID_ARGUMENT;
+  exclusive_scan_u32_kernel<<<1, kScanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      counts_dev, count, offsets_dev, reinterpret_cast<unsigned long long*>(total_dev));
+  return check_launch("exclusive_scan_u32_kernel");
+}
+
+extern "C" int ep_compact_streams(const uint16_t* scratch_dev, const uint32_t* offsets_dev, uint16_t* payload_dev,
+                                  int64_t slot_words, int64_t streams, ep_stream_t stream) {
+  if (scratch_dev == nullptr || offsets_dev == nullptr || slot_words <= 0 || streams <= 0) return EP_ERR_INVALID_ARGUMENT;
+  if (payload_dev == nullptr) return EP_ERR_INVALID_ARGUMENT;
+  const int64_t wanted = streams < kSmCount * 8 ? streams : kSmCount * 8;
+  compact_streams_kernel<<<static_cast<unsigned>(wanted), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      scratch_dev, offsets_dev, payload_dev, slot_words, streams);
+  return check_launch("compact_streams_kernel");
+}

@@ -1,0 +1,103 @@
+/*
+ * entropack_b200 -- C ABI of the B200 (sm_100a) kernels behind the entropack compression hot path.
+ *
+ * One shared object, plain pointers and sizes, no framework types. Every entry point is what a
+ * backend "lane" module of the reference would bind (the reference launches its kernels from Python
+ * through raw device pointers, entropack/backends/cuda/kernels.py:31-62); each declaration names the
+ * reference interface it stands in for.
+ *
+ * Conventions
+ *  - Pointers named *_dev are device pointers on the current CUDA device; *_host are host pointers.
+ *    Device buffers need the 16-byte alignment the container format guarantees
+ *    (entropack/compression/compressed_tensor.py:13-14) unless a comment asks for less.
+ *  - The caller owns every allocation. Nothing here allocates device memory.
+ *  - Calls are asynchronous on `stream` (a cudaStream_t passed as void*) unless stated otherwise.
+ *  - Return value: EP_OK or a negative EP_ERR_* code; ep_status_string() names it. Kernels never
+ *    trap: a malformed bitstream is reported through the optional `error_dev` word (device int32,
+ *    zero-initialised by the caller, first non-zero code wins) and the offending tile is skipped.
+ */
+#ifndef ENTROPACK_B200_H
+#define ENTROPACK_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EP_OK 0
+#define EP_ERR_INVALID_ARGUMENT (-1)
+#define EP_ERR_UNSUPPORTED (-2)
+#define EP_ERR_CUDA (-3)
+#define EP_ERR_NORMALIZE (-4)
+#define EP_ERR_ALPHABET (-5)
+#define EP_ERR_TOO_LARGE (-6)
+
+/* codes written to error_dev by decode kernels */
+#define EP_STREAM_BAD_OFFSETS 1
+#define EP_STREAM_UNDERRUN 2
+#define EP_STREAM_NOT_CONSUMED 3
+#define EP_STREAM_BAD_RAW_LENGTH 4
+
+typedef void* ep_stream_t;
+
+const char* ep_status_string(int status);
+/* ABI version of this header; bumped on any signature change. */
+int ep_abi_version(void);
+/* Last CUDA runtime error text seen by this library on the calling thread (for EP_ERR_CUDA). */
+const char* ep_last_cuda_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Tile-ANS (lossless, byte-lane rANS).  Buffer schema: entropack/schemes/tile_ans/format.py:58-64.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Decode a Tile-ANS container into `output_dev` (num_elements * num_lanes bytes, whole elements are
+ * written with one store each). Stands in for decode() of entropack/schemes/tile_ans/cuda.py:122-170
+ * and the four kernels it picks from (tile_ans.cu:175-469). `lane_modes_host` is the container's
+ * lane_modes buffer copied to the host (0 = ANS, 1 = raw), as the reference caches it.
+ * `payload_words` is the length of `payload_dev` and bounds every read. */
+int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                       const uint32_t* states_dev, const uint32_t* decode_tables_dev, const uint8_t* lane_modes_host,
+                       void* output_dev, int64_t num_elements, int64_t tile_elements, int prob_bits, int num_lanes,
+                       int* error_dev, ep_stream_t stream);
+
+/* Per-byte-lane 256-bin histogram of the tensor's bytes into histograms_dev[num_lanes][256] (u64,
+ * cleared by the call). Stands in for _lane_histogram, entropack/schemes/tile_ans/cuda.py:31-47 /
+ * tile_ans_histogram_kernel, tile_ans.cu:27-65. */
+int ep_tile_ans_histogram(const void* input_dev, int64_t num_elements, int num_lanes, uint64_t* histograms_dev,
+                          ep_stream_t stream);
+
+/* Host-only: choose probability_bits (0 = automatic) and lane modes and build the coding tables from
+ * the histograms. Stands in for _lane_tables, entropack/schemes/tile_ans/cuda.py:50-61, i.e.
+ * select_coding_options / build_tables_from_counts / lane_modes_from_counts of
+ * entropack/schemes/tile_ans/eager.py:16-145. Outputs: frequencies[num_lanes][256],
+ * cdfs[num_lanes][256], decode_tables[num_lanes][1 << *prob_bits_out] (room for 4096 entries per
+ * lane), lane_modes[num_lanes]. */
+int ep_tile_ans_plan(const uint64_t* histograms_host, int num_lanes, int64_t tile_elements, double raw_lane_threshold,
+                     int prob_bits_in, int* prob_bits_out, uint16_t* frequencies_host, uint16_t* cdfs_host,
+                     uint32_t* decode_tables_host, uint8_t* lane_modes_host);
+
+/* Encode every (byte lane, tile) stream into its own slot of scratch_dev
+ * (num_lanes * tiles * tile_elements u16 words), writing word_counts_dev[streams] and
+ * states_dev[ans_lanes * tiles][32]. Stands in for tile_ans_encode_kernel, tile_ans.cu:67-155
+ * (launch at entropack/schemes/tile_ans/cuda.py:64-98). */
+int ep_tile_ans_encode(const void* input_dev, int64_t num_elements, int num_lanes, int64_t tile_elements, int prob_bits,
+                       const uint16_t* frequencies_dev, const uint16_t* cdfs_dev, const uint8_t* lane_modes_host,
+                       uint16_t* scratch_dev, uint32_t* word_counts_dev, uint32_t* states_dev, ep_stream_t stream);
+
+/* Exclusive prefix sum of u32 counts into offsets_dev[count + 1] (u32) with the u64 grand total in
+ * total_dev[0]; the device-side stand-in for the cupy.cumsum calls of the reference's encoders
+ * (tile_ans/cuda.py:99-104, lattice_rans/cuda.py:543-551). `count` up to 2^31-1. */
+int ep_exclusive_scan_u32(const uint32_t* counts_dev, int64_t count, uint32_t* offsets_dev, uint64_t* total_dev,
+                          ep_stream_t stream);
+
+/* Gather per-stream scratch slots (stride `slot_words`) into the contiguous payload. Stands in for
+ * tile_ans_compact_kernel (tile_ans.cu:157-173) and e8_compact_kernel (lattice_rans.cu:467-481). */
+int ep_compact_streams(const uint16_t* scratch_dev, const uint32_t* offsets_dev, uint16_t* payload_dev, int64_t slot_words,
+                       int64_t streams, ep_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ENTROPACK_B200_H */

@@ -1,0 +1,101 @@
+"""Host-side logic that needs no GPU: the C-ABI library loads and exports what the header declares,
+the table planner matches the oracle, configs validate like the reference's, the container is
+byte-compatible."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, buffers_of, golden_names, load_golden
+
+
+def test_library_exports_every_declared_symbol():
+    from entropack_b200 import _native, build
+
+    build.build()
+    lib = ctypes.CDLL(str(_native.library_path()))
+    declared = []
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        declared += re.findall(r"\b(ep_[a-z0-9_]+)\s*\(", text)
+    assert declared, "no declarations found"
+    for name in sorted(set(declared)):
+        assert hasattr(lib, name), f"{name} is declared but not exported"
+    assert _native.load().ep_abi_version() >= 1
+
+
+@pytest.mark.parametrize("name", golden_names("tile_ans_"))
+def test_table_planner_matches_reference(name):
+    from entropack_b200.schemes.tile_ans import b200
+
+    record = load_golden(f"tile_ans_{name}")
+    reference = buffers_of(record)
+    itemsize = int(record["itemsize"])
+    lanes = record["input_bytes"].reshape(-1, itemsize)
+    counts = np.stack([np.bincount(lanes[:, b], minlength=256) for b in range(itemsize)]).astype(np.uint64)
+    pb, _freq, _cdf, tables, modes = b200.plan_tables(
+        np.ascontiguousarray(counts), int(reference["layout"][0]), int(record["probability_bits_arg"]), 7.9)
+    assert pb == int(reference["layout"][1])
+    assert np.array_equal(modes, reference["lane_modes"])
+    assert np.array_equal(tables, reference["decode_tables"])
+
+
+def test_config_validation_matches_reference_rules():
+    import entropack_b200 as ep
+    from entropack_b200.schemes.config import validate_config
+
+    validate_config(ep.TileANSConfig())
+    with pytest.raises(ValueError):
+        validate_config(ep.TileANSConfig(probability_bits=8))
+    with pytest.raises(ValueError):
+        validate_config(ep.TileANSConfig(tile_elements=-1))
+    with pytest.raises(TypeError):
+        validate_config(ep.TileANSConfig(tile_elements=1.5))
+    with pytest.raises(TypeError):
+        validate_config(ep.TileANSConfig(raw_lane_threshold=None))
+    with pytest.raises(ValueError):
+        validate_config(ep.TileANSConfig(raw_lane_threshold=8.5))
+
+
+@pytest.mark.parametrize("stem", ["tile_ans_bf16", "tile_ans_int64_mixed", "tile_ans_int8_single"])
+def test_container_is_byte_compatible(stem):
+    import entropack_b200 as ep
+
+    record = load_golden(stem)
+    blob = torch.from_numpy(record["blob"].copy())
+    container = ep.CompressedTensor.unpack(blob)
+    assert tuple(container.shape) == tuple(int(v) for v in record["shape"])
+    for key, value in buffers_of(record).items():
+        assert np.array_equal(container.buffers[key].numpy(), value), key
+    rebuilt = ep.CompressedTensor(header=container.header, buffers=container.buffers, shape=container.shape, dtype=container.dtype)
+    assert torch.equal(rebuilt.entropack_quant_state, blob)
+    assert container.actual_bpp == blob.numel() * 8 / container.numel()
+    state = container.state_dict()
+    again = ep.CompressedTensor.from_state_dict(state)
+    assert torch.equal(again.entropack_quant_state, blob)
+    with pytest.raises(ValueError):
+        ep.CompressedTensor.unpack(blob[:-16])
+    container.scheme.validate_buffers(container.buffers, tuple(container.shape), container.encoded_dtype)
+
+
+def test_no_cpu_fallback():
+    import entropack_b200 as ep
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(ep.DispatchError):
+        ep.compress(torch.zeros(64, 64), ep.TileANSConfig())
+    with pytest.raises(ep.DispatchError):
+        ep.compress(torch.zeros(64, 64), ep.TileANSConfig(execution_backend="eager"))
+
+
+def test_product_never_imports_the_oracle():
+    offenders = []
+    for path in (ROOT / "entropack_b200").rglob("*.py"):
+        text = path.read_text()
+        if re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M):
+            offenders.append(str(path))
+    assert not offenders, offenders

@@ -1,0 +1,133 @@
+"""Tile-ANS kernels against the golden fixtures and the CPU oracle (bit-exact), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import buffers_of, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {
+    1: torch.uint8, 2: torch.uint16, 4: torch.uint32, 8: torch.uint64,
+}
+
+
+def _to_device(buffers: dict):
+    from entropack_b200.schemes.tile_ans.format import TileBuffers
+
+    return TileBuffers(**{key: torch.from_numpy(np.ascontiguousarray(value)).cuda() for key, value in buffers.items()})
+
+
+def _gpu_decode(buffers: dict, itemsize: int) -> np.ndarray:
+    from entropack_b200.schemes.tile_ans import b200
+
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b200.decode(_to_device(buffers), dtype=DTYPES[itemsize], error=error)
+    assert int(error.item()) == 0
+    return out.view(torch.uint8).cpu().numpy()
+
+
+def _gpu_encode(data: np.ndarray, itemsize: int, tile_elements: int, probability_bits: int = 0) -> dict:
+    from entropack_b200.schemes.tile_ans import b200
+
+    weight = torch.from_numpy(data.copy()).cuda().view(DTYPES[itemsize])
+    buffers = b200.encode(weight=weight, tile_elements=tile_elements, probability_bits=probability_bits,
+                          raw_lane_threshold=7.9, threads_per_block=None)
+    return {key: value.cpu().numpy() for key, value in buffers._asdict().items()}
+
+
+@pytest.mark.parametrize("name", golden_names("tile_ans_"))
+def test_decode_reference_bitstreams(name):
+    record = load_golden(f"tile_ans_{name}")
+    decoded = _gpu_decode(buffers_of(record), int(record["itemsize"]))
+    assert np.array_equal(decoded, record["input_bytes"])
+
+
+@pytest.mark.parametrize("name", golden_names("tile_ans_"))
+def test_encode_reproduces_reference_bitstreams(name):
+    record = load_golden(f"tile_ans_{name}")
+    reference = buffers_of(record)
+    ours = _gpu_encode(record["input_bytes"], int(record["itemsize"]), int(reference["layout"][0]),
+                       int(record["probability_bits_arg"]))
+    for key in ("layout", "lane_modes", "decode_tables", "offsets", "states", "payload"):
+        assert np.array_equal(ours[key], reference[key]), key
+
+
+def _seeded(kind: str, n: int, seed: int) -> tuple[np.ndarray, int]:
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, generator=g)
+    if kind == "fp8":
+        t = (x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn)
+    elif kind == "int8":
+        t = (x * 20).round().clamp(-127, 127).to(torch.int8)
+    elif kind == "fp16":
+        t = (x * 0.02).to(torch.float16)
+    elif kind == "bf16":
+        t = (x * 0.02).to(torch.bfloat16)
+    elif kind == "fp32":
+        t = x * 0.02
+    elif kind == "int64":
+        t = (x * 3000).round().to(torch.int64)
+    else:
+        raise AssertionError(kind)
+    return t.view(torch.uint8).numpy().copy(), t.element_size()
+
+
+@pytest.mark.parametrize("kind,n,tile", [
+    ("fp8", 1 << 20, 8192), ("int8", (1 << 20) + 13, 4096), ("fp16", 700001, 8192), ("bf16", 1 << 19, 4096),
+    ("fp32", 300007, 8192), ("int64", 100003, 8192), ("fp8", 31, 4096), ("fp16", 33, 32), ("bf16", 1, 4096),
+])
+def test_against_oracle_both_directions(oracle_module, kind, n, tile):
+    data, itemsize = _seeded(kind, n, seed=n % 97)
+    expected = oracle_module.tile_ans_encode(data, itemsize, tile)
+    ours = _gpu_encode(data, itemsize, tile)
+    for key in ("layout", "lane_modes", "decode_tables", "offsets", "states", "payload"):
+        assert np.array_equal(ours[key], expected[key]), key
+    assert np.array_equal(_gpu_decode(expected, itemsize), data)
+    assert np.array_equal(oracle_module.tile_ans_decode(ours), data)
+
+
+@pytest.mark.parametrize("kind", ["fp8", "int8", "fp16", "fp32"])
+def test_full_size_round_trip(kind):
+    """8192 x 8192 of each benchmark dtype: encode and decode on the GPU, bit-exact restore, and the
+    public API agrees with the lane."""
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed({"fp8": 1, "int8": 2, "fp16": 3, "fp32": 4}[kind])
+    x = torch.randn(8192, 8192, generator=g, device="cuda")
+    if kind == "fp8":
+        t = (x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn)
+    elif kind == "int8":
+        t = (x * 20).round().clamp(-127, 127).to(torch.int8)
+    elif kind == "fp16":
+        t = (x * 0.02).to(torch.float16)
+    else:
+        t = x * 0.02
+    del x
+    compressed = ep.compress(t, ep.TileANSConfig())
+    assert compressed.compress_method == "tile_ans"
+    compressed.scheme.validate_buffers(compressed.buffers, tuple(t.shape), t.dtype)
+    restored = ep.decompress(compressed, ep.TileANSConfig())
+    assert restored.dtype == t.dtype and restored.shape == t.shape
+    assert torch.equal(restored.view(torch.uint8), t.view(torch.uint8))
+    assert compressed.actual_bpp < t.element_size() * 8
+
+
+def test_malformed_streams_are_reported_not_faulted():
+    from entropack_b200.schemes.tile_ans import b200
+
+    record = load_golden("tile_ans_fp8_e4m3_large")
+    buffers = buffers_of(record)
+    # truncated payload: offsets now point past the end
+    bad = dict(buffers)
+    bad["payload"] = buffers["payload"][: buffers["payload"].size // 2].copy()
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    b200.decode(_to_device(bad), dtype=torch.uint8, error=error)
+    assert int(error.item()) == 1
+    # corrupted states: streams are no longer consumed exactly
+    bad = dict(buffers)
+    bad["states"] = (buffers["states"] ^ np.uint32(0x00013570)).astype(np.uint32)
+    error.zero_()
+    b200.decode(_to_device(bad), dtype=torch.uint8, error=error)
+    assert int(error.item()) in (2, 3)
+    torch.cuda.synchronize()
