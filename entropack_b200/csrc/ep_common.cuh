@@ -28,17 +28,23 @@ inline int check_launch(const char* where) {
   return error == cudaSuccess ? EP_OK : record_cuda_error(error, where);
 }
 
-__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
+// The special-register reads are volatile so the compiler keeps the value in a register instead of
+// re-reading the (slow) special register wherever it is used.
+__device__ __forceinline__ uint32_t lane_id() {
+  uint32_t lane;
+  asm volatile("mov.u32 %0, %%laneid;" : "=r"(lane));
+  return lane;
+}
 
 __device__ __forceinline__ uint32_t lanemask_ge() {
   uint32_t mask;
-  asm("mov.u32 %0, %%lanemask_ge;" : "=r"(mask));
+  asm volatile("mov.u32 %0, %%lanemask_ge;" : "=r"(mask));
   return mask;
 }
 
 __device__ __forceinline__ uint32_t lanemask_lt() {
   uint32_t mask;
-  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(mask));
+  asm volatile("mov.u32 %0, %%lanemask_lt;" : "=r"(mask));
   return mask;
 }
 

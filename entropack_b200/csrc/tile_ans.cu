@@ -51,11 +51,7 @@ template <> struct Element<8> { using type = uint64_t; };
 // Shared table entry: symbol | frequency << 8 | (slot - cdf) << 20. A frequency field of 0 can only
 // mean "the whole table" (one symbol, 4096 slots): such a lane decodes to a constant and never reads.
 template <int NLANES>
-__global__ void __launch_bounds__(kThreads) tile_ans_decode_kernel(const DecodeParams p) {
-  extern __shared__ __align__(16) uint32_t shared_tables[];
-  __shared__ int constant_symbol[kMaxLanes];
-  using element_t = typename Element<NLANES>::type;
-
+__device__ __forceinline__ void stage_decode_tables(const DecodeParams& p, uint32_t* shared_tables, int* constant_symbol) {
   const uint32_t table_size = 1u << p.prob_bits;
   if (threadIdx.x < kMaxLanes) constant_symbol[threadIdx.x] = -1;
   __syncthreads();
@@ -71,6 +67,18 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_kernel(const DecodeP
     }
   }
   __syncthreads();
+}
+
+// General-purpose decoder: one element per thread per step, words read straight from global memory.
+// Used when the tile size is odd or the buffers are not 16-byte aligned, i.e. when the staged decoder
+// below cannot use vector stores and 16-byte copies.
+template <int NLANES>
+__global__ void __launch_bounds__(kThreads) tile_ans_decode_simple_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint32_t shared_tables[];
+  __shared__ int constant_symbol[kMaxLanes];
+  using element_t = typename Element<NLANES>::type;
+  const uint32_t table_size = 1u << p.prob_bits;
+  stage_decode_tables<NLANES>(p, shared_tables, constant_symbol);
 
   const int64_t tile = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
   if (tile >= p.tiles) return;
@@ -150,6 +158,272 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_kernel(const DecodeP
     const bool dirty = __any_sync(0xFFFFFFFFu, state[b] != kStateMin);
     if (position[b] < 0) failure = EP_STREAM_UNDERRUN;
     else if (position[b] != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
+  }
+  if (failure && lane == 0) report(p.error, failure);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Staged decoder (the fast path).
+//
+// The rANS chain is serial per thread, so every memory access inside it has to be on chip and cheap
+// to address:
+//   * the stream's 16-bit words are pulled into a per-warp shared-memory ring by 16-byte cp.async
+//     copies issued a chunk (128 words) ahead of the chunks being consumed; ring reads are masked
+//     into the ring, so even a corrupt stream cannot read out of bounds;
+//   * decoded symbols go to a per-warp shared staging block of 512 elements; the 16 groups of a full
+//     block are unrolled so every staging store has an immediate offset;
+//   * after each block the warp merges staged symbols with the raw lanes' bytes (plain coalesced
+//     loads, independent of the chain, many in flight) and writes whole elements with vector stores
+//     (two elements per thread; sixteen for one-byte elements).
+// All shared-memory state is addressed by 32-bit offsets from the one dynamic shared array, so the
+// compiler emits plain LDS/STS with scaled addressing.
+// ------------------------------------------------------------------------------------------------
+constexpr int kBlockElems = 512;   // elements staged per warp between merges (16 groups of 32)
+constexpr int kChunkLog = 7;       // ring chunk: 128 words = 256 bytes = sixteen 16-byte copies
+constexpr int kChunkWords = 1 << kChunkLog;
+constexpr int kRingWords = 4 * kChunkWords;
+constexpr int kDecodeBlocksPerSm = 7;
+
+// Copies chunk `chunk` of the payload into its ring slot (threads 0..15, 16 bytes each). The first
+// chunks of a stream may straddle the end of the payload, so the copy length is clipped there.
+__device__ __forceinline__ void ring_fetch_clipped(const uint16_t* __restrict__ payload, int64_t payload_words,
+                                                   uint32_t ring_address, int chunk, uint32_t lane) {
+  if (chunk < 0 || lane >= kChunkWords / 8) return;
+  const int64_t word = static_cast<int64_t>(chunk) * kChunkWords + lane * 8;
+  const int64_t remaining = payload_words - word;
+  if (remaining <= 0) return;
+  const int bytes = remaining >= 8 ? 16 : static_cast<int>(remaining) * 2;
+  const uint32_t target = ring_address + static_cast<uint32_t>(((chunk & 3) * kChunkWords + lane * 8) * 2);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(payload + word), "r"(bytes) : "memory");
+}
+
+// Same for a chunk known to lie wholly inside the payload (any chunk below one already fetched).
+__device__ __forceinline__ void ring_fetch_interior(const uint16_t* __restrict__ payload, uint32_t ring_address, int chunk,
+                                                    uint32_t lane) {
+  if (chunk >= 0 && lane < kChunkWords / 8) {
+    const uint32_t target = ring_address + static_cast<uint32_t>(((chunk & 3) * kChunkWords + lane * 8) * 2);
+    const uint16_t* source = payload + (static_cast<int64_t>(chunk) * kChunkWords + lane * 8);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(source) : "memory");
+  }
+}
+
+__device__ __forceinline__ void ring_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void ring_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+template <int BYTES> struct Pair;
+template <> struct Pair<1> { using type = uint16_t; };
+template <> struct Pair<2> { using type = uint32_t; };
+template <> struct Pair<4> { using type = uint2; };
+template <> struct Pair<8> { using type = ulonglong2; };
+
+__device__ __forceinline__ uint16_t make_pair(uint8_t a, uint8_t b) { return static_cast<uint16_t>(a | (b << 8)); }
+__device__ __forceinline__ uint32_t make_pair(uint16_t a, uint16_t b) { return a | (static_cast<uint32_t>(b) << 16); }
+__device__ __forceinline__ uint2 make_pair(uint32_t a, uint32_t b) { return make_uint2(a, b); }
+__device__ __forceinline__ ulonglong2 make_pair(uint64_t a, uint64_t b) { return make_ulonglong2(a, b); }
+
+// State of one coded byte lane of the tile a warp is decoding.
+struct CodedLane {
+  uint32_t state;       // this thread's rANS state
+  uint32_t table;       // index (in u32) of the lane's table inside the shared array
+  uint32_t ring;        // index (in u16) of the warp's word ring inside the shared array
+  uint32_t stage;       // index (in bytes) of this thread's byte in the warp's staging block (block base + lane)
+  int cursor;           // (stream begin mod ring size) + words not yet consumed: next read is at cursor - 1
+  int refill_at;        // cursor value at or below which the chunk boundary has been crossed
+  int origin;           // stream begin mod ring size
+  int chunk;            // payload chunk holding the next word to be read
+};
+
+// RAW_MASK >= 0 fixes the lane pattern at compile time (dead per-lane state disappears from the register file);
+// RAW_MASK < 0 reads it from the parameters.
+template <int NLANES, int RAW_MASK>
+__global__ void __launch_bounds__(kThreads, NLANES <= 2 ? kDecodeBlocksPerSm : (NLANES == 4 ? 5 : 1))
+tile_ans_decode_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint32_t shared_tables[];
+  __shared__ int constant_symbol[kMaxLanes];
+  using element_t = typename Element<NLANES>::type;
+  using pair_t = typename Pair<NLANES>::type;
+  uint16_t* const shared_words = reinterpret_cast<uint16_t*>(shared_tables);
+  uint8_t* const shared_bytes = reinterpret_cast<uint8_t*>(shared_tables);
+  const uint32_t table_size = 1u << p.prob_bits;
+  const uint32_t raw_mask = RAW_MASK >= 0 ? static_cast<uint32_t>(RAW_MASK) : p.lanes.raw_mask;
+  stage_decode_tables<NLANES>(p, shared_tables, constant_symbol);
+
+  const int warp = threadIdx.x >> 5;
+  const int64_t tile = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (tile >= p.tiles) return;
+  const uint32_t lane = lane_id();
+  const uint32_t mask_ge = lanemask_ge();
+  const uint32_t slot_mask = table_size - 1u;
+  const int prob_bits = p.prob_bits;
+  const int64_t tile_begin = tile * p.tile_elements;
+  const int count = static_cast<int>(min(p.tile_elements, p.num_elements - tile_begin));
+  const int ans_lanes = p.lanes.ans_lanes;
+  const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
+
+  // dynamic shared memory: tables | rings[warp][rank] | staging[warp][rank]
+  const uint32_t rings_at = static_cast<uint32_t>(ans_lanes) * table_size * 2u;                         // in u16
+  const uint32_t staging_at = (rings_at + static_cast<uint32_t>(kWarps * ans_lanes * kRingWords)) * 2u;  // in bytes
+
+  const uint8_t* raw_bytes[NLANES];
+  CodedLane coded[NLANES];
+  int constant[NLANES];
+  int failure = 0;
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    const int64_t stream = static_cast<int64_t>(b) * p.tiles + tile;
+    const uint32_t begin = p.offsets[stream];
+    const uint32_t end = p.offsets[stream + 1];
+    if (end < begin || static_cast<int64_t>(end) > p.payload_words) failure = EP_STREAM_BAD_OFFSETS;
+    raw_bytes[b] = reinterpret_cast<const uint8_t*>(p.payload + begin);
+    constant[b] = constant_symbol[b];
+    const uint32_t rank = RAW_MASK >= 0 ? static_cast<uint32_t>(__builtin_popcount(~static_cast<uint32_t>(RAW_MASK) & ((1u << b) - 1u)))
+                                        : p.lanes.ans_rank[b];
+    CodedLane& c = coded[b];
+    c.table = rank * table_size;
+    c.ring = rings_at + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kRingWords;
+    c.stage = staging_at + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kBlockElems + lane;
+    c.origin = static_cast<int>(begin & (kRingWords - 1));
+    c.cursor = c.origin + static_cast<int>(end - begin);
+    c.chunk = end > begin ? static_cast<int>((end - 1u) >> kChunkLog) : -1;
+    c.refill_at = c.origin + static_cast<int>((static_cast<int64_t>(c.chunk) << kChunkLog) - static_cast<int64_t>(begin));
+    c.state = kStateMin;
+    if ((raw_mask >> b) & 1u) {
+      if (!failure && end - begin != static_cast<uint32_t>((count + 1) >> 1)) failure = EP_STREAM_BAD_RAW_LENGTH;
+    } else {
+      c.state = p.states[(static_cast<int64_t>(rank) * p.tiles + tile) * kNumStates + lane];
+    }
+  }
+  if (failure) {
+    if (lane == 0) report(p.error, failure);
+    return;
+  }
+  // Three chunks resident, the fourth on its way.
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    if ((raw_mask >> b) & 1u) continue;
+    const uint32_t ring_address = shared_base + coded[b].ring * 2u;
+    ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk, lane);
+    ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 1, lane);
+    ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 2, lane);
+  }
+  ring_commit();
+  ring_wait_all();
+  __syncwarp();
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    if ((raw_mask >> b) & 1u) continue;
+    ring_fetch_interior(p.payload, shared_base + coded[b].ring * 2u, coded[b].chunk - 3, lane);
+  }
+  ring_commit();
+
+  // One decode step of every coded lane for the group at `in_block` (offset inside the staging block).
+  // Branch-free: every thread loads a ring word and only the threads that need it merge it in. A
+  // single-symbol lane (frequency field 0) runs through the same code: its table yields the right
+  // symbol for every slot, its state and cursor become meaningless, all ring reads stay inside the
+  // ring, and its final consistency check is skipped.
+  auto chain_step = [&](int in_block, bool valid) {
+#pragma unroll
+    for (int b = 0; b < NLANES; ++b) {
+      if ((raw_mask >> b) & 1u) continue;
+      CodedLane& c = coded[b];
+      uint32_t x = c.state;
+      if (valid) {
+        const uint32_t entry = shared_tables[c.table + (x & slot_mask)];
+        shared_bytes[c.stage + in_block] = static_cast<uint8_t>(entry);
+        x = ((entry >> 8) & 0xFFFu) * (x >> prob_bits) + (entry >> 20);
+      }
+      const bool need = valid && x < kStateMin;
+      const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
+      const uint32_t at = static_cast<uint32_t>(c.cursor - static_cast<int>(__popc(vote & mask_ge))) & (kRingWords - 1);
+      const uint32_t merged = __byte_perm(static_cast<uint32_t>(shared_words[c.ring + at]), x, 0x5410);
+      c.state = need ? merged : x;
+      c.cursor -= __popc(vote);
+    }
+  };
+  // Ring upkeep, run once every four steps. Three chunks at and below the cursor's chunk are resident
+  // and a fourth is in flight; four steps consume at most 128 words = one chunk, so at most one chunk
+  // boundary is crossed between two calls and every read in between stays inside resident chunks.
+  // On a crossing, the chunk requested one crossing ago is made visible to the warp and the next one
+  // down is requested into the ring slot that has just been vacated.
+  auto ring_upkeep = [&]() {
+#pragma unroll
+    for (int b = 0; b < NLANES; ++b) {
+      if ((raw_mask >> b) & 1u) continue;
+      CodedLane& c = coded[b];
+      if (c.cursor <= c.refill_at) {
+        c.refill_at -= kChunkWords;
+        c.chunk -= 1;
+        ring_wait_all();
+        __syncwarp();
+        ring_fetch_interior(p.payload, shared_base + c.ring * 2u, c.chunk - 3, lane);
+        ring_commit();
+      }
+    }
+  };
+
+  element_t* out = static_cast<element_t*>(p.output) + tile_begin;
+  const bool wide_bytes = NLANES == 1 && (p.tile_elements & 15) == 0;
+  for (int block_lo = ((count - 1) / kBlockElems) * kBlockElems; block_lo >= 0; block_lo -= kBlockElems) {
+    const int block_hi = min(block_lo + kBlockElems, count);
+    // ---- chain phase: groups of 32 symbols, back to front; only the tile's last group can be partial
+    if (block_hi - block_lo == kBlockElems) {
+#pragma unroll
+      for (int group = kBlockElems / 32 - 1; group >= 0; --group) {
+        chain_step(group * 32, true);
+        if ((group & 3) == 0) ring_upkeep();
+      }
+    } else {
+      const int tail = (block_hi - block_lo) & 31;
+      for (int offset = block_hi - (tail ? tail : 32); offset >= block_lo; offset -= 32) {
+        chain_step(offset - block_lo, offset + static_cast<int>(lane) < block_hi);
+        ring_upkeep();
+      }
+    }
+    __syncwarp();
+    // ---- merge phase: raw bytes + staged symbols -> whole elements, vector stores
+    if (wide_bytes) {
+      const int e = block_lo + static_cast<int>(lane) * 16;
+      uint8_t* out_bytes = reinterpret_cast<uint8_t*>(out);
+      const uint32_t staged = coded[0].stage - lane;
+      if (!(raw_mask & 1u) && e + 16 <= block_hi) {
+        *reinterpret_cast<uint4*>(out_bytes + e) = *reinterpret_cast<const uint4*>(shared_bytes + staged + lane * 16);
+      } else {
+        for (int k = e; k < min(e + 16, block_hi); ++k) {
+          out_bytes[k] = (raw_mask & 1u) ? __ldg(raw_bytes[0] + k) : shared_bytes[staged + (k - block_lo)];
+        }
+      }
+    } else {
+#pragma unroll 8
+      for (int e = block_lo + static_cast<int>(lane) * 2; e < block_hi; e += 64) {
+        element_t first = 0, second = 0;
+#pragma unroll
+        for (int b = 0; b < NLANES; ++b) {
+          uint32_t both;
+          if ((raw_mask >> b) & 1u) {
+            both = __ldg(reinterpret_cast<const uint16_t*>(raw_bytes[b] + e));
+          } else {
+            both = shared_words[((coded[b].stage - lane) + static_cast<uint32_t>(e - block_lo)) >> 1];
+          }
+          first |= static_cast<element_t>(static_cast<element_t>(both & 0xFFu) << (8 * b));
+          second |= static_cast<element_t>(static_cast<element_t>(both >> 8) << (8 * b));
+        }
+        if (e + 1 < block_hi) {
+          *reinterpret_cast<pair_t*>(out + e) = make_pair(first, second);
+        } else {
+          out[e] = first;
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int b = 0; b < NLANES; ++b) {
+    if (((raw_mask >> b) & 1u) || constant[b] >= 0) continue;
+    const bool dirty = __any_sync(0xFFFFFFFFu, coded[b].state != kStateMin);
+    const int left = coded[b].cursor - coded[b].origin;
+    if (left < 0) failure = EP_STREAM_UNDERRUN;
+    else if (left != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
   }
   if (failure && lane == 0) report(p.error, failure);
 }
@@ -379,6 +653,34 @@ int allow_shared(Kernel kernel, size_t bytes) {
   return EP_OK;
 }
 
+template <int NLANES>
+int launch_decode(const DecodeParams& p, dim3 grid, size_t table_bytes, bool staged, cudaStream_t stream) {
+  if (staged) {
+    const size_t per_warp_lane = kRingWords * sizeof(uint16_t) + kBlockElems;
+    const size_t shared = table_bytes + static_cast<size_t>(kWarps) * p.lanes.ans_lanes * per_warp_lane;
+    // common patterns get their own instantiation: everything coded, or only the top byte coded
+    constexpr int top_only = (1 << (NLANES - 1)) - 1;
+    if (p.lanes.raw_mask == 0u && NLANES <= 2) {
+      const int rc = allow_shared(tile_ans_decode_kernel<NLANES, 0>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<NLANES, 0><<<grid, kThreads, shared, stream>>>(p);
+    } else if (NLANES > 1 && p.lanes.raw_mask == static_cast<uint32_t>(top_only)) {
+      const int rc = allow_shared(tile_ans_decode_kernel<NLANES, top_only>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<NLANES, top_only><<<grid, kThreads, shared, stream>>>(p);
+    } else {
+      const int rc = allow_shared(tile_ans_decode_kernel<NLANES, -1>, shared);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_kernel<NLANES, -1><<<grid, kThreads, shared, stream>>>(p);
+    }
+  } else {
+    const int rc = allow_shared(tile_ans_decode_simple_kernel<NLANES>, table_bytes);
+    if (rc != EP_OK) return rc;
+    tile_ans_decode_simple_kernel<NLANES><<<grid, kThreads, table_bytes, stream>>>(p);
+  }
+  return EP_OK;
+}
+
 }  // namespace
 }  // namespace ep
 
@@ -410,35 +712,21 @@ extern "C" int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_w
   p.error = error_dev;
   const int64_t blocks = (p.tiles + kWarps - 1) / kWarps;
   if (blocks > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
-  const size_t shared = static_cast<size_t>(p.lanes.ans_lanes) * sizeof(uint32_t) << prob_bits;
+  const size_t table_bytes = static_cast<size_t>(p.lanes.ans_lanes) * sizeof(uint32_t) << prob_bits;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid(static_cast<unsigned>(blocks));
+  // The staged decoder needs 16-byte aligned payload and output and an even tile size; anything else
+  // takes the general kernel.
+  const bool staged = (tile_elements & 1) == 0 && (reinterpret_cast<uintptr_t>(payload_dev) & 15u) == 0 &&
+                      (reinterpret_cast<uintptr_t>(output_dev) & 15u) == 0;
+  int rc = EP_OK;
   switch (num_lanes) {
-    case 1: {
-      const int rc = allow_shared(tile_ans_decode_kernel<1>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<1><<<grid, kThreads, shared, s>>>(p);
-      break;
-    }
-    case 2: {
-      const int rc = allow_shared(tile_ans_decode_kernel<2>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<2><<<grid, kThreads, shared, s>>>(p);
-      break;
-    }
-    case 4: {
-      const int rc = allow_shared(tile_ans_decode_kernel<4>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<4><<<grid, kThreads, shared, s>>>(p);
-      break;
-    }
-    default: {
-      const int rc = allow_shared(tile_ans_decode_kernel<8>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<8><<<grid, kThreads, shared, s>>>(p);
-      break;
-    }
+    case 1: rc = launch_decode<1>(p, grid, table_bytes, staged, s); break;
+    case 2: rc = launch_decode<2>(p, grid, table_bytes, staged, s); break;
+    case 4: rc = launch_decode<4>(p, grid, table_bytes, staged, s); break;
+    default: rc = launch_decode<8>(p, grid, table_bytes, staged, s); break;
   }
+  if (rc != EP_OK) return rc;
   return check_launch("tile_ans_decode_kernel");
 }
 

@@ -1,0 +1,60 @@
+"""Runs one kernel of the hot path a few times on a seeded synthetic case, for use under a profiler.
+
+    python -m entropack_b200.profiling --op tile_ans_decode --kind fp8_e4m3 --rows 8192 --cols 8192 --reps 3
+
+Set-up (tensor generation, encoding) happens first; the profiled kernel then runs ``--reps`` times
+back to back, so ``ncu -k regex:<kernel> -c <reps>`` captures exactly those launches.
+"""
+import argparse
+
+import torch
+
+
+def make_tensor(kind: str, rows: int, cols: int, device, seed: int = 1) -> torch.Tensor:
+    generator = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(rows, cols, generator=generator, device=device)
+    if kind == "fp8_e4m3":
+        return (x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn)
+    if kind == "int8":
+        return (x * 20).round().clamp(-127, 127).to(torch.int8)
+    if kind == "fp16":
+        return (x * 0.02).to(torch.float16)
+    if kind == "bf16":
+        return (x * 0.02).to(torch.bfloat16)
+    if kind == "fp32":
+        return x * 0.02
+    raise ValueError(kind)
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--op", default="tile_ans_decode", choices=("tile_ans_decode", "tile_ans_encode"))
+    parser.add_argument("--kind", default="fp8_e4m3")
+    parser.add_argument("--rows", type=int, default=8192)
+    parser.add_argument("--cols", type=int, default=8192)
+    parser.add_argument("--reps", type=int, default=3)
+    args = parser.parse_args()
+
+    import entropack_b200 as ep
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    tensor = make_tensor(args.kind, args.rows, args.cols, device)
+    config = ep.TileANSConfig()
+    if args.op == "tile_ans_decode":
+        container = ep.compress(tensor, config)
+        torch.cuda.synchronize()
+        for _ in range(args.reps):
+            out = ep.decompress(container, config)
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.uint8), tensor.view(torch.uint8))
+        print(f"{args.op} {args.kind} {args.rows}x{args.cols}: {container.actual_bpp:.4f} bpp, {args.reps} launches")
+    else:
+        for _ in range(args.reps):
+            container = ep.compress(tensor, config)
+        torch.cuda.synchronize()
+        print(f"{args.op} {args.kind} {args.rows}x{args.cols}: {container.actual_bpp:.4f} bpp, {args.reps} launches")
+
+
+if __name__ == "__main__":
+    main()
