@@ -207,6 +207,12 @@ __device__ __forceinline__ void ring_fetch_interior(const uint16_t* __restrict__
   }
 }
 
+__device__ __forceinline__ uint32_t load_shared_u16(uint32_t address) {
+  uint16_t value;
+  asm("ld.shared.u16 %0, [%1];" : "=h"(value) : "r"(address));
+  return value;
+}
+
 __device__ __forceinline__ void ring_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void ring_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
@@ -225,11 +231,11 @@ __device__ __forceinline__ ulonglong2 make_pair(uint64_t a, uint64_t b) { return
 struct CodedLane {
   uint32_t state;       // this thread's rANS state
   uint32_t table;       // index (in u32) of the lane's table inside the shared array
-  uint32_t ring;        // index (in u16) of the warp's word ring inside the shared array
+  uint32_t ring;        // shared address of the warp's word ring (aligned to the ring size, 1 KB)
   uint32_t stage;       // index (in bytes) of this thread's byte in the warp's staging block (block base + lane)
-  int cursor;           // (stream begin mod ring size) + words not yet consumed: next read is at cursor - 1
+  int cursor;           // 2 * ((stream begin mod ring size) + words not yet consumed): byte offset just past the next word
   int refill_at;        // cursor value at or below which the chunk boundary has been crossed
-  int origin;           // stream begin mod ring size
+  int origin;           // 2 * (stream begin mod ring size)
   int chunk;            // payload chunk holding the next word to be read
 };
 
@@ -260,9 +266,10 @@ tile_ans_decode_kernel(const DecodeParams p) {
   const int ans_lanes = p.lanes.ans_lanes;
   const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
 
-  // dynamic shared memory: tables | rings[warp][rank] | staging[warp][rank]
-  const uint32_t rings_at = static_cast<uint32_t>(ans_lanes) * table_size * 2u;                         // in u16
-  const uint32_t staging_at = (rings_at + static_cast<uint32_t>(kWarps * ans_lanes * kRingWords)) * 2u;  // in bytes
+  // dynamic shared memory: tables | pad to 1 KB | rings[warp][rank] | staging[warp][rank]
+  constexpr uint32_t kRingBytes = kRingWords * 2u;
+  const uint32_t rings_address = (shared_base + static_cast<uint32_t>(ans_lanes) * table_size * 4u + kRingBytes - 1u) & ~(kRingBytes - 1u);
+  const uint32_t staging_at = (rings_address - shared_base) + static_cast<uint32_t>(kWarps * ans_lanes) * kRingBytes;  // in bytes
 
   const uint8_t* raw_bytes[NLANES];
   CodedLane coded[NLANES];
@@ -280,12 +287,12 @@ tile_ans_decode_kernel(const DecodeParams p) {
                                         : p.lanes.ans_rank[b];
     CodedLane& c = coded[b];
     c.table = rank * table_size;
-    c.ring = rings_at + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kRingWords;
+    c.ring = rings_address + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kRingBytes;
     c.stage = staging_at + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kBlockElems + lane;
-    c.origin = static_cast<int>(begin & (kRingWords - 1));
-    c.cursor = c.origin + static_cast<int>(end - begin);
+    c.origin = 2 * static_cast<int>(begin & (kRingWords - 1));
+    c.cursor = c.origin + 2 * static_cast<int>(end - begin);
     c.chunk = end > begin ? static_cast<int>((end - 1u) >> kChunkLog) : -1;
-    c.refill_at = c.origin + static_cast<int>((static_cast<int64_t>(c.chunk) << kChunkLog) - static_cast<int64_t>(begin));
+    c.refill_at = c.origin + 2 * static_cast<int>((static_cast<int64_t>(c.chunk) << kChunkLog) - static_cast<int64_t>(begin));
     c.state = kStateMin;
     if ((raw_mask >> b) & 1u) {
       if (!failure && end - begin != static_cast<uint32_t>((count + 1) >> 1)) failure = EP_STREAM_BAD_RAW_LENGTH;
@@ -301,7 +308,7 @@ tile_ans_decode_kernel(const DecodeParams p) {
 #pragma unroll
   for (int b = 0; b < NLANES; ++b) {
     if ((raw_mask >> b) & 1u) continue;
-    const uint32_t ring_address = shared_base + coded[b].ring * 2u;
+    const uint32_t ring_address = coded[b].ring;
     ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk, lane);
     ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 1, lane);
     ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 2, lane);
@@ -312,7 +319,7 @@ tile_ans_decode_kernel(const DecodeParams p) {
 #pragma unroll
   for (int b = 0; b < NLANES; ++b) {
     if ((raw_mask >> b) & 1u) continue;
-    ring_fetch_interior(p.payload, shared_base + coded[b].ring * 2u, coded[b].chunk - 3, lane);
+    ring_fetch_interior(p.payload, coded[b].ring, coded[b].chunk - 3, lane);
   }
   ring_commit();
 
@@ -334,10 +341,12 @@ tile_ans_decode_kernel(const DecodeParams p) {
       }
       const bool need = valid && x < kStateMin;
       const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
-      const uint32_t at = static_cast<uint32_t>(c.cursor - static_cast<int>(__popc(vote & mask_ge))) & (kRingWords - 1);
-      const uint32_t merged = __byte_perm(static_cast<uint32_t>(shared_words[c.ring + at]), x, 0x5410);
+      // this thread's word sits 2 * (readers at or above this lane) bytes below the cursor; thread 0 counts every
+      // reader, so its position is the cursor for the next step
+      const int below = c.cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
+      const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingWords * 2u - 2u)) | c.ring), x, 0x5410);
       c.state = need ? merged : x;
-      c.cursor -= __popc(vote);
+      c.cursor = __shfl_sync(0xFFFFFFFFu, below, 0);
     }
   };
   // Ring upkeep, run once every four steps. Three chunks at and below the cursor's chunk are resident
@@ -351,11 +360,11 @@ tile_ans_decode_kernel(const DecodeParams p) {
       if ((raw_mask >> b) & 1u) continue;
       CodedLane& c = coded[b];
       if (c.cursor <= c.refill_at) {
-        c.refill_at -= kChunkWords;
+        c.refill_at -= 2 * kChunkWords;
         c.chunk -= 1;
         ring_wait_all();
         __syncwarp();
-        ring_fetch_interior(p.payload, shared_base + c.ring * 2u, c.chunk - 3, lane);
+        ring_fetch_interior(p.payload, c.ring, c.chunk - 3, lane);
         ring_commit();
       }
     }
@@ -421,7 +430,7 @@ tile_ans_decode_kernel(const DecodeParams p) {
   for (int b = 0; b < NLANES; ++b) {
     if (((raw_mask >> b) & 1u) || constant[b] >= 0) continue;
     const bool dirty = __any_sync(0xFFFFFFFFu, coded[b].state != kStateMin);
-    const int left = coded[b].cursor - coded[b].origin;
+    const int left = (coded[b].cursor - coded[b].origin) / 2;
     if (left < 0) failure = EP_STREAM_UNDERRUN;
     else if (left != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
   }
@@ -657,7 +666,8 @@ template <int NLANES>
 int launch_decode(const DecodeParams& p, dim3 grid, size_t table_bytes, bool staged, cudaStream_t stream) {
   if (staged) {
     const size_t per_warp_lane = kRingWords * sizeof(uint16_t) + kBlockElems;
-    const size_t shared = table_bytes + static_cast<size_t>(kWarps) * p.lanes.ans_lanes * per_warp_lane;
+    // one ring's worth of padding lets the kernel align the rings to their own size
+    const size_t shared = table_bytes + kRingWords * sizeof(uint16_t) + static_cast<size_t>(kWarps) * p.lanes.ans_lanes * per_warp_lane;
     // common patterns get their own instantiation: everything coded, or only the top byte coded
     constexpr int top_only = (1 << (NLANES - 1)) - 1;
     if (p.lanes.raw_mask == 0u && NLANES <= 2) {
