@@ -7,11 +7,12 @@ there is no CPU or eager execution path.
 """
 from .compression import CompressedTensor, CompressionFallbackWarning, compress, decompress
 from .registry import DispatchError
-from .schemes import CompressionConfig, RawConfig, TileANSConfig
+from .schemes import CompressionConfig, EntroPackLossyConfig, LatticeRANSConfig, RawConfig, TileANSConfig
 
 __version__ = "0.1.0"
 
 __all__ = [
-    "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DispatchError", "RawConfig", "TileANSConfig",
+    "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DispatchError", "EntroPackLossyConfig",
+    "LatticeRANSConfig", "RawConfig", "TileANSConfig",
     "__version__", "compress", "decompress",
 ]

@@ -34,8 +34,21 @@ _PROTOTYPES = {
     "ep_tile_ans_encode": [_ptr, _i64, _i32, _i64, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "ep_exclusive_scan_u32": [_ptr, _i64, _ptr, _ptr, _ptr],
     "ep_compact_streams": [_ptr, _ptr, _ptr, _i64, _i64, _ptr],
+    "ep_lattice_decode": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _ptr, _ptr],
+    "ep_lattice_decode_scratch_bytes": [_i32, _i32],
+    "ep_lattice_row_rms": [_ptr, _i32, _i64, _i64, _ptr, _ptr],
+    "ep_lattice_quantize": [_ptr, _i32, _ptr, _i64, _i64, _f32, _ptr, _ptr, _ptr, _ptr],
+    "ep_lattice_histogram": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr],
+    "ep_lattice_bins_needed": [_ptr],
+    "ep_lattice_max_alphabet": [_ptr],
+    "ep_lattice_coded_bytes": [_ptr, _ptr, _i64, _i32, _i64, _ptr],
+    "ep_lattice_tables": [_ptr, _ptr, _i64, _i32, _ptr, _ptr, _i64, _ptr],
+    "ep_lattice_refit_scales": [_ptr, _i32, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr, _ptr],
+    "ep_lattice_encode_scratch_words": [_i64, _i64],
+    "ep_lattice_encode": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _i32, _i64, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
 _RESTYPES = {"ep_status_string": ctypes.c_char_p, "ep_last_cuda_error": ctypes.c_char_p}
+_INT64_RESULTS = ("ep_lattice_decode_scratch_bytes", "ep_lattice_bins_needed", "ep_lattice_encode_scratch_words")
 
 
 def library_path() -> Path:
@@ -55,7 +68,7 @@ def load():
         for name, argtypes in _PROTOTYPES.items():
             function = getattr(lib, name)
             function.argtypes = argtypes
-            function.restype = ctypes.c_int
+            function.restype = ctypes.c_int64 if name in _INT64_RESULTS else ctypes.c_int
         for name, restype in _RESTYPES.items():
             function = getattr(lib, name)
             function.restype = restype

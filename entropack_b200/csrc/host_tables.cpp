@@ -108,6 +108,182 @@ void choose_modes(const uint64_t* histograms, int lanes, double threshold, int64
 }  // namespace
 }  // namespace ep
 
+namespace ep {
+namespace {
+
+constexpr int kLatticeTables = 17;
+
+// Largest-remainder allocation for the lossy codec's tables (alphabets up to 2^15): one stable sort
+// by fractional part instead of a heap; same results as normalize() above for every histogram.
+// Mirrors _normalize_counts, entropack/schemes/lattice_rans/rans.py:12-53.
+int normalize_sorted(const int64_t* counts, int symbols, int table_size, uint16_t* frequencies) {
+  if (symbols <= 0) return EP_ERR_NORMALIZE;
+  if (symbols > table_size) return EP_ERR_ALPHABET;
+  int64_t total = 0;
+  for (int s = 0; s < symbols; ++s) total += counts[s];
+  if (total == 0) return EP_ERR_NORMALIZE;
+  std::vector<double> residual(symbols);
+  std::vector<int64_t> freq(symbols);
+  const double ratio = static_cast<double>(table_size) / static_cast<double>(total);
+  int64_t sum = 0;
+  for (int s = 0; s < symbols; ++s) {
+    const double target = static_cast<double>(counts[s]) * ratio;
+    freq[s] = static_cast<int64_t>(std::floor(target));
+    if (counts[s] != 0 && freq[s] < 1) freq[s] = 1;
+    residual[s] = target - static_cast<double>(freq[s]);
+    sum += freq[s];
+  }
+  int64_t difference = table_size - sum;
+  std::vector<int> order;
+  order.reserve(symbols);
+  if (difference > 0) {
+    for (int s = 0; s < symbols; ++s) if (counts[s] != 0) order.push_back(s);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return residual[a] > residual[b]; });
+    while (difference > 0) {
+      const int64_t take = std::min<int64_t>(difference, static_cast<int64_t>(order.size()));
+      for (int64_t i = 0; i < take; ++i) freq[order[i]] += 1;
+      difference -= take;
+    }
+  } else if (difference < 0) {
+    for (int s = 0; s < symbols; ++s) if (counts[s] != 0 && freq[s] > 1) order.push_back(s);
+    if (order.empty()) return EP_ERR_NORMALIZE;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return residual[a] < residual[b]; });
+    int64_t need = -difference;
+    while (need > 0) {
+      int64_t live = 0;
+      for (int s : order) live += freq[s] > 1;
+      if (live == 0) return EP_ERR_NORMALIZE;
+      int64_t quota = std::min(need, live);
+      need -= quota;
+      for (int s : order) {
+        if (quota == 0) break;
+        if (freq[s] > 1) {
+          freq[s] -= 1;
+          --quota;
+        }
+      }
+    }
+  }
+  for (int s = 0; s < symbols; ++s) frequencies[s] = static_cast<uint16_t>(freq[s]);
+  return EP_OK;
+}
+
+// Tables of one quantisation pass, from the device's min/max record and compact bins.
+struct LatticeStats {
+  int64_t n_symbols[kLatticeTables];
+  int64_t sym_min[kLatticeTables];
+  int64_t alphabet[kLatticeTables];
+  std::vector<int64_t> counts[kLatticeTables];
+};
+
+int gather_stats(const int32_t* minmax, const int32_t* bins, int64_t vectors, LatticeStats* stats) {
+  constexpr int32_t kUnset = 0x7FFFFFFF;
+  if (minmax[33] != 0) return EP_ERR_ALPHABET;  // a field left the int16 range
+  int64_t cursor = 2;
+  stats->alphabet[0] = static_cast<int64_t>(minmax[32]) + 1;
+  stats->sym_min[0] = 0;
+  stats->n_symbols[0] = vectors;
+  stats->counts[0].assign(bins, bins + stats->alphabet[0]);
+  const int64_t by_coset[2] = {bins[0], bins[1]};
+  if (by_coset[0] + by_coset[1] != vectors) return EP_ERR_INVALID_ARGUMENT;
+  for (int st = 0; st < 16; ++st) {
+    const int t = 1 + st;
+    const bool live = minmax[st * 2] != kUnset;
+    stats->alphabet[t] = live ? static_cast<int64_t>(minmax[st * 2 + 1]) - minmax[st * 2] + 1 : 0;
+    stats->sym_min[t] = live ? minmax[st * 2] : 0;
+    stats->n_symbols[t] = by_coset[st & 1];
+    stats->counts[t].assign(bins + cursor, bins + cursor + stats->alphabet[t]);
+    cursor += stats->alphabet[t];
+  }
+  return EP_OK;
+}
+
+}  // namespace
+}  // namespace ep
+
+extern "C" int64_t ep_lattice_bins_needed(const int32_t* minmax_host) {
+  if (!minmax_host) return EP_ERR_INVALID_ARGUMENT;
+  int64_t cursor = 2;
+  for (int st = 0; st < 16; ++st) {
+    if (minmax_host[st * 2] != 0x7FFFFFFF) cursor += static_cast<int64_t>(minmax_host[st * 2 + 1]) - minmax_host[st * 2] + 1;
+  }
+  return cursor;
+}
+
+extern "C" int ep_lattice_max_alphabet(const int32_t* minmax_host) {
+  if (!minmax_host) return EP_ERR_INVALID_ARGUMENT;
+  int64_t widest = static_cast<int64_t>(minmax_host[32]) + 1;
+  for (int st = 0; st < 16; ++st) {
+    if (minmax_host[st * 2] != 0x7FFFFFFF) widest = std::max(widest, static_cast<int64_t>(minmax_host[st * 2 + 1]) - minmax_host[st * 2] + 1);
+  }
+  return widest > 0x7FFFFFFF ? 0x7FFFFFFF : static_cast<int>(widest);
+}
+
+extern "C" int ep_lattice_coded_bytes(const int32_t* minmax_host, const int32_t* bins_host, int64_t vectors, int prob_bits,
+                                      int64_t tile_elements, double* bytes_out) {
+  using namespace ep;
+  if (!minmax_host || !bins_host || !bytes_out || vectors <= 0 || prob_bits < 9 || prob_bits > 15 || tile_elements <= 0) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  LatticeStats stats;
+  const int rc = gather_stats(minmax_host, bins_host, vectors, &stats);
+  if (rc != EP_OK) return rc;
+  const int table_size = 1 << prob_bits;
+  double bits = 0.0, overflow_bits = 0.0;
+  int64_t frequency_bytes = 0;
+  std::vector<uint16_t> freq;
+  for (int t = 0; t < kLatticeTables; ++t) {
+    if (stats.n_symbols[t] && stats.alphabet[t] <= table_size) {
+      freq.resize(stats.alphabet[t]);
+      const int status = normalize_sorted(stats.counts[t].data(), static_cast<int>(stats.alphabet[t]), table_size, freq.data());
+      if (status != EP_OK) return status;
+      for (int64_t s = 0; s < stats.alphabet[t]; ++s) {
+        if (stats.counts[t][s] > 0) bits += static_cast<double>(stats.counts[t][s]) * (prob_bits - std::log2(static_cast<double>(freq[s])));
+      }
+      frequency_bytes += stats.alphabet[t] * 2;
+    } else {
+      overflow_bits += static_cast<double>(stats.n_symbols[t]) * prob_bits;
+    }
+  }
+  const int64_t tile_vectors = std::max<int64_t>(32, tile_elements / 9);
+  const int64_t tiles = std::max<int64_t>(1, (vectors + tile_vectors - 1) / tile_vectors);
+  const double excess = std::max(0.0, bits - static_cast<double>(tiles * 32 * 16));
+  const int64_t payload_words = static_cast<int64_t>(std::ceil(excess / 16.0));
+  *bytes_out = static_cast<double>(payload_words * 2 + tiles * 32 * 4 + (tiles + 1) * 4 + frequency_bytes) + overflow_bits / 8.0;
+  return EP_OK;
+}
+
+extern "C" int ep_lattice_tables(const int32_t* minmax_host, const int32_t* bins_host, int64_t vectors, int prob_bits,
+                                 int32_t* stream_meta_host, uint16_t* freq_tables_host, int64_t freq_capacity,
+                                 int64_t* freq_entries_out) {
+  using namespace ep;
+  if (!minmax_host || !bins_host || !stream_meta_host || !freq_tables_host || !freq_entries_out || vectors <= 0 ||
+      prob_bits < 9 || prob_bits > 15) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  LatticeStats stats;
+  const int rc = gather_stats(minmax_host, bins_host, vectors, &stats);
+  if (rc != EP_OK) return rc;
+  const int table_size = 1 << prob_bits;
+  int64_t cursor = 0;
+  for (int t = 0; t < kLatticeTables; ++t) {
+    const int64_t alphabet = stats.n_symbols[t] ? stats.alphabet[t] : 0;
+    if (alphabet > table_size) return EP_ERR_ALPHABET;
+    if (cursor + alphabet > freq_capacity) return EP_ERR_INVALID_ARGUMENT;
+    if (alphabet) {
+      const int status = normalize_sorted(stats.counts[t].data(), static_cast<int>(alphabet), table_size, freq_tables_host + cursor);
+      if (status != EP_OK) return status;
+    }
+    stream_meta_host[t * 4 + 0] = static_cast<int32_t>(stats.n_symbols[t]);
+    stream_meta_host[t * 4 + 1] = static_cast<int32_t>(stats.sym_min[t]);
+    stream_meta_host[t * 4 + 2] = static_cast<int32_t>(cursor);
+    stream_meta_host[t * 4 + 3] = static_cast<int32_t>(alphabet);
+    cursor += alphabet;
+  }
+  *freq_entries_out = cursor;
+  return EP_OK;
+}
+
 extern "C" const char* ep_status_string(int status) {
   switch (status) {
     case EP_OK: return "ok";

@@ -1,0 +1,393 @@
+// EntroPack-Lossy decode for sm_100a: coset-conditioned rANS over 17 tables, E8 reconstruction and the
+// container cast, fused into one kernel.
+//
+// Format (entropack/schemes/lattice_rans/format.py:91-98, rans.py:133-221): vectors of 8 values in
+// row-major order are cut into tiles of `tile_vectors`; a tile is a 32-way interleaved rANS stream
+// read back to front. Per group of 32 vectors the decoder reads the coset (table 0) and then fields
+// 0..7 (table 1 + 2*field + coset). Field 7 is m with z7 = 2m + (sum(z0..z6) & 1). A value is
+// fl32(fl32(z + coset/2) * scale[row]) cast to the container dtype.
+//
+// One warp decodes one tile at a time; a persistent block walks the tile list. The slot tables are
+// rebuilt from the stored frequencies inside the kernel -- no host-side plan, no cached side tables:
+//   * shared path (prob_bits <= 11, every alphabet <= 512): each block builds all 17 tables as packed
+//     32-bit entries (symbol | freq << 9 | (slot - cdf) << 21) in its own shared memory;
+//   * global path (anything else): a small kernel first writes 64-bit entries
+//     (symbol | freq << 16 | (slot - cdf) << 32) into caller-provided scratch, read through L1.
+// Payload words reach the chain through the per-warp cp.async ring of rans_ring.cuh.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+
+#include "ep_common.cuh"
+#include "rans_ring.cuh"
+
+namespace ep {
+namespace {
+
+constexpr int kTables = 17;
+constexpr int kDecodeWarps = 24;
+constexpr int kDecodeThreads = kDecodeWarps * 32;
+constexpr int kSharedMaxProbBits = 11;
+constexpr int kSharedMaxAlphabet = 512;
+
+struct LatticeDecodeParams {
+  const uint16_t* payload;
+  int64_t payload_words;
+  const uint32_t* offsets;
+  const uint32_t* states;
+  const int32_t* stream_meta;   // [17][4]: n_symbols, sym_min, freq_offset, alphabet
+  const uint16_t* freq_tables;
+  const float* scales;
+  void* output;
+  const uint64_t* global_tables;  // [17][1 << prob_bits], global path only
+  int64_t vectors;
+  int64_t tiles;
+  int tile_vectors;
+  int vecs_per_row;
+  int prob_bits;
+  int store_kind;
+  int* error;
+};
+
+// ---- container cast (entropack/schemes/lattice_rans/format.py:153-168) ---------------------------
+template <typename T>
+__device__ __forceinline__ T snap_integer(float value, float low, float high_exclusive) {
+  const float high = nextafterf(high_exclusive, 0.0f);
+  return static_cast<T>(fminf(fmaxf(rintf(value), low), high));
+}
+
+__device__ __forceinline__ uint32_t bf16_bits(float v) {
+  const float limit = 3.3895313892515355e38f;  // largest finite bf16
+  const __nv_bfloat16 h = __float2bfloat16_rn(fminf(fmaxf(v, -limit), limit));
+  return static_cast<uint32_t>(__bfloat16_as_ushort(h));
+}
+
+// Writes the eight reconstructed values of vector `vector` as `kind` elements.
+__device__ __forceinline__ void store_vector(void* output, int64_t vector, const float* v, int kind) {
+  char* const base = static_cast<char*>(output);
+  switch (kind) {
+    case EP_STORE_BF16: {
+      uint4 packed;
+      packed.x = bf16_bits(v[0]) | (bf16_bits(v[1]) << 16);
+      packed.y = bf16_bits(v[2]) | (bf16_bits(v[3]) << 16);
+      packed.z = bf16_bits(v[4]) | (bf16_bits(v[5]) << 16);
+      packed.w = bf16_bits(v[6]) | (bf16_bits(v[7]) << 16);
+      *reinterpret_cast<uint4*>(base + vector * 16) = packed;
+      break;
+    }
+    case EP_STORE_F16: {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t lo = __half_as_ushort(__float2half_rn(fminf(fmaxf(v[2 * j], -65504.0f), 65504.0f)));
+        const uint32_t hi = __half_as_ushort(__float2half_rn(fminf(fmaxf(v[2 * j + 1], -65504.0f), 65504.0f)));
+        w[j] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4*>(base + vector * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      break;
+    }
+    case EP_STORE_F32: {
+      float4* out = reinterpret_cast<float4*>(base + vector * 32);
+      out[0] = make_float4(v[0], v[1], v[2], v[3]);
+      out[1] = make_float4(v[4], v[5], v[6], v[7]);
+      break;
+    }
+    case EP_STORE_F8_E4M3:
+    case EP_STORE_F8_E5M2: {
+      const float limit = kind == EP_STORE_F8_E4M3 ? 448.0f : 57344.0f;
+      const __nv_fp8_interpretation_t interpretation = kind == EP_STORE_F8_E4M3 ? __NV_E4M3 : __NV_E5M2;
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t bits = __nv_cvt_float_to_fp8(fminf(fmaxf(v[j], -limit), limit), __NV_SATFINITE, interpretation);
+        w[j >> 2] |= bits << (8 * (j & 3));
+      }
+      *reinterpret_cast<uint2*>(base + vector * 8) = make_uint2(w[0], w[1]);
+      break;
+    }
+    case EP_STORE_I8:
+    case EP_STORE_U8:
+    case EP_STORE_BOOL: {
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t bits;
+        if (kind == EP_STORE_I8) bits = static_cast<uint8_t>(snap_integer<int8_t>(v[j], -128.0f, 128.0f));
+        else if (kind == EP_STORE_U8) bits = snap_integer<uint8_t>(v[j], 0.0f, 256.0f);
+        else bits = rintf(v[j]) != 0.0f ? 1u : 0u;
+        w[j >> 2] |= bits << (8 * (j & 3));
+      }
+      *reinterpret_cast<uint2*>(base + vector * 8) = make_uint2(w[0], w[1]);
+      break;
+    }
+    case EP_STORE_I16:
+    case EP_STORE_U16: {
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t bits = kind == EP_STORE_I16 ? static_cast<uint16_t>(snap_integer<int16_t>(v[j], -32768.0f, 32768.0f))
+                                                   : snap_integer<uint16_t>(v[j], 0.0f, 65536.0f);
+        w[j >> 1] |= bits << (16 * (j & 1));
+      }
+      *reinterpret_cast<uint4*>(base + vector * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      break;
+    }
+    case EP_STORE_I32:
+    case EP_STORE_U32: {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        w[j] = kind == EP_STORE_I32 ? static_cast<uint32_t>(snap_integer<int32_t>(v[j], -2147483648.0f, 2147483648.0f))
+                                    : snap_integer<uint32_t>(v[j], 0.0f, 4294967296.0f);
+      }
+      uint4* out = reinterpret_cast<uint4*>(base + vector * 32);
+      out[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      break;
+    }
+    default: {  // EP_STORE_I64 / EP_STORE_U64
+      unsigned long long* out = reinterpret_cast<unsigned long long*>(base + vector * 64);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        out[j] = kind == EP_STORE_I64
+            ? static_cast<unsigned long long>(snap_integer<long long>(v[j], -9223372036854775808.0f, 9223372036854775808.0f))
+            : snap_integer<unsigned long long>(v[j], 0.0f, 18446744073709551616.0f);
+      }
+      break;
+    }
+  }
+}
+
+// ---- slot tables -----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_entry32(uint32_t symbol, uint32_t freq, uint32_t delta) {
+  return symbol | (freq << 9) | (delta << 21);
+}
+__device__ __forceinline__ uint64_t pack_entry64(uint32_t symbol, uint32_t freq, uint32_t delta) {
+  return static_cast<uint64_t>(symbol) | (static_cast<uint64_t>(freq) << 16) | (static_cast<uint64_t>(delta) << 32);
+}
+
+// One warp fills table `t`: symbols in order, the 32 threads sharing each symbol's run of slots. Slots
+// the stored frequencies do not cover (a corrupt table) keep entry 0, which decodes to symbol 0.
+template <typename Entry, typename Pack>
+__device__ __forceinline__ void fill_table(Entry* table, const int32_t* stream_meta, const uint16_t* freq_tables, int t,
+                                           uint32_t table_size, uint32_t lane, Pack pack) {
+  const int offset = stream_meta[t * 4 + 2];
+  const int alphabet = stream_meta[t * 4 + 3];
+  for (uint32_t slot = lane; slot < table_size; slot += 32) table[slot] = Entry(0);
+  __syncwarp();
+  uint32_t running = 0;
+  for (int base = 0; base < alphabet; base += 32) {
+    const uint32_t mine = base + static_cast<int>(lane) < alphabet ? freq_tables[offset + base + lane] : 0u;
+    const int batch = min(32, alphabet - base);
+    for (int k = 0; k < batch; ++k) {
+      const uint32_t freq = __shfl_sync(0xFFFFFFFFu, mine, k);
+      const uint32_t end = min(running + freq, table_size);
+      for (uint32_t slot = running + lane; slot < end; slot += 32) table[slot] = pack(static_cast<uint32_t>(base + k), freq, slot - running);
+      running = end;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(32) lattice_build_tables_kernel(uint64_t* tables, const int32_t* stream_meta,
+                                                                  const uint16_t* freq_tables, int prob_bits) {
+  const uint32_t table_size = 1u << prob_bits;
+  fill_table<uint64_t>(tables + static_cast<size_t>(blockIdx.x) * table_size, stream_meta, freq_tables, blockIdx.x, table_size,
+                       lane_id(), pack_entry64);
+}
+
+// ---- decode ----------------------------------------------------------------------------------------
+template <bool SHARED_TABLES>
+__global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const LatticeDecodeParams p) {
+  extern __shared__ __align__(16) uint32_t shared_tables[];  // [17][table_size] when SHARED_TABLES
+  __shared__ int sym_min[kTables + 1];
+  const uint32_t lane = lane_id();
+  const int warp = threadIdx.x >> 5;
+  const uint32_t table_size = 1u << p.prob_bits;
+  const uint32_t slot_mask = table_size - 1u;
+  const int prob_bits = p.prob_bits;
+  const uint32_t mask_ge = lanemask_ge();
+  const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
+
+  if (threadIdx.x < kTables) sym_min[threadIdx.x] = p.stream_meta[threadIdx.x * 4 + 1];
+  if (SHARED_TABLES) {
+    for (int t = warp; t < kTables; t += kDecodeWarps) {
+      fill_table<uint32_t>(shared_tables + static_cast<size_t>(t) * table_size, p.stream_meta, p.freq_tables, t, table_size, lane,
+                           pack_entry32);
+    }
+  }
+  __syncthreads();
+
+  constexpr uint32_t kRingBytes = kRingWords * 2u;
+  const uint32_t table_bytes = SHARED_TABLES ? kTables * table_size * 4u : 0u;
+  const uint32_t ring = ((shared_base + table_bytes + kRingBytes - 1u) & ~(kRingBytes - 1u)) + static_cast<uint32_t>(warp) * kRingBytes;
+
+  for (int64_t tile = static_cast<int64_t>(blockIdx.x) * kDecodeWarps + warp; tile < p.tiles;
+       tile += static_cast<int64_t>(gridDim.x) * kDecodeWarps) {
+    const int64_t tile_begin = tile * p.tile_vectors;
+    const int count = static_cast<int>(min(static_cast<int64_t>(p.tile_vectors), p.vectors - tile_begin));
+    const uint32_t begin = p.offsets[tile];
+    const uint32_t end = p.offsets[tile + 1];
+    if (end < begin || static_cast<int64_t>(end) > p.payload_words) {
+      if (lane == 0) report(p.error, EP_STREAM_BAD_OFFSETS);
+      continue;
+    }
+    uint32_t x = p.states[tile * kNumStates + lane];
+    const int origin = 2 * static_cast<int>(begin & (kRingWords - 1));
+    int cursor = origin + 2 * static_cast<int>(end - begin);
+    int chunk = end > begin ? static_cast<int>((end - 1u) >> kChunkLog) : -1;
+    int refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(chunk) << kChunkLog) - static_cast<int64_t>(begin));
+    // the previous tile's last prefetch may still be in flight and every thread must be past its reads
+    // of the old ring contents before the ring is refilled
+    ring_wait_all();
+    __syncwarp();
+    ring_fetch_clipped(p.payload, p.payload_words, ring, chunk, lane);
+    ring_fetch_clipped(p.payload, p.payload_words, ring, chunk - 1, lane);
+    ring_fetch_clipped(p.payload, p.payload_words, ring, chunk - 2, lane);
+    ring_commit();
+    ring_wait_all();
+    __syncwarp();
+    ring_fetch_interior(p.payload, ring, chunk - 3, lane);
+    ring_commit();
+
+    // One symbol from table `t`; returns the symbol. Same chain as the Tile-ANS decoder.
+    auto step = [&](int t, bool valid) -> uint32_t {
+      uint32_t symbol = 0;
+      if (valid) {
+        const uint32_t slot = x & slot_mask;
+        if (SHARED_TABLES) {
+          const uint32_t entry = shared_tables[static_cast<uint32_t>(t) * table_size + slot];
+          symbol = entry & 0x1FFu;
+          x = ((entry >> 9) & 0xFFFu) * (x >> prob_bits) + (entry >> 21);
+        } else {
+          const uint64_t entry = __ldg(p.global_tables + static_cast<size_t>(t) * table_size + slot);
+          symbol = static_cast<uint32_t>(entry) & 0xFFFFu;
+          x = ((static_cast<uint32_t>(entry) >> 16) & 0xFFFFu) * (x >> prob_bits) + static_cast<uint32_t>(entry >> 32);
+        }
+      }
+      const bool need = valid && x < kStateMin;
+      const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
+      const int below = cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
+      const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingBytes - 2u)) | ring), x, 0x5410);
+      x = need ? merged : x;
+      cursor = __shfl_sync(0xFFFFFFFFu, below, 0);
+      return symbol;
+    };
+    auto upkeep = [&]() {
+      if (cursor <= refill_at) {
+        refill_at -= 2 * kChunkWords;
+        chunk -= 1;
+        ring_wait_all();
+        __syncwarp();
+        ring_fetch_interior(p.payload, ring, chunk - 3, lane);
+        ring_commit();
+      }
+    };
+
+    // groups of 32 vectors, back to front; a partial group at the tile's end comes first
+    int offset = count - (count & 31);
+    bool valid = lane < static_cast<uint32_t>(count & 31);
+    if ((count & 31) == 0) {
+      offset -= 32;
+      valid = true;
+    }
+    for (; offset >= 0; offset -= 32, valid = true) {
+      const int coset = static_cast<int>(step(0, valid));
+      int value[8];
+#pragma unroll
+      for (int field = 0; field < 8; ++field) {
+        const int t = 1 + 2 * field + coset;
+        value[field] = static_cast<int>(step(t, valid)) + sym_min[t];
+        if (field == 1 || field == 4 || field == 7) upkeep();  // every three steps: at most 96 words
+      }
+      if (valid) {
+        int parity = 0;
+#pragma unroll
+        for (int field = 0; field < 7; ++field) parity += value[field];
+        value[7] = 2 * value[7] + (parity & 1);
+        const int64_t vector = tile_begin + offset + lane;
+        const float scale = __ldg(p.scales + static_cast<uint32_t>(vector) / static_cast<uint32_t>(p.vecs_per_row));
+        const float half = coset ? 0.5f : 0.0f;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fadd_rn(static_cast<float>(value[j]), half), scale);
+        store_vector(p.output, vector, v, p.store_kind);
+      }
+    }
+    const bool dirty = __any_sync(0xFFFFFFFFu, x != kStateMin);
+    const int left = (cursor - origin) / 2;
+    if (lane == 0) {
+      if (left < 0) report(p.error, EP_STREAM_UNDERRUN);
+      else if (left != 0 || dirty) report(p.error, EP_STREAM_NOT_CONSUMED);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace ep
+
+using namespace ep;
+
+extern "C" int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphabet) {
+  if (prob_bits < 9 || prob_bits > 15) return EP_ERR_INVALID_ARGUMENT;
+  if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) return 0;
+  return static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
+}
+
+extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                 const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
+                                 const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
+                                 int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
+                                 int64_t table_scratch_bytes, int* error_dev, ep_stream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 7) != 0 || prob_bits < 9 || prob_bits > 15 || tile_elements <= 0 ||
+      store_kind < 0 || store_kind > EP_STORE_BOOL || max_alphabet < 0 || max_alphabet > (1 << prob_bits) ||
+      payload_words < 0 || !offsets_dev || !states_dev || !stream_meta_dev || !freq_tables_dev || !scales_dev || !output_dev) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (payload_words > 0 && !payload_dev) return EP_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(payload_dev) & 15u) || (reinterpret_cast<uintptr_t>(output_dev) & 15u)) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  const int64_t vectors = rows * (cols / 8);
+  if (vectors >= (int64_t(1) << 31)) return EP_ERR_TOO_LARGE;
+  LatticeDecodeParams p;
+  p.payload = payload_dev;
+  p.payload_words = payload_words;
+  p.offsets = offsets_dev;
+  p.states = states_dev;
+  p.stream_meta = stream_meta_dev;
+  p.freq_tables = freq_tables_dev;
+  p.scales = scales_dev;
+  p.output = output_dev;
+  p.global_tables = nullptr;
+  p.vectors = vectors;
+  const int64_t tile_vectors = tile_elements / 9 < 32 ? 32 : tile_elements / 9;
+  if (tile_vectors > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
+  p.tile_vectors = static_cast<int>(tile_vectors);
+  p.tiles = (vectors + tile_vectors - 1) / tile_vectors;
+  p.vecs_per_row = static_cast<int>(cols / 8);
+  p.prob_bits = prob_bits;
+  p.store_kind = store_kind;
+  p.error = error_dev;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t wanted = (p.tiles + kDecodeWarps - 1) / kDecodeWarps;
+  const unsigned blocks = static_cast<unsigned>(wanted < kSmCount ? wanted : kSmCount);
+  const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
+  if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) {
+    const size_t shared = (static_cast<size_t>(kTables) * sizeof(uint32_t) << prob_bits) + ring_bytes;
+    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(shared)));
+    lattice_decode_kernel<true><<<blocks, kDecodeThreads, shared, s>>>(p);
+  } else {
+    const int64_t needed = static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
+    if (!table_scratch_dev || table_scratch_bytes < needed || (reinterpret_cast<uintptr_t>(table_scratch_dev) & 7u)) {
+      return EP_ERR_INVALID_ARGUMENT;
+    }
+    uint64_t* tables = static_cast<uint64_t*>(table_scratch_dev);
+    lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, prob_bits);
+    p.global_tables = tables;
+    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(ring_bytes)));
+    lattice_decode_kernel<false><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+  }
+  return check_launch("lattice_decode_kernel");
+}

@@ -13,6 +13,7 @@
 // Encode: one warp owns one tile across all byte lanes as well, so the input is read once as whole
 // elements. Division by the symbol frequency uses a per-symbol 32-bit reciprocal with one correction.
 #include "ep_common.cuh"
+#include "rans_ring.cuh"
 
 namespace ep {
 namespace {
@@ -179,43 +180,7 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_simple_kernel(const 
 // compiler emits plain LDS/STS with scaled addressing.
 // ------------------------------------------------------------------------------------------------
 constexpr int kBlockElems = 512;   // elements staged per warp between merges (16 groups of 32)
-constexpr int kChunkLog = 7;       // ring chunk: 128 words = 256 bytes = sixteen 16-byte copies
-constexpr int kChunkWords = 1 << kChunkLog;
-constexpr int kRingWords = 4 * kChunkWords;
 constexpr int kDecodeBlocksPerSm = 7;
-
-// Copies chunk `chunk` of the payload into its ring slot (threads 0..15, 16 bytes each). The first
-// chunks of a stream may straddle the end of the payload, so the copy length is clipped there.
-__device__ __forceinline__ void ring_fetch_clipped(const uint16_t* __restrict__ payload, int64_t payload_words,
-                                                   uint32_t ring_address, int chunk, uint32_t lane) {
-  if (chunk < 0 || lane >= kChunkWords / 8) return;
-  const int64_t word = static_cast<int64_t>(chunk) * kChunkWords + lane * 8;
-  const int64_t remaining = payload_words - word;
-  if (remaining <= 0) return;
-  const int bytes = remaining >= 8 ? 16 : static_cast<int>(remaining) * 2;
-  const uint32_t target = ring_address + static_cast<uint32_t>(((chunk & 3) * kChunkWords + lane * 8) * 2);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(payload + word), "r"(bytes) : "memory");
-}
-
-// Same for a chunk known to lie wholly inside the payload (any chunk below one already fetched).
-__device__ __forceinline__ void ring_fetch_interior(const uint16_t* __restrict__ payload, uint32_t ring_address, int chunk,
-                                                    uint32_t lane) {
-  if (chunk >= 0 && lane < kChunkWords / 8) {
-    const uint32_t target = ring_address + static_cast<uint32_t>(((chunk & 3) * kChunkWords + lane * 8) * 2);
-    const uint16_t* source = payload + (static_cast<int64_t>(chunk) * kChunkWords + lane * 8);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(source) : "memory");
-  }
-}
-
-__device__ __forceinline__ uint32_t load_shared_u16(uint32_t address) {
-  uint16_t value;
-  asm("ld.shared.u16 %0, [%1];" : "=h"(value) : "r"(address));
-  return value;
-}
-
-__device__ __forceinline__ void ring_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void ring_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 template <int BYTES> struct Pair;
 template <> struct Pair<1> { using type = uint16_t; };
 template <> struct Pair<2> { using type = uint32_t; };

@@ -1,0 +1,67 @@
+"""EntroPack-Lossy lane over the sm_100a kernel library.
+
+Entry points mirror the reference's lane (entropack/schemes/lattice_rans/cuda.py:561,781):
+``encode(weight, *, target_bpp, prob_bits, tile_elements, row_rdo_iterations, row_rdo_candidates,
+scale_search_iterations, scale_search_max_vectors)`` and ``decode(buffers, *, shape, dtype,
+threads_per_block, l2_prefetch)``.
+"""
+import torch
+
+from ... import _native
+from .format import LATTICE_DIM, LatticeBuffers, decode_geometry, snap_to_container
+
+STORE_KINDS = {
+    torch.bfloat16: 0, torch.float16: 1, torch.float32: 2, torch.float8_e4m3fn: 3, torch.float8_e5m2: 4, torch.int8: 5,
+    torch.uint8: 6, torch.int16: 7, torch.uint16: 8, torch.int32: 9, torch.uint32: 10, torch.int64: 11, torch.uint64: 12,
+    torch.bool: 13,
+}
+#: no saturating device cast exists for these; they are decoded to fp32 and cast by torch, as in the reference
+_VIA_FLOAT32 = frozenset({torch.float8_e4m3fnuz, torch.float8_e5m2fnuz})
+
+
+def max_alphabet(buffers: LatticeBuffers) -> int:
+    """Largest alphabet of the 17 tables; read from the device once per container and cached on the layout."""
+    cached = getattr(buffers.layout, "_lattice_rans_max_alphabet", None)
+    if cached is None:
+        cached = int(buffers.stream_meta[:, 3].max().item())
+        buffers.layout._lattice_rans_max_alphabet = cached
+    return cached
+
+
+def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_block=None, l2_prefetch=True,
+           error: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Decode to ``[rows, cols_padded]`` of ``dtype`` on the buffers' device (one or two launches, no host sync
+    after the first call on a container)."""
+    payload = buffers.payload
+    _native.require_cuda(payload)
+    info = decode_geometry(buffers._asdict(), shape)
+    rows, cols, prob_bits = info["rows"], info["cols"], info["prob_bits"]
+    device = payload.device
+    via_float = dtype in _VIA_FLOAT32
+    out_dtype = torch.float32 if via_float else dtype
+    if out is None:
+        out = torch.empty((rows, cols), dtype=out_dtype, device=device)
+    alphabet = max_alphabet(buffers)
+    lib = _native.load()
+    scratch_bytes = lib.ep_lattice_decode_scratch_bytes(prob_bits, alphabet)
+    if scratch_bytes < 0:
+        _native.check(int(scratch_bytes), "lattice_rans decode")
+    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=device) if scratch_bytes else None
+    with torch.cuda.device(device):
+        status = lib.ep_lattice_decode(
+            _native.ptr(payload), payload.numel(), _native.ptr(buffers.offsets), _native.ptr(buffers.states),
+            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), _native.ptr(buffers.scales), _native.ptr(out),
+            STORE_KINDS[out_dtype], rows, cols, prob_bits, info["tile_elements"], alphabet, _native.ptr(scratch),
+            scratch_bytes, _native.ptr(error), _native.stream_handle(device))
+    _native.check(status, "lattice_rans decode")
+    return snap_to_container(out, dtype) if via_float else out
+
+
+def encode(weight, *, target_bpp, prob_bits, tile_elements, row_rdo_iterations, row_rdo_candidates,
+           scale_search_iterations, scale_search_max_vectors) -> LatticeBuffers:
+    from . import encoder
+
+    return encoder.encode(
+        weight, target_bpp=float(target_bpp), prob_bits=prob_bits, tile_elements=int(tile_elements),
+        row_rdo_iterations=int(row_rdo_iterations), scale_search_iterations=int(scale_search_iterations),
+        scale_search_max_vectors=int(scale_search_max_vectors))

@@ -96,6 +96,93 @@ int ep_exclusive_scan_u32(const uint32_t* counts_dev, int64_t count, uint32_t* o
 int ep_compact_streams(const uint16_t* scratch_dev, const uint32_t* offsets_dev, uint16_t* payload_dev, int64_t slot_words,
                        int64_t streams, ep_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * EntroPack-Lossy (E8 lattice + coset-conditioned rANS).
+ * Buffer schema: entropack/schemes/lattice_rans/format.py:91-98.
+ * ------------------------------------------------------------------------------------------- */
+
+/* element type written by ep_lattice_decode (the reference's store kinds, lattice_rans/cuda.py:65-69) */
+#define EP_STORE_BF16 0
+#define EP_STORE_F16 1
+#define EP_STORE_F32 2
+#define EP_STORE_F8_E4M3 3
+#define EP_STORE_F8_E5M2 4
+#define EP_STORE_I8 5
+#define EP_STORE_U8 6
+#define EP_STORE_I16 7
+#define EP_STORE_U16 8
+#define EP_STORE_I32 9
+#define EP_STORE_U32 10
+#define EP_STORE_I64 11
+#define EP_STORE_U64 12
+#define EP_STORE_BOOL 13
+
+/* Bytes of table scratch ep_lattice_decode needs for a container: 0 when the slot tables fit in
+ * shared memory (prob_bits <= 11 and every alphabet <= 512), else 17 * 2^prob_bits * 8. */
+int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphabet);
+
+/* Decode + reconstruct + container cast into output_dev[rows][cols] (cols = the padded column count
+ * stored in the layout, a multiple of 8). Stands in for decode() of
+ * entropack/schemes/lattice_rans/cuda.py:781-805 together with its host-side _decode_plan (:697-741)
+ * and the e8_decode_vector_* kernels (lattice_rans.cu:732-1141): the slot tables are rebuilt on the
+ * device from freq_tables, so there is no plan to cache. `max_alphabet` is the largest alphabet in
+ * stream_meta (the caller reads that 17x4 buffer once). bf16 output saturates at the largest finite
+ * value, as the reference's eager lane does. */
+int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                      const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
+                      const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols, int prob_bits,
+                      int64_t tile_elements, int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes,
+                      int* error_dev, ep_stream_t stream);
+
+/* --- encode. Work tensors are bf16 or fp32 [rows][cols], cols a multiple of 8 (is_bf16 selects);
+ * quantised symbols travel as fields_dev int16[vectors][8] (z0..z6, m) and cosets_dev u8[vectors].
+ * Replaces the kernels and host glue of entropack/schemes/lattice_rans/cuda.py:115-597. --- */
+
+/* rms_dev[row] = max(sqrt(mean(x^2)), 1e-12) in fp32 with a fixed summation order
+ * (the torch reduction at lattice_rans/cuda.py:580). */
+int ep_lattice_row_rms(const void* weight_dev, int is_bf16, int64_t rows, int64_t cols, float* rms_dev, ep_stream_t stream);
+
+/* Nearest-E8 quantisation of (x / rms_row) / scale, plus per-stream min/max into minmax_dev[34]
+ * (16 x (min, max), max coset, int16-overflow flag; initialised by the call). Stands in for
+ * e8_quantize_fields_kernel, lattice_rans.cu:149-241 (call site cuda.py:115-139). */
+int ep_lattice_quantize(const void* weight_dev, int is_bf16, const float* rms_dev, int64_t rows, int64_t cols, float scale,
+                        int16_t* fields_dev, uint8_t* cosets_dev, int32_t* minmax_dev, ep_stream_t stream);
+
+/* Exact per-stream symbol counts into compact bins (2 coset bins, then max - min + 1 bins per live
+ * stream, in table order); bins_used_dev[0] receives the number of bins the min/max record implies and
+ * nothing is counted when that exceeds bins_capacity. Stands in for e8_histogram_kernel,
+ * lattice_rans.cu:376-396 (call site cuda.py:181-220). */
+int ep_lattice_histogram(const int16_t* fields_dev, const uint8_t* cosets_dev, int64_t vectors, const int32_t* minmax_dev,
+                         int32_t* bins_dev, int64_t bins_capacity, int32_t* bins_used_dev, ep_stream_t stream);
+
+/* Host-only helpers over a min/max record and its bins copied to the host. */
+int64_t ep_lattice_bins_needed(const int32_t* minmax_host);
+int ep_lattice_max_alphabet(const int32_t* minmax_host);
+/* Container-size model of the rate search: rans.coded_bytes, entropack/schemes/lattice_rans/rans.py:224-258. */
+int ep_lattice_coded_bytes(const int32_t* minmax_host, const int32_t* bins_host, int64_t vectors, int prob_bits,
+                           int64_t tile_elements, double* bytes_out);
+/* stream_meta[17][4] and the concatenated normalised frequency tables for the final encode:
+ * _build_codec_tables, entropack/schemes/lattice_rans/cuda.py:481-517. */
+int ep_lattice_tables(const int32_t* minmax_host, const int32_t* bins_host, int64_t vectors, int prob_bits,
+                      int32_t* stream_meta_host, uint16_t* freq_tables_host, int64_t freq_capacity, int64_t* freq_entries_out);
+
+/* Least-squares row scales against the quantised points (fallback scale * rms_row). Stands in for
+ * e8_refit_scales_kernel, lattice_rans.cu:243-332. */
+int ep_lattice_refit_scales(const void* weight_dev, int is_bf16, const int16_t* fields_dev, const uint8_t* cosets_dev,
+                            const float* rms_dev, float scale, int64_t rows, int64_t cols, float* scales_dev, ep_stream_t stream);
+
+/* u16 words of per-tile scratch ep_lattice_encode writes into (tiles * tile_vectors * 9). */
+int64_t ep_lattice_encode_scratch_words(int64_t vectors, int64_t tile_elements);
+
+/* rANS-encode every tile into its scratch slot; word_counts_dev[tiles], states_dev[tiles][32].
+ * symbol_scratch_dev: freq_entries * 8 bytes of scratch for the per-symbol encode records.
+ * Follow with ep_exclusive_scan_u32 and ep_compact_streams (slot = tile_vectors * 9 words). Stands in
+ * for e8_rans_encode_vector_kernel, lattice_rans.cu:400-465 (call site cuda.py:520-558). */
+int ep_lattice_encode(const int16_t* fields_dev, const uint8_t* cosets_dev, int64_t vectors, const int32_t* stream_meta_dev,
+                      const uint16_t* freq_tables_dev, int64_t freq_entries, int prob_bits, int64_t tile_elements,
+                      void* symbol_scratch_dev, uint16_t* scratch_dev, uint32_t* word_counts_dev, uint32_t* states_dev,
+                      ep_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
