@@ -333,11 +333,17 @@ extern "C" int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphab
   return static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
 }
 
-extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
-                                 const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
-                                 const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
-                                 int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
-                                 int64_t table_scratch_bytes, int* error_dev, ep_stream_t stream) {
+namespace ep {
+namespace {
+
+// Validates the arguments, fills the parameter block and launches the decode (plus the table-build
+// kernel on the global path). `tables` must hold 17 * 2^prob_bits 64-bit entries when the container
+// needs the global path; it is ignored otherwise.
+int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                          const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
+                          const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols, int prob_bits,
+                          int64_t tile_elements, int max_alphabet, uint64_t* tables, int64_t table_bytes, int* error_dev,
+                          cudaStream_t s) {
   if (rows <= 0 || cols <= 0 || (cols & 7) != 0 || prob_bits < 9 || prob_bits > 15 || tile_elements <= 0 ||
       store_kind < 0 || store_kind > EP_STORE_BOOL || max_alphabet < 0 || max_alphabet > (1 << prob_bits) ||
       payload_words < 0 || !offsets_dev || !states_dev || !stream_meta_dev || !freq_tables_dev || !scales_dev || !output_dev) {
@@ -368,7 +374,6 @@ extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_wo
   p.prob_bits = prob_bits;
   p.store_kind = store_kind;
   p.error = error_dev;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t wanted = (p.tiles + kDecodeWarps - 1) / kDecodeWarps;
   const unsigned blocks = static_cast<unsigned>(wanted < kSmCount ? wanted : kSmCount);
   const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
@@ -379,10 +384,7 @@ extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_wo
     lattice_decode_kernel<true><<<blocks, kDecodeThreads, shared, s>>>(p);
   } else {
     const int64_t needed = static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
-    if (!table_scratch_dev || table_scratch_bytes < needed || (reinterpret_cast<uintptr_t>(table_scratch_dev) & 7u)) {
-      return EP_ERR_INVALID_ARGUMENT;
-    }
-    uint64_t* tables = static_cast<uint64_t*>(table_scratch_dev);
+    if (!tables || table_bytes < needed || (reinterpret_cast<uintptr_t>(tables) & 7u)) return EP_ERR_INVALID_ARGUMENT;
     lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, prob_bits);
     p.global_tables = tables;
     EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -390,4 +392,18 @@ extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_wo
     lattice_decode_kernel<false><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
   }
   return check_launch("lattice_decode_kernel");
+}
+
+}  // namespace
+}  // namespace ep
+
+extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                 const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
+                                 const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
+                                 int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
+                                 int64_t table_scratch_bytes, int* error_dev, ep_stream_t stream) {
+  return launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, scales_dev,
+                               output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet,
+                               static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, error_dev,
+                               static_cast<cudaStream_t>(stream));
 }
