@@ -36,6 +36,8 @@ _PROTOTYPES = {
     "ep_compact_streams": [_ptr, _ptr, _ptr, _i64, _i64, _ptr],
     "ep_lattice_decode": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _ptr, _ptr],
     "ep_lattice_decode_scratch_bytes": [_i32, _i32],
+    "ep_lattice_decode_static": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _ptr],
+    "ep_lattice_decode_static_max_prob_bits": [],
     "ep_lattice_row_rms": [_ptr, _i32, _i64, _i64, _ptr, _ptr],
     "ep_lattice_quantize": [_ptr, _i32, _ptr, _i64, _i64, _f32, _ptr, _ptr, _ptr, _ptr],
     "ep_lattice_histogram": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr],

@@ -18,6 +18,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <mutex>
+
 #include "ep_common.cuh"
 #include "rans_ring.cuh"
 
@@ -406,4 +408,55 @@ extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_wo
                                output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet,
                                static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, error_dev,
                                static_cast<cudaStream_t>(stream));
+}
+
+// ---- decode without any allocation --------------------------------------------------------------------
+// Some hosts of this library may not allocate device memory at the moment they need a decode: an
+// inference server that has handed all of HBM to its own pool, or a thread running between a
+// framework's allocator callbacks where a cudaMalloc would deadlock or synchronise the device. For
+// them the 64-bit slot tables of the global-table path live in this fixed array instead of in
+// caller-provided scratch. It costs 17 * 2^13 * 8 bytes (1.06 MB) on every GPU that loads the library,
+// until the process exits, and caps the containers this entry point accepts on that path at
+// prob_bits 13. Containers that take the shared-memory path never touch it.
+constexpr int kStaticMaxProbBits = 13;
+constexpr size_t kStaticTableBytes = (static_cast<size_t>(ep::kTables) * sizeof(uint64_t)) << kStaticMaxProbBits;
+static __device__ __align__(256) unsigned char g_static_slot_tables[kStaticTableBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+uint64_t* g_static_address[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; kernels need its device address, which differs per GPU.
+// Looked up once per device, with that device current (the caller's current device).
+int static_tables_for_current_device(uint64_t** tables) {
+  int device = -1;
+  EP_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) return EP_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> guard(g_static_mutex);
+  if (g_static_address[device] == nullptr) {
+    void* address = nullptr;
+    EP_CUDA_CHECK(cudaGetSymbolAddress(&address, g_static_slot_tables));
+    g_static_address[device] = static_cast<uint64_t*>(address);
+  }
+  *tables = g_static_address[device];
+  return EP_OK;
+}
+}  // namespace
+
+extern "C" int ep_lattice_decode_static_max_prob_bits(void) { return kStaticMaxProbBits; }
+
+extern "C" int ep_lattice_decode_static(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                        const uint32_t* states_dev, const int32_t* stream_meta_dev,
+                                        const uint16_t* freq_tables_dev, const float* scales_dev, void* output_dev,
+                                        int store_kind, int64_t rows, int64_t cols, int prob_bits, int64_t tile_elements,
+                                        int max_alphabet, int* error_dev, ep_stream_t stream) {
+  const bool shared_path = prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet;
+  if (!shared_path && prob_bits > kStaticMaxProbBits && prob_bits <= 15) return EP_ERR_TOO_LARGE;
+  uint64_t* tables = nullptr;
+  const int rc = static_tables_for_current_device(&tables);
+  if (rc != EP_OK) return rc;
+  return launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, scales_dev,
+                               output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet, tables,
+                               static_cast<int64_t>(kStaticTableBytes), error_dev, static_cast<cudaStream_t>(stream));
 }

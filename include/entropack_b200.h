@@ -134,6 +134,25 @@ int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const 
                       int64_t tile_elements, int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes,
                       int* error_dev, ep_stream_t stream);
 
+/* Same decode for callers that cannot allocate device memory when they need it -- for example a
+ * serving process that has given all of HBM to its own pool, or code running inside an allocator
+ * callback. This entry point has no counterpart in the reference. The slot tables of the global-table
+ * path are kept in a fixed 1.06 MB array inside the library (resident on every GPU that loads it, for
+ * the life of the process), so no scratch is passed and nothing is allocated. Limits and rules:
+ *   - a container that needs the global-table path must have prob_bits <= 13
+ *     (ep_lattice_decode_static_max_prob_bits()); larger ones return EP_ERR_TOO_LARGE. Containers whose
+ *     tables fit in shared memory (prob_bits <= 11, alphabets <= 512) are always accepted;
+ *   - the first call on each device looks up the array's device address (no allocation, but a runtime
+ *     query): make that first call outside any stream capture;
+ *   - every call on a device shares the one array. It is rewritten in full by each call that uses it,
+ *     so stale contents never matter, but two such calls in flight at once on the same device
+ *     (different streams or threads) race; serialise them. */
+int ep_lattice_decode_static_max_prob_bits(void);
+int ep_lattice_decode_static(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                             const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
+                             const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
+                             int prob_bits, int64_t tile_elements, int max_alphabet, int* error_dev, ep_stream_t stream);
+
 /* --- encode. Work tensors are bf16 or fp32 [rows][cols], cols a multiple of 8 (is_bf16 selects);
  * quantised symbols travel as fields_dev int16[vectors][8] (z0..z6, m) and cosets_dev u8[vectors].
  * Replaces the kernels and host glue of entropack/schemes/lattice_rans/cuda.py:115-597. --- */
