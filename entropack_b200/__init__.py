@@ -7,12 +7,12 @@ there is no CPU or eager execution path.
 """
 from .compression import CompressedTensor, CompressionFallbackWarning, compress, decompress
 from .registry import DispatchError
-from .schemes import CompressionConfig, EntroPackLossyConfig, LatticeRANSConfig, RawConfig, TileANSConfig
+from .schemes import CompressionConfig, DFloat11Config, EntroPackLossyConfig, LatticeRANSConfig, RawConfig, TileANSConfig
 
 __version__ = "0.1.0"
 
 __all__ = [
-    "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DispatchError", "EntroPackLossyConfig",
+    "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DFloat11Config", "DispatchError", "EntroPackLossyConfig",
     "LatticeRANSConfig", "RawConfig", "TileANSConfig",
     "__version__", "compress", "decompress",
 ]

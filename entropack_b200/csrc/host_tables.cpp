@@ -379,3 +379,150 @@ extern "C" int ep_tile_ans_plan(const uint64_t* histograms_host, int num_lanes, 
   }
   return EP_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// DFloat11: prefix code over the 256 bf16 exponent values plus one end-of-stream codeword, and the
+// multi-level byte look-up tables the bitstream carries.
+// ------------------------------------------------------------------------------------------------
+namespace ep {
+namespace {
+
+constexpr int kDfSymbols = 257;  // 256 exponents + end of stream (index 256, weight 1)
+
+// Huffman code lengths: merge the two lightest nodes until one is left; among equal weights the node
+// created first (leaves in symbol order, then internal nodes in creation order) is taken first.
+int huffman_lengths(const uint64_t* weight, int* length) {
+  struct Node { uint64_t weight; int order; };
+  auto heavier = [](const Node& a, const Node& b) { return a.weight != b.weight ? a.weight > b.weight : a.order > b.order; };
+  std::priority_queue<Node, std::vector<Node>, decltype(heavier)> queue(heavier);
+  std::vector<int> parent;
+  int leaf[kDfSymbols];
+  for (int s = 0; s < kDfSymbols; ++s) {
+    leaf[s] = -1;
+    length[s] = 0;
+    if (weight[s]) {
+      leaf[s] = static_cast<int>(parent.size());
+      queue.push({weight[s], leaf[s]});
+      parent.push_back(-1);
+    }
+  }
+  if (queue.size() == 1) {
+    for (int s = 0; s < kDfSymbols; ++s) if (leaf[s] >= 0) length[s] = 1;
+    return 1;
+  }
+  while (queue.size() > 1) {
+    const Node a = queue.top(); queue.pop();
+    const Node b = queue.top(); queue.pop();
+    const int merged = static_cast<int>(parent.size());
+    parent.push_back(-1);
+    parent[a.order] = parent[b.order] = merged;
+    queue.push({a.weight + b.weight, merged});
+  }
+  int longest = 0;
+  for (int s = 0; s < kDfSymbols; ++s) {
+    if (leaf[s] < 0) continue;
+    int depth = 0;
+    for (int node = leaf[s]; parent[node] >= 0; node = parent[node]) ++depth;
+    length[s] = depth;
+    longest = std::max(longest, depth);
+  }
+  return longest;
+}
+
+}  // namespace
+}  // namespace ep
+
+extern "C" int ep_dfloat11_build_code(const uint64_t* histogram_host, int32_t* code_len_host, uint32_t* code_val_host) {
+  using namespace ep;
+  if (!histogram_host || !code_len_host || !code_val_host) return EP_ERR_INVALID_ARGUMENT;
+  uint64_t weight[kDfSymbols];
+  int present = 0;
+  for (int s = 0; s < 256; ++s) present += histogram_host[s] != 0;
+  if (present == 0) return EP_ERR_INVALID_ARGUMENT;
+  int length[kDfSymbols];
+  std::copy(histogram_host, histogram_host + 256, weight);
+  weight[256] = 1;
+  int longest = huffman_lengths(weight, length);
+  // Codes must fit 32 bits: if they do not, count the k rarest symbols as 1 and rebuild, k = 2, 3, ...
+  // (the reference's rule, entropack/schemes/dfloat11/eager.py:53-67).
+  for (int k = 2; longest > 32 && k <= present; ++k) {
+    std::copy(histogram_host, histogram_host + 256, weight);
+    std::vector<int> order;
+    for (int s = 0; s < 256; ++s) if (histogram_host[s]) order.push_back(s);
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return histogram_host[a] < histogram_host[b]; });
+    for (int i = 0; i < k; ++i) weight[order[i]] = 1;
+    longest = huffman_lengths(weight, length);
+  }
+  if (longest > 32) return EP_ERR_UNSUPPORTED;
+  uint64_t code = 0;
+  int previous = 0;
+  for (int bits = 1; bits <= 32; ++bits) {  // canonical: ascending (length, symbol)
+    for (int s = 0; s < kDfSymbols; ++s) {
+      if (length[s] != bits) continue;
+      code <<= (bits - previous);
+      previous = bits;
+      code_len_host[s] = bits;
+      code_val_host[s] = static_cast<uint32_t>(code++);
+    }
+  }
+  for (int s = 0; s < kDfSymbols; ++s) if (length[s] == 0) code_len_host[s] = 0, code_val_host[s] = 0;
+  return EP_OK;
+}
+
+extern "C" int ep_dfloat11_build_luts(const int32_t* code_len_host, const uint32_t* code_val_host, uint8_t* luts_host,
+                                      int max_rows, int* rows_out) {
+  // Level k serves one byte-aligned proper prefix of the codewords (level 0: the empty prefix; the others
+  // ordered by prefix length, then value). A level's entry for a byte is the symbol whose code ends inside
+  // that byte, or 256 - child level when the code continues; gaps repeat the entry before them. The last
+  // row is the code length per symbol. Layout of get_luts, entropack/schemes/dfloat11/eager.py:72-116.
+  if (!code_len_host || !code_val_host || !luts_host || !rows_out || max_rows < 2) return EP_ERR_INVALID_ARGUMENT;
+  struct Prefix { int bits; uint32_t value; };
+  std::vector<Prefix> levels{{0, 0u}};
+  for (int bits = 8; bits <= 24; bits += 8) {
+    std::vector<uint32_t> found;
+    for (int s = 0; s < 256; ++s) {
+      const int len = code_len_host[s];
+      if (len && (len - 1) / 8 * 8 == bits) found.push_back(code_val_host[s] >> (len - bits));
+    }
+    std::sort(found.begin(), found.end());
+    found.erase(std::unique(found.begin(), found.end()), found.end());
+    for (uint32_t value : found) levels.push_back({bits, value});
+  }
+  const int count = static_cast<int>(levels.size());
+  if (count + 1 > max_rows) return EP_ERR_UNSUPPORTED;
+  std::memset(luts_host, 0, static_cast<size_t>(count + 1) * 256);
+  for (int level = 0; level < count; ++level) {
+    int slot[256];
+    std::fill(slot, slot + 256, -1);
+    const int skip = levels[level].bits;
+    for (int s = 0; s < 256; ++s) {
+      const int len = code_len_host[s];
+      if (len == 0 || len <= skip) continue;
+      if (skip && (code_val_host[s] >> (len - skip)) != levels[level].value) continue;
+      const int rest = len - skip;
+      const uint32_t tail = rest >= 32 ? code_val_host[s] : (code_val_host[s] & ((1u << rest) - 1u));
+      int key, value;
+      if (rest <= 8) {
+        key = static_cast<int>(tail << (8 - rest));
+        value = s;
+      } else {
+        key = static_cast<int>(tail >> (rest - 8));
+        const uint32_t child_prefix = code_val_host[s] >> (rest - 8);
+        int child = -1;
+        for (int i = 0; i < count; ++i) if (levels[i].bits == skip + 8 && levels[i].value == child_prefix) child = i;
+        if (child < 0) return EP_ERR_UNSUPPORTED;
+        value = 256 - child;
+      }
+      if (slot[key] >= 0 && slot[key] != value) return EP_ERR_UNSUPPORTED;
+      slot[key] = value;
+    }
+    int current = 0;
+    for (int byte = 0; byte < 256; ++byte) {
+      if (slot[byte] >= 0) current = slot[byte];
+      luts_host[level * 256 + byte] = static_cast<uint8_t>(current);
+    }
+  }
+  for (int s = 0; s < 256; ++s) luts_host[count * 256 + s] = static_cast<uint8_t>(code_len_host[s]);
+  *rows_out = count + 1;
+  return EP_OK;
+}

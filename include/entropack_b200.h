@@ -202,6 +202,45 @@ int ep_lattice_encode(const int16_t* fields_dev, const uint8_t* cosets_dev, int6
                       void* symbol_scratch_dev, uint16_t* scratch_dev, uint32_t* word_counts_dev, uint32_t* states_dev,
                       ep_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * DFloat11 (Huffman-coded bf16 exponents). Buffer schema: entropack/schemes/dfloat11/format.py:32-63.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Decode into output_dev (bf16[n_elements]). bytes_per_thread / threads_per_block / max_block_elems are
+ * the container's layout values. Stands in for decode(), entropack/schemes/dfloat11/cuda.py:57-101 /
+ * dfloat11_decode_kernel, dfloat11.cu:314-522. threads_per_block up to 1024. */
+int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const uint8_t* encoded_dev, int64_t n_bytes,
+                       const uint8_t* sign_mantissa_dev, const uint32_t* output_positions_dev, const uint16_t* thread_meta_dev,
+                       void* output_dev, int64_t n_elements, int bytes_per_thread, int threads_per_block, int max_block_elems,
+                       int* error_dev, ep_stream_t stream);
+
+/* 256-bin histogram of the exponent byte (u64, cleared by the call). Stands in for exponent_counter,
+ * entropack/schemes/dfloat11/cuda.py:104-122. */
+int ep_dfloat11_histogram(const void* bf16_dev, int64_t n_elements, uint64_t* histogram_dev, ep_stream_t stream);
+
+/* Host-only: prefix code for the histogram -- code_len[257] / code_val[257], index 256 = end of stream --
+ * and the multi-level LUT rows (levels + 1 rows of 256 bytes; luts_host holds max_rows rows). Stand in for
+ * get_32bit_codec / get_luts, entropack/schemes/dfloat11/eager.py:42-116; the reference takes its code
+ * from the dahuffman package, this library builds a canonical Huffman code (same lengths as any optimal
+ * code up to ties; the bitstream carries its own tables, so either side decodes the other's). */
+int ep_dfloat11_build_code(const uint64_t* histogram_host, int32_t* code_len_host, uint32_t* code_val_host);
+int ep_dfloat11_build_luts(const int32_t* code_len_host, const uint32_t* code_val_host, uint8_t* luts_host, int max_rows,
+                           int* rows_out);
+
+/* Encode, in three calls replacing the five kernels + cumsum of entropack/schemes/dfloat11/cuda.py:136-223:
+ * ep_dfloat11_chunk_bits sums code lengths per chunk (ep_dfloat11_chunks(n) chunks), ep_exclusive_scan_u32
+ * turns them into bit offsets and the total, ep_dfloat11_pack writes the bitstream (encoded_dev must hold
+ * ceil(total_bits / 8) rounded up to 4, plus 4 bytes), sign_mantissa, thread_meta[blocks * threads_per_block]
+ * and output_positions[blocks + 1]. region_scratch_dev: 2 * blocks * threads_per_block u32 of scratch.
+ * total_bits must be below 2^32. */
+int64_t ep_dfloat11_chunks(int64_t n_elements);
+int ep_dfloat11_chunk_bits(const void* bf16_dev, int64_t n_elements, const int32_t* code_len_dev, uint32_t* chunk_bits_dev,
+                           ep_stream_t stream);
+int ep_dfloat11_pack(const void* bf16_dev, int64_t n_elements, const int32_t* code_len_dev, const int32_t* code_val_dev,
+                     const uint32_t* chunk_offsets_dev, uint64_t total_bits, int bytes_per_thread, int threads_per_block,
+                     int eof_length, uint32_t eof_value, uint8_t* encoded_dev, uint8_t* sign_mantissa_dev,
+                     uint16_t* thread_meta_dev, uint32_t* output_positions_dev, uint32_t* region_scratch_dev, ep_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,98 @@
+"""DFloat11 kernels against the golden fixtures and the CPU oracle (bit-exact), through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import buffers_of, golden_names, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _to_device(buffers: dict):
+    from entropack_b200.schemes.dfloat11.format import DFloat11Buffers
+
+    return DFloat11Buffers(**{key: torch.from_numpy(np.ascontiguousarray(value)).cuda() for key, value in buffers.items()})
+
+
+def _gpu_decode(buffers: dict) -> np.ndarray:
+    from entropack_b200.schemes.dfloat11 import b200
+
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b200.decode(_to_device(buffers), error=error)
+    assert int(error.item()) == 0
+    return out.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def _gpu_encode(bits: np.ndarray, bytes_per_thread=16, threads_per_block=128) -> dict:
+    from entropack_b200.schemes.dfloat11 import b200
+
+    weight = torch.from_numpy(bits.view(np.int16).copy()).cuda().view(torch.bfloat16)
+    codec = b200.build_codec(b200.exponent_counter(weight, threads_per_block))
+    buffers = b200.encode(weight=weight, codec=codec, luts=b200.build_luts(codec), bytes_per_thread=bytes_per_thread,
+                          threads_per_block=threads_per_block)
+    return {key: value.cpu().numpy() for key, value in buffers._asdict().items()}
+
+
+@pytest.mark.parametrize("name", golden_names("dfloat11_"))
+def test_decode_reference_bitstreams(name):
+    record = load_golden(f"dfloat11_{name}")
+    assert np.array_equal(_gpu_decode(buffers_of(record)), record["input_bits"])
+
+
+@pytest.mark.parametrize("name", golden_names("dfloat11_"))
+def test_encode_reproduces_reference_bitstreams(name):
+    """With the same code table the reference's encoder was given, every buffer is byte-identical."""
+    record = load_golden(f"dfloat11_{name}")
+    reference = buffers_of(record)
+    ours = _gpu_encode(record["input_bits"])
+    for key in ("layout", "luts", "sign_mantissa", "encoded_exponent", "thread_meta", "output_positions"):
+        assert np.array_equal(ours[key], reference[key]), key
+
+
+@pytest.mark.parametrize("n,bpt,tpb", [(1 << 20, 16, 128), (700001, 16, 128), (50000, 5, 32), (123457, 37, 96), (33, 16, 128), (1, 16, 128),
+                                      (300000, 255, 64)])
+def test_against_oracle_both_directions(oracle_module, n, bpt, tpb):
+    g = torch.Generator().manual_seed(n)
+    values = torch.randn(n, generator=g) * torch.exp(torch.randn(n, generator=g) * (3.0 if n % 2 else 0.3)) * 0.02
+    bits = values.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    expected = oracle_module.dfloat11_encode(bits, bpt, tpb)
+    ours = _gpu_encode(bits, bpt, tpb)
+    for key in ("layout", "luts", "sign_mantissa", "encoded_exponent", "thread_meta", "output_positions"):
+        assert np.array_equal(ours[key], expected[key]), key
+    assert np.array_equal(_gpu_decode(expected), bits)
+    assert np.array_equal(oracle_module.dfloat11_decode(ours, use_regions=True), bits)
+
+
+def test_full_size_round_trip_public_api():
+    """BF16 4096 x 4096, N(0, 0.02^2): compress and decompress through the public API, bit-exact, ~11 bpp."""
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    weight = (torch.randn(4096, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    compressed = ep.compress(weight, ep.DFloat11Config())
+    assert compressed.compress_method == "dfloat11"
+    compressed.scheme.validate_buffers(compressed.buffers, tuple(weight.shape), weight.dtype)
+    assert 10.5 < compressed.actual_bpp < 11.2
+    restored = ep.decompress(compressed, ep.DFloat11Config())
+    assert torch.equal(restored.view(torch.int16), weight.view(torch.int16))
+
+
+def test_malformed_metadata_is_reported_not_faulted():
+    from entropack_b200.schemes.dfloat11 import b200
+
+    record = load_golden("dfloat11_wide")
+    buffers = buffers_of(record)
+    bad = dict(buffers)
+    positions = buffers["output_positions"].copy()
+    positions[1] = positions[-1] + 1000
+    bad["output_positions"] = positions
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    b200.decode(_to_device(bad), error=error)
+    torch.cuda.synchronize()
+    assert int(error.item()) != 0
+    bad = dict(buffers)
+    luts = buffers["luts"].copy()
+    luts[0, :] = 255  # every byte of level 0 points at a child level that may not exist
+    bad["luts"] = luts
+    b200.decode(_to_device(bad))
+    torch.cuda.synchronize()

@@ -99,3 +99,53 @@ def test_product_never_imports_the_oracle():
         if re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M):
             offenders.append(str(path))
     assert not offenders, offenders
+
+
+@pytest.mark.parametrize("name", golden_names("dfloat11_"))
+def test_dfloat11_code_and_luts_match_reference(oracle_module, name):
+    from entropack_b200.schemes.dfloat11 import b200
+
+    record = load_golden(f"dfloat11_{name}")
+    counts = np.bincount((record["input_bits"] >> 7) & 0xFF, minlength=256)
+    codec = b200.build_codec({i: int(c) for i, c in enumerate(counts) if c})
+    expected_len, expected_val = oracle_module.dfloat11_code(counts)
+    assert np.array_equal(codec[0], expected_len) and np.array_equal(codec[1], expected_val)
+    assert np.array_equal(b200.build_luts(codec).numpy(), buffers_of(record)["luts"])
+
+
+def test_lattice_host_model_matches_reference():
+    """ep_lattice_coded_bytes / ep_lattice_tables on the unit fixture's symbols (min/max record and compact
+    bins rebuilt with numpy the way the device kernels lay them out)."""
+    import ctypes
+
+    from entropack_b200 import _native
+
+    units = load_golden("lattice_units")
+    fields = np.concatenate([units["z0_6"], units["m"][:, None]], axis=1).astype(np.int64)
+    cosets = units["c"].astype(np.int64)
+    vectors = cosets.size
+    minmax = np.zeros(34, dtype=np.int32)
+    bins = [np.bincount(cosets, minlength=2)]
+    for st in range(16):
+        values = fields[cosets == (st & 1), st >> 1]
+        if values.size:
+            minmax[2 * st], minmax[2 * st + 1] = values.min(), values.max()
+            bins.append(np.bincount(values - values.min()))
+        else:
+            minmax[2 * st], minmax[2 * st + 1] = np.iinfo(np.int32).max, np.iinfo(np.int32).min
+    minmax[32] = cosets.max()
+    bins = np.ascontiguousarray(np.concatenate(bins).astype(np.int32))
+    lib = _native.load()
+    assert lib.ep_lattice_bins_needed(minmax.ctypes.data) == bins.size
+    for (pb, tile_elements), expected in zip(units["coded_args"], units["coded_bytes"]):
+        value = ctypes.c_double()
+        assert lib.ep_lattice_coded_bytes(minmax.ctypes.data, bins.ctypes.data, vectors, int(pb), int(tile_elements),
+                                          ctypes.addressof(value)) == 0
+        assert value.value == expected
+    meta = np.zeros((17, 4), dtype=np.int32)
+    freq = np.zeros(bins.size, dtype=np.uint16)
+    entries = ctypes.c_int64()
+    assert lib.ep_lattice_tables(minmax.ctypes.data, bins.ctypes.data, vectors, 11, meta.ctypes.data, freq.ctypes.data, freq.size,
+                                 ctypes.addressof(entries)) == 0
+    assert np.array_equal(meta, units["enc_meta"])
+    assert np.array_equal(freq[: entries.value], units["enc_freq"])
