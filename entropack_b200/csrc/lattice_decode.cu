@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(32) lattice_build_tables_kernel(uint64_t* tabl
 }
 
 // ---- decode ----------------------------------------------------------------------------------------
-template <bool SHARED_TABLES>
+template <bool SHARED_TABLES, bool BF16_OUT>
 __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const LatticeDecodeParams p) {
   extern __shared__ __align__(16) uint32_t shared_tables[];  // [17][table_size] when SHARED_TABLES
   __shared__ int sym_min[kTables + 1];
@@ -251,17 +251,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     ring_fetch_interior(p.payload, ring, chunk - 3, lane);
     ring_commit();
 
-    // One symbol from table `t`; returns the symbol. Same chain as the Tile-ANS decoder.
-    auto step = [&](int t, bool valid) -> uint32_t {
+    // One symbol from the table that starts `table_at` entries into the table array. Same chain as the
+    // Tile-ANS decoder; `valid` is a literal in the main loop, so its tests fold away there.
+    auto step = [&](uint32_t table_at, bool valid) -> uint32_t {
       uint32_t symbol = 0;
       if (valid) {
         const uint32_t slot = x & slot_mask;
         if (SHARED_TABLES) {
-          const uint32_t entry = shared_tables[static_cast<uint32_t>(t) * table_size + slot];
+          const uint32_t entry = shared_tables[table_at + slot];
           symbol = entry & 0x1FFu;
           x = ((entry >> 9) & 0xFFFu) * (x >> prob_bits) + (entry >> 21);
         } else {
-          const uint64_t entry = __ldg(p.global_tables + static_cast<size_t>(t) * table_size + slot);
+          const uint64_t entry = __ldg(p.global_tables + table_at + slot);
           symbol = static_cast<uint32_t>(entry) & 0xFFFFu;
           x = ((static_cast<uint32_t>(entry) >> 16) & 0xFFFFu) * (x >> prob_bits) + static_cast<uint32_t>(entry >> 32);
         }
@@ -287,18 +288,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
 
     // groups of 32 vectors, back to front; a partial group at the tile's end comes first
     int offset = count - (count & 31);
-    bool valid = lane < static_cast<uint32_t>(count & 31);
-    if ((count & 31) == 0) {
-      offset -= 32;
-      valid = true;
-    }
-    for (; offset >= 0; offset -= 32, valid = true) {
-      const int coset = static_cast<int>(step(0, valid));
+    if ((count & 31) == 0) offset -= 32;
+    // row and column (in vectors) of this thread's vector in the current group, stepped back 32 per group
+    int row = static_cast<int>(static_cast<uint32_t>(tile_begin + offset + lane) / static_cast<uint32_t>(p.vecs_per_row));
+    int col = static_cast<int>(static_cast<uint32_t>(tile_begin + offset + lane) - static_cast<uint32_t>(row) * p.vecs_per_row);
+    auto decode_group = [&](bool valid) {
+      const uint32_t coset = step(0, valid);
+      const uint32_t coset_at = coset * table_size;
       int value[8];
 #pragma unroll
       for (int field = 0; field < 8; ++field) {
-        const int t = 1 + 2 * field + coset;
-        value[field] = static_cast<int>(step(t, valid)) + sym_min[t];
+        value[field] = static_cast<int>(step((1 + 2 * field) * table_size + coset_at, valid)) + sym_min[1 + 2 * field + coset];
         if (field == 1 || field == 4 || field == 7) upkeep();  // every three steps: at most 96 words
       }
       if (valid) {
@@ -307,14 +307,38 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
         for (int field = 0; field < 7; ++field) parity += value[field];
         value[7] = 2 * value[7] + (parity & 1);
         const int64_t vector = tile_begin + offset + lane;
-        const float scale = __ldg(p.scales + static_cast<uint32_t>(vector) / static_cast<uint32_t>(p.vecs_per_row));
+        const float scale = __ldg(p.scales + row);
         const float half = coset ? 0.5f : 0.0f;
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fadd_rn(static_cast<float>(value[j]), half), scale);
-        store_vector(p.output, vector, v, p.store_kind);
+        if (BF16_OUT) {
+          // |z + c/2| < 2^15.5, so the product can only leave the bf16 range when the scale is astronomically large
+          if (scale < 1.0e33f) {
+            uint4 packed;
+            const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+            const __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+            packed.x = *reinterpret_cast<const uint32_t*>(&a);
+            packed.y = *reinterpret_cast<const uint32_t*>(&b);
+            packed.z = *reinterpret_cast<const uint32_t*>(&c);
+            packed.w = *reinterpret_cast<const uint32_t*>(&d);
+            *reinterpret_cast<uint4*>(static_cast<char*>(p.output) + vector * 16) = packed;
+          } else {
+            store_vector(p.output, vector, v, EP_STORE_BF16);
+          }
+        } else {
+          store_vector(p.output, vector, v, p.store_kind);
+        }
       }
-    }
+      offset -= 32;
+      col -= 32;
+      while (col < 0) {
+        col += p.vecs_per_row;
+        row -= 1;
+      }
+    };
+    if (count & 31) decode_group(lane < static_cast<uint32_t>(count & 31));
+    while (offset >= 0) decode_group(true);
     const bool dirty = __any_sync(0xFFFFFFFFu, x != kStateMin);
     const int left = (cursor - origin) / 2;
     if (lane == 0) {
@@ -381,17 +405,23 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
   if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) {
     const size_t shared = (static_cast<size_t>(kTables) * sizeof(uint32_t) << prob_bits) + ring_bytes;
-    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(shared)));
-    lattice_decode_kernel<true><<<blocks, kDecodeThreads, shared, s>>>(p);
+    if (store_kind == EP_STORE_BF16) {
+      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(shared)));
+      lattice_decode_kernel<true, true><<<blocks, kDecodeThreads, shared, s>>>(p);
+    } else {
+      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(shared)));
+      lattice_decode_kernel<true, false><<<blocks, kDecodeThreads, shared, s>>>(p);
+    }
   } else {
     const int64_t needed = static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
     if (!tables || table_bytes < needed || (reinterpret_cast<uintptr_t>(tables) & 7u)) return EP_ERR_INVALID_ARGUMENT;
     lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, prob_bits);
     p.global_tables = tables;
-    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(ring_bytes)));
-    lattice_decode_kernel<false><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+    lattice_decode_kernel<false, false><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
   }
   return check_launch("lattice_decode_kernel");
 }

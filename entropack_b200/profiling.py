@@ -28,7 +28,10 @@ def make_tensor(kind: str, rows: int, cols: int, device, seed: int = 1) -> torch
 
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("--op", default="tile_ans_decode", choices=("tile_ans_decode", "tile_ans_encode"))
+    parser.add_argument("--op", default="tile_ans_decode",
+                        choices=("tile_ans_decode", "tile_ans_encode", "lattice_decode", "lattice_encode", "dfloat11_decode",
+                                 "dfloat11_encode"))
+    parser.add_argument("--bpp", type=float, default=4.0)
     parser.add_argument("--kind", default="fp8_e4m3")
     parser.add_argument("--rows", type=int, default=8192)
     parser.add_argument("--cols", type=int, default=8192)
@@ -41,7 +44,18 @@ def main() -> None:
     torch.cuda.set_device(device)
     tensor = make_tensor(args.kind, args.rows, args.cols, device)
     config = ep.TileANSConfig()
-    if args.op == "tile_ans_decode":
+    if args.op.startswith("lattice"):
+        config = ep.EntroPackLossyConfig(target_bpp=args.bpp)
+    elif args.op.startswith("dfloat11"):
+        config = ep.DFloat11Config()
+    if args.op.endswith("_decode") and not args.op.startswith("tile_ans"):
+        container = ep.compress(tensor, config)
+        torch.cuda.synchronize()
+        for _ in range(args.reps):
+            out = ep.decompress(container, config)
+        torch.cuda.synchronize()
+        print(f"{args.op} {args.kind} {args.rows}x{args.cols}: {container.actual_bpp:.4f} bpp, {args.reps} launches")
+    elif args.op == "tile_ans_decode":
         container = ep.compress(tensor, config)
         torch.cuda.synchronize()
         for _ in range(args.reps):
