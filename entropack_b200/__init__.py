@@ -6,13 +6,14 @@ compute runs in hand-written CUDA kernels reached through a C ABI (``include/ent
 there is no CPU or eager execution path.
 """
 from .compression import CompressedTensor, CompressionFallbackWarning, compress, decompress
+from .linear import CompressedFP8Linear, CompressedINT8Linear, CompressedLinear
 from .registry import DispatchError
 from .schemes import CompressionConfig, DFloat11Config, EntroPackLossyConfig, LatticeRANSConfig, RawConfig, TileANSConfig
 
 __version__ = "0.1.0"
 
 __all__ = [
-    "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DFloat11Config", "DispatchError", "EntroPackLossyConfig",
+    "CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DFloat11Config", "DispatchError", "EntroPackLossyConfig",
     "LatticeRANSConfig", "RawConfig", "TileANSConfig",
     "__version__", "compress", "decompress",
 ]

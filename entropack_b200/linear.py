@@ -1,0 +1,373 @@
+"""Linear layers that keep their weight compressed and decode it on every forward.
+
+Stands in for entropack/linear/linear.py:18-490: same class names, constructor arguments, properties
+(``qweight``, ``stored_nbytes``, ``compressed_bits``, ``container_dtype``), ``from_linear`` /
+``compress_weight`` / ``dequantize`` / ``codes`` and the same checkpoint keys
+(``<prefix>weight.entropack_quant_state``, ``<prefix>weight_quant_scale``, ``<prefix>bias``), so a
+state_dict written by either implementation loads into the other.
+
+Forward: the weight is decoded by the fused sm_100a decode kernel (entropy decode, dequantisation and
+the container cast in one pass, straight from the packed blob) into a dense operand that a GEMM consumes
+while it is still resident in the 126 MB L2. The INT8 layer's optional ConvRot rotation is not part of
+this package.
+"""
+import dataclasses
+from numbers import Real
+from typing import ClassVar
+
+import torch
+from torch.nn import functional as F
+
+from .compression import CompressedTensor, compress, decompress
+from .registry import default_config, get_scheme, name_for_config, require_dtype
+from .schemes import EntroPackLossyConfig, RawConfig
+
+_EPS = torch.finfo(torch.float32).eps
+
+
+def _pad_to(tensor: torch.Tensor, dim: int, size: int) -> torch.Tensor:
+    missing = size - tensor.shape[dim]
+    if missing <= 0:
+        return tensor
+    shape = list(tensor.shape)
+    shape[dim] = missing
+    return torch.cat([tensor, tensor.new_zeros(shape)], dim=dim)
+
+
+def _round_up(value: int, multiple: int) -> int:
+    return -(-value // multiple) * multiple
+
+
+class CompressedLinear(torch.nn.Linear):
+    """``torch.nn.Linear`` whose frozen weight is a :class:`CompressedTensor` parameter.
+
+    Args:
+        in_features, out_features, bias: as for ``torch.nn.Linear``; the bias is stored uncompressed.
+        config: compression configuration; ``None`` picks the lossless scheme for ``dtype``.
+        device: device of the bias (compressed buffers stay where the source weight was).
+        dtype: container dtype the weight is compressed in.
+    """
+
+    state_buffer_names: ClassVar[tuple[str, ...]] = ()
+    state_buffer_dtypes: ClassVar[dict[str, torch.dtype]] = {}
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, *, config=None,
+                 device: str | torch.device | None = None, dtype: torch.dtype = torch.bfloat16):
+        with torch.device("meta"):
+            super().__init__(in_features, out_features, bias=False, dtype=dtype)
+        if bias:
+            self.bias = torch.nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device), requires_grad=False)
+        self.config = config
+        self._init_dtype = require_dtype(dtype)
+        if config is not None:
+            scheme = get_scheme(name_for_config(config))
+            if not scheme.supports(self.container_dtype):
+                raise ValueError(f"'{scheme.name}' does not support format {self.container_dtype}")
+        self.weight = torch.nn.Parameter(torch.zeros(0, dtype=self._init_dtype, device=device), requires_grad=False)
+        for name in self.state_buffer_names:
+            self.register_buffer(name, torch.zeros(out_features, dtype=self.state_buffer_dtypes[name], device=device), persistent=True)
+
+    # ---- configuration -------------------------------------------------------------------------
+    @property
+    def _encode_config(self):
+        return default_config(self.container_dtype) if self.config is None else dataclasses.replace(self.config)
+
+    @property
+    def _decode_config(self):
+        return self.weight.scheme.make_config({}) if self.config is None else dataclasses.replace(self.config)
+
+    @property
+    def container_dtype(self) -> torch.dtype:
+        """The dtype the weight is compressed in; layer casts (``.to(dtype)``) do not change it."""
+        return self._init_dtype
+
+    @property
+    def qweight(self) -> torch.Tensor:
+        """The packed blob, under the attribute name quantisation frameworks look for."""
+        return self.weight.entropack_quant_state if isinstance(self.weight, CompressedTensor) else self.bias
+
+    @property
+    def stored_nbytes(self) -> int:
+        total = self.weight.storage_nbytes()
+        for name in self.state_buffer_names:
+            buffer = self._buffers.get(name)
+            if buffer is not None:
+                total += buffer.numel() * buffer.element_size()
+        return total
+
+    @property
+    def compressed_bits(self) -> float:
+        rows, cols = self.weight.shape
+        return self.stored_nbytes * 8 / (rows * cols)
+
+    @property
+    def device(self) -> torch.device:
+        if self.weight is not None:
+            return self.weight.device
+        return self.bias.device if self.bias is not None else torch.device("meta")
+
+    # ---- compression ---------------------------------------------------------------------------
+    def _check_weight_shape(self, shape) -> None:
+        expected = (self.out_features, self.in_features)
+        if tuple(shape) != expected:
+            raise ValueError(f"weight has shape {tuple(shape)}, but the layer expects {expected}")
+
+    def _compress_tensor(self, tensor: torch.Tensor) -> CompressedTensor:
+        compressed = compress(tensor.to(self.container_dtype), self._encode_config)
+        if compressed.compress_method == "raw" and "reason" in compressed.header:
+            raise RuntimeError(
+                f"{compressed.header['requested']} cannot store a {tuple(tensor.shape)} {self.container_dtype} weight for "
+                f"{type(self).__name__}: {compressed.header['reason']}")
+        return compressed
+
+    def compress_weight(self, weight: torch.Tensor) -> None:
+        """Compress ``weight`` and make it this layer's weight."""
+        self._check_weight_shape(weight.shape)
+        self.weight = torch.nn.Parameter(self._compress_tensor(weight.detach()), requires_grad=False)
+
+    @classmethod
+    def from_linear(cls, linear: torch.nn.Linear, **kwargs) -> "CompressedLinear":
+        """A layer of this class holding ``linear``'s weight compressed and a copy of its bias."""
+        weight = linear.weight
+        if weight is None or weight.device.type == "meta":
+            raise ValueError("cannot compress a Linear whose weight is not materialized")
+        kwargs.setdefault("dtype", weight.dtype)
+        layer = cls(linear.in_features, linear.out_features, bias=linear.bias is not None, device=weight.device, **kwargs)
+        layer.compress_weight(weight.data)
+        if linear.bias is not None:
+            layer.bias = torch.nn.Parameter(linear.bias.data.clone(), requires_grad=False)
+        return layer
+
+    # ---- decode and forward ----------------------------------------------------------------------
+    def _container(self) -> CompressedTensor:
+        if not isinstance(self.weight, CompressedTensor):
+            raise RuntimeError(f"{type(self).__name__}({self.in_features}, {self.out_features}) has nothing to decode: "
+                               "the weight was not correctly loaded")
+        return self.weight
+
+    def dequantize(self, device: str | torch.device | None = None) -> torch.Tensor:
+        """The dense weight, decoded on ``device`` (default: where the blob lives)."""
+        return decompress(self._container().to(device=device), self._decode_config)
+
+    def _bias_on(self, device: torch.device) -> torch.Tensor | None:
+        return None if self.bias is None else self.bias.to(device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return F.linear(x, self.dequantize(x.device).to(x.dtype), self._bias_on(x.device))
+
+    def extra_repr(self) -> str:
+        scheme = "auto" if self.config is None else name_for_config(self.config)
+        parts = [f"scheme={scheme}", f"container={str(self.container_dtype).removeprefix('torch.')}"]
+        if isinstance(self.weight, CompressedTensor):
+            parts.append(f"bits={self.compressed_bits:.3f}")
+        if self.config is not None:
+            parts.append(f"config={type(self.config).__name__}")
+        return ", ".join(parts)
+
+    # ---- module plumbing -------------------------------------------------------------------------
+    def _apply(self, fn, recurse=True):
+        # auxiliary scale buffers keep their dtype when the module is cast
+        held = {name: self._buffers.pop(name) for name in self.state_buffer_names if name in self._buffers}
+        try:
+            super()._apply(fn, recurse=recurse)
+        finally:
+            for name, buffer in held.items():
+                if buffer is None:
+                    self._buffers[name] = None
+                    continue
+                moved = fn(buffer)
+                self._buffers[name] = moved if moved.dtype == buffer.dtype else buffer.to(device=moved.device)
+        return self
+
+    def _save_to_state_dict(self, destination: dict, prefix: str, keep_vars: bool) -> None:
+        super()._save_to_state_dict(destination, prefix, keep_vars)
+        if isinstance(self.weight, CompressedTensor):
+            destination.pop(prefix + "weight")
+            blob = self.weight.entropack_quant_state
+            destination[prefix + "weight.entropack_quant_state"] = blob if keep_vars else blob.detach()
+
+    def _load_from_state_dict(self, state_dict: dict, prefix: str, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        key = prefix + "weight.entropack_quant_state"
+        if key in state_dict:
+            try:
+                blob = state_dict[key]
+                assign = local_metadata.get("assign_to_params_buffers", False)
+                current = self._parameters.get("weight")
+                if not assign:
+                    if current is not None and current.device.type != "meta":
+                        device = current.device
+                    elif self.bias is not None and self.bias.device.type != "meta":
+                        device = self.bias.device
+                    else:
+                        device = blob.device
+                    blob = blob.to(device=device, copy=True)
+                container = CompressedTensor.unpack(blob)
+                self._check_weight_shape(container.shape)
+                loaded = torch.nn.Parameter(container, requires_grad=False)
+                if not assign and isinstance(current, CompressedTensor):
+                    torch.utils.swap_tensors(current, loaded)
+                else:
+                    self._parameters["weight"] = loaded
+            except (TypeError, ValueError) as error:
+                error_msgs.append(f"{prefix[:-1]}: {error}")
+            state_dict.pop(key)
+        elif strict:
+            missing_keys.append(key)
+        weight = self._parameters.pop("weight")
+        super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs)
+        self._parameters["weight"] = weight
+
+
+class _W8A8Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, layer):
+        ctx.layer, ctx.x_shape = layer, x.shape
+        return layer._forward8(x.detach())
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad_output):
+        grad = grad_output.reshape(-1, grad_output.shape[-1])
+        weight = ctx.layer.dequantize(grad.device).to(grad.dtype)
+        return torch.mm(grad, weight).reshape(ctx.x_shape), None
+
+
+class QuantizedLinear(CompressedLinear):
+    """Base of the 8-bit layers: per-row scaled codes, optionally lattice-coded, 8-bit GEMM at run time."""
+
+    code_dtype: ClassVar[torch.dtype]
+    code_max: ClassVar[float]
+    rounds_to_integer: ClassVar[bool]
+    code_alignment: ClassVar[int]
+    min_tokens: ClassVar[int]
+    min_capability: ClassVar[tuple[int, int]]
+    state_buffer_names = ("weight_quant_scale",)
+    state_buffer_dtypes = {"weight_quant_scale": torch.float32}
+
+    def __init__(self, in_features, out_features, bias=True, *, config=None, device=None, dtype=torch.bfloat16):
+        super().__init__(in_features, out_features, bias=bias, config=self._coded(config), device=device, dtype=dtype)
+
+    @property
+    def container_dtype(self) -> torch.dtype:
+        return self.code_dtype
+
+    @classmethod
+    def _coded(cls, config):
+        if config is None:
+            return RawConfig()
+        if isinstance(config, RawConfig):
+            return config
+        if not isinstance(config, EntroPackLossyConfig):
+            raise TypeError(f"{cls.__name__} stores {cls.code_dtype} codes: either uncoded (RawConfig) or lattice-coded "
+                            f"(EntroPackLossyConfig), got {type(config).__name__}")
+        rate = config.target_bpp
+        if isinstance(rate, bool) or not isinstance(rate, Real) or not 0.0 < float(rate) < 8.0:
+            raise ValueError(f"{cls.__name__} stores {cls.code_dtype} codes, 8 bits wide, so a target_bpp only pays below 8; "
+                             f"got {rate!r}. Pass RawConfig to store the codes uncoded.")
+        return config
+
+    def _quantize_rows(self, tensor: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        flat = tensor.reshape(-1, tensor.shape[-1]).float()
+        scale = (flat.abs().amax(dim=1) / self.code_max).clamp(min=_EPS)
+        scaled = flat / scale.unsqueeze(1)
+        if self.rounds_to_integer:
+            scaled = scaled.round()
+        return scaled.clamp(-self.code_max, self.code_max).to(self.code_dtype), scale
+
+    def compress_weight(self, weight: torch.Tensor) -> None:
+        self._check_weight_shape(weight.shape)
+        codes, scale = self._quantize_rows(weight.detach())
+        self.weight = torch.nn.Parameter(self._compress_tensor(codes), requires_grad=False)
+        self.weight_quant_scale = scale
+
+    def codes(self, device: str | torch.device | None = None) -> torch.Tensor:
+        """The weight codes in ``code_dtype``, decoded for the 8-bit GEMM."""
+        return decompress(self._container().to(device=device, dtype=self.code_dtype), self._decode_config)
+
+    def _scale(self, device: torch.device) -> torch.Tensor:
+        return self.weight_quant_scale.to(device=device, dtype=torch.float32)
+
+    def dequantize(self, device: str | torch.device | None = None) -> torch.Tensor:
+        codes = self.codes(device)
+        return (codes.float() * self._scale(codes.device).unsqueeze(1)).to(self._init_dtype)
+
+    def _require_8bit_gemm(self, device: torch.device) -> None:
+        if device.type != "cuda":
+            raise RuntimeError(f"{type(self).__name__} needs a CUDA device with an 8-bit tensor core, compute capability "
+                               f"{self.min_capability} or later; got {device}.")
+        capability = torch.cuda.get_device_capability(device)
+        if capability < self.min_capability:
+            raise RuntimeError(f"{type(self).__name__} needs compute capability {self.min_capability} or later and "
+                               f"{torch.cuda.get_device_name(device)} reports {capability}.")
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        self._require_8bit_gemm(x.device)
+        return _W8A8Function.apply(x, self) if x.requires_grad else self._forward8(x)
+
+    def _forward8(self, x: torch.Tensor) -> torch.Tensor:
+        flat = x.reshape(-1, x.shape[-1])
+        activation, scale = self._quantize_rows(flat.detach())
+        codes = self.codes(x.device)
+        weight_scale = self._scale(codes.device)
+        tokens = activation.shape[0]
+        rows = max(tokens, self.min_tokens)
+        outs = _round_up(self.out_features, self.code_alignment)
+        cols = _round_up(self.in_features, self.code_alignment)
+        out = self._gemm(_pad_to(_pad_to(activation, 0, rows), 1, cols), _pad_to(_pad_to(codes, 0, outs), 1, cols),
+                         _pad_to(scale, 0, rows), _pad_to(weight_scale, 0, outs), x.dtype)
+        return out[:tokens, : self.out_features].reshape(*x.shape[:-1], self.out_features)
+
+    def _bias_padded(self, device: torch.device, columns: int) -> torch.Tensor | None:
+        bias = self._bias_on(device)
+        return None if bias is None else _pad_to(bias, 0, columns)
+
+    def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
+        raise NotImplementedError
+
+
+class CompressedFP8Linear(QuantizedLinear):
+    """FP8 E4M3 weights and activations with per-row scales; codes stored raw or lattice-coded below 8 bpp."""
+
+    code_dtype = torch.float8_e4m3fn
+    code_max = float(torch.finfo(torch.float8_e4m3fn).max)
+    rounds_to_integer = False
+    code_alignment = 16
+    min_tokens = 1
+    min_capability = (8, 9)
+
+    def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
+        bias = self._bias_padded(codes.device, weight_scale.shape[0])
+        fused = bias is None or out_dtype is not torch.float32
+        out = torch._scaled_mm(activation, codes.t(), scale_a=activation_scale.unsqueeze(1), scale_b=weight_scale.unsqueeze(0),
+                               bias=bias if fused else None, out_dtype=out_dtype)
+        return out if fused else out.add_(bias)
+
+
+class CompressedINT8Linear(QuantizedLinear):
+    """Symmetric INT8 weights and activations with per-row scales (``torch._int_mm``). The reference's optional
+    ConvRot rotation is not implemented: ``use_convrot=True`` raises."""
+
+    code_dtype = torch.int8
+    code_max = 127.0
+    rounds_to_integer = True
+    code_alignment = 8
+    min_tokens = 17
+    min_capability = (8, 0)
+
+    def __init__(self, in_features, out_features, bias=True, *, config=None, device=None, dtype=torch.bfloat16,
+                 use_convrot: bool = False, convrot_groupsize: int = 256):
+        if use_convrot:
+            raise NotImplementedError("ConvRot rotation is outside this package's scope; construct with use_convrot=False")
+        self.use_convrot = False
+        super().__init__(in_features, out_features, bias=bias, config=config, device=device, dtype=dtype)
+
+    def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
+        out = torch._int_mm(activation, codes.t()).to(torch.float32)
+        out.mul_(activation_scale.unsqueeze(1))
+        bias = self._bias_padded(codes.device, weight_scale.shape[0])
+        if bias is None:
+            return out.mul_(weight_scale).to(out_dtype)
+        return torch.addcmul(bias.to(torch.float32), out, weight_scale).to(out_dtype)
+
+
+__all__ = ["CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "QuantizedLinear"]

@@ -1,0 +1,137 @@
+"""Whole-model compression across the GPUs of one node, and a column-sharded compressed linear.
+
+The reference has no multi-GPU code; every layer (and every tile inside a layer) is independent, so the
+work shards without any exchange on the data path:
+
+* :func:`partition_layers` assigns layers to ranks, largest first onto the lightest rank;
+* :func:`compress_layers` compresses this rank's share (one process per GPU, ``torch.distributed`` only
+  to learn rank and world size) and returns ``{layer index: CompressedTensor}``;
+* :class:`ColumnShardedLinear` keeps rows ``[rank * N / G, (rank + 1) * N / G)`` of a weight on each rank
+  (row scales and whole E8 vectors stay local) and all-gathers only the ``[M, N / G]`` outputs -- the one
+  collective of the package (NCCL over NVLink on GPUs).
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+#: The synthetic 276-linear DiT used as the whole-model workload: 30 blocks of 9 linears plus 6
+#: embed/head linears, hidden 3840, MLP 10240. (out_features, in_features) per layer, in model order.
+DIT_HIDDEN, DIT_MLP, DIT_BLOCKS = 3840, 10240, 30
+_BLOCK_LAYERS = (
+    (3 * DIT_HIDDEN, DIT_HIDDEN),   # fused qkv
+    (DIT_HIDDEN, DIT_HIDDEN),       # attention output
+    (DIT_MLP, DIT_HIDDEN),          # mlp up
+    (DIT_HIDDEN, DIT_MLP),          # mlp down
+    (DIT_HIDDEN, DIT_HIDDEN), (DIT_HIDDEN, DIT_HIDDEN), (DIT_HIDDEN, DIT_HIDDEN),   # modulation / projection layers
+    (DIT_HIDDEN, DIT_HIDDEN), (DIT_HIDDEN, DIT_HIDDEN),
+)
+
+
+def dit_layer_shapes() -> list[tuple[int, int]]:
+    shapes = [(DIT_HIDDEN, DIT_HIDDEN)] * 3
+    for _ in range(DIT_BLOCKS):
+        shapes.extend(_BLOCK_LAYERS)
+    shapes.extend([(DIT_HIDDEN, DIT_HIDDEN)] * 3)
+    return shapes
+
+
+def mixed_bit_targets(shapes, mean_bpp: float = 2.3, seed: int = 0) -> list[float]:
+    """Per-layer targets from a fixed seeded draw, rescaled so the element-weighted mean is ``mean_bpp``
+    (the reference's sensitivity-based allocator is not public; this stands in for its output)."""
+    generator = torch.Generator().manual_seed(seed)
+    raw = 1.6 + 1.6 * torch.rand(len(shapes), generator=generator)
+    weights = torch.tensor([float(r * c) for r, c in shapes])
+    raw = raw * (mean_bpp / float((raw * weights).sum() / weights.sum()))
+    return [round(float(v), 3) for v in raw]
+
+
+def partition_layers(sizes, world_size: int) -> list[list[int]]:
+    """Greedy longest-processing-time assignment: layers by decreasing size onto the least-loaded rank.
+    Deterministic (ties go to the lower layer index, then the lower rank)."""
+    if world_size < 1:
+        raise ValueError("world_size must be positive")
+    order = sorted(range(len(sizes)), key=lambda i: (-sizes[i], i))
+    load = [0] * world_size
+    shares: list[list[int]] = [[] for _ in range(world_size)]
+    for index in order:
+        rank = min(range(world_size), key=lambda r: (load[r], r))
+        shares[rank].append(index)
+        load[rank] += sizes[index]
+    return [sorted(share) for share in shares]
+
+
+def _rank_and_world(group=None) -> tuple[int, int]:
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
+def compress_layers(weights, configs, group=None, compress_fn=None) -> dict:
+    """Compress this rank's share of ``weights`` (a sequence of callables or tensors; callables are only
+    invoked for layers this rank owns, so a rank never materialises the others' weights).
+    ``configs`` is one config or one per layer. Returns ``{layer index: compressed}``."""
+    from .compression import compress
+
+    compress_fn = compress_fn or compress
+    rank, world = _rank_and_world(group)
+    sizes = [getattr(w, "numel", lambda: 0)() if isinstance(w, torch.Tensor) else int(getattr(w, "size_hint", 1)) for w in weights]
+    mine = partition_layers(sizes, world)[rank]
+    per_layer = configs if isinstance(configs, (list, tuple)) else [configs] * len(weights)
+    result = {}
+    for index in mine:
+        weight = weights[index] if isinstance(weights[index], torch.Tensor) else weights[index]()
+        result[index] = compress_fn(weight, per_layer[index])
+    return result
+
+
+def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather ``[..., N / G]`` shards along the last dimension into ``[..., N]`` (rank order)."""
+    _rank, world = _rank_and_world(group)
+    if world == 1:
+        return local
+    local = local.contiguous()
+    pieces = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(pieces, local, group=group)
+    return torch.cat(pieces, dim=-1)
+
+
+@dataclass
+class RowSlice:
+    begin: int
+    end: int
+
+
+def row_slice(out_features: int, rank: int, world: int) -> RowSlice:
+    if out_features % world:
+        raise ValueError(f"out_features {out_features} is not divisible by the {world} ranks of the group")
+    rows = out_features // world
+    return RowSlice(rank * rows, (rank + 1) * rows)
+
+
+class ColumnShardedLinear(torch.nn.Module):
+    """A compressed linear whose output features are split over the ranks of a process group.
+
+    Each rank compresses and decodes only its own rows of the weight; activations are replicated; the
+    forward computes ``x @ W_rank^T`` locally and all-gathers the outputs."""
+
+    def __init__(self, linear: torch.nn.Linear, layer_cls=None, group=None, **layer_kwargs):
+        super().__init__()
+        from .linear import CompressedLinear
+
+        layer_cls = layer_cls or CompressedLinear
+        self.group = group
+        rank, world = _rank_and_world(group)
+        rows = row_slice(linear.out_features, rank, world)
+        shard = torch.nn.Linear(linear.in_features, rows.end - rows.begin, bias=linear.bias is not None,
+                                device=linear.weight.device, dtype=linear.weight.dtype)
+        with torch.no_grad():
+            shard.weight.copy_(linear.weight[rows.begin : rows.end])
+            if linear.bias is not None:
+                shard.bias.copy_(linear.bias[rows.begin : rows.end])
+        self.rows = rows
+        self.out_features = linear.out_features
+        self.local = layer_cls.from_linear(shard, **layer_kwargs)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return gather_columns(self.local(x), self.group)

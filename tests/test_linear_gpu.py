@@ -1,0 +1,93 @@
+"""Compressed linear layers: API, checkpoint format, forward numerics (GEMM outputs within bf16 tolerance)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import buffers_of, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _relative(a: torch.Tensor, b: torch.Tensor) -> float:
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 256])
+def test_compressed_linear_forward_matches_dense_on_decoded_weight(tokens):
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(6)
+    dense = torch.nn.Linear(3840, 1536, bias=True, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        dense.weight.copy_((torch.randn(1536, 3840, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
+    layer = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
+    assert abs(layer.compressed_bits - 4.0) < 0.05
+    x = torch.randn(tokens, 3840, generator=g, device="cuda").to(torch.bfloat16)
+    weight = layer.dequantize()
+    assert weight.shape == dense.weight.shape and weight.dtype == torch.bfloat16
+    expected = torch.nn.functional.linear(x.float(), weight.float(), dense.bias.float())
+    assert _relative(layer(x), expected) <= 1e-2
+    # and the lossy weight is close to the original (about 7 % relative L2 at 4 bpp)
+    assert float((weight.float() - dense.weight.float()).norm() / dense.weight.float().norm()) < 0.09
+
+
+def test_lossless_default_config_round_trips_exactly():
+    import entropack_b200 as ep
+
+    dense = torch.nn.Linear(512, 384, bias=False, device="cuda", dtype=torch.bfloat16)
+    layer = ep.CompressedLinear.from_linear(dense)
+    assert layer.weight.compress_method == "dfloat11"
+    assert torch.equal(layer.dequantize().view(torch.int16), dense.weight.view(torch.int16))
+    x = torch.randn(8, 512, device="cuda", dtype=torch.bfloat16)
+    assert torch.equal(layer(x), dense(x))
+
+
+def test_state_dict_round_trip_and_reference_checkpoint_loads():
+    import entropack_b200 as ep
+
+    dense = torch.nn.Linear(256, 64, bias=True, device="cuda", dtype=torch.bfloat16)
+    layer = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
+    state = layer.state_dict()
+    assert set(state) == {"weight.entropack_quant_state", "bias"}
+    fresh = ep.CompressedLinear(256, 64, bias=True, config=ep.EntroPackLossyConfig(target_bpp=4.0), device="cuda")
+    fresh.load_state_dict(state)
+    assert torch.equal(fresh.dequantize().view(torch.int16), layer.dequantize().view(torch.int16))
+    # a blob written by the reference (golden fixture, 64 x 256 bf16 at 4 bpp) loads and decodes to its bytes
+    record = load_golden("lattice_bf16_4p0")
+    reference_state = {"weight.entropack_quant_state": torch.from_numpy(record["blob"].copy()), "bias": torch.zeros(64, dtype=torch.bfloat16)}
+    fresh.load_state_dict(reference_state)
+    decoded = fresh.dequantize()
+    assert decoded.cpu().contiguous().view(torch.uint8).numpy().tobytes() == record["decoded_bytes"].tobytes()
+
+
+@pytest.mark.parametrize("tokens", [1, 16, 256])
+def test_fp8_linear_forward(tokens):
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(7)
+    dense = torch.nn.Linear(1024, 768, bias=True, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        dense.weight.copy_((torch.randn(768, 1024, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
+    layer = ep.CompressedFP8Linear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=5.0))
+    assert set(layer.state_dict()) == {"weight.entropack_quant_state", "bias", "weight_quant_scale"}
+    assert layer.codes().dtype == torch.float8_e4m3fn
+    x = torch.randn(tokens, 1024, generator=g, device="cuda").to(torch.bfloat16)
+    out = layer(x)
+    # reference formula on the decoded codes: per-token fp8 activations, fp32 accumulate, row/col scales, bias
+    codes = layer.codes().float()
+    a_scale = (x.float().abs().amax(dim=1) / 448.0).clamp(min=torch.finfo(torch.float32).eps)
+    a_codes = (x.float() / a_scale.unsqueeze(1)).clamp(-448, 448).to(torch.float8_e4m3fn).float()
+    expected = (a_codes @ codes.t()) * a_scale.unsqueeze(1) * layer.weight_quant_scale.unsqueeze(0) + dense.bias.float()
+    assert _relative(out, expected) <= 1e-2
+    assert _relative(out, dense(x)) < 0.08
+
+
+def test_int8_linear_forward_and_unsupported_rotation():
+    import entropack_b200 as ep
+
+    dense = torch.nn.Linear(512, 256, bias=False, device="cuda", dtype=torch.bfloat16)
+    layer = ep.CompressedINT8Linear.from_linear(dense)
+    x = torch.randn(32, 512, device="cuda", dtype=torch.bfloat16)
+    assert _relative(layer(x), dense(x)) < 0.05
+    with pytest.raises(NotImplementedError):
+        ep.CompressedINT8Linear(512, 256, use_convrot=True)
