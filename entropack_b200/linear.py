@@ -18,11 +18,35 @@ from typing import ClassVar
 import torch
 from torch.nn import functional as F
 
+from . import _native
 from .compression import CompressedTensor, compress, decompress
 from .registry import default_config, get_scheme, name_for_config, require_dtype
 from .schemes import EntroPackLossyConfig, RawConfig
 
 _EPS = torch.finfo(torch.float32).eps
+
+
+def _native_gemm_applies(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> bool:
+    """The library GEMM takes bf16 operands on one CUDA device with K a multiple of 8; gradients, other dtypes
+    and odd shapes go through torch."""
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.device == x.device
+            and (bias is None or (bias.dtype == torch.bfloat16 and bias.device == x.device))
+            and x.shape[-1] % 8 == 0 and x.numel() > 0 and not (torch.is_grad_enabled() and x.requires_grad))
+
+
+def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                   error: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T + bias`` in bf16 through ``ep_linear_forward`` (CUDA-core kernel for up to 16 tokens,
+    tcgen05 tensor-core kernel above)."""
+    flat = x.reshape(-1, x.shape[-1]).contiguous()
+    weight = weight.contiguous()
+    out = torch.empty((flat.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        status = _native.load().ep_linear_forward(
+            _native.ptr(flat), _native.ptr(weight), _native.ptr(bias.contiguous() if bias is not None else None), _native.ptr(out),
+            flat.shape[0], weight.shape[0], flat.shape[1], _native.ptr(error), _native.stream_handle(x.device))
+    _native.check(status, "linear forward")
+    return out.reshape(*x.shape[:-1], weight.shape[0])
 
 
 def _pad_to(tensor: torch.Tensor, dim: int, size: int) -> torch.Tensor:
@@ -153,7 +177,11 @@ class CompressedLinear(torch.nn.Linear):
         return None if self.bias is None else self.bias.to(device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(x, self.dequantize(x.device).to(x.dtype), self._bias_on(x.device))
+        weight = self.dequantize(x.device)
+        bias = self._bias_on(x.device)
+        if _native_gemm_applies(x, weight, bias):
+            return linear_forward(x, weight, bias)
+        return F.linear(x, weight.to(x.dtype), bias)
 
     def extra_repr(self) -> str:
         scheme = "auto" if self.config is None else name_for_config(self.config)

@@ -241,6 +241,18 @@ int ep_dfloat11_pack(const void* bf16_dev, int64_t n_elements, const int32_t* co
                      int eof_length, uint32_t eof_value, uint8_t* encoded_dev, uint8_t* sign_mantissa_dev,
                      uint16_t* thread_meta_dev, uint32_t* output_positions_dev, uint32_t* region_scratch_dev, ep_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Linear forward on a decoded weight.
+ * ------------------------------------------------------------------------------------------- */
+
+/* y[m][n] = x[m][k] . weight[n][k]^T (+ bias[n]), all bf16, fp32 accumulation. k must be a multiple of 8
+ * and the three matrices 16-byte aligned. Stands in for the F.linear call of CompressedLinear.forward
+ * (entropack/linear/linear.py:163-165): m <= 16 runs a bandwidth kernel on CUDA cores, larger m the
+ * tcgen05 / TMEM tensor-core kernel fed by TMA. A wait that runs out inside the tensor-core kernel is
+ * reported as code 9 in error_dev (optional device int32, zeroed by the caller). */
+int ep_linear_forward(const void* x_dev, const void* weight_dev, const void* bias_dev, void* y_dev, int64_t m, int64_t n,
+                      int64_t k, int* error_dev, ep_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
