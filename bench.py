@@ -269,6 +269,9 @@ def run_b200(args) -> None:
     # reported for context under "others", not part of the headline value
     others = measure_others(ep, device, flush, args.steps)
 
+    # whole-model encode: this rank's share of the synthetic 276-linear DiT at 4 bpp (layers sharded, no collectives)
+    model = measure_model_encode(ep, device, rank, world)
+
     # end to end through the public API from pinned host blobs
     host_blobs = [c.entropack_quant_state.cpu().pin_memory() for c in containers]
     host_outputs = [torch.empty(c.numel() * c.element_size(), dtype=torch.uint8).pin_memory() for c in containers]
@@ -295,9 +298,9 @@ def run_b200(args) -> None:
     assert torch.equal(host_outputs[0], launches[0][4].view(torch.uint8).reshape(-1).cpu())
 
     if distributed:
-        times = torch.tensor([total_ms, e2e_seconds], dtype=torch.float64, device=device)
+        times = torch.tensor([total_ms, e2e_seconds, model["seconds"]], dtype=torch.float64, device=device)
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        total_ms, e2e_seconds = float(times[0]), float(times[1])
+        total_ms, e2e_seconds, model["seconds"] = float(times[0]), float(times[1]), float(times[2])
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -325,12 +328,38 @@ def run_b200(args) -> None:
         "e2e": {"value": world * bytes_per_step * e2e_steps / e2e_seconds / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
         "others": others,
+        "model_encode": {"workload": "synthetic DiT, 276 linears (hidden 3840, mlp 10240), bf16 N(0,0.02^2), 4 bpp, layers sharded "
+                                     "largest-first over the ranks", "seconds": model["seconds"], "layers_on_rank0": model["layers"],
+                         "mean_bpp_rank0": model["bpp"]},
         "gpu_launches": len(launches) * args.steps,
         "clocks": clocks,
     }
     print(json.dumps(line))
     if distributed:
         dist.destroy_process_group()
+
+
+def measure_model_encode(ep, device, rank: int, world: int) -> dict:
+    from entropack_b200 import sharding
+
+    shapes = sharding.dit_layer_shapes()
+    mine = sharding.partition_layers([r * c for r, c in shapes], world)[rank]
+    config = ep.EntroPackLossyConfig(target_bpp=4.0)
+    generator = torch.Generator(device=device).manual_seed(1000 + rank)
+    seconds, stored, elements = 0.0, 0, 0
+    warm = (torch.randn(3840, 3840, generator=generator, device=device) * 0.02).to(torch.bfloat16)
+    ep.compress(warm, config)
+    for index in mine:
+        rows, cols = shapes[index]
+        weight = (torch.randn(rows, cols, generator=generator, device=device) * 0.02).to(torch.bfloat16)
+        torch.cuda.synchronize(device)
+        begin = time.perf_counter()
+        container = ep.compress(weight, config)
+        torch.cuda.synchronize(device)
+        seconds += time.perf_counter() - begin
+        stored += container.storage_nbytes()
+        elements += rows * cols
+    return {"seconds": seconds, "layers": len(mine), "bpp": stored * 8 / max(1, elements)}
 
 
 def measure_others(ep, device, flush, reps: int) -> dict:
@@ -386,6 +415,33 @@ def measure_others(ep, device, flush, reps: int) -> dict:
     config = ep.TileANSConfig()
     ms = timed(lambda: ep.compress(tensor, config))
     results["tile_ans_encode_fp8_8192x8192"] = {"ms": ms}
+    del tensor, weight, container
+
+    # CompressedLinear forward (decode every call + library GEMM) against bf16 cuBLAS on the dense weight, L2 cold
+    from entropack_b200.linear import linear_forward
+
+    generator = torch.Generator(device=device).manual_seed(6)
+    for out_features, in_features in ((3840, 3840), (10240, 3840)):
+        dense = torch.nn.Linear(in_features, out_features, bias=False, device=device, dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_((torch.randn(out_features, in_features, generator=generator, device=device) * 0.02).to(torch.bfloat16))
+        layer = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
+        decoded = layer.dequantize()
+        for tokens in (1, 16, 256, 4096):
+            x = torch.randn(tokens, in_features, generator=generator, device=device).to(torch.bfloat16)
+            reference = torch.nn.functional.linear(x.float(), decoded.float())
+            ours = layer(x)
+            error = float((ours.float() - reference).abs().max() / reference.abs().max())
+            entry = {
+                "compressed_forward_us": timed(lambda: layer(x)) * 1e3,
+                "library_gemm_us": timed(lambda: linear_forward(x, decoded)) * 1e3,
+                "cublas_dense_us": timed(lambda: torch.nn.functional.linear(x, dense.weight)) * 1e3,
+                "max_rel_err": error, "bits": layer.compressed_bits,
+            }
+            if tokens == 4096:
+                entry["library_gemm_tflops"] = 2.0 * tokens * out_features * in_features / entry["library_gemm_us"] / 1e6
+                entry["cublas_tflops"] = 2.0 * tokens * out_features * in_features / entry["cublas_dense_us"] / 1e6
+            results[f"linear_{in_features}x{out_features}_M{tokens}"] = entry
     return results
 
 
