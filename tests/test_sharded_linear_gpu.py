@@ -1,0 +1,66 @@
+"""Column-sharded compressed linear over NCCL (needs two GPUs; skipped on a single-GPU box)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _dense(device):
+    g = torch.Generator().manual_seed(11)
+    layer = torch.nn.Linear(1024, 768, bias=True, dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer.weight.copy_((torch.randn(768, 1024, generator=g) * 0.02).to(torch.bfloat16))
+        layer.bias.copy_(torch.randn(768, generator=g).to(torch.bfloat16))
+    x = torch.randn(48, 1024, generator=g).to(torch.bfloat16)
+    return layer.to(device), x.to(device)
+
+
+def _worker(rank: int, world: int, port: int, results):
+    import entropack_b200 as ep
+    from entropack_b200 import sharding
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        dense, x = _dense(device)
+        layer = sharding.ColumnShardedLinear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
+        out = layer(x)
+        torch.cuda.synchronize()
+        # what a single device computes for the same two row shards, each compressed on its own
+        pieces = []
+        for r in range(world):
+            rows = sharding.row_slice(dense.out_features, r, world)
+            shard = torch.nn.Linear(1024, rows.end - rows.begin, bias=True, device=device, dtype=torch.bfloat16)
+            with torch.no_grad():
+                shard.weight.copy_(dense.weight[rows.begin : rows.end])
+                shard.bias.copy_(dense.bias[rows.begin : rows.end])
+            pieces.append(ep.CompressedLinear.from_linear(shard, config=ep.EntroPackLossyConfig(target_bpp=4.0))(x))
+        expected = torch.cat(pieces, dim=-1)
+        results[rank] = (tuple(out.shape), bool(torch.equal(out.view(torch.int16), expected.view(torch.int16))),
+                         float((out.float() - dense(x).float()).norm() / dense(x).float().norm()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_column_sharded_linear_all_gathers_outputs():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    results = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    for rank in range(world):
+        shape, identical, relative = results[rank]
+        assert shape == (48, 768) and identical and relative < 0.12
