@@ -61,10 +61,22 @@ __device__ __forceinline__ void stage_decode_tables(const DecodeParams& p, uint3
     if ((p.lanes.raw_mask >> b) & 1u) continue;
     const uint32_t* source = p.tables + static_cast<size_t>(b) * table_size;
     uint32_t* staged = shared_tables + static_cast<size_t>(p.lanes.ans_rank[b]) * table_size;
-    for (uint32_t slot = threadIdx.x; slot < table_size; slot += kThreads) {
-      const uint32_t entry = source[slot];
-      if (((entry >> 8) & 0xFFFu) == 0u && slot == 0u) constant_symbol[b] = static_cast<int>(entry & 0xFFu);
-      staged[slot] = (entry & 0xFFFFFu) | ((slot - (entry >> 20)) << 20);
+    const auto repack = [](uint32_t entry, uint32_t slot) { return (entry & 0xFFFFFu) | ((slot - (entry >> 20)) << 20); };
+    if (threadIdx.x == 0) {
+      const uint32_t entry = source[0];
+      if (((entry >> 8) & 0xFFFu) == 0u) constant_symbol[b] = static_cast<int>(entry & 0xFFu);
+    }
+    if ((reinterpret_cast<uintptr_t>(source) & 15u) == 0) {
+      // four entries per load and store (the table has at least 512 entries)
+      const uint4* source4 = reinterpret_cast<const uint4*>(source);
+      uint4* staged4 = reinterpret_cast<uint4*>(staged);
+      for (uint32_t quad = threadIdx.x; quad < table_size / 4; quad += kThreads) {
+        const uint4 e = __ldg(source4 + quad);
+        const uint32_t slot = quad * 4;
+        staged4[quad] = make_uint4(repack(e.x, slot), repack(e.y, slot + 1), repack(e.z, slot + 2), repack(e.w, slot + 3));
+      }
+    } else {
+      for (uint32_t slot = threadIdx.x; slot < table_size; slot += kThreads) staged[slot] = repack(source[slot], slot);
     }
   }
   __syncthreads();
@@ -243,8 +255,11 @@ tile_ans_decode_kernel(const DecodeParams p) {
 #pragma unroll
   for (int b = 0; b < NLANES; ++b) {
     const int64_t stream = static_cast<int64_t>(b) * p.tiles + tile;
-    const uint32_t begin = p.offsets[stream];
-    const uint32_t end = p.offsets[stream + 1];
+    // The bounds of a coded stream pass through a warp-wide reduction: it tells the compiler that they, and the
+    // cursor arithmetic built on them, are the same in all 32 threads, so tests on them become uniform branches.
+    const bool is_raw = (raw_mask >> b) & 1u;
+    const uint32_t begin = is_raw ? p.offsets[stream] : __reduce_min_sync(0xFFFFFFFFu, p.offsets[stream]);
+    const uint32_t end = is_raw ? p.offsets[stream + 1] : __reduce_min_sync(0xFFFFFFFFu, p.offsets[stream + 1]);
     if (end < begin || static_cast<int64_t>(end) > p.payload_words) failure = EP_STREAM_BAD_OFFSETS;
     raw_bytes[b] = reinterpret_cast<const uint8_t*>(p.payload + begin);
     constant[b] = constant_symbol[b];
@@ -307,11 +322,12 @@ tile_ans_decode_kernel(const DecodeParams p) {
       const bool need = valid && x < kStateMin;
       const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
       // this thread's word sits 2 * (readers at or above this lane) bytes below the cursor; thread 0 counts every
-      // reader, so its position is the cursor for the next step
+      // reader, so the lowest position in the warp is the cursor for the next step (a reduction, whose result
+      // the compiler knows to be warp-uniform)
       const int below = c.cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
       const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingWords * 2u - 2u)) | c.ring), x, 0x5410);
       c.state = need ? merged : x;
-      c.cursor = __shfl_sync(0xFFFFFFFFu, below, 0);
+      c.cursor = __reduce_min_sync(0xFFFFFFFFu, below);
     }
   };
   // Ring upkeep, run once every four steps. Three chunks at and below the cursor's chunk are resident
@@ -341,11 +357,18 @@ tile_ans_decode_kernel(const DecodeParams p) {
     const int block_hi = min(block_lo + kBlockElems, count);
     // ---- chain phase: groups of 32 symbols, back to front; only the tile's last group can be partial
     if (block_hi - block_lo == kBlockElems) {
-#pragma unroll
-      for (int group = kBlockElems / 32 - 1; group >= 0; --group) {
-        chain_step(group * 32, true);
-        if ((group & 3) == 0) ring_upkeep();
-      }
+      static_assert(kBlockElems == 512, "sixteen steps are written out below");
+#define EP_FOUR_STEPS(first)          \
+  chain_step((first) * 32 + 96, true); \
+  chain_step((first) * 32 + 64, true); \
+  chain_step((first) * 32 + 32, true); \
+  chain_step((first) * 32, true);      \
+  ring_upkeep();
+      EP_FOUR_STEPS(12)
+      EP_FOUR_STEPS(8)
+      EP_FOUR_STEPS(4)
+      EP_FOUR_STEPS(0)
+#undef EP_FOUR_STEPS
     } else {
       const int tail = (block_hi - block_lo) & 31;
       for (int offset = block_hi - (tail ? tail : 32); offset >= block_lo; offset -= 32) {
