@@ -23,6 +23,11 @@ def make_tensor(kind: str, rows: int, cols: int, device, seed: int = 1) -> torch
         return (x * 0.02).to(torch.bfloat16)
     if kind == "fp32":
         return x * 0.02
+    if kind == "int16_pair":
+        # two independent small-valued bytes per element: both byte lanes are entropy coded
+        low = (x * 20).round().clamp(-127, 127).to(torch.int16) & 0xFF
+        high = (torch.randn(rows, cols, generator=generator, device=device) * 20).round().clamp(-127, 127).to(torch.int16)
+        return low | (high << 8)
     raise ValueError(kind)
 
 
