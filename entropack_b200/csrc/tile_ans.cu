@@ -248,10 +248,10 @@ tile_ans_decode_kernel(const DecodeParams p) {
   const uint32_t rings_address = (shared_base + static_cast<uint32_t>(ans_lanes) * table_size * 4u + kRingBytes - 1u) & ~(kRingBytes - 1u);
   const uint32_t staging_at = (rings_address - shared_base) + static_cast<uint32_t>(kWarps * ans_lanes) * kRingBytes;  // in bytes
 
-  const uint8_t* raw_bytes[NLANES];
+  uint32_t raw_begin[NLANES];   // raw lanes: index of the stream's first 16-bit word in the payload
   CodedLane coded[NLANES];
-  int constant[NLANES];
   int failure = 0;
+  bool raw_near_end = false;    // a raw stream ends within 8 bytes of the payload's end: no over-reading loads there
 #pragma unroll
   for (int b = 0; b < NLANES; ++b) {
     const int64_t stream = static_cast<int64_t>(b) * p.tiles + tile;
@@ -261,8 +261,7 @@ tile_ans_decode_kernel(const DecodeParams p) {
     const uint32_t begin = is_raw ? p.offsets[stream] : __reduce_min_sync(0xFFFFFFFFu, p.offsets[stream]);
     const uint32_t end = is_raw ? p.offsets[stream + 1] : __reduce_min_sync(0xFFFFFFFFu, p.offsets[stream + 1]);
     if (end < begin || static_cast<int64_t>(end) > p.payload_words) failure = EP_STREAM_BAD_OFFSETS;
-    raw_bytes[b] = reinterpret_cast<const uint8_t*>(p.payload + begin);
-    constant[b] = constant_symbol[b];
+    raw_begin[b] = begin;
     const uint32_t rank = RAW_MASK >= 0 ? static_cast<uint32_t>(__builtin_popcount(~static_cast<uint32_t>(RAW_MASK) & ((1u << b) - 1u)))
                                         : p.lanes.ans_rank[b];
     CodedLane& c = coded[b];
@@ -276,6 +275,7 @@ tile_ans_decode_kernel(const DecodeParams p) {
     c.state = kStateMin;
     if ((raw_mask >> b) & 1u) {
       if (!failure && end - begin != static_cast<uint32_t>((count + 1) >> 1)) failure = EP_STREAM_BAD_RAW_LENGTH;
+      raw_near_end = raw_near_end || static_cast<int64_t>(end) + 4 > p.payload_words;
     } else {
       c.state = p.states[(static_cast<int64_t>(rank) * p.tiles + tile) * kNumStates + lane];
     }
@@ -352,11 +352,15 @@ tile_ans_decode_kernel(const DecodeParams p) {
   };
 
   element_t* out = static_cast<element_t*>(p.output) + tile_begin;
-  const bool wide_bytes = NLANES == 1 && (p.tile_elements & 15) == 0;
+  const uint8_t* payload_bytes = reinterpret_cast<const uint8_t*>(p.payload);
+  // kGroup elements = 16 bytes of output per thread; needs every tile to start on a 16-byte boundary
+  constexpr int kGroup = 16 / NLANES;
+  const bool wide = (p.tile_elements % kGroup) == 0;
   for (int block_lo = ((count - 1) / kBlockElems) * kBlockElems; block_lo >= 0; block_lo -= kBlockElems) {
     const int block_hi = min(block_lo + kBlockElems, count);
+    const bool full = block_hi - block_lo == kBlockElems;
     // ---- chain phase: groups of 32 symbols, back to front; only the tile's last group can be partial
-    if (block_hi - block_lo == kBlockElems) {
+    if (full) {
       static_assert(kBlockElems == 512, "sixteen steps are written out below");
 #define EP_FOUR_STEPS(first)          \
   chain_step((first) * 32 + 96, true); \
@@ -377,38 +381,89 @@ tile_ans_decode_kernel(const DecodeParams p) {
       }
     }
     __syncwarp();
-    // ---- merge phase: raw bytes + staged symbols -> whole elements, vector stores
-    if (wide_bytes) {
-      const int e = block_lo + static_cast<int>(lane) * 16;
-      uint8_t* out_bytes = reinterpret_cast<uint8_t*>(out);
-      const uint32_t staged = coded[0].stage - lane;
-      if (!(raw_mask & 1u) && e + 16 <= block_hi) {
-        *reinterpret_cast<uint4*>(out_bytes + e) = *reinterpret_cast<const uint4*>(shared_bytes + staged + lane * 16);
-      } else {
-        for (int k = e; k < min(e + 16, block_hi); ++k) {
-          out_bytes[k] = (raw_mask & 1u) ? __ldg(raw_bytes[0] + k) : shared_bytes[staged + (k - block_lo)];
-        }
-      }
-    } else {
-#pragma unroll 8
-      for (int e = block_lo + static_cast<int>(lane) * 2; e < block_hi; e += 64) {
-        element_t first = 0, second = 0;
+    // ---- merge phase: raw bytes + staged symbols -> whole elements
+    if (full && wide && !(raw_near_end && block_hi == count)) {
+      // Every thread gathers kGroup consecutive bytes of each lane (one vector read of the staging block, or
+      // aligned 32-bit loads of the raw stream, shifted by 16 bits where the stream starts on an odd word),
+      // transposes them into kGroup whole elements and stores 16 bytes.
+      constexpr int kWords = kGroup / 4 > 0 ? kGroup / 4 : 1;   // 32-bit words per lane and thread
+#pragma unroll 2
+      for (int in_block = static_cast<int>(lane) * kGroup; in_block < kBlockElems; in_block += 32 * kGroup) {
+        uint32_t bytes[NLANES][kWords];
 #pragma unroll
         for (int b = 0; b < NLANES; ++b) {
-          uint32_t both;
           if ((raw_mask >> b) & 1u) {
-            both = __ldg(reinterpret_cast<const uint16_t*>(raw_bytes[b] + e));
+            const uint32_t first_word = raw_begin[b] + (static_cast<uint32_t>(block_lo + in_block) >> 1);   // 16-bit units
+            if (kGroup >= 4) {
+              const uint32_t* aligned = reinterpret_cast<const uint32_t*>(p.payload) + (first_word >> 1);
+              const uint32_t shift = (first_word & 1u) << 4;
+              uint32_t loaded[kWords + 1];
+#pragma unroll
+              for (int w = 0; w < kWords; ++w) loaded[w] = __ldg(aligned + w);
+              loaded[kWords] = shift ? __ldg(aligned + kWords) : 0u;
+#pragma unroll
+              for (int w = 0; w < kWords; ++w) bytes[b][w] = __funnelshift_r(loaded[w], loaded[w + 1], shift);
+            } else {
+              bytes[b][0] = __ldg(p.payload + first_word);
+            }
           } else {
-            both = shared_words[((coded[b].stage - lane) + static_cast<uint32_t>(e - block_lo)) >> 1];
+            const uint32_t at = (coded[b].stage - lane) + static_cast<uint32_t>(in_block);
+            if (kGroup == 16) {
+              const uint4 v = *reinterpret_cast<const uint4*>(shared_bytes + at);
+              bytes[b][0] = v.x; bytes[b][kWords > 1 ? 1 : 0] = v.y; bytes[b][kWords > 2 ? 2 : 0] = v.z; bytes[b][kWords > 3 ? 3 : 0] = v.w;
+            } else if (kGroup == 8) {
+              const uint2 v = *reinterpret_cast<const uint2*>(shared_bytes + at);
+              bytes[b][0] = v.x; bytes[b][kWords > 1 ? 1 : 0] = v.y;
+            } else if (kGroup == 4) {
+              bytes[b][0] = shared_tables[at >> 2];
+            } else {
+              bytes[b][0] = shared_words[at >> 1];
+            }
           }
-          first |= static_cast<element_t>(static_cast<element_t>(both & 0xFFu) << (8 * b));
-          second |= static_cast<element_t>(static_cast<element_t>(both >> 8) << (8 * b));
         }
-        if (e + 1 < block_hi) {
-          *reinterpret_cast<pair_t*>(out + e) = make_pair(first, second);
+        uint4 packed;
+        if (NLANES == 1) {
+          packed = make_uint4(bytes[0][0], bytes[0][kWords > 1 ? 1 : 0], bytes[0][kWords > 2 ? 2 : 0], bytes[0][kWords > 3 ? 3 : 0]);
+        } else if (NLANES == 2) {
+          const uint32_t* a = bytes[0];
+          const uint32_t* c = bytes[NLANES > 1 ? 1 : 0];
+          packed = make_uint4(__byte_perm(a[0], c[0], 0x5140), __byte_perm(a[0], c[0], 0x7362),
+                              __byte_perm(a[kWords > 1 ? 1 : 0], c[kWords > 1 ? 1 : 0], 0x5140),
+                              __byte_perm(a[kWords > 1 ? 1 : 0], c[kWords > 1 ? 1 : 0], 0x7362));
+        } else if (NLANES == 4) {
+          const uint32_t ab_low = __byte_perm(bytes[0][0], bytes[NLANES > 1 ? 1 : 0][0], 0x5140);
+          const uint32_t ab_high = __byte_perm(bytes[0][0], bytes[NLANES > 1 ? 1 : 0][0], 0x7362);
+          const uint32_t cd_low = __byte_perm(bytes[NLANES > 2 ? 2 : 0][0], bytes[NLANES > 3 ? 3 : 0][0], 0x5140);
+          const uint32_t cd_high = __byte_perm(bytes[NLANES > 2 ? 2 : 0][0], bytes[NLANES > 3 ? 3 : 0][0], 0x7362);
+          packed = make_uint4(__byte_perm(ab_low, cd_low, 0x5410), __byte_perm(ab_low, cd_low, 0x7632),
+                              __byte_perm(ab_high, cd_high, 0x5410), __byte_perm(ab_high, cd_high, 0x7632));
         } else {
-          out[e] = first;
+          // two 8-byte elements: byte b of element k is byte k of lane b's pair
+          uint32_t words[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+          for (int b = 0; b < NLANES; ++b) {
+            words[b >> 2] |= (bytes[b][0] & 0xFFu) << (8 * (b & 3));
+            words[2 + (b >> 2)] |= ((bytes[b][0] >> 8) & 0xFFu) << (8 * (b & 3));
+          }
+          packed = make_uint4(words[0], words[1], words[2], words[3]);
         }
+        *reinterpret_cast<uint4*>(out + block_lo + in_block) = packed;
+      }
+    } else {
+      // ragged block, tile size that breaks the 16-byte alignment, or end of the payload: one element per thread
+      for (int k = static_cast<int>(lane); k < block_hi - block_lo; k += 32) {
+        element_t value = 0;
+#pragma unroll
+        for (int b = 0; b < NLANES; ++b) {
+          uint32_t byte;
+          if ((raw_mask >> b) & 1u) {
+            byte = __ldg(payload_bytes + 2 * static_cast<int64_t>(raw_begin[b]) + block_lo + k);
+          } else {
+            byte = shared_bytes[(coded[b].stage - lane) + static_cast<uint32_t>(k)];
+          }
+          value |= static_cast<element_t>(static_cast<element_t>(byte) << (8 * b));
+        }
+        out[block_lo + k] = value;
       }
     }
     __syncwarp();
@@ -416,7 +471,7 @@ tile_ans_decode_kernel(const DecodeParams p) {
 
 #pragma unroll
   for (int b = 0; b < NLANES; ++b) {
-    if (((raw_mask >> b) & 1u) || constant[b] >= 0) continue;
+    if (((raw_mask >> b) & 1u) || constant_symbol[b] >= 0) continue;
     const bool dirty = __any_sync(0xFFFFFFFFu, coded[b].state != kStateMin);
     const int left = (coded[b].cursor - coded[b].origin) / 2;
     if (left < 0) failure = EP_STREAM_UNDERRUN;
