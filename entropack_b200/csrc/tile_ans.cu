@@ -192,18 +192,7 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_simple_kernel(const 
 // compiler emits plain LDS/STS with scaled addressing.
 // ------------------------------------------------------------------------------------------------
 constexpr int kBlockElems = 512;   // elements staged per warp between merges (16 groups of 32)
-constexpr int kDecodeBlocksPerSm = 7;
-template <int BYTES> struct Pair;
-template <> struct Pair<1> { using type = uint16_t; };
-template <> struct Pair<2> { using type = uint32_t; };
-template <> struct Pair<4> { using type = uint2; };
-template <> struct Pair<8> { using type = ulonglong2; };
-
-__device__ __forceinline__ uint16_t make_pair(uint8_t a, uint8_t b) { return static_cast<uint16_t>(a | (b << 8)); }
-__device__ __forceinline__ uint32_t make_pair(uint16_t a, uint16_t b) { return a | (static_cast<uint32_t>(b) << 16); }
-__device__ __forceinline__ uint2 make_pair(uint32_t a, uint32_t b) { return make_uint2(a, b); }
-__device__ __forceinline__ ulonglong2 make_pair(uint64_t a, uint64_t b) { return make_ulonglong2(a, b); }
-
+constexpr int kDecodeBlocksPerSm = 7;   // 56 warps of 32 registers: a tensor of 8192 tiles is resident all at once
 // State of one coded byte lane of the tile a warp is decoding.
 struct CodedLane {
   uint32_t state;       // this thread's rANS state
@@ -212,19 +201,18 @@ struct CodedLane {
   uint32_t stage;       // index (in bytes) of this thread's byte in the warp's staging block (block base + lane)
   int cursor;           // 2 * ((stream begin mod ring size) + words not yet consumed): byte offset just past the next word
   int refill_at;        // cursor value at or below which the chunk boundary has been crossed
-  int origin;           // 2 * (stream begin mod ring size)
   int chunk;            // payload chunk holding the next word to be read
 };
 
 // RAW_MASK >= 0 fixes the lane pattern at compile time (dead per-lane state disappears from the register file);
 // RAW_MASK < 0 reads it from the parameters.
 template <int NLANES, int RAW_MASK>
-__global__ void __launch_bounds__(kThreads, NLANES <= 2 ? kDecodeBlocksPerSm : (NLANES == 4 ? 5 : 1))
+__global__ void __launch_bounds__(kThreads, (NLANES <= 2 || (NLANES == 4 && RAW_MASK == 7)) ? kDecodeBlocksPerSm : (NLANES == 4 ? 3 : 1))
 tile_ans_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint32_t shared_tables[];
   __shared__ int constant_symbol[kMaxLanes];
+  __shared__ uint32_t raw_begins[kWarps][kMaxLanes];
   using element_t = typename Element<NLANES>::type;
-  using pair_t = typename Pair<NLANES>::type;
   uint16_t* const shared_words = reinterpret_cast<uint16_t*>(shared_tables);
   uint8_t* const shared_bytes = reinterpret_cast<uint8_t*>(shared_tables);
   const uint32_t table_size = 1u << p.prob_bits;
@@ -248,7 +236,8 @@ tile_ans_decode_kernel(const DecodeParams p) {
   const uint32_t rings_address = (shared_base + static_cast<uint32_t>(ans_lanes) * table_size * 4u + kRingBytes - 1u) & ~(kRingBytes - 1u);
   const uint32_t staging_at = (rings_address - shared_base) + static_cast<uint32_t>(kWarps * ans_lanes) * kRingBytes;  // in bytes
 
-  uint32_t raw_begin[NLANES];   // raw lanes: index of the stream's first 16-bit word in the payload
+  // raw lanes: index of the stream's first 16-bit word in the payload, kept in shared memory (read once per merge)
+  uint32_t* const raw_begin = raw_begins[warp];
   CodedLane coded[NLANES];
   int failure = 0;
   bool raw_near_end = false;    // a raw stream ends within 8 bytes of the payload's end: no over-reading loads there
@@ -261,17 +250,17 @@ tile_ans_decode_kernel(const DecodeParams p) {
     const uint32_t begin = is_raw ? p.offsets[stream] : __reduce_min_sync(0xFFFFFFFFu, p.offsets[stream]);
     const uint32_t end = is_raw ? p.offsets[stream + 1] : __reduce_min_sync(0xFFFFFFFFu, p.offsets[stream + 1]);
     if (end < begin || static_cast<int64_t>(end) > p.payload_words) failure = EP_STREAM_BAD_OFFSETS;
-    raw_begin[b] = begin;
+    if (lane == 0) raw_begin[b] = begin;
     const uint32_t rank = RAW_MASK >= 0 ? static_cast<uint32_t>(__builtin_popcount(~static_cast<uint32_t>(RAW_MASK) & ((1u << b) - 1u)))
                                         : p.lanes.ans_rank[b];
     CodedLane& c = coded[b];
     c.table = rank * table_size;
     c.ring = rings_address + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kRingBytes;
     c.stage = staging_at + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kBlockElems + lane;
-    c.origin = 2 * static_cast<int>(begin & (kRingWords - 1));
-    c.cursor = c.origin + 2 * static_cast<int>(end - begin);
+    const int origin = 2 * static_cast<int>(begin & (kRingWords - 1));
+    c.cursor = origin + 2 * static_cast<int>(end - begin);
     c.chunk = end > begin ? static_cast<int>((end - 1u) >> kChunkLog) : -1;
-    c.refill_at = c.origin + 2 * static_cast<int>((static_cast<int64_t>(c.chunk) << kChunkLog) - static_cast<int64_t>(begin));
+    c.refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(c.chunk) << kChunkLog) - static_cast<int64_t>(begin));
     c.state = kStateMin;
     if ((raw_mask >> b) & 1u) {
       if (!failure && end - begin != static_cast<uint32_t>((count + 1) >> 1)) failure = EP_STREAM_BAD_RAW_LENGTH;
@@ -395,8 +384,10 @@ tile_ans_decode_kernel(const DecodeParams p) {
           if ((raw_mask >> b) & 1u) {
             const uint32_t first_word = raw_begin[b] + (static_cast<uint32_t>(block_lo + in_block) >> 1);   // 16-bit units
             if (kGroup >= 4) {
-              const uint32_t* aligned = reinterpret_cast<const uint32_t*>(p.payload) + (first_word >> 1);
-              const uint32_t shift = (first_word & 1u) << 4;
+              // block_lo + in_block is a multiple of 4, so the stream's first word alone decides the shift
+              const uint32_t* aligned = reinterpret_cast<const uint32_t*>(p.payload) + (raw_begin[b] >> 1) +
+                                        (static_cast<uint32_t>(block_lo + in_block) >> 2);
+              const uint32_t shift = (raw_begin[b] & 1u) << 4;
               uint32_t loaded[kWords + 1];
 #pragma unroll
               for (int w = 0; w < kWords; ++w) loaded[w] = __ldg(aligned + w);
@@ -473,7 +464,9 @@ tile_ans_decode_kernel(const DecodeParams p) {
   for (int b = 0; b < NLANES; ++b) {
     if (((raw_mask >> b) & 1u) || constant_symbol[b] >= 0) continue;
     const bool dirty = __any_sync(0xFFFFFFFFu, coded[b].state != kStateMin);
-    const int left = (coded[b].cursor - coded[b].origin) / 2;
+    // words left = (cursor - 2 * (stream begin mod ring size)) / 2; the begin is read again rather than kept in a register
+    const uint32_t begin = __reduce_min_sync(0xFFFFFFFFu, p.offsets[static_cast<int64_t>(b) * p.tiles + tile]);
+    const int left = (coded[b].cursor - 2 * static_cast<int>(begin & (kRingWords - 1))) / 2;
     if (left < 0) failure = EP_STREAM_UNDERRUN;
     else if (left != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
   }
