@@ -17,6 +17,8 @@ def make_tensor(kind: str, rows: int, cols: int, device, seed: int = 1) -> torch
         return (x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn)
     if kind == "int8":
         return (x * 20).round().clamp(-127, 127).to(torch.int8)
+    if kind == "int8_narrow":
+        return (x * 2).round().clamp(-127, 127).to(torch.int8)
     if kind == "fp16":
         return (x * 0.02).to(torch.float16)
     if kind == "bf16":
@@ -41,6 +43,7 @@ def main() -> None:
     parser.add_argument("--rows", type=int, default=8192)
     parser.add_argument("--cols", type=int, default=8192)
     parser.add_argument("--reps", type=int, default=3)
+    parser.add_argument("--tile-elements", type=int, default=0, help="tile-ANS tile size (0 = automatic)")
     args = parser.parse_args()
 
     import entropack_b200 as ep
@@ -48,7 +51,7 @@ def main() -> None:
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     tensor = make_tensor(args.kind, args.rows, args.cols, device)
-    config = ep.TileANSConfig()
+    config = ep.TileANSConfig(tile_elements=args.tile_elements)
     if args.op.startswith("lattice"):
         config = ep.EntroPackLossyConfig(target_bpp=args.bpp)
     elif args.op.startswith("dfloat11"):
