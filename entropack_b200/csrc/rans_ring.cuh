@@ -1,4 +1,4 @@
-// Per-warp shared-memory ring of rANS payload words, filled by 16-byte cp.async copies.
+// Per-warp shared-memory ring of rANS payload words, filled by cp.async copies.
 //
 // A decoder warp consumes its stream back to front, at most 32 words per step. The ring holds four
 // chunks of 128 words and is indexed by (payload word index mod 512), so a word's ring slot never
@@ -28,13 +28,14 @@ __device__ __forceinline__ void ring_fetch_clipped(const uint16_t* __restrict__ 
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(target), "l"(payload + word), "r"(bytes) : "memory");
 }
 
-// Same for a chunk known to lie wholly inside the payload (any chunk below one already fetched).
+// Same for a chunk known to lie wholly inside the payload (any chunk below one already fetched): all
+// 32 threads copy 8 bytes each. `chunk` is the same in every thread, so the test does not split the warp.
 __device__ __forceinline__ void ring_fetch_interior(const uint16_t* __restrict__ payload, uint32_t ring_address, int chunk,
                                                     uint32_t lane) {
-  if (chunk >= 0 && lane < kChunkWords / 8) {
-    const uint32_t target = ring_address + static_cast<uint32_t>(((chunk & 3) * kChunkWords + lane * 8) * 2);
-    const uint16_t* source = payload + (static_cast<int64_t>(chunk) * kChunkWords + lane * 8);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(target), "l"(source) : "memory");
+  if (chunk >= 0) {
+    const uint32_t target = ring_address + static_cast<uint32_t>(((chunk & 3) * kChunkWords + lane * 4) * 2);
+    const uint16_t* source = payload + (static_cast<int64_t>(chunk) * kChunkWords + lane * 4);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(target), "l"(source) : "memory");
   }
 }
 
