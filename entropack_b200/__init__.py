@@ -5,7 +5,7 @@ byte layout of modelscope/entropack, so containers written by either side decode
 compute runs in hand-written CUDA kernels reached through a C ABI (``include/entropack_b200.h``);
 there is no CPU or eager execution path.
 """
-from .compression import CompressedTensor, CompressionFallbackWarning, compress, decompress
+from .compression import CompressedTensor, CompressionFallbackWarning, compress, decompress, decompress_many
 from .linear import CompressedFP8Linear, CompressedINT8Linear, CompressedLinear
 from .registry import DispatchError
 from .schemes import CompressionConfig, DFloat11Config, EntroPackLossyConfig, LatticeRANSConfig, RawConfig, TileANSConfig
@@ -15,5 +15,5 @@ __version__ = "0.1.0"
 __all__ = [
     "CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DFloat11Config", "DispatchError", "EntroPackLossyConfig",
     "LatticeRANSConfig", "RawConfig", "TileANSConfig",
-    "__version__", "compress", "decompress",
+    "__version__", "compress", "decompress", "decompress_many",
 ]

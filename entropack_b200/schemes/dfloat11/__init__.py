@@ -27,6 +27,11 @@ class DFloat11Scheme(Scheme):
     def validate_buffers(self, buffers, shape, dtype):
         validate_packed(buffers, shape)
 
+    def prime_host_metadata(self, buffers: dict) -> None:
+        from .format import parse_layout_cached
+
+        parse_layout_cached(buffers["layout"])
+
     def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: DFloat11Config) -> torch.Tensor:
         buffers = packed_buffers(packed, DFloat11Buffers)
         source = buffers.layout.device

@@ -39,6 +39,14 @@ class LatticeRANSScheme(Scheme):
     def validate_buffers(self, buffers, shape, dtype):
         validate_packed(buffers, tuple(shape), dtype)
 
+    def prime_host_metadata(self, buffers: dict) -> None:
+        from ..base import cached_parse
+        from .b200 import max_alphabet
+        from .format import parse_layout
+
+        cached_parse(buffers["layout"], parse_layout, "_lattice_rans_layout")
+        max_alphabet(packed_buffers(buffers, LatticeBuffers))
+
     def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: EntroPackLossyConfig) -> torch.Tensor:
         buffers = packed_buffers(packed, LatticeBuffers)
         source = buffers.layout.device

@@ -3,7 +3,7 @@ import torch
 
 from ..base import Scheme, packed_buffers, register_scheme
 from ..checks import prepare_weight
-from .format import OPTIONS_BY_DTYPE, PACKED_KEYS, TileANSConfig, TileBuffers, validate_packed
+from .format import OPTIONS_BY_DTYPE, PACKED_KEYS, TileANSConfig, TileBuffers, parse_layout_cached, validate_packed
 
 
 class TileANSScheme(Scheme):
@@ -33,6 +33,13 @@ class TileANSScheme(Scheme):
 
     def validate_buffers(self, buffers, shape, dtype):
         validate_packed(buffers, shape, dtype)
+
+    def prime_host_metadata(self, buffers: dict) -> None:
+        from .b200 import _lane_modes_host   # host-only helpers; importing them does not load the kernel library
+
+        packed = packed_buffers(buffers, TileBuffers)
+        parse_layout_cached(packed.layout)
+        _lane_modes_host(packed)
 
     def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: TileANSConfig) -> torch.Tensor:
         buffers = packed_buffers(packed, TileBuffers)

@@ -81,6 +81,30 @@ def test_container_is_byte_compatible(stem):
     container.scheme.validate_buffers(container.buffers, tuple(container.shape), container.encoded_dtype)
 
 
+
+def test_moved_container_keeps_parsed_header_and_host_metadata(monkeypatch):
+    """clone / detach / to reuse the parsed header (no second read of the blob) and carry the metadata a scheme
+    cached on the small buffers, so a container primed in host memory decodes without device-to-host reads."""
+    import entropack_b200 as ep
+    from entropack_b200.compression import compressed_tensor
+
+    record = load_golden("tile_ans_bf16")
+    container = ep.CompressedTensor.unpack(torch.from_numpy(record["blob"].copy()))
+    container.scheme.prime_host_metadata(container.buffers)
+    layout = container.buffers["layout"]
+    assert layout._tile_ans_layout[0] > 0 and layout._tile_ans_lane_modes.dtype == np.uint8
+
+    calls = []
+    original = compressed_tensor.parse_blob
+    monkeypatch.setattr(compressed_tensor, "parse_blob", lambda blob: calls.append(1) or original(blob))
+    for moved in (container.clone(), container.detach(), container.to("cpu", copy=True)):
+        assert moved.header == container.header and tuple(moved.shape) == tuple(container.shape)
+        assert torch.equal(moved.entropack_quant_state, container.entropack_quant_state)
+        assert moved.buffers["layout"]._tile_ans_layout == layout._tile_ans_layout
+        assert moved.buffers["layout"]._tile_ans_lane_modes is layout._tile_ans_lane_modes
+    assert not calls
+
+
 def test_no_cpu_fallback():
     import entropack_b200 as ep
 

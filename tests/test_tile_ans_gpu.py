@@ -131,3 +131,29 @@ def test_malformed_streams_are_reported_not_faulted():
     b200.decode(_to_device(bad), dtype=torch.uint8, error=error)
     assert int(error.item()) in (2, 3)
     torch.cuda.synchronize()
+
+
+def test_decompress_many_matches_decompress_and_fills_pinned_outputs():
+    """The pipelined bulk decode (three streams) returns what per-tensor decompress returns, for mixed schemes,
+    and leaves the same bytes in the pinned host outputs."""
+    import entropack_b200 as ep
+
+    generator = torch.Generator(device="cuda").manual_seed(11)
+    tensors = [
+        (torch.randn(300, 257, generator=generator, device="cuda") * 0.02).to(torch.bfloat16),
+        (torch.randn(64, 4096, generator=generator, device="cuda") * 20).round().clamp(-127, 127).to(torch.int8),
+        torch.randn(129, 512, generator=generator, device="cuda"),
+        (torch.randn(256, 512, generator=generator, device="cuda") * 0.02).to(torch.bfloat16),
+    ]
+    configs = [ep.TileANSConfig(), ep.TileANSConfig(), ep.TileANSConfig(), ep.DFloat11Config()]
+    containers = [ep.compress(t, c) for t, c in zip(tensors, configs)]
+    expected = [ep.decompress(c, cfg) for c, cfg in zip(containers, configs)]
+    blobs = [c.entropack_quant_state.cpu().pin_memory() for c in containers]
+    outputs = [torch.empty(t.numel() * t.element_size(), dtype=torch.uint8).pin_memory() for t in tensors]
+    for _ in range(2):   # the second pass reuses the streams
+        decoded = ep.decompress_many(blobs, configs, device="cuda", out=outputs)
+        for want, got, source, host in zip(expected, decoded, tensors, outputs):
+            assert got.dtype == want.dtype and got.shape == want.shape
+            assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+            assert torch.equal(got.view(torch.uint8), source.view(torch.uint8))
+            assert torch.equal(host, want.reshape(-1).view(torch.uint8).cpu())
