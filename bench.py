@@ -44,6 +44,11 @@ ROWS, COLS = 8192, 8192
 METRIC = "decode GB/s/GPU (HBM frac)"
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the four decode launches of one step, from one ncu capture per
+# tensor kind (profiles/tile_ans_decode_traffic.md): fp8 82.06 MB, int8 80.77 MB, fp16 213.04 MB, fp32 475.13 MB
+DRAM_TRAFFIC_BYTES = 851.0e6
+
+
 def make_tensor(kind: str, rows: int, cols: int, device) -> torch.Tensor:
     generator = torch.Generator(device=device).manual_seed(SEEDS[kind])
     x = torch.randn(rows, cols, generator=generator, device=device)
@@ -319,7 +324,7 @@ def run_b200(args) -> None:
                    "l2": "inputs larger than L2, plus a 512 MB flush between timed steps", "per_gpu_GBps": value / world,
                    "hbm_frac_of_" + peak_kind: value / world / peak},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_kind, "traffic": None, "kernel": "tile_ans_decode_kernel",
+                     "peak_source": peak_kind, "traffic": DRAM_TRAFFIC_BYTES, "kernel": "tile_ans_decode_kernel",
                      "per_launch_ms": dict(zip(KINDS, kernel_ms)),
                      "per_launch_GBps": {k: b / (ms * 1e-3) / 1e9 for k, b, ms in zip(KINDS, per_kind_bytes, kernel_ms)}},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
