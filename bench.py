@@ -377,6 +377,9 @@ def measure_others(ep, device, flush, reps: int) -> dict:
         total = 0.0
         for _ in range(reps):
             flush.zero_()
+            # a spin of about a millisecond lets the host queue the whole call behind it, so that the events
+            # bracket device work only and not the Python time between the two records
+            torch.cuda._sleep(2_000_000)
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record(stream)
             fn()

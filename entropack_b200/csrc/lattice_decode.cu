@@ -223,12 +223,14 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
   const uint32_t table_bytes = SHARED_TABLES ? kTables * table_size * 4u : 0u;
   const uint32_t ring = ((shared_base + table_bytes + kRingBytes - 1u) & ~(kRingBytes - 1u)) + static_cast<uint32_t>(warp) * kRingBytes;
 
-  for (int64_t tile = static_cast<int64_t>(blockIdx.x) * kDecodeWarps + warp; tile < p.tiles;
+  // tile t goes to block t mod grid: every SM gets its share even when there are fewer tiles than warp slots
+  for (int64_t tile = static_cast<int64_t>(warp) * gridDim.x + blockIdx.x; tile < p.tiles;
        tile += static_cast<int64_t>(gridDim.x) * kDecodeWarps) {
     const int64_t tile_begin = tile * p.tile_vectors;
     const int count = static_cast<int>(min(static_cast<int64_t>(p.tile_vectors), p.vectors - tile_begin));
-    const uint32_t begin = p.offsets[tile];
-    const uint32_t end = p.offsets[tile + 1];
+    // through a warp reduction, so that the cursor arithmetic and its tests are known to be warp-uniform
+    const uint32_t begin = __reduce_min_sync(0xFFFFFFFFu, p.offsets[tile]);
+    const uint32_t end = __reduce_min_sync(0xFFFFFFFFu, p.offsets[tile + 1]);
     if (end < begin || static_cast<int64_t>(end) > p.payload_words) {
       if (lane == 0) report(p.error, EP_STREAM_BAD_OFFSETS);
       continue;
@@ -272,7 +274,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       const int below = cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
       const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingBytes - 2u)) | ring), x, 0x5410);
       x = need ? merged : x;
-      cursor = __shfl_sync(0xFFFFFFFFu, below, 0);
+      cursor = __reduce_min_sync(0xFFFFFFFFu, below);   // thread 0's position, as a value the compiler knows is warp-uniform
       return symbol;
     };
     auto upkeep = [&]() {
@@ -400,8 +402,8 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   p.prob_bits = prob_bits;
   p.store_kind = store_kind;
   p.error = error_dev;
-  const int64_t wanted = (p.tiles + kDecodeWarps - 1) / kDecodeWarps;
-  const unsigned blocks = static_cast<unsigned>(wanted < kSmCount ? wanted : kSmCount);
+  // one persistent block per SM; with fewer tiles than SMs, one block per tile
+  const unsigned blocks = static_cast<unsigned>(p.tiles < kSmCount ? p.tiles : kSmCount);
   const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
   if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) {
     const size_t shared = (static_cast<size_t>(kTables) * sizeof(uint32_t) << prob_bits) + ring_bytes;

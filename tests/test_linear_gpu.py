@@ -38,8 +38,13 @@ def test_lossless_default_config_round_trips_exactly():
     layer = ep.CompressedLinear.from_linear(dense)
     assert layer.weight.compress_method == "dfloat11"
     assert torch.equal(layer.dequantize().view(torch.int16), dense.weight.view(torch.int16))
-    x = torch.randn(8, 512, device="cuda", dtype=torch.bfloat16)
-    assert torch.equal(layer(x), dense(x))
+    # The weights are bit-exact; the product is not compared bit for bit with cuBLAS, whose summation order differs:
+    # both must sit within one bf16 rounding step (2^-8 relative, 2^-7 allowed) of the fp32 product.
+    x = torch.randn(8, 512, device="cuda", dtype=torch.bfloat16, generator=torch.Generator(device="cuda").manual_seed(5))
+    exact = torch.nn.functional.linear(x.float(), dense.weight.float())
+    for produced in (layer(x), dense(x)):
+        assert produced.dtype == torch.bfloat16
+        assert bool(((produced.float() - exact).abs() <= 2.0 ** -7 * exact.abs() + 1e-3).all())
 
 
 def test_state_dict_round_trip_and_reference_checkpoint_loads():
