@@ -3,18 +3,19 @@
 // W is the weight the fused decode kernel has just written (K-contiguous rows, exactly the K-major B
 // operand); for the layer shapes in question it is still resident in the 126 MB L2 when this runs.
 //
-//   * M <= 16: `linear_small_m_kernel` -- a bandwidth kernel on CUDA cores. One warp per output feature
-//     streams that weight row once with 16-byte loads and keeps up to 16 dot products going against the
-//     activations staged in shared memory; a 5-step shuffle reduction finishes each.
-//   * M > 16: `linear_tcgen05_kernel` -- 128 x 128 output tile per block on the 5th-generation tensor cores.
-//     TMA (cp.async.bulk.tensor, 128-byte swizzle) fills a 4-stage shared-memory ring of 128 x 64 A and B
-//     tiles; one elected thread issues tcgen05.mma (M128 N128 K16, fp32 accumulators in TMEM) straight from
-//     shared memory; four warps read the accumulator back with tcgen05.ld, add the bias, round to bf16 and
-//     store. Every mbarrier wait is bounded: on a timeout the block raises the error word, frees its TMEM
-//     and returns.
+//   * M <= 16: `linear_stream_kernel` -- a bandwidth kernel: the weight goes from global memory straight
+//     into m16n8k16 fragments, eight features per block, K split over the block's eight warps.
+//   * M > 16: `linear_tcgen05_kernel` -- persistent blocks, 128 x TILE_N output tiles on the 5th-generation
+//     tensor cores. TMA (cp.async.bulk.tensor, 128-byte swizzle) fills a shared-memory ring of A and B
+//     tiles; one elected thread issues tcgen05.mma (M128 x TILE_N x K16, fp32 accumulators in TMEM) straight
+//     from shared memory; four warps read an accumulator back with tcgen05.ld, add the bias, round to bf16
+//     and store, while the MMA thread already fills the second accumulator buffer with the block's next
+//     tile. TILE_N (32..256) is chosen per call. Every mbarrier wait is bounded: on a timeout the block
+//     raises the error word, frees its TMEM and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "ep_common.cuh"
@@ -23,60 +24,77 @@ namespace ep {
 namespace {
 
 // ------------------------------------------------------------------------------------------------
-// small M
+// few rows of activations: the weight is streamed once, straight into MMA fragments
 // ------------------------------------------------------------------------------------------------
-constexpr int kSmallThreads = 256;
-constexpr int kSmallMaxM = 16;
+// With M <= 64 the product is a pass over the weight at memory speed, and the 128-row tcgen05 tile is the
+// wrong tool: its shortest instruction still reads 128 rows of A from shared memory, so a narrow tile is
+// bound by instruction issue, not by bytes. Here a block of eight warps owns eight output features. Each
+// warp takes every eighth 32-element slice of K: a thread loads 16 bytes (8 consecutive k) of its feature's
+// weight row -- the block's loads cover whole 64-byte runs of eight rows -- and the matching 16 bytes of
+// each activation row it needs (a few hundred KB in all, so they come from L1/L2), and feeds them to two
+// m16n8k16 tensor-core instructions. The instruction's k index is only a summation index, so "thread t
+// holds k = 8t .. 8t+7" is as good as the canonical fragment order as long as A and B agree. The eight
+// partial tiles meet in shared memory at the end. Nothing is staged, every load of a thread is independent
+// of the others, and the loop is unrolled so that a dozen 16-byte loads per thread are in flight.
+constexpr int kStreamThreads = 256;
+constexpr int kStreamWarps = kStreamThreads / 32;
+constexpr int kStreamMaxM = 16;
 
-template <int MROWS>
-__global__ void __launch_bounds__(kSmallThreads) linear_small_m_kernel(const __nv_bfloat16* __restrict__ x,
+__device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MTILES 16-row tiles of activations (M <= 16 * MTILES)
+template <int MTILES>
+__global__ void __launch_bounds__(kStreamThreads) linear_stream_kernel(const __nv_bfloat16* __restrict__ x,
                                                                        const __nv_bfloat16* __restrict__ w,
                                                                        const __nv_bfloat16* __restrict__ bias,
                                                                        __nv_bfloat16* __restrict__ y, int m, int n, int k) {
-  extern __shared__ __align__(16) __nv_bfloat16 staged_x[];  // [MROWS][k], rows beyond m are zero
-  for (int i = threadIdx.x * 8; i < MROWS * k; i += kSmallThreads * 8) {
-    const int row = i / k;
-    uint4 value = make_uint4(0, 0, 0, 0);
-    if (row < m) value = *reinterpret_cast<const uint4*>(x + i);
-    *reinterpret_cast<uint4*>(staged_x + i) = value;
+  __shared__ float partial[kStreamWarps][MTILES][4][32];
+  const uint32_t lane = lane_id();
+  const int warp = threadIdx.x >> 5;
+  const int group = lane >> 2;      // feature within the block's eight / activation row within a tile
+  const int quad = lane & 3;        // which 8 of the slice's 32 k
+  const int feature = blockIdx.x * 8 + group;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  const uint4* w_row = reinterpret_cast<const uint4*>(w + static_cast<int64_t>(min(feature, n - 1)) * k);
+  float acc[MTILES][4];
+#pragma unroll
+  for (int t = 0; t < MTILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+
+  const int slices = (k + 31) / 32;
+#pragma unroll 4
+  for (int slice = warp; slice < slices; slice += kStreamWarps) {
+    const int at = slice * 32 + quad * 8;                 // first k of this thread's 16 bytes
+    const bool inside = at < k;                           // k is a multiple of 8: a 16-byte piece is in or out as a whole
+    const uint4 b = inside && feature < n ? __ldg(w_row + (at >> 3)) : zero;
+#pragma unroll
+    for (int t = 0; t < MTILES; ++t) {
+      const int upper = t * 16 + group, lower = upper + 8;
+      const uint4 au = inside && upper < m ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(upper) * k + at)) : zero;
+      const uint4 al = inside && lower < m ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(lower) * k + at)) : zero;
+      mma_m16n8k16(acc[t], au.x, al.x, au.y, al.y, b.x, b.y);
+      mma_m16n8k16(acc[t], au.z, al.z, au.w, al.w, b.z, b.w);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < MTILES; ++t) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) partial[warp][t][j][lane] = acc[t][j];
   }
   __syncthreads();
-  const uint32_t lane = lane_id();
-  const int warps = kSmallThreads / 32;
-  for (int feature = blockIdx.x * warps + (threadIdx.x >> 5); feature < n; feature += gridDim.x * warps) {
-    float acc[MROWS];
+  // accumulator fragment: c0, c1 = (row group, columns 2 quad, 2 quad + 1), c2, c3 = the same columns of row group + 8
+  for (int item = threadIdx.x; item < MTILES * 4 * 32; item += kStreamThreads) {
+    const int t = item / 128, j = (item >> 5) & 3, holder = item & 31;
+    float total = 0.0f;
 #pragma unroll
-    for (int r = 0; r < MROWS; ++r) acc[r] = 0.0f;
-    const __nv_bfloat16* row = w + static_cast<int64_t>(feature) * k;
-    for (int c = lane * 8; c < k; c += 32 * 8) {
-      const uint4 packed = __ldg(reinterpret_cast<const uint4*>(row + c));
-      const __nv_bfloat162* wv = reinterpret_cast<const __nv_bfloat162*>(&packed);
-      float wf[8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 pair = __bfloat1622float2(wv[j]);
-        wf[2 * j] = pair.x;
-        wf[2 * j + 1] = pair.y;
-      }
-#pragma unroll
-      for (int r = 0; r < MROWS; ++r) {
-        const uint4 xp = *reinterpret_cast<const uint4*>(staged_x + r * k + c);
-        const __nv_bfloat162* xv = reinterpret_cast<const __nv_bfloat162*>(&xp);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 pair = __bfloat1622float2(xv[j]);
-          acc[r] = fmaf(wf[2 * j], pair.x, acc[r]);
-          acc[r] = fmaf(wf[2 * j + 1], pair.y, acc[r]);
-        }
-      }
-    }
-    const float b = bias ? __bfloat162float(bias[feature]) : 0.0f;
-#pragma unroll
-    for (int r = 0; r < MROWS; ++r) {
-      float total = acc[r];
-#pragma unroll
-      for (int step = 16; step > 0; step >>= 1) total += __shfl_xor_sync(0xFFFFFFFFu, total, step);
-      if (lane == 0 && r < m) y[static_cast<int64_t>(r) * n + feature] = __float2bfloat16_rn(total + b);
+    for (int v = 0; v < kStreamWarps; ++v) total += partial[v][t][j][holder];
+    const int row = t * 16 + (holder >> 2) + (j >= 2 ? 8 : 0);
+    const int column = blockIdx.x * 8 + (holder & 3) * 2 + (j & 1);
+    if (row < m && column < n) {
+      const float b = bias ? __bfloat162float(bias[column]) : 0.0f;
+      y[static_cast<int64_t>(row) * n + column] = __float2bfloat16_rn(total + b);
     }
   }
 }
@@ -85,14 +103,38 @@ __global__ void __launch_bounds__(kSmallThreads) linear_small_m_kernel(const __n
 // tcgen05 GEMM
 // ------------------------------------------------------------------------------------------------
 constexpr int kTileM = 128;
-constexpr int kTileN = 128;
 constexpr int kTileK = 64;               // 64 bf16 = one 128-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kTileBytes = kTileM * kTileK * 2;         // 16 KB, A and B tiles alike
+constexpr int kTileBytesA = kTileM * kTileK * 2;        // 16 KB
 constexpr int kGemmThreads = 192;        // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr uint32_t kTmemColumns = 128;   // fp32 accumulator: 128 lanes x 128 columns
 constexpr uint32_t kWaitLimit = 1u << 24;
 constexpr int kGemmTimeout = 9;          // value written to the error word when a wait runs out
+
+// The output tile is 128 rows by TILE_N columns, of which the first A_ROWS rows are real.
+//   * TILE_N = 256 is for large M: a 128 x 128 tile would need 8 KB of operands per 64-cycle MMA, all the
+//     shared-memory bandwidth there is, and twice the L2 traffic per flop.
+//   * Narrow tiles (32, 64) are for few rows of activations, where the weight is streamed once: the grid has
+//     to cover the SMs, and what counts is weight bytes in flight. There the TMA box of the activations is
+//     cut down to A_ROWS rows (16, 32 or 64) -- boxes that hang over the end of the tensor are slow to fill --
+//     which makes a stage small enough for a deep ring and three blocks per SM. The MMA still reads 128
+//     rows: the rest of its A operand is whatever follows in shared memory (the next A tiles, then the B
+//     tiles), and the accumulator rows that come out of it are never stored.
+template <int TILE_N, int A_ROWS> struct TileShape {
+  static_assert(TILE_N == 32 || TILE_N == 64 || TILE_N == 128 || TILE_N == 256, "accumulator columns: a power of two from 32 to 256");
+  static_assert(A_ROWS == 16 || A_ROWS == 32 || A_ROWS == 64 || A_ROWS == 128, "activation rows per box");
+  static constexpr int kBytesA = A_ROWS * kTileK * 2;
+  static constexpr int kBytesB = TILE_N * kTileK * 2;
+  static constexpr int kStageBytes = kBytesA + kBytesB;
+  static constexpr int kBlocksPerSm = A_ROWS < 128 ? 3 : 1;
+  static constexpr int kBudget = A_ROWS < 128 ? 72 * 1024 : 192 * 1024;
+  static constexpr int kStages = kBudget / kStageBytes < 16 ? kBudget / kStageBytes : 16;
+  static constexpr int kSharedBytes = kStages * kStageBytes + 1024;
+  static_assert(kStages >= 3, "the ring needs a few stages");
+  static_assert(kStages * kBytesB >= kTileBytesA - kBytesA, "the MMA's 128-row read of the last A tile must stay inside the B tiles");
+  static constexpr uint32_t kTmemColumns = TILE_N;
+  // Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major, N and M encoded /8 and /16.
+  static constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TILE_N >> 3) << 17) |
+                                           (static_cast<uint32_t>(kTileM >> 4) << 24);
+};
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -129,10 +171,6 @@ __device__ __forceinline__ uint64_t matrix_descriptor(uint32_t tile_address) {
   d |= static_cast<uint64_t>(2) << 61;            // 128-byte swizzle
   return d;
 }
-// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major, N and M encoded /8 and /16.
-constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kTileN >> 3) << 17) |
-                                  (static_cast<uint32_t>(kTileM >> 4) << 24);
-
 struct GemmParams {
   const __nv_bfloat16* bias;
   __nv_bfloat16* y;
@@ -140,34 +178,48 @@ struct GemmParams {
   int* error;
 };
 
-__global__ void __launch_bounds__(kGemmThreads, 1) linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
-                                                                         const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+template <int TILE_N, int A_ROWS>
+__global__ void __launch_bounds__(kGemmThreads, TileShape<TILE_N, A_ROWS>::kBlocksPerSm)
+linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+  using Shape = TileShape<TILE_N, A_ROWS>;
+  constexpr int kStages = Shape::kStages;
+  constexpr int kBytesA = Shape::kBytesA;
+  constexpr int kBytesB = Shape::kBytesB;
+  constexpr uint32_t kTmemColumns = Shape::kTmemColumns;
+  constexpr uint32_t kInstruction = Shape::kInstruction;
   extern __shared__ uint8_t raw_shared[];
   __shared__ __align__(8) uint64_t full[kStages];
   __shared__ __align__(8) uint64_t empty[kStages];
-  __shared__ __align__(8) uint64_t accumulator_ready;
+  __shared__ __align__(8) uint64_t accumulator_ready[2];   // MMA -> epilogue, one per accumulator buffer
+  __shared__ __align__(8) uint64_t accumulator_free[2];    // epilogue -> MMA
   __shared__ uint32_t tmem_base_holder;
   __shared__ int failed;
-  // tiles need 1024-byte alignment for the 128-byte swizzle pattern
-  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
+  // tiles need 1024-byte alignment for the 128-byte swizzle pattern; all A tiles come first, then all B tiles
+  uint8_t* tiles_a = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* tiles_b = tiles_a + kStages * kBytesA;
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
-  const int m0 = blockIdx.y * kTileM;
-  const int n0 = blockIdx.x * kTileN;
   const int k_steps = (p.k + kTileK - 1) / kTileK;
+  // The block is persistent: it takes output tiles blockIdx.x, blockIdx.x + gridDim.x, ... in an order that
+  // runs along N first, so the blocks at work at any moment share their rows of activations in L2.
+  const int n_tiles = (p.n + TILE_N - 1) / TILE_N;
+  const int total_tiles = n_tiles * ((p.m + kTileM - 1) / kTileM);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       barrier_init(&full[s], 1);
       barrier_init(&empty[s], 1);
     }
-    barrier_init(&accumulator_ready, 1);
+    for (int b = 0; b < 2; ++b) {
+      barrier_init(&accumulator_ready[b], 1);
+      barrier_init(&accumulator_free[b], 4);   // one arrival per epilogue warp
+    }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(shared_address(&tmem_base_holder)),
-                 "r"(kTmemColumns) : "memory");
+                 "r"(2u * kTmemColumns) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -176,50 +228,79 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_tcgen05_kernel(const _
   const uint32_t tmem_base = tmem_base_holder;
 
   if (warp == 0 && lane == 0) {
-    // ---- producer: one thread feeds the ring
-    for (int step = 0; step < k_steps; ++step) {
-      const int s = step % kStages;
-      if (step >= kStages && !barrier_wait(&empty[s], ((step / kStages) - 1) & 1)) {
+    // ---- producer: one thread feeds the ring, straight through tile boundaries
+    int step = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x) {
+      const int m0 = (tile / n_tiles) * kTileM;
+      const int n0 = (tile % n_tiles) * TILE_N;
+      for (int ks = 0; ks < k_steps; ++ks, ++step) {
+        const int s = step % kStages;
+        if (step >= kStages && !barrier_wait(&empty[s], ((step / kStages) - 1) & 1)) {
+          failed = 1;
+          break;
+        }
+        barrier_expect(&full[s], kBytesA + kBytesB);
+        tma_load_2d(tiles_a + s * kBytesA, &map_x, &full[s], ks * kTileK, m0);
+        tma_load_2d(tiles_b + s * kBytesB, &map_w, &full[s], ks * kTileK, n0);
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer: four K16 instructions per stage into the tile's accumulator buffer, stage handed back after
+    int step = 0;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && !failed; tile += gridDim.x, ++local) {
+      const int buffer = local & 1;
+      // the epilogue must have drained this buffer (two tiles ago); a fresh barrier passes the first two waits
+      if (!barrier_wait(&accumulator_free[buffer], ((local >> 1) & 1) ^ 1)) {
         failed = 1;
         break;
       }
-      barrier_expect(&full[s], 2 * kTileBytes);
-      tma_load_2d(tiles + s * 2 * kTileBytes, &map_x, &full[s], step * kTileK, m0);
-      tma_load_2d(tiles + s * 2 * kTileBytes + kTileBytes, &map_w, &full[s], step * kTileK, n0);
-    }
-  } else if (warp == 1 && lane == 0) {
-    // ---- MMA issuer: four K16 instructions per stage, then hand the stage back
-    bool ok = true;
-    for (int step = 0; step < k_steps && ok; ++step) {
-      const int s = step % kStages;
-      ok = barrier_wait(&full[s], (step / kStages) & 1);
-      if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t a = matrix_descriptor(shared_address(tiles + s * 2 * kTileBytes));
-      const uint64_t b = matrix_descriptor(shared_address(tiles + s * 2 * kTileBytes + kTileBytes));
+      const uint32_t accumulator = tmem_base + static_cast<uint32_t>(buffer) * kTmemColumns;
+      bool ok = true;
+      for (int ks = 0; ks < k_steps; ++ks, ++step) {
+        const int s = step % kStages;
+        ok = barrier_wait(&full[s], (step / kStages) & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t a = matrix_descriptor(shared_address(tiles_a + s * kBytesA));
+        const uint64_t b = matrix_descriptor(shared_address(tiles_b + s * kBytesB));
 #pragma unroll
-      for (int kk = 0; kk < kTileK / 16; ++kk) {
-        const uint32_t accumulate = (step | kk) ? 1u : 0u;
-        asm volatile(
-            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-            ::"r"(tmem_base), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+        for (int kk = 0; kk < kTileK / 16; ++kk) {
+          const uint32_t accumulate = (ks | kk) ? 1u : 0u;
+          asm volatile(
+              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+              ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(shared_address(&empty[s])) : "memory");
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(shared_address(&empty[s])) : "memory");
+      if (!ok) failed = 1;
+      // arrives once every MMA issued so far has completed (also on the failure path, so the epilogue wakes)
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                   ::"r"(shared_address(&accumulator_ready[buffer])) : "memory");
+      if (!ok) break;
     }
-    if (!ok) failed = 1;
-    // arrives once every MMA issued so far has completed (also on the failure path, so the epilogue wakes)
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(shared_address(&accumulator_ready)) : "memory");
   } else if (warp >= 2) {
-    // ---- epilogue: each warp owns the 32 TMEM lanes of its quadrant (warp index mod 4)
+    // ---- epilogue: each warp owns the 32 TMEM lanes of its quadrant (warp index mod 4); it drains one buffer
+    // while the MMA issuer fills the other
     const int quadrant = warp & 3;
-    const bool ready = barrier_wait(&accumulator_ready, 0);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int row = m0 + quadrant * 32 + static_cast<int>(lane);
-    if (ready && !failed) {
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int buffer = local & 1;
+      const int m0 = (tile / n_tiles) * kTileM;
+      const int n0 = (tile % n_tiles) * TILE_N;
+      const bool ready = barrier_wait(&accumulator_ready[buffer], (local >> 1) & 1);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!ready || failed) {
+        if (lane == 0) failed = 1;
+        break;
+      }
+      const int row = m0 + quadrant * 32 + static_cast<int>(lane);
 #pragma unroll 1
-      for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+      for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
         uint32_t v[32];
-        const uint32_t address = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) + static_cast<uint32_t>(chunk * 32);
+        const uint32_t address = tmem_base + static_cast<uint32_t>(buffer) * kTmemColumns +
+                                 (static_cast<uint32_t>(quadrant * 32) << 16) + static_cast<uint32_t>(chunk * 32);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
             "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
@@ -229,6 +310,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_tcgen05_kernel(const _
               "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
             : "r"(address) : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (chunk == TILE_N / 32 - 1) {
+          // the whole buffer is in registers: hand it back before the stores
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(shared_address(&accumulator_free[buffer])) : "memory");
+          }
+        }
         const int col = n0 + chunk * 32;
         if (row < p.m && col < p.n) {
           __nv_bfloat16* out = p.y + static_cast<int64_t>(row) * p.n + col;
@@ -254,14 +343,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) linear_tcgen05_kernel(const _
           }
         }
       }
-    } else if (lane == 0) {
-      failed = 1;
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * kTmemColumns) : "memory");
   }
   if (threadIdx.x == 0 && failed) report(p.error, kGemmTimeout);
 }
@@ -291,32 +378,46 @@ EncodeTiled tensor_map_encoder() {
   return encoder;
 }
 
-// rows x k bf16, row-major; boxes of 128 rows x 64 columns, 128-byte swizzle, zero fill outside the tensor
-bool make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k) {
+// rows x k bf16, row-major; boxes of box_rows rows x 64 columns, 128-byte swizzle, zero fill outside the tensor
+bool make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
   EncodeTiled encode = tensor_map_encoder();
   if (!encode) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {kTileK, kTileM};
+  const cuuint32_t box[2] = {kTileK, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t element_strides[2] = {1, 1};
   return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MROWS>
-int launch_small(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* bias, __nv_bfloat16* y, int m, int n, int k,
-                 cudaStream_t s) {
-  const size_t shared = static_cast<size_t>(MROWS) * k * sizeof(__nv_bfloat16);
-  if (shared > 200 * 1024) return EP_ERR_UNSUPPORTED;
-  if (shared > 48 * 1024) {
-    EP_CUDA_CHECK(cudaFuncSetAttribute(linear_small_m_kernel<MROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
-  }
-  const int warps = kSmallThreads / 32;
-  const int wanted = (n + warps - 1) / warps;
-  const int blocks = wanted < kSmCount * 2 ? wanted : kSmCount * 2;
-  linear_small_m_kernel<MROWS><<<blocks, kSmallThreads, shared, s>>>(x, w, bias, y, m, n, k);
-  return check_launch("linear_small_m_kernel");
+template <int MTILES>
+int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* bias, __nv_bfloat16* y, int m, int n, int k,
+                  cudaStream_t s) {
+  linear_stream_kernel<MTILES><<<(n + 7) / 8, kStreamThreads, 0, s>>>(x, w, bias, y, m, n, k);
+  return check_launch("linear_stream_kernel");
+}
+
+template <int TILE_N, int A_ROWS>
+int launch_tcgen05(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
+  using Shape = TileShape<TILE_N, A_ROWS>;
+  CUtensorMap map_x, map_w;
+  if (!make_tile_map(&map_x, x_dev, p.m, p.k, A_ROWS) || !make_tile_map(&map_w, weight_dev, p.n, p.k, TILE_N)) return EP_ERR_UNSUPPORTED;
+  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_kernel<TILE_N, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Shape::kSharedBytes));
+  const int64_t tiles = static_cast<int64_t>((p.n + TILE_N - 1) / TILE_N) * ((p.m + kTileM - 1) / kTileM);
+  const int64_t resident = static_cast<int64_t>(kSmCount) * Shape::kBlocksPerSm;
+  const unsigned grid = static_cast<unsigned>(tiles < resident ? tiles : resident);
+  linear_tcgen05_kernel<TILE_N, A_ROWS><<<grid, kGemmThreads, Shape::kSharedBytes, s>>>(map_x, map_w, p);
+  return EP_OK;
+}
+
+template <int TILE_N>
+int launch_narrow(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
+  if (p.m <= 16) return launch_tcgen05<TILE_N, 16>(x_dev, weight_dev, p, s);
+  if (p.m <= 32) return launch_tcgen05<TILE_N, 32>(x_dev, weight_dev, p, s);
+  if (p.m <= 64) return launch_tcgen05<TILE_N, 64>(x_dev, weight_dev, p, s);
+  return launch_tcgen05<TILE_N, 128>(x_dev, weight_dev, p, s);
 }
 
 }  // namespace
@@ -340,16 +441,7 @@ extern "C" int ep_linear_forward(const void* x_dev, const void* weight_dev, cons
   const auto* bias = static_cast<const __nv_bfloat16*>(bias_dev);
   auto* y = static_cast<__nv_bfloat16*>(y_dev);
   const int mi = static_cast<int>(m), ni = static_cast<int>(n), ki = static_cast<int>(k);
-  if (m <= kSmallMaxM) {
-    int rc = EP_ERR_UNSUPPORTED;
-    if (m == 1) rc = launch_small<1>(x, w, bias, y, mi, ni, ki, s);
-    else if (m <= 4) rc = launch_small<4>(x, w, bias, y, mi, ni, ki, s);
-    else if (m <= 8) rc = launch_small<8>(x, w, bias, y, mi, ni, ki, s);
-    else rc = launch_small<16>(x, w, bias, y, mi, ni, ki, s);
-    if (rc != EP_ERR_UNSUPPORTED) return rc;   // very wide K does not fit shared memory: use the tensor-core kernel
-  }
-  CUtensorMap map_x, map_w;
-  if (!make_tile_map(&map_x, x_dev, m, k) || !make_tile_map(&map_w, weight_dev, n, k)) return EP_ERR_UNSUPPORTED;
+  if (m <= kStreamMaxM) return launch_stream<1>(x, w, bias, y, mi, ni, ki, s);
   GemmParams p;
   p.bias = bias;
   p.y = y;
@@ -357,9 +449,31 @@ extern "C" int ep_linear_forward(const void* x_dev, const void* weight_dev, cons
   p.n = ni;
   p.k = ki;
   p.error = error_dev;
-  const size_t shared = static_cast<size_t>(kStages) * 2 * kTileBytes + 1024;
-  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
-  const dim3 grid(static_cast<unsigned>((n + kTileN - 1) / kTileN), static_cast<unsigned>((m + kTileM - 1) / kTileM));
-  linear_tcgen05_kernel<<<grid, kGemmThreads, shared, s>>>(map_x, map_w, p);
+  // Tile width. A block's time goes with the bytes it pulls through L2 per K step (activation box + weight box);
+  // blocks beyond what the SMs hold at once run in further rounds. Take the width with the least rounds x bytes.
+  const int64_t row_tiles = (m + kTileM - 1) / kTileM;
+  const int a_rows = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
+  int tile_n = 32;
+  int64_t best = -1;
+  for (int candidate = 256; candidate >= 32; candidate >>= 1) {
+    const bool narrow = candidate <= 64;
+    const int box_a = narrow ? a_rows : 128;
+    const int64_t blocks = row_tiles * ((n + candidate - 1) / candidate);
+    const int64_t resident = static_cast<int64_t>(kSmCount) * (box_a < 128 ? 3 : 1);
+    const int64_t cost = ((blocks + resident - 1) / resident) * (box_a + candidate);
+    if (best < 0 || cost < best) {
+      best = cost;
+      tile_n = candidate;
+    }
+  }
+  int rc = EP_ERR_UNSUPPORTED;
+  switch (tile_n) {
+    case 256: rc = launch_tcgen05<256, 128>(x_dev, weight_dev, p, s); break;
+    case 128: rc = launch_tcgen05<128, 128>(x_dev, weight_dev, p, s); break;
+    case 64: rc = launch_narrow<64>(x_dev, weight_dev, p, s); break;
+    case 32: rc = launch_narrow<32>(x_dev, weight_dev, p, s); break;
+    default: return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (rc != EP_OK) return rc;
   return check_launch("linear_tcgen05_kernel");
 }
