@@ -37,19 +37,30 @@ def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--op", default="tile_ans_decode",
                         choices=("tile_ans_decode", "tile_ans_encode", "lattice_decode", "lattice_encode", "dfloat11_decode",
-                                 "dfloat11_encode"))
+                                 "dfloat11_encode", "linear"))
     parser.add_argument("--bpp", type=float, default=4.0)
     parser.add_argument("--kind", default="fp8_e4m3")
     parser.add_argument("--rows", type=int, default=8192)
     parser.add_argument("--cols", type=int, default=8192)
     parser.add_argument("--reps", type=int, default=3)
     parser.add_argument("--tile-elements", type=int, default=0, help="tile-ANS tile size (0 = automatic)")
+    parser.add_argument("--inner", type=int, default=3840, help="linear: K (rows = tokens M, cols = features N)")
     args = parser.parse_args()
 
     import entropack_b200 as ep
 
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
+    if args.op == "linear":
+        from entropack_b200.linear import linear_forward
+
+        weight = make_tensor("bf16", args.cols, args.inner, device)
+        tokens = make_tensor("bf16", args.rows, args.inner, device, seed=2) * 50
+        for _ in range(args.reps):
+            out = linear_forward(tokens, weight)
+        torch.cuda.synchronize()
+        print(f"linear M={args.rows} N={args.cols} K={args.inner}: {args.reps} launches")
+        return
     tensor = make_tensor(args.kind, args.rows, args.cols, device)
     config = ep.TileANSConfig(tile_elements=args.tile_elements)
     if args.op.startswith("lattice"):
