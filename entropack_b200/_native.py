@@ -54,6 +54,10 @@ _PROTOTYPES = {
     "ep_lattice_coded_bytes": [_ptr, _ptr, _i64, _i32, _i64, _ptr],
     "ep_lattice_tables": [_ptr, _ptr, _i64, _i32, _ptr, _ptr, _i64, _ptr],
     "ep_lattice_refit_scales": [_ptr, _i32, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr, _ptr],
+    "ep_lattice_refit_rows": [_ptr, _i32, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr, _ptr, _ptr],
+    "ep_lattice_minmax": [_ptr, _ptr, _i64, _ptr, _ptr],
+    "ep_lattice_row_rates": [_ptr, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _ptr, _ptr],
+    "ep_lattice_select_rows": [_ptr, _ptr, _i32, _ptr, _i64, _i64, _ptr, _ptr, _ptr],
     "ep_lattice_encode_scratch_words": [_i64, _i64],
     "ep_lattice_encode": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _i32, _i64, _ptr, _ptr, _ptr, _ptr, _ptr],
 }

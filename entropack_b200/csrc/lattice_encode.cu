@@ -246,11 +246,11 @@ __global__ void __launch_bounds__(kThreads) histogram_kernel(const int16_t* __re
 template <typename T>
 __global__ void __launch_bounds__(kThreads) refit_kernel(const T* __restrict__ weight, const int16_t* __restrict__ fields,
                                                          const uint8_t* __restrict__ cosets, const float* __restrict__ rms, float s,
-                                                         int64_t cols, float* __restrict__ scales) {
+                                                         int64_t cols, float* __restrict__ scales, float* __restrict__ row_sse) {
   __shared__ float partial[kThreads];
   const int64_t row = blockIdx.x;
   const int vecs_per_row = static_cast<int>(cols >> 3);
-  float numerator = 0.0f, denominator = 0.0f;
+  float numerator = 0.0f, denominator = 0.0f, energy = 0.0f;
   for (int v = threadIdx.x; v < vecs_per_row; v += kThreads) {
     const int64_t vector = row * vecs_per_row + v;
     float x[8];
@@ -271,15 +271,125 @@ __global__ void __launch_bounds__(kThreads) refit_kernel(const T* __restrict__ w
       const float point = __fadd_rn(static_cast<float>(z[j]), half);
       numerator = __fadd_rn(numerator, __fmul_rn(x[j], point));
       denominator = __fadd_rn(denominator, __fmul_rn(point, point));
+      energy = __fadd_rn(energy, __fmul_rn(x[j], x[j]));
     }
   }
   const float num = tree_reduce(partial, numerator);
   const float den = tree_reduce(partial, denominator);
+  const float total_energy = row_sse ? tree_reduce(partial, energy) : 0.0f;   // same for the whole block
   if (threadIdx.x == 0) {
     const float fallback = __fmul_rn(s, rms[row]);
     float fitted = den > 0.0f ? __fdiv_rn(num, den) : fallback;
     if (!(isfinite(fitted) && fitted > 0.0f)) fitted = fallback;
     scales[row] = fitted;
+    // squared error of the row at its least-squares scale: |x|^2 - (x.p)^2 / |p|^2, never below zero
+    if (row_sse) row_sse[row] = den > 0.0f ? fmaxf(__fsub_rn(total_energy, __fdiv_rn(__fmul_rn(num, num), den)), 0.0f) : total_energy;
+  }
+}
+
+// ---- per-row rate-distortion refinement --------------------------------------------------------------
+// Per-stream bounds of symbols that are already quantised (a mixture of rows taken from several candidate
+// quantisations has no quantiser pass of its own to collect them).
+__global__ void __launch_bounds__(kThreads) minmax_kernel(const int16_t* __restrict__ fields, const uint8_t* __restrict__ cosets,
+                                                          int64_t vectors, int* __restrict__ minmax) {
+  __shared__ int block_minmax[kMinMaxLen];
+  for (int t = threadIdx.x; t < kMinMaxLen; t += kThreads) block_minmax[t] = (t < 32 && !(t & 1)) ? kIntMax : (t < 32 ? kIntMin : 0);
+  __syncthreads();
+  int low[2][8], high[2][8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    low[0][j] = low[1][j] = kIntMax;
+    high[0][j] = high[1][j] = kIntMin;
+  }
+  int any_coset = 0;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; v < vectors; v += stride) {
+    const int c = cosets[v] ? 1 : 0;
+    any_coset |= c;
+    const uint4 raw = *reinterpret_cast<const uint4*>(fields + v * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int value = static_cast<int16_t>((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
+      if (c) {
+        low[1][j] = min(low[1][j], value);
+        high[1][j] = max(high[1][j], value);
+      } else {
+        low[0][j] = min(low[0][j], value);
+        high[0][j] = max(high[0][j], value);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      if (low[c][j] != kIntMax) {
+        atomicMin(&block_minmax[(j * 2 + c) * 2], low[c][j]);
+        atomicMax(&block_minmax[(j * 2 + c) * 2 + 1], high[c][j]);
+      }
+    }
+  }
+  if (any_coset) atomicMax(&block_minmax[32], 1);
+  __syncthreads();
+  for (int t = threadIdx.x; t < kMinMaxLen; t += kThreads) {
+    const int value = block_minmax[t];
+    if (t < 32 && !(t & 1)) {
+      if (value != kIntMax) atomicMin(&minmax[t], value);
+    } else if (value != (t < 32 ? kIntMin : 0)) {
+      atomicMax(&minmax[t], value);
+    }
+  }
+}
+
+// rates[row] = sum over the row's vectors of the modelled bits of its nine symbols: the coset from table 0,
+// field f given coset c from table 1 + 2 f + c (rdo.row_rates, entropack/schemes/lattice_rans/rdo.py:70-84).
+// `values` holds the 17 tables back to back, table t at offsets[t] with its first entry standing for symbol
+// minima[t]. A vector's nine terms are added in stream order, as in the reference; vectors are then summed in
+// the fixed order of the other row reductions.
+__global__ void __launch_bounds__(kThreads) row_rates_kernel(const int16_t* __restrict__ fields, const uint8_t* __restrict__ cosets,
+                                                             int vecs_per_row, const float* __restrict__ values,
+                                                             const int* __restrict__ offsets, const int* __restrict__ minima,
+                                                             float* __restrict__ rates) {
+  __shared__ float partial[kThreads];
+  __shared__ int offset[kTables + 1];
+  __shared__ int minimum[kTables];
+  if (threadIdx.x <= kTables) offset[threadIdx.x] = offsets[threadIdx.x];
+  if (threadIdx.x < kTables) minimum[threadIdx.x] = minima[threadIdx.x];
+  __syncthreads();
+  const int64_t row = blockIdx.x;
+  float acc = 0.0f;
+  for (int v = threadIdx.x; v < vecs_per_row; v += kThreads) {
+    const int64_t vector = row * vecs_per_row + v;
+    const int c = cosets[vector] ? 1 : 0;
+    const uint4 raw = *reinterpret_cast<const uint4*>(fields + vector * 8);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float rate = __ldg(values + offset[0] + min(c, offset[1] - offset[0] - 1));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int value = static_cast<int16_t>((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
+      const int table = 1 + 2 * j + c;
+      const int width = offset[table + 1] - offset[table];
+      const int index = max(0, min(value - minimum[table], width - 1));   // the tables span every candidate's range
+      rate = __fadd_rn(rate, width > 0 ? __ldg(values + offset[table] + index) : 0.0f);
+    }
+    acc = __fadd_rn(acc, rate);
+  }
+  const float total = tree_reduce(partial, acc);
+  if (threadIdx.x == 0) rates[row] = total;
+}
+
+// Row r of the output is row r of candidate choice[r] (rdo.select_candidate_rows, rdo.py:103-120).
+__global__ void __launch_bounds__(kThreads) select_rows_kernel(const int16_t* const* __restrict__ candidate_fields,
+                                                               const uint8_t* const* __restrict__ candidate_cosets, int candidates,
+                                                               const int* __restrict__ choice, int64_t vectors, int vecs_per_row,
+                                                               int16_t* __restrict__ fields, uint8_t* __restrict__ cosets) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; v < vectors; v += stride) {
+    const uint32_t row = static_cast<uint32_t>(v) / static_cast<uint32_t>(vecs_per_row);
+    const int k = max(0, min(choice[row], candidates - 1));
+    *reinterpret_cast<uint4*>(fields + v * 8) = *reinterpret_cast<const uint4*>(candidate_fields[k] + v * 8);
+    cosets[v] = candidate_cosets[k][v];
   }
 }
 
@@ -477,12 +587,72 @@ extern "C" int ep_lattice_refit_scales(const void* weight_dev, int is_bf16, cons
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (is_bf16) {
     refit_kernel<<<static_cast<unsigned>(rows), kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(weight_dev), fields_dev, cosets_dev,
-                                                                  rms_dev, scale, cols, scales_dev);
+                                                                  rms_dev, scale, cols, scales_dev, nullptr);
   } else {
     refit_kernel<<<static_cast<unsigned>(rows), kThreads, 0, s>>>(static_cast<const float*>(weight_dev), fields_dev, cosets_dev, rms_dev,
-                                                                  scale, cols, scales_dev);
+                                                                  scale, cols, scales_dev, nullptr);
   }
   return check_launch("refit_kernel");
+}
+
+extern "C" int ep_lattice_refit_rows(const void* weight_dev, int is_bf16, const int16_t* fields_dev, const uint8_t* cosets_dev,
+                                     const float* rms_dev, float scale, int64_t rows, int64_t cols, float* scales_dev,
+                                     float* row_sse_dev, ep_stream_t stream) {
+  const int rc = check_matrix(weight_dev, rows, cols);
+  if (rc != EP_OK) return rc;
+  if (!fields_dev || !cosets_dev || !rms_dev || !scales_dev || !row_sse_dev) return EP_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (is_bf16) {
+    refit_kernel<<<static_cast<unsigned>(rows), kThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(weight_dev), fields_dev, cosets_dev,
+                                                                  rms_dev, scale, cols, scales_dev, row_sse_dev);
+  } else {
+    refit_kernel<<<static_cast<unsigned>(rows), kThreads, 0, s>>>(static_cast<const float*>(weight_dev), fields_dev, cosets_dev, rms_dev,
+                                                                  scale, cols, scales_dev, row_sse_dev);
+  }
+  return check_launch("refit_kernel");
+}
+
+extern "C" int ep_lattice_minmax(const int16_t* fields_dev, const uint8_t* cosets_dev, int64_t vectors, int32_t* minmax_dev,
+                                 ep_stream_t stream) {
+  if (!fields_dev || !cosets_dev || !minmax_dev || vectors <= 0) return EP_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(fields_dev) & 15u) return EP_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int initial[kMinMaxLen];
+  for (int t = 0; t < kMinMaxLen; ++t) initial[t] = (t < 32 && !(t & 1)) ? kIntMax : (t < 32 ? kIntMin : 0);
+  EP_CUDA_CHECK(cudaMemcpyAsync(minmax_dev, initial, sizeof(initial), cudaMemcpyHostToDevice, s));
+  const int64_t wanted = (vectors + kThreads - 1) / kThreads;
+  const unsigned blocks = static_cast<unsigned>(wanted < kSmCount * 8 ? wanted : kSmCount * 8);
+  minmax_kernel<<<blocks, kThreads, 0, s>>>(fields_dev, cosets_dev, vectors, minmax_dev);
+  return check_launch("minmax_kernel");
+}
+
+extern "C" int ep_lattice_row_rates(const int16_t* fields_dev, const uint8_t* cosets_dev, int64_t rows, int64_t cols,
+                                    const float* rate_values_dev, const int32_t* rate_offsets_dev, const int32_t* rate_minima_dev,
+                                    float* rates_dev, ep_stream_t stream) {
+  if (!fields_dev || !cosets_dev || !rate_values_dev || !rate_offsets_dev || !rate_minima_dev || !rates_dev || rows <= 0 ||
+      cols <= 0 || (cols & 7) != 0 || rows > 0x7FFFFFFF || cols / 8 > 0x7FFFFFFF) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (reinterpret_cast<uintptr_t>(fields_dev) & 15u) return EP_ERR_INVALID_ARGUMENT;
+  row_rates_kernel<<<static_cast<unsigned>(rows), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      fields_dev, cosets_dev, static_cast<int>(cols / 8), rate_values_dev, rate_offsets_dev, rate_minima_dev, rates_dev);
+  return check_launch("row_rates_kernel");
+}
+
+extern "C" int ep_lattice_select_rows(const int16_t* const* candidate_fields_dev, const uint8_t* const* candidate_cosets_dev,
+                                      int candidates, const int32_t* choice_dev, int64_t rows, int64_t cols, int16_t* fields_dev,
+                                      uint8_t* cosets_dev, ep_stream_t stream) {
+  if (!candidate_fields_dev || !candidate_cosets_dev || candidates <= 0 || !choice_dev || !fields_dev || !cosets_dev || rows <= 0 ||
+      cols <= 0 || (cols & 7) != 0 || cols / 8 > 0x7FFFFFFF) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  const int64_t vectors = rows * (cols / 8);
+  if (vectors >= (int64_t(1) << 32)) return EP_ERR_TOO_LARGE;
+  const int64_t wanted = (vectors + kThreads - 1) / kThreads;
+  const unsigned blocks = static_cast<unsigned>(wanted < kSmCount * 8 ? wanted : kSmCount * 8);
+  select_rows_kernel<<<blocks, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      candidate_fields_dev, candidate_cosets_dev, candidates, choice_dev, vectors, static_cast<int>(cols / 8), fields_dev, cosets_dev);
+  return check_launch("select_rows_kernel");
 }
 
 extern "C" int64_t ep_lattice_encode_scratch_words(int64_t vectors, int64_t tile_elements) {

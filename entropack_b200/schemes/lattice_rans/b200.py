@@ -63,5 +63,5 @@ def encode(weight, *, target_bpp, prob_bits, tile_elements, row_rdo_iterations, 
 
     return encoder.encode(
         weight, target_bpp=float(target_bpp), prob_bits=prob_bits, tile_elements=int(tile_elements),
-        row_rdo_iterations=int(row_rdo_iterations), scale_search_iterations=int(scale_search_iterations),
-        scale_search_max_vectors=int(scale_search_max_vectors))
+        row_rdo_iterations=int(row_rdo_iterations), row_rdo_candidates=int(row_rdo_candidates),
+        scale_search_iterations=int(scale_search_iterations), scale_search_max_vectors=int(scale_search_max_vectors))

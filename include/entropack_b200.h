@@ -190,6 +190,32 @@ int ep_lattice_tables(const int32_t* minmax_host, const int32_t* bins_host, int6
 int ep_lattice_refit_scales(const void* weight_dev, int is_bf16, const int16_t* fields_dev, const uint8_t* cosets_dev,
                             const float* rms_dev, float scale, int64_t rows, int64_t cols, float* scales_dev, ep_stream_t stream);
 
+/* The same fit, plus row_sse_dev[row] = |x|^2 - (x.p)^2 / |p|^2 clamped at zero (|x|^2 when the row
+ * quantised to zero): _refit_row_scales, entropack/schemes/lattice_rans/eager.py:209-224. */
+int ep_lattice_refit_rows(const void* weight_dev, int is_bf16, const int16_t* fields_dev, const uint8_t* cosets_dev,
+                          const float* rms_dev, float scale, int64_t rows, int64_t cols, float* scales_dev, float* row_sse_dev,
+                          ep_stream_t stream);
+
+/* --- per-row rate-distortion refinement (row_rdo_iterations > 0): the device side of
+ * entropack/schemes/lattice_rans/rdo.py:70-162. --- */
+
+/* Min/max record (same 34 words as ep_lattice_quantize writes) of symbols that are already quantised. */
+int ep_lattice_minmax(const int16_t* fields_dev, const uint8_t* cosets_dev, int64_t vectors, int32_t* minmax_dev,
+                      ep_stream_t stream);
+
+/* rates_dev[row] = modelled bits of the row's symbols under a 17-table rate model: table t starts at
+ * rate_offsets_dev[t] (18 entries) inside rate_values_dev and its first entry prices symbol
+ * rate_minima_dev[t]. rdo.row_rates, rdo.py:70-84. */
+int ep_lattice_row_rates(const int16_t* fields_dev, const uint8_t* cosets_dev, int64_t rows, int64_t cols,
+                         const float* rate_values_dev, const int32_t* rate_offsets_dev, const int32_t* rate_minima_dev,
+                         float* rates_dev, ep_stream_t stream);
+
+/* Output row r = row r of candidate choice_dev[r]; the two pointer arrays (device memory, `candidates`
+ * entries) name each candidate's fields and cosets. rdo.select_candidate_rows, rdo.py:103-120. */
+int ep_lattice_select_rows(const int16_t* const* candidate_fields_dev, const uint8_t* const* candidate_cosets_dev, int candidates,
+                           const int32_t* choice_dev, int64_t rows, int64_t cols, int16_t* fields_dev, uint8_t* cosets_dev,
+                           ep_stream_t stream);
+
 /* u16 words of per-tile scratch ep_lattice_encode writes into (tiles * tile_vectors * 9). */
 int64_t ep_lattice_encode_scratch_words(int64_t vectors, int64_t tile_elements);
 

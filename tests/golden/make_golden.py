@@ -208,6 +208,38 @@ def make_lattice(ep, out_dir: Path):
     print("lattice units: coded_bytes", coded)
 
 
+def make_rdo(ep, out_dir: Path):
+    """Per-row rate-distortion refinement (row_rdo_iterations > 0). Row choices hang on float32 sums whose order is
+    torch's, so these records pin what the refinement achieves (size, error, valid bitstream), not its exact picks."""
+    from entropack.schemes.lattice_rans import rdo
+
+    torch.manual_seed(123)
+    cases = {
+        "bf16_4p0": (lattice_weight(192, 512, 21, 8).to(torch.bfloat16), 4.0, {"row_rdo_iterations": 2}),
+        "bf16_3p0_k7": (lattice_weight(128, 384, 22, 5).to(torch.bfloat16), 3.0, {"row_rdo_iterations": 3, "row_rdo_candidates": 7}),
+    }
+    for name, (tensor, bpp, options) in cases.items():
+        plain = ep.EntroPackLossyConfig(target_bpp=bpp, execution_backend="eager")
+        refined = ep.EntroPackLossyConfig(target_bpp=bpp, execution_backend="eager", **options)
+        record = {"input_bytes": raw_bytes(tensor), "dtype": np.array(str(tensor.dtype).removeprefix("torch.")),
+                  "shape": np.array(tensor.shape, dtype=np.int64), "target_bpp": np.array(bpp), "options": np.array(repr(options))}
+        for label, config in (("plain", plain), ("rdo", refined)):
+            compressed = ep.compress(tensor, config)
+            assert compressed.compress_method == "lattice_rans", (name, compressed.header)
+            restored = ep.decompress(compressed, config)
+            record[f"{label}_actual_bpp"] = np.array(compressed.actual_bpp)
+            record[f"{label}_rel_l2"] = np.array(((restored.float() - tensor.float()).norm() / tensor.float().norm()).item())
+            if label == "rdo":
+                for key, value in as_numpy(compressed.buffers).items():
+                    record[f"buf_{key}"] = value
+                record["decoded_bytes"] = raw_bytes(restored)
+        np.savez_compressed(out_dir / f"rdo_{name}.npz", **record)
+        print(f"rdo {name}: plain {float(record['plain_actual_bpp']):.4f} bpp / {float(record['plain_rel_l2']):.5f}, "
+              f"refined {float(record['rdo_actual_bpp']):.4f} bpp / {float(record['rdo_rel_l2']):.5f}")
+    ladders = {str(count): np.array(rdo.ratio_ladder(count)) for count in range(1, 10)}
+    np.savez_compressed(out_dir / "rdo_ratio_ladders.npz", **ladders)
+
+
 def make_dfloat11(ep, out_dir: Path):
     g = torch.Generator().manual_seed(77)
     cases = {
@@ -233,14 +265,20 @@ def make_dfloat11(ep, out_dir: Path):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--only", default="all", choices=("all", "tile_ans", "lattice", "rdo", "dfloat11"))
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     install_huffman_stand_in()
     import entropack as ep
 
-    make_tile_ans(ep, HERE)
-    make_lattice(ep, HERE)
-    make_dfloat11(ep, HERE)
+    if args.only in ("all", "tile_ans"):
+        make_tile_ans(ep, HERE)
+    if args.only in ("all", "lattice"):
+        make_lattice(ep, HERE)
+    if args.only in ("all", "rdo"):
+        make_rdo(ep, HERE)
+    if args.only in ("all", "dfloat11"):
+        make_dfloat11(ep, HERE)
 
 
 if __name__ == "__main__":

@@ -105,6 +105,31 @@ def test_moved_container_keeps_parsed_header_and_host_metadata(monkeypatch):
     assert not calls
 
 
+
+def test_ratio_ladder_matches_the_reference():
+    from entropack_b200.schemes.lattice_rans.encoder import ratio_ladder
+
+    ladders = load_golden("rdo_ratio_ladders")
+    for count, expected in ladders.items():
+        assert list(ratio_ladder(int(count))) == expected.tolist()
+
+
+def test_rate_tradeoff_keeps_the_rate_budget():
+    from entropack_b200.schemes.lattice_rans.encoder import _choose_rate_tradeoff
+
+    rng = np.random.default_rng(4)
+    rates = np.sort(rng.uniform(500.0, 900.0, size=(200, 5)).astype(np.float32), axis=1)        # finer candidates cost more
+    distortion = np.sort(rng.uniform(1.0, 2.0, size=(200, 5)).astype(np.float32), axis=1)[:, ::-1].copy()  # and err less
+    row = np.arange(200)
+    unconstrained = _choose_rate_tradeoff(distortion, rates, 1e9)
+    assert np.array_equal(unconstrained, distortion.argmin(1))
+    budget = float(rates[:, 2].sum())
+    choice = _choose_rate_tradeoff(distortion, rates, budget)
+    assert rates[row, choice].sum(dtype=np.float32) <= budget
+    # spending the budget on finer candidates must beat giving every row the middle one
+    assert distortion[row, choice].sum() <= distortion[:, 2].sum()
+
+
 def test_no_cpu_fallback():
     import entropack_b200 as ep
 

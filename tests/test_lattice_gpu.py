@@ -145,3 +145,112 @@ def test_malformed_lossy_stream_is_reported():
     b200.decode(_to_device(bad), shape=tuple(int(v) for v in record["shape"]), dtype=torch.bfloat16, error=error)
     torch.cuda.synchronize()
     assert int(error.item()) in (2, 3)
+
+
+# ---- per-row rate-distortion refinement ------------------------------------------------------------------
+def _quantized_pass(rows=96, cols=512, scale=0.9, seed=3):
+    from entropack_b200.schemes.lattice_rans import encoder
+
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    work = (torch.randn(rows, cols, generator=generator, device="cuda") * 0.02).to(torch.bfloat16)
+    work[5] *= 7.0
+    item = encoder._Pass(work, encoder._row_rms(work))
+    minmax, bins = item.quantize(scale)
+    return item, minmax, bins
+
+
+def test_minmax_and_histogram_of_quantised_symbols_match_the_quantiser_pass():
+    item, minmax, bins = _quantized_pass()
+    again_minmax, again_bins = item.summarize()
+    assert np.array_equal(again_minmax[:33], minmax[:33]) and again_minmax[33] == 0
+    assert np.array_equal(again_bins, bins)
+
+
+def test_refit_rows_reports_scales_and_squared_error():
+    from entropack_b200 import _native
+
+    item, _, _ = _quantized_pass(scale=0.8)
+    scales, row_sse = item.refit(0.8)
+    plain = torch.empty_like(scales)
+    _native.check(_native.load().ep_lattice_refit_scales(
+        _native.ptr(item.work), 1, _native.ptr(item.fields), _native.ptr(item.cosets), _native.ptr(item.rms), 0.8, item.rows, item.cols,
+        _native.ptr(plain), _native.stream_handle(item.device)), "refit")
+    assert torch.equal(scales, plain)   # the scale is the one the plain refit gives, bit for bit
+    fields = item.fields.cpu().numpy().astype(np.int64)
+    coset = item.cosets.cpu().numpy().astype(np.float64)[:, None] * 0.5
+    z = fields.copy()
+    z[:, 7] = 2 * fields[:, 7] + (fields[:, :7].sum(1) & 1)
+    points = (z + coset).reshape(item.rows, item.cols)
+    x = item.work.float().cpu().numpy().astype(np.float64)
+    expected = (x * x).sum(1) - (x * points).sum(1) ** 2 / (points * points).sum(1)
+    # fp32 sums of a few hundred terms against fp64: 1e-4 relative to the row energy
+    assert np.allclose(row_sse.cpu().numpy(), expected, rtol=0, atol=1e-4 * float((x * x).sum(1).max()))
+
+
+def test_row_rates_and_row_selection_match_numpy():
+    from entropack_b200 import _native
+    from entropack_b200.schemes.lattice_rans import encoder
+
+    first, minmax_a, bins_a = _quantized_pass(scale=0.9)
+    second = encoder._Pass(first.work, first.rms)
+    minmax_b, bins_b = second.quantize(0.7)
+    streams_a, streams_b = encoder._stream_counts(minmax_a, bins_a), encoder._stream_counts(minmax_b, bins_b)
+    minima, maxima = [0] * 17, [0] * 17
+    for table in range(17):
+        alive = [(f, f + c.size - 1) for c, f in (streams_a[table], streams_b[table]) if c.size]
+        if alive:
+            minima[table], maxima[table] = min(a for a, _ in alive), max(b for _, b in alive)
+    values, offsets, table_minima = encoder._rate_table(streams_a, minima, maxima, first.device)
+    lib = _native.load()
+    for item in (first, second):
+        rates = torch.empty(item.rows, dtype=torch.float32, device="cuda")
+        _native.check(lib.ep_lattice_row_rates(
+            _native.ptr(item.fields), _native.ptr(item.cosets), item.rows, item.cols, _native.ptr(values), _native.ptr(offsets),
+            _native.ptr(table_minima), _native.ptr(rates), _native.stream_handle(item.device)), "row rates")
+        fields = item.fields.cpu().numpy().astype(np.int64)
+        coset = item.cosets.cpu().numpy().astype(np.int64)
+        table_values, table_offsets = values.cpu().numpy().astype(np.float64), offsets.cpu().numpy()
+        per_vector = table_values[table_offsets[0] + coset]
+        for field in range(8):
+            stream = 1 + 2 * field + coset
+            per_vector = per_vector + table_values[table_offsets[stream] + fields[:, field] - np.asarray(minima)[stream]]
+        expected = per_vector.reshape(item.rows, -1).sum(1)
+        assert np.allclose(rates.cpu().numpy(), expected, rtol=1e-5)   # fp32 row sums of a few hundred positive terms
+
+    choice = torch.arange(first.rows, device="cuda", dtype=torch.int32) % 2
+    pointers = [torch.tensor([p.data_ptr() for p in group], dtype=torch.int64, device="cuda")
+                for group in ((first.fields, second.fields), (first.cosets, second.cosets))]
+    mixed = encoder._Pass(first.work, first.rms)
+    _native.check(lib.ep_lattice_select_rows(
+        _native.ptr(pointers[0]), _native.ptr(pointers[1]), 2, _native.ptr(choice), first.rows, first.cols, _native.ptr(mixed.fields),
+        _native.ptr(mixed.cosets), _native.stream_handle(first.device)), "select rows")
+    per_row = first.cols // 8
+    take_second = (choice.bool()).repeat_interleave(per_row)
+    assert torch.equal(mixed.fields, torch.where(take_second[:, None], second.fields, first.fields))
+    assert torch.equal(mixed.cosets, torch.where(take_second, second.cosets, first.cosets))
+
+
+@pytest.mark.parametrize("name", golden_names("rdo_bf16"))
+def test_row_refinement_reaches_the_reference_rate_and_error(oracle_module, name):
+    """Row choices hang on float32 sums whose order differs between torch and these kernels, so the refinement is
+    held to what it achieves: the reference's refined bitstream decodes bit-exactly here, and our refined container
+    is a valid bitstream (the CPU decoder agrees), sits within 0.01 bpp of the reference's refined size, and has an
+    error no more than 0.5 % above the reference's refined error and below the unrefined encode's."""
+    import entropack_b200 as ep
+
+    record = load_golden(f"rdo_bf16{name}")
+    shape = tuple(int(v) for v in record["shape"])
+    assert _bytes(_gpu_decode(buffers_of(record), shape, torch.bfloat16)) == record["decoded_bytes"].tobytes()
+
+    options = ast.literal_eval(str(record["options"]))
+    source = torch.from_numpy(record["input_bytes"].copy()).view(torch.bfloat16).reshape(shape).cuda()
+    config = ep.EntroPackLossyConfig(target_bpp=float(record["target_bpp"]), **options)
+    container = ep.compress(source, config)
+    assert container.compress_method == "lattice_rans"
+    restored = ep.decompress(container, config)
+    host_buffers = {key: value.cpu().numpy() for key, value in container.buffers.items()}
+    assert _bytes(restored) == _bytes(oracle_module.lattice_decode(host_buffers, shape, torch.bfloat16))
+    relative = float((restored.float() - source.float()).norm() / source.float().norm())
+    assert abs(container.actual_bpp - float(record["rdo_actual_bpp"])) <= 0.01
+    assert relative <= float(record["rdo_rel_l2"]) * 1.005
+    assert relative < float(record["plain_rel_l2"])
