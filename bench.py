@@ -464,6 +464,29 @@ def measure_others(ep, device, flush, reps: int) -> dict:
                 entry["library_gemm_tflops"] = 2.0 * tokens * out_features * in_features / entry["library_gemm_us"] / 1e6
                 entry["cublas_tflops"] = 2.0 * tokens * out_features * in_features / entry["cublas_dense_us"] / 1e6
             results[f"linear_{in_features}x{out_features}_M{tokens}"] = entry
+
+    # FP8 layer (codes lattice-coded at 5 bpp): activation quantisation + scaled fp8 product on the library's
+    # tcgen05 kernel, against torch._scaled_mm on the same codes
+    dense = torch.nn.Linear(3840, 3840, bias=False, device=device, dtype=torch.bfloat16)
+    with torch.no_grad():
+        dense.weight.copy_((torch.randn(3840, 3840, generator=generator, device=device) * 0.02).to(torch.bfloat16))
+    layer = ep.CompressedFP8Linear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=5.0))
+    codes, weight_scale = layer.codes(device), layer.weight_quant_scale.to(device)
+    for tokens in (16, 4096):
+        x = torch.randn(tokens, 3840, generator=generator, device=device).to(torch.bfloat16)
+        a_codes, a_scale = layer._quantize_rows(x)
+        entry = {
+            "compressed_forward_us": timed(lambda: layer(x)) * 1e3,
+            "quantize_activations_us": timed(lambda: layer._quantize_rows(x)) * 1e3,
+            "library_fp8_gemm_us": timed(lambda: layer._gemm(a_codes, codes, a_scale, weight_scale, torch.bfloat16)) * 1e3,
+            "scaled_mm_us": timed(lambda: torch._scaled_mm(a_codes, codes.t(), scale_a=a_scale.unsqueeze(1),
+                                                           scale_b=weight_scale.unsqueeze(0), out_dtype=torch.bfloat16)) * 1e3,
+            "bits": layer.compressed_bits,
+        }
+        if tokens == 4096:
+            entry["library_fp8_gemm_tflops"] = 2.0 * tokens * 3840 * 3840 / entry["library_fp8_gemm_us"] / 1e6
+            entry["scaled_mm_tflops"] = 2.0 * tokens * 3840 * 3840 / entry["scaled_mm_us"] / 1e6
+        results[f"fp8_linear_3840x3840_M{tokens}"] = entry
     return results
 
 

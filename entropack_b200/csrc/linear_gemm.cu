@@ -14,6 +14,8 @@
 //     raises the error word, frees its TMEM and returns.
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <cstdlib>
 #include <mutex>
@@ -100,6 +102,43 @@ __global__ void __launch_bounds__(kStreamThreads) linear_stream_kernel(const __n
 }
 
 // ------------------------------------------------------------------------------------------------
+// per-row FP8 quantisation of activations (QuantizedLinear._quantize_rows, entropack/linear/linear.py:286-293)
+// ------------------------------------------------------------------------------------------------
+// scale = max(absmax / 448, eps); code = e4m3(clamp(fl32(x / scale), -448, 448)), round to nearest even.
+__device__ __forceinline__ float as_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float as_float(float v) { return v; }
+
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_rows_fp8_kernel(const T* __restrict__ x, int64_t cols, uint8_t* __restrict__ codes,
+                                                                float* __restrict__ scales) {
+  __shared__ float partial[8];
+  __shared__ float row_scale;
+  const T* row = x + static_cast<int64_t>(blockIdx.x) * cols;
+  float largest = 0.0f;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) largest = fmaxf(largest, fabsf(as_float(row[c])));
+#pragma unroll
+  for (int step = 16; step > 0; step >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xFFFFFFFFu, largest, step));
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = largest;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = partial[0];
+    for (int w = 1; w < 8; ++w) total = fmaxf(total, partial[w]);
+    // absmax / 448 the way torch evaluates a division by a host scalar on a GPU: times the fp32 reciprocal;
+    // clamped at the float32 epsilon like the reference
+    row_scale = fmaxf(__fmul_rn(total, __fdiv_rn(1.0f, 448.0f)), 1.1920928955078125e-07f);
+    scales[blockIdx.x] = row_scale;
+  }
+  __syncthreads();
+  const float scale = row_scale;
+  uint8_t* out = codes + static_cast<int64_t>(blockIdx.x) * cols;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) {
+    const float scaled = fminf(fmaxf(__fdiv_rn(as_float(row[c]), scale), -448.0f), 448.0f);
+    out[c] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // tcgen05 GEMM
 // ------------------------------------------------------------------------------------------------
 constexpr int kTileM = 128;
@@ -131,10 +170,17 @@ template <int TILE_N, int A_ROWS> struct TileShape {
   static_assert(kStages >= 3, "the ring needs a few stages");
   static_assert(kStages * kBytesB >= kTileBytesA - kBytesA, "the MMA's 128-row read of the last A tile must stay inside the B tiles");
   static constexpr uint32_t kTmemColumns = TILE_N;
-  // Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, both K-major, N and M encoded /8 and /16.
-  static constexpr uint32_t kInstruction = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(TILE_N >> 3) << 17) |
-                                           (static_cast<uint32_t>(kTileM >> 4) << 24);
+  // Instruction descriptors: fp32 accumulate (bit 4), both operands K-major, N and M encoded /8 and /16.
+  // kind::f16 with bf16 A and B (format 1 in bits 7-9 and 10-12); kind::f8f6f4 with e4m3 A and B (format 0).
+  static constexpr uint32_t kShapeBits = (static_cast<uint32_t>(TILE_N >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+  static constexpr uint32_t kInstructionBf16 = (1u << 4) | (1u << 7) | (1u << 10) | kShapeBits;
+  static constexpr uint32_t kInstructionFp8 = (1u << 4) | kShapeBits;
 };
+
+// Operand kinds of the tensor-core kernel. A shared-memory row is 128 bytes either way: 64 bf16 or 128 fp8
+// elements, consumed by four MMAs of 32 bytes of K each.
+constexpr int kOperandBf16 = 0;
+constexpr int kOperandFp8 = 1;
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -172,13 +218,18 @@ __device__ __forceinline__ uint64_t matrix_descriptor(uint32_t tile_address) {
   return d;
 }
 struct GemmParams {
-  const __nv_bfloat16* bias;
+  const __nv_bfloat16* bias;     // bf16 operands: optional bias in bf16
   __nv_bfloat16* y;
-  int m, n, k;
+  int m, n, k;                   // k in elements
   int* error;
+  // fp8 operands: y = acc * row_scale[row] * column_scale[col] + bias_f32[col], written as bf16 (y) or fp32 (y_f32)
+  const float* row_scale;
+  const float* column_scale;
+  const float* bias_f32;
+  float* y_f32;
 };
 
-template <int TILE_N, int A_ROWS>
+template <int TILE_N, int A_ROWS, int OPERAND>
 __global__ void __launch_bounds__(kGemmThreads, TileShape<TILE_N, A_ROWS>::kBlocksPerSm)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
   using Shape = TileShape<TILE_N, A_ROWS>;
@@ -186,7 +237,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   constexpr int kBytesA = Shape::kBytesA;
   constexpr int kBytesB = Shape::kBytesB;
   constexpr uint32_t kTmemColumns = Shape::kTmemColumns;
-  constexpr uint32_t kInstruction = Shape::kInstruction;
+  constexpr uint32_t kInstruction = OPERAND == kOperandFp8 ? Shape::kInstructionFp8 : Shape::kInstructionBf16;
+  constexpr int kElementsPerStep = OPERAND == kOperandFp8 ? 128 : 64;   // one 128-byte row of K
   extern __shared__ uint8_t raw_shared[];
   __shared__ __align__(8) uint64_t full[kStages];
   __shared__ __align__(8) uint64_t empty[kStages];
@@ -199,7 +251,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   uint8_t* tiles_b = tiles_a + kStages * kBytesA;
   const int warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
-  const int k_steps = (p.k + kTileK - 1) / kTileK;
+  const int k_steps = (p.k + kElementsPerStep - 1) / kElementsPerStep;
   // The block is persistent: it takes output tiles blockIdx.x, blockIdx.x + gridDim.x, ... in an order that
   // runs along N first, so the blocks at work at any moment share their rows of activations in L2.
   const int n_tiles = (p.n + TILE_N - 1) / TILE_N;
@@ -240,8 +292,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           break;
         }
         barrier_expect(&full[s], kBytesA + kBytesB);
-        tma_load_2d(tiles_a + s * kBytesA, &map_x, &full[s], ks * kTileK, m0);
-        tma_load_2d(tiles_b + s * kBytesB, &map_w, &full[s], ks * kTileK, n0);
+        tma_load_2d(tiles_a + s * kBytesA, &map_x, &full[s], ks * kElementsPerStep, m0);
+        tma_load_2d(tiles_b + s * kBytesB, &map_w, &full[s], ks * kElementsPerStep, n0);
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -268,9 +320,15 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
         for (int kk = 0; kk < kTileK / 16; ++kk) {
           const uint32_t accumulate = (ks | kk) ? 1u : 0u;
-          asm volatile(
-              "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-              ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          if (OPERAND == kOperandFp8) {
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          } else {
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          }
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(shared_address(&empty[s])) : "memory");
       }
@@ -320,6 +378,42 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         const int col = n0 + chunk * 32;
         if (row < p.m && col < p.n) {
+          if (OPERAND == kOperandFp8) {
+            // scaled epilogue of the 8-bit layers: the row's activation scale times the column's weight scale
+            const float row_scale = p.row_scale[row];
+            const int64_t at = static_cast<int64_t>(row) * p.n + col;
+            const bool whole = col + 32 <= p.n && (p.n & 7) == 0;
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+              const bool inside = whole || col + c < p.n;
+              const float scale = inside ? row_scale * p.column_scale[col + c] : 0.0f;
+              const float b = inside && p.bias_f32 ? p.bias_f32[col + c] : 0.0f;
+              v[c] = __float_as_uint(fmaf(__uint_as_float(v[c]), scale, b));
+            }
+            if (p.y_f32) {
+              if (whole) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  *reinterpret_cast<uint4*>(p.y_f32 + at + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                }
+              } else {
+                for (int c = 0; c < 32 && col + c < p.n; ++c) p.y_f32[at + c] = __uint_as_float(v[c]);
+              }
+            } else if (whole) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + j * 2]), __uint_as_float(v[g * 8 + j * 2 + 1]));
+                  packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
+                }
+                *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              }
+            } else {
+              for (int c = 0; c < 32 && col + c < p.n; ++c) p.y[at + c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+            }
+          } else {
           __nv_bfloat16* out = p.y + static_cast<int64_t>(row) * p.n + col;
           if (col + 32 <= p.n && (p.n & 7) == 0) {
 #pragma unroll
@@ -340,6 +434,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
               const float b = p.bias ? __bfloat162float(p.bias[col + c]) : 0.0f;
               out[c] = __float2bfloat16_rn(__uint_as_float(v[c]) + b);
             }
+          }
           }
         }
       }
@@ -378,15 +473,18 @@ EncodeTiled tensor_map_encoder() {
   return encoder;
 }
 
-// rows x k bf16, row-major; boxes of box_rows rows x 64 columns, 128-byte swizzle, zero fill outside the tensor
-bool make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows) {
+// rows x k row-major matrix of bf16 or one-byte elements; boxes of box_rows rows x 128 bytes, 128-byte swizzle, zero
+// fill outside the tensor
+bool make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows, int operand) {
   EncodeTiled encode = tensor_map_encoder();
   if (!encode) return false;
+  const int element_bytes = operand == kOperandFp8 ? 1 : 2;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * 2};
-  const cuuint32_t box[2] = {kTileK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * element_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / element_bytes), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t element_strides[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+  return encode(map, operand == kOperandFp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                const_cast<void*>(base), dims, strides, box, element_strides,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -398,26 +496,58 @@ int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfl
   return check_launch("linear_stream_kernel");
 }
 
-template <int TILE_N, int A_ROWS>
+template <int TILE_N, int A_ROWS, int OPERAND>
 int launch_tcgen05(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
   using Shape = TileShape<TILE_N, A_ROWS>;
   CUtensorMap map_x, map_w;
-  if (!make_tile_map(&map_x, x_dev, p.m, p.k, A_ROWS) || !make_tile_map(&map_w, weight_dev, p.n, p.k, TILE_N)) return EP_ERR_UNSUPPORTED;
-  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_kernel<TILE_N, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (!make_tile_map(&map_x, x_dev, p.m, p.k, A_ROWS, OPERAND) || !make_tile_map(&map_w, weight_dev, p.n, p.k, TILE_N, OPERAND)) {
+    return EP_ERR_UNSUPPORTED;
+  }
+  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_kernel<TILE_N, A_ROWS, OPERAND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Shape::kSharedBytes));
   const int64_t tiles = static_cast<int64_t>((p.n + TILE_N - 1) / TILE_N) * ((p.m + kTileM - 1) / kTileM);
   const int64_t resident = static_cast<int64_t>(kSmCount) * Shape::kBlocksPerSm;
   const unsigned grid = static_cast<unsigned>(tiles < resident ? tiles : resident);
-  linear_tcgen05_kernel<TILE_N, A_ROWS><<<grid, kGemmThreads, Shape::kSharedBytes, s>>>(map_x, map_w, p);
+  linear_tcgen05_kernel<TILE_N, A_ROWS, OPERAND><<<grid, kGemmThreads, Shape::kSharedBytes, s>>>(map_x, map_w, p);
   return EP_OK;
 }
 
-template <int TILE_N>
+template <int TILE_N, int OPERAND>
 int launch_narrow(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
-  if (p.m <= 16) return launch_tcgen05<TILE_N, 16>(x_dev, weight_dev, p, s);
-  if (p.m <= 32) return launch_tcgen05<TILE_N, 32>(x_dev, weight_dev, p, s);
-  if (p.m <= 64) return launch_tcgen05<TILE_N, 64>(x_dev, weight_dev, p, s);
-  return launch_tcgen05<TILE_N, 128>(x_dev, weight_dev, p, s);
+  if (p.m <= 16) return launch_tcgen05<TILE_N, 16, OPERAND>(x_dev, weight_dev, p, s);
+  if (p.m <= 32) return launch_tcgen05<TILE_N, 32, OPERAND>(x_dev, weight_dev, p, s);
+  if (p.m <= 64) return launch_tcgen05<TILE_N, 64, OPERAND>(x_dev, weight_dev, p, s);
+  return launch_tcgen05<TILE_N, 128, OPERAND>(x_dev, weight_dev, p, s);
+}
+
+// Tile width. A block's time goes with the bytes it pulls through L2 per K step (activation box + weight box);
+// blocks beyond what the SMs hold at once run in further rounds. Take the width with the least rounds x bytes.
+template <int OPERAND>
+int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
+  const int64_t row_tiles = (p.m + kTileM - 1) / kTileM;
+  const int a_rows = p.m <= 16 ? 16 : (p.m <= 32 ? 32 : (p.m <= 64 ? 64 : 128));
+  int tile_n = 32;
+  int64_t best = -1;
+  for (int candidate = 256; candidate >= 32; candidate >>= 1) {
+    const bool narrow = candidate <= 64;
+    const int box_a = narrow ? a_rows : 128;
+    const int64_t blocks = row_tiles * ((p.n + candidate - 1) / candidate);
+    const int64_t resident = static_cast<int64_t>(kSmCount) * (box_a < 128 ? 3 : 1);
+    const int64_t cost = ((blocks + resident - 1) / resident) * (box_a + candidate);
+    if (best < 0 || cost < best) {
+      best = cost;
+      tile_n = candidate;
+    }
+  }
+  int rc = EP_ERR_UNSUPPORTED;
+  switch (tile_n) {
+    case 256: rc = launch_tcgen05<256, 128, OPERAND>(x_dev, weight_dev, p, s); break;
+    case 128: rc = launch_tcgen05<128, 128, OPERAND>(x_dev, weight_dev, p, s); break;
+    case 64: rc = launch_narrow<64, OPERAND>(x_dev, weight_dev, p, s); break;
+    default: rc = launch_narrow<32, OPERAND>(x_dev, weight_dev, p, s); break;
+  }
+  if (rc != EP_OK) return rc;
+  return check_launch("linear_tcgen05_kernel");
 }
 
 }  // namespace
@@ -442,38 +572,52 @@ extern "C" int ep_linear_forward(const void* x_dev, const void* weight_dev, cons
   auto* y = static_cast<__nv_bfloat16*>(y_dev);
   const int mi = static_cast<int>(m), ni = static_cast<int>(n), ki = static_cast<int>(k);
   if (m <= kStreamMaxM) return launch_stream<1>(x, w, bias, y, mi, ni, ki, s);
-  GemmParams p;
+  GemmParams p = {};
   p.bias = bias;
   p.y = y;
   p.m = mi;
   p.n = ni;
   p.k = ki;
   p.error = error_dev;
-  // Tile width. A block's time goes with the bytes it pulls through L2 per K step (activation box + weight box);
-  // blocks beyond what the SMs hold at once run in further rounds. Take the width with the least rounds x bytes.
-  const int64_t row_tiles = (m + kTileM - 1) / kTileM;
-  const int a_rows = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : 128));
-  int tile_n = 32;
-  int64_t best = -1;
-  for (int candidate = 256; candidate >= 32; candidate >>= 1) {
-    const bool narrow = candidate <= 64;
-    const int box_a = narrow ? a_rows : 128;
-    const int64_t blocks = row_tiles * ((n + candidate - 1) / candidate);
-    const int64_t resident = static_cast<int64_t>(kSmCount) * (box_a < 128 ? 3 : 1);
-    const int64_t cost = ((blocks + resident - 1) / resident) * (box_a + candidate);
-    if (best < 0 || cost < best) {
-      best = cost;
-      tile_n = candidate;
-    }
+  return launch_best_tile<kOperandBf16>(x_dev, weight_dev, p, s);
+}
+
+extern "C" int ep_linear_forward_fp8(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev,
+                                     const float* weight_scale_dev, const float* bias_dev, void* y_dev, int y_is_f32, int64_t m,
+                                     int64_t n, int64_t k, int* error_dev, ep_stream_t stream) {
+  if (!x_codes_dev || !weight_codes_dev || !x_scale_dev || !weight_scale_dev || !y_dev || m <= 0 || n <= 0 || k <= 0 ||
+      (k & 15) != 0 || m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) {
+    return EP_ERR_INVALID_ARGUMENT;
   }
-  int rc = EP_ERR_UNSUPPORTED;
-  switch (tile_n) {
-    case 256: rc = launch_tcgen05<256, 128>(x_dev, weight_dev, p, s); break;
-    case 128: rc = launch_tcgen05<128, 128>(x_dev, weight_dev, p, s); break;
-    case 64: rc = launch_narrow<64>(x_dev, weight_dev, p, s); break;
-    case 32: rc = launch_narrow<32>(x_dev, weight_dev, p, s); break;
-    default: return EP_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x_codes_dev) & 15u) || (reinterpret_cast<uintptr_t>(weight_codes_dev) & 15u) ||
+      (reinterpret_cast<uintptr_t>(y_dev) & 15u)) {
+    return EP_ERR_INVALID_ARGUMENT;
   }
-  if (rc != EP_OK) return rc;
-  return check_launch("linear_tcgen05_kernel");
+  GemmParams p = {};
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.error = error_dev;
+  p.row_scale = x_scale_dev;
+  p.column_scale = weight_scale_dev;
+  p.bias_f32 = bias_dev;
+  if (y_is_f32) p.y_f32 = static_cast<float*>(y_dev);
+  else p.y = static_cast<__nv_bfloat16*>(y_dev);
+  return launch_best_tile<kOperandFp8>(x_codes_dev, weight_codes_dev, p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
+                                    ep_stream_t stream) {
+  if (!x_dev || !codes_dev || !scales_dev || rows <= 0 || cols <= 0 || rows > 0x7FFFFFFF || x_kind < 0 || x_kind > 2) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>(rows);
+  auto* codes = static_cast<uint8_t*>(codes_dev);
+  switch (x_kind) {
+    case 0: quantize_rows_fp8_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_dev), cols, codes, scales_dev); break;
+    case 1: quantize_rows_fp8_kernel<<<blocks, 256, 0, s>>>(static_cast<const __half*>(x_dev), cols, codes, scales_dev); break;
+    default: quantize_rows_fp8_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(x_dev), cols, codes, scales_dev); break;
+  }
+  return check_launch("quantize_rows_fp8_kernel");
 }

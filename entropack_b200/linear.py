@@ -24,6 +24,7 @@ from .registry import default_config, get_scheme, name_for_config, require_dtype
 from .schemes import EntroPackLossyConfig, RawConfig
 
 _EPS = torch.finfo(torch.float32).eps
+_FP8_SOURCE_KINDS = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
 def _native_gemm_applies(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> bool:
@@ -363,12 +364,36 @@ class CompressedFP8Linear(QuantizedLinear):
     min_tokens = 1
     min_capability = (8, 9)
 
+    def _quantize_rows(self, tensor: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Weights (once, at compression time) go through the torch expression of the base class; activations on a
+        GPU, every forward, through one kernel that computes the same scale and codes."""
+        kind = _FP8_SOURCE_KINDS.get(tensor.dtype)
+        if not tensor.is_cuda or kind is None or tensor.numel() == 0:
+            return super()._quantize_rows(tensor)
+        flat = tensor.reshape(-1, tensor.shape[-1]).contiguous()
+        codes = torch.empty(flat.shape, dtype=torch.float8_e4m3fn, device=flat.device)
+        scale = torch.empty(flat.shape[0], dtype=torch.float32, device=flat.device)
+        with torch.cuda.device(flat.device):
+            status = _native.load().ep_quantize_rows_fp8(_native.ptr(flat), kind, flat.shape[0], flat.shape[1], _native.ptr(codes),
+                                                         _native.ptr(scale), _native.stream_handle(flat.device))
+        _native.check(status, "fp8 activation quantisation")
+        return codes, scale
+
     def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
+        """Scaled FP8 product on the library's tcgen05 kernel (bf16 or fp32 results; fp16 goes through fp32)."""
         bias = self._bias_padded(codes.device, weight_scale.shape[0])
-        fused = bias is None or out_dtype is not torch.float32
-        out = torch._scaled_mm(activation, codes.t(), scale_a=activation_scale.unsqueeze(1), scale_b=weight_scale.unsqueeze(0),
-                               bias=bias if fused else None, out_dtype=out_dtype)
-        return out if fused else out.add_(bias)
+        direct = out_dtype in (torch.bfloat16, torch.float32)
+        out = torch.empty((activation.shape[0], codes.shape[0]), dtype=out_dtype if direct else torch.float32, device=codes.device)
+        activation, codes = activation.contiguous(), codes.contiguous()
+        activation_scale, weight_scale = activation_scale.contiguous(), weight_scale.contiguous()
+        bias32 = None if bias is None else bias.float().contiguous()   # held until after the launch
+        with torch.cuda.device(codes.device):
+            status = _native.load().ep_linear_forward_fp8(
+                _native.ptr(activation), _native.ptr(codes), _native.ptr(activation_scale), _native.ptr(weight_scale),
+                _native.ptr(bias32), _native.ptr(out), int(out.dtype == torch.float32), activation.shape[0], codes.shape[0],
+                activation.shape[1], None, _native.stream_handle(codes.device))
+        _native.check(status, "fp8 linear forward")
+        return out if direct else out.to(out_dtype)
 
 
 class CompressedINT8Linear(QuantizedLinear):

@@ -273,11 +273,25 @@ int ep_dfloat11_pack(const void* bf16_dev, int64_t n_elements, const int32_t* co
 
 /* y[m][n] = x[m][k] . weight[n][k]^T (+ bias[n]), all bf16, fp32 accumulation. k must be a multiple of 8
  * and the three matrices 16-byte aligned. Stands in for the F.linear call of CompressedLinear.forward
- * (entropack/linear/linear.py:163-165): m <= 16 runs a bandwidth kernel on CUDA cores, larger m the
- * tcgen05 / TMEM tensor-core kernel fed by TMA. A wait that runs out inside the tensor-core kernel is
+ * (entropack/linear/linear.py:163-165): m <= 16 streams the weight straight into m16n8k16 fragments,
+ * larger m runs the persistent tcgen05 / TMEM tensor-core kernel fed by TMA. A wait that runs out inside the tensor-core kernel is
  * reported as code 9 in error_dev (optional device int32, zeroed by the caller). */
 int ep_linear_forward(const void* x_dev, const void* weight_dev, const void* bias_dev, void* y_dev, int64_t m, int64_t n,
                       int64_t k, int* error_dev, ep_stream_t stream);
+
+/* The 8-bit layer's product: y[m][n] = (x_codes[m][k] . weight_codes[n][k]^T) * x_scale[m] * weight_scale[n]
+ * (+ bias[n], fp32), both code matrices fp8 e4m3, accumulation in fp32 on the tcgen05 kernel
+ * (kind::f8f6f4), y written as bf16 (y_is_f32 = 0) or fp32. k must be a multiple of 16. Stands in for
+ * the torch._scaled_mm call of CompressedFP8Linear (entropack/linear/linear.py:399-418). */
+int ep_linear_forward_fp8(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev,
+                          const float* weight_scale_dev, const float* bias_dev, void* y_dev, int y_is_f32, int64_t m, int64_t n,
+                          int64_t k, int* error_dev, ep_stream_t stream);
+
+/* Per-row activation quantisation of the FP8 layer: scales_dev[r] = max(absmax(x[r]) / 448, eps32),
+ * codes_dev[r][c] = e4m3(clamp(x[r][c] / scale, -448, 448)). x_kind: 0 bf16, 1 fp16, 2 fp32.
+ * QuantizedLinear._quantize_rows, entropack/linear/linear.py:286-293. */
+int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
+                         ep_stream_t stream);
 
 #ifdef __cplusplus
 }

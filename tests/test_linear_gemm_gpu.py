@@ -24,3 +24,56 @@ def test_matches_fp32_reference(m, n, k, bias):
     expected = x.float() @ w.float().t() + (b.float() if bias else 0.0)
     # tolerance from the metric definition: max |y - y_ref| / max |y_ref| <= 1e-2 (bf16 output rounding is ~4e-3)
     assert float((out.float() - expected).abs().max() / expected.abs().max()) <= 1e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_fp8_row_quantisation_matches_the_torch_expression(dtype):
+    """Same scale and the same e4m3 codes, bit for bit, as QuantizedLinear._quantize_rows computes with torch ops."""
+    from entropack_b200 import _native
+
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    x = (torch.randn(37, 1000, generator=generator, device="cuda") * 3).to(dtype)
+    x[5] = 0          # an all-zero row takes the epsilon scale
+    x[6, 10] = 7e4 if dtype is not torch.float16 else 6e4
+    codes = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device="cuda")
+    scales = torch.empty(x.shape[0], dtype=torch.float32, device="cuda")
+    kind = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[dtype]
+    _native.check(_native.load().ep_quantize_rows_fp8(_native.ptr(x), kind, x.shape[0], x.shape[1], _native.ptr(codes), _native.ptr(scales),
+                                                      _native.stream_handle(x.device)), "quantise")
+    flat = x.float()
+    expected_scale = (flat.abs().amax(dim=1) / 448.0).clamp(min=torch.finfo(torch.float32).eps)
+    expected_codes = (flat / expected_scale.unsqueeze(1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    assert torch.equal(scales, expected_scale)
+    assert torch.equal(codes.view(torch.uint8), expected_codes.view(torch.uint8))
+
+
+@pytest.mark.parametrize("m,n,k,out_dtype,with_bias", [
+    (1, 768, 1024, torch.bfloat16, True), (16, 3840, 3840, torch.bfloat16, False), (200, 1000, 2048, torch.float32, True),
+    (4096, 3840, 3840, torch.bfloat16, True), (300, 520, 4096, torch.bfloat16, False),
+])
+def test_fp8_gemm_matches_scaled_mm(m, n, k, out_dtype, with_bias):
+    """tcgen05 kind::f8f6f4 kernel against torch._scaled_mm on the same codes and scales. Products of e4m3 values are
+    exact in fp32, so only the summation order differs: 1e-4 of the largest output for fp32 results; bf16 results add
+    their own rounding, half a unit in the 8th bit, 2^-8 relative."""
+    from entropack_b200 import _native
+
+    generator = torch.Generator(device="cuda").manual_seed(11)
+    a = (torch.randn(m, k, generator=generator, device="cuda") * 50).clamp(-448, 448).to(torch.float8_e4m3fn)
+    b = (torch.randn(n, k, generator=generator, device="cuda") * 50).clamp(-448, 448).to(torch.float8_e4m3fn)
+    a_scale = torch.rand(m, generator=generator, device="cuda") * 0.01 + 0.001
+    b_scale = torch.rand(n, generator=generator, device="cuda") * 0.01 + 0.001
+    bias = torch.randn(n, generator=generator, device="cuda") if with_bias else None
+    out = torch.empty((m, n), dtype=out_dtype, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _native.check(_native.load().ep_linear_forward_fp8(
+        _native.ptr(a), _native.ptr(b), _native.ptr(a_scale), _native.ptr(b_scale), _native.ptr(bias), _native.ptr(out),
+        int(out_dtype == torch.float32), m, n, k, _native.ptr(error), _native.stream_handle(out.device)), "fp8 gemm")
+    assert int(error.item()) == 0
+    expected = (a.float() @ b.float().t()) * a_scale.unsqueeze(1) * b_scale.unsqueeze(0)
+    if bias is not None:
+        expected = expected + bias
+    assert float((out.float() - expected).abs().max() / expected.abs().max()) <= (1e-4 if out_dtype is torch.float32 else 2.0 ** -8)
+    if n % 16 == 0 and k % 16 == 0 and out_dtype is torch.bfloat16:
+        library = torch._scaled_mm(a, b.t(), scale_a=a_scale.unsqueeze(1), scale_b=b_scale.unsqueeze(0),
+                                   bias=None if bias is None else bias.to(torch.bfloat16), out_dtype=torch.bfloat16)
+        assert float((out.float() - library.float()).abs().max() / expected.abs().max()) <= 1e-2
