@@ -35,6 +35,8 @@ _PROTOTYPES = {
     "ep_exclusive_scan_u32": [_ptr, _i64, _ptr, _ptr, _ptr],
     "ep_compact_streams": [_ptr, _ptr, _ptr, _i64, _i64, _ptr],
     "ep_lattice_decode": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _ptr, _ptr],
+    "ep_lattice_linear_forward": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _ptr, _ptr, _i32,
+                                  _ptr, _ptr, _ptr, _ptr],
     "ep_lattice_decode_scratch_bytes": [_i32, _i32],
     "ep_lattice_decode_static": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _ptr],
     "ep_lattice_decode_static_max_prob_bits": [],

@@ -49,7 +49,20 @@ struct LatticeDecodeParams {
   int prob_bits;
   int store_kind;
   int* error;
+  // fused product (kModeProduct): activations bf16 [tokens][8 * vecs_per_row], accumulators fp32 [tokens][rows]
+  const __nv_bfloat16* activations;
+  float* products;           // [tokens][rows] accumulators, then one word counting the blocks that are done
+  const __nv_bfloat16* bias;  // [rows] or null
+  __nv_bfloat16* product_out; // [tokens][rows]
+  int tokens;
+  int rows;
 };
+
+// What the decode kernel does with a reconstructed vector.
+constexpr int kModeStore = 0;       // any container dtype (store_kind)
+constexpr int kModeStoreBf16 = 1;   // bf16, one 16-byte store
+constexpr int kModeProduct = 2;     // nothing is stored: the vector is multiplied into up to kMaxTokens dot products
+constexpr int kMaxTokens = 4;    // instantiated for 1, 2 and 4 tokens: every token costs its instructions whether used or not
 
 // ---- container cast (entropack/schemes/lattice_rans/format.py:153-168) ---------------------------
 template <typename T>
@@ -198,7 +211,7 @@ __global__ void __launch_bounds__(32) lattice_build_tables_kernel(uint64_t* tabl
 }
 
 // ---- decode ----------------------------------------------------------------------------------------
-template <bool SHARED_TABLES, bool BF16_OUT>
+template <bool SHARED_TABLES, int MODE, int TOKENS = 0>
 __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const LatticeDecodeParams p) {
   extern __shared__ __align__(16) uint32_t shared_tables[];  // [17][table_size] when SHARED_TABLES
   __shared__ int sym_min[kTables + 1];
@@ -294,7 +307,32 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     // row and column (in vectors) of this thread's vector in the current group, stepped back 32 per group
     int row = static_cast<int>(static_cast<uint32_t>(tile_begin + offset + lane) / static_cast<uint32_t>(p.vecs_per_row));
     int col = static_cast<int>(static_cast<uint32_t>(tile_begin + offset + lane) - static_cast<uint32_t>(row) * p.vecs_per_row);
+    // kModeProduct: this thread's running dot products for the weight row it is in, flushed with one atomic add per
+    // token whenever its vectors move on to another row, and at the end of the tile
+    constexpr int kTokens = TOKENS > 0 ? TOKENS : 1;
+    float running[kTokens];
+    int running_row = -1;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) running[t] = 0.0f;
+    auto flush_products = [&]() {
+      if (running_row >= 0) {
+#pragma unroll
+        for (int t = 0; t < kTokens; ++t) {
+          if (t < p.tokens) atomicAdd(p.products + static_cast<int64_t>(t) * p.rows + running_row, running[t]);
+          running[t] = 0.0f;
+        }
+      }
+    };
     auto decode_group = [&](bool valid) {
+      // kModeProduct: the activations this vector will meet are requested before its nine chain steps, so that
+      // their latency (an L2 round trip once the payload stream has pushed them out of L1) hides behind the chain
+      uint4 early[kTokens];
+      if (MODE == kModeProduct && valid) {
+#pragma unroll
+        for (int t = 0; t < kTokens; ++t) {
+          if (t < p.tokens) early[t] = __ldg(reinterpret_cast<const uint4*>(p.activations + (static_cast<int64_t>(t) * p.vecs_per_row + col) * 8));
+        }
+      }
       const uint32_t coset = step(0, valid);
       const uint32_t coset_at = coset * table_size;
       int value[8];
@@ -314,7 +352,29 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
         float v[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fadd_rn(static_cast<float>(value[j]), half), scale);
-        if (BF16_OUT) {
+        if (MODE == kModeProduct) {
+          if (row != running_row) {
+            flush_products();
+            running_row = row;
+          }
+          // the weight as the dense layer sees it: rounded to bf16 first
+          float w[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) w[j] = __bfloat162float(__float2bfloat16_rn(v[j]));
+#pragma unroll
+          for (int t = 0; t < kTokens; ++t) {
+            if (t < p.tokens) {
+              const uint32_t words[4] = {early[t].x, early[t].y, early[t].z, early[t].w};
+              float sum = running[t];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                sum = fmaf(w[2 * j], __uint_as_float(words[j] << 16), sum);
+                sum = fmaf(w[2 * j + 1], __uint_as_float(words[j] & 0xFFFF0000u), sum);
+              }
+              running[t] = sum;
+            }
+          }
+        } else if (MODE == kModeStoreBf16) {
           // |z + c/2| < 2^15.5, so the product can only leave the bf16 range when the scale is astronomically large
           if (scale < 1.0e33f) {
             uint4 packed;
@@ -341,11 +401,34 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     };
     if (count & 31) decode_group(lane < static_cast<uint32_t>(count & 31));
     while (offset >= 0) decode_group(true);
+    if (MODE == kModeProduct) {
+      flush_products();
+      running_row = -1;
+    }
     const bool dirty = __any_sync(0xFFFFFFFFu, x != kStateMin);
     const int left = (cursor - origin) / 2;
     if (lane == 0) {
       if (left < 0) report(p.error, EP_STREAM_UNDERRUN);
       else if (left != 0 || dirty) report(p.error, EP_STREAM_NOT_CONSUMED);
+    }
+  }
+  if (MODE == kModeProduct) {
+    // The block that finishes last turns the accumulators into the layer's output: y = bf16(sum + bias).
+    __shared__ bool last_block;
+    __threadfence();
+    __syncthreads();
+    const int64_t total = static_cast<int64_t>(p.tokens) * p.rows;
+    if (threadIdx.x == 0) {
+      const unsigned int done = atomicAdd(reinterpret_cast<unsigned int*>(p.products + total), 1u);
+      last_block = done == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (last_block) {
+      __threadfence();
+      for (int64_t i = threadIdx.x; i < total; i += kDecodeThreads) {
+        const float sum = __ldcg(p.products + i);   // from L2, where the other blocks' atomic adds landed
+        p.product_out[i] = __float2bfloat16_rn(sum + (p.bias ? __bfloat162float(p.bias[i % p.rows]) : 0.0f));
+      }
     }
   }
 }
@@ -371,10 +454,12 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
                           const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
                           const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols, int prob_bits,
                           int64_t tile_elements, int max_alphabet, uint64_t* tables, int64_t table_bytes, int* error_dev,
-                          cudaStream_t s) {
+                          cudaStream_t s, const __nv_bfloat16* activations = nullptr, float* products = nullptr, int tokens = 0,
+                          const __nv_bfloat16* bias = nullptr, __nv_bfloat16* product_out = nullptr) {
   if (rows <= 0 || cols <= 0 || (cols & 7) != 0 || prob_bits < 9 || prob_bits > 15 || tile_elements <= 0 ||
       store_kind < 0 || store_kind > EP_STORE_BOOL || max_alphabet < 0 || max_alphabet > (1 << prob_bits) ||
-      payload_words < 0 || !offsets_dev || !states_dev || !stream_meta_dev || !freq_tables_dev || !scales_dev || !output_dev) {
+      payload_words < 0 || !offsets_dev || !states_dev || !stream_meta_dev || !freq_tables_dev || !scales_dev ||
+      (!output_dev && !products)) {
     return EP_ERR_INVALID_ARGUMENT;
   }
   if (payload_words > 0 && !payload_dev) return EP_ERR_INVALID_ARGUMENT;
@@ -402,34 +487,72 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   p.prob_bits = prob_bits;
   p.store_kind = store_kind;
   p.error = error_dev;
+  p.activations = activations;
+  p.products = products;
+  p.bias = bias;
+  p.product_out = product_out;
+  p.tokens = tokens;
+  p.rows = static_cast<int>(rows);
   // one persistent block per SM; with fewer tiles than SMs, one block per tile
   const unsigned blocks = static_cast<unsigned>(p.tiles < kSmCount ? p.tiles : kSmCount);
   const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
   if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) {
     const size_t shared = (static_cast<size_t>(kTables) * sizeof(uint32_t) << prob_bits) + ring_bytes;
-    if (store_kind == EP_STORE_BF16) {
-      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (products) {
+      auto kernel = tokens == 1 ? lattice_decode_kernel<true, kModeProduct, 1>
+                                : (tokens == 2 ? lattice_decode_kernel<true, kModeProduct, 2> : lattice_decode_kernel<true, kModeProduct, 4>);
+      EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+      kernel<<<blocks, kDecodeThreads, shared, s>>>(p);
+    } else if (store_kind == EP_STORE_BF16) {
+      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, kModeStoreBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(shared)));
-      lattice_decode_kernel<true, true><<<blocks, kDecodeThreads, shared, s>>>(p);
+      lattice_decode_kernel<true, kModeStoreBf16><<<blocks, kDecodeThreads, shared, s>>>(p);
     } else {
-      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, kModeStore>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(shared)));
-      lattice_decode_kernel<true, false><<<blocks, kDecodeThreads, shared, s>>>(p);
+      lattice_decode_kernel<true, kModeStore><<<blocks, kDecodeThreads, shared, s>>>(p);
     }
   } else {
     const int64_t needed = static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
     if (!tables || table_bytes < needed || (reinterpret_cast<uintptr_t>(tables) & 7u)) return EP_ERR_INVALID_ARGUMENT;
     lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, prob_bits);
     p.global_tables = tables;
-    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(ring_bytes)));
-    lattice_decode_kernel<false, false><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+    if (products) {
+      auto kernel = tokens == 1 ? lattice_decode_kernel<false, kModeProduct, 1>
+                                : (tokens == 2 ? lattice_decode_kernel<false, kModeProduct, 2> : lattice_decode_kernel<false, kModeProduct, 4>);
+      EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_bytes)));
+      kernel<<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+    } else {
+      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false, kModeStore>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(ring_bytes)));
+      lattice_decode_kernel<false, kModeStore><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+    }
   }
   return check_launch("lattice_decode_kernel");
 }
 
 }  // namespace
 }  // namespace ep
+
+extern "C" int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                         const uint32_t* states_dev, const int32_t* stream_meta_dev,
+                                         const uint16_t* freq_tables_dev, const float* scales_dev, int64_t rows, int64_t cols,
+                                         int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
+                                         int64_t table_scratch_bytes, const void* x_dev, const void* bias_dev, int tokens,
+                                         float* products_dev, void* y_dev, int* error_dev, ep_stream_t stream) {
+  if (!x_dev || !products_dev || !y_dev || tokens < 1 || tokens > ep::kMaxTokens || rows <= 0 || rows > 0x7FFFFFFF) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (reinterpret_cast<uintptr_t>(x_dev) & 15u) return EP_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t total = static_cast<int64_t>(tokens) * rows;
+  EP_CUDA_CHECK(cudaMemsetAsync(products_dev, 0, sizeof(float) * (total + 1), s));   // accumulators and the block counter
+  return ep::launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, scales_dev,
+                                   nullptr, EP_STORE_BF16, rows, cols, prob_bits, tile_elements, max_alphabet,
+                                   static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, error_dev, s,
+                                   static_cast<const __nv_bfloat16*>(x_dev), products_dev, tokens,
+                                   static_cast<const __nv_bfloat16*>(bias_dev), static_cast<__nv_bfloat16*>(y_dev));
+}
 
 extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                                  const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,

@@ -178,11 +178,34 @@ class CompressedLinear(torch.nn.Linear):
         return None if self.bias is None else self.bias.to(device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        fused = self._fused_forward(x)
+        if fused is not None:
+            return fused
         weight = self.dequantize(x.device)
         bias = self._bias_on(x.device)
         if _native_gemm_applies(x, weight, bias):
             return linear_forward(x, weight, bias)
         return F.linear(x, weight.to(x.dtype), bias)
+
+    def _fused_forward(self, x: torch.Tensor) -> torch.Tensor | None:
+        """At decode-time batch sizes (up to 4 tokens) a lossy-coded bf16 weight is multiplied while it is being
+        decoded, without ever being written out; None when that path does not apply."""
+        container = self.weight
+        if (type(self) is not CompressedLinear or not isinstance(container, CompressedTensor) or container.compress_method != "lattice_rans"
+                or container.encoded_dtype != torch.bfloat16 or container.dtype != torch.bfloat16 or x.dtype != torch.bfloat16
+                or not x.is_cuda or container.device != x.device or self.in_features % 8 != 0 or x.numel() == 0
+                or (torch.is_grad_enabled() and x.requires_grad)):
+            return None
+        flat = x.reshape(-1, x.shape[-1])
+        lane = container.scheme.lane()
+        if flat.shape[0] > lane.MAX_FUSED_TOKENS:
+            return None
+        from .schemes.base import packed_buffers
+        from .schemes.lattice_rans.format import LatticeBuffers
+
+        out = lane.linear_forward(packed_buffers(container.buffers, LatticeBuffers), shape=tuple(container.shape), x=flat,
+                                  bias=self._bias_on(x.device))
+        return out.reshape(*x.shape[:-1], self.out_features)
 
     def extra_repr(self) -> str:
         scheme = "auto" if self.config is None else name_for_config(self.config)

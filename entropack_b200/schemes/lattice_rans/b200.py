@@ -57,6 +57,43 @@ def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_bl
     return snap_to_container(out, dtype) if via_float else out
 
 
+MAX_FUSED_TOKENS = 4
+
+
+def linear_forward(buffers: LatticeBuffers, *, shape, x: torch.Tensor, bias: torch.Tensor | None,
+                   error: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ decode(W).T + bias`` for up to four rows of bf16 activations without materialising ``W``: the decode
+    kernel multiplies every reconstructed vector (rounded to bf16, as the dense weight would be) into the tokens'
+    dot products and adds them, per weight row, into fp32 accumulators; the block that finishes last adds the bias
+    and rounds to bf16. ``x`` is ``[tokens, cols]`` with ``cols`` equal to the stored (multiple of 8) column count."""
+    payload = buffers.payload
+    _native.require_cuda(payload)
+    info = decode_geometry(buffers._asdict(), shape)
+    rows, cols, prob_bits = info["rows"], info["cols"], info["prob_bits"]
+    tokens = x.shape[0]
+    if x.dtype != torch.bfloat16 or x.ndim != 2 or x.shape[1] != cols or not 1 <= tokens <= MAX_FUSED_TOKENS:
+        raise ValueError(f"fused forward takes bf16 activations [1..{MAX_FUSED_TOKENS}, {cols}], got {tuple(x.shape)} {x.dtype}")
+    device = payload.device
+    x = x.contiguous()
+    bias = None if bias is None else bias.to(torch.bfloat16).contiguous()
+    products = torch.empty(tokens * rows + 1, dtype=torch.float32, device=device)   # accumulators + the kernel's block counter
+    out = torch.empty((tokens, rows), dtype=torch.bfloat16, device=device)
+    alphabet = max_alphabet(buffers)
+    lib = _native.load()
+    scratch_bytes = lib.ep_lattice_decode_scratch_bytes(prob_bits, alphabet)
+    if scratch_bytes < 0:
+        _native.check(int(scratch_bytes), "lattice_rans fused forward")
+    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=device) if scratch_bytes else None
+    with torch.cuda.device(device):
+        status = lib.ep_lattice_linear_forward(
+            _native.ptr(payload), payload.numel(), _native.ptr(buffers.offsets), _native.ptr(buffers.states),
+            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), _native.ptr(buffers.scales), rows, cols, prob_bits,
+            info["tile_elements"], alphabet, _native.ptr(scratch), scratch_bytes, _native.ptr(x), _native.ptr(bias), tokens,
+            _native.ptr(products), _native.ptr(out), _native.ptr(error), _native.stream_handle(device))
+    _native.check(status, "lattice_rans fused forward")
+    return out
+
+
 def encode(weight, *, target_bpp, prob_bits, tile_elements, row_rdo_iterations, row_rdo_candidates,
            scale_search_iterations, scale_search_max_vectors) -> LatticeBuffers:
     from . import encoder

@@ -134,6 +134,21 @@ int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const 
                       int64_t tile_elements, int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes,
                       int* error_dev, ep_stream_t stream);
 
+/* Fused forward of a lossy-coded bf16 layer for 1..4 tokens: y[t][r] = bf16(sum_c x[t][c] * W[r][c] + bias[r]) with
+ * W the decoded weight rounded to bf16, which is never written out: the decode kernel multiplies every
+ * reconstructed vector into the tokens' dot products and adds them per weight row into products_dev
+ * (fp32, tokens * rows + 1 words, cleared by the call; the last word counts finished blocks, and the block
+ * that finishes last writes y). x_dev bf16 [tokens][cols], bias_dev bf16 [rows] or null, y_dev bf16
+ * [tokens][rows]. Decode arguments as for ep_lattice_decode. Sums are added with atomics, so the last bits of a
+ * result can differ between runs. Stands in for decode + F.linear of CompressedLinear.forward
+ * (entropack/linear/linear.py:125-130, 163-165) at decode-time batch sizes. */
+int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                              const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
+                              const float* scales_dev, int64_t rows, int64_t cols, int prob_bits, int64_t tile_elements,
+                              int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes, const void* x_dev,
+                              const void* bias_dev, int tokens, float* products_dev, void* y_dev, int* error_dev,
+                              ep_stream_t stream);
+
 /* Same decode for callers that cannot allocate device memory when they need it -- for example a
  * serving process that has given all of HBM to its own pool, or code running inside an allocator
  * callback. This entry point has no counterpart in the reference. The slot tables of the global-table

@@ -96,3 +96,34 @@ def test_int8_linear_forward_and_unsupported_rotation():
     assert _relative(layer(x), dense(x)) < 0.05
     with pytest.raises(NotImplementedError):
         ep.CompressedINT8Linear(512, 256, use_convrot=True)
+
+
+@pytest.mark.parametrize("tokens,features,bias", [(1, 3840, True), (3, 1536, False), (4, 264, True), (2, 1024, True)])
+def test_fused_small_batch_forward_matches_product_with_decoded_weight(tokens, features, bias):
+    """Up to 4 tokens the lossy-coded layer multiplies while it decodes (no dense weight is written). The result must
+    be the product with the decoded bf16 weight: fp32 sums in another order, then one bf16 rounding, 2^-7 relative to
+    the largest output."""
+    import entropack_b200 as ep
+    from entropack_b200.schemes.base import packed_buffers
+    from entropack_b200.schemes.lattice_rans.format import LatticeBuffers
+
+    g = torch.Generator(device="cuda").manual_seed(21)
+    dense = torch.nn.Linear(features, 520, bias=bias, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        dense.weight.copy_((torch.randn(520, features, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
+    layer = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
+    x = torch.randn(2, tokens // 2 if tokens % 2 == 0 else tokens, features, generator=g, device="cuda").to(torch.bfloat16)
+    x = x[:1] if tokens % 2 else x        # [1, tokens, K] or [2, tokens / 2, K]: leading dimensions are flattened
+    weight = layer.dequantize()
+    expected = torch.nn.functional.linear(x.float(), weight.float(), None if not bias else dense.bias.float())
+    assert layer._fused_forward(x) is not None
+    out = layer(x)
+    assert out.shape == expected.shape and out.dtype == torch.bfloat16
+    assert float((out.float() - expected).abs().max() / expected.abs().max()) <= 2.0 ** -7
+    # the error word stays clear and five tokens take the two-kernel path
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lane = layer.weight.scheme.lane()
+    lane.linear_forward(packed_buffers(layer.weight.buffers, LatticeBuffers), shape=tuple(layer.weight.shape), x=x.reshape(-1, features),
+                        bias=None, error=error)
+    assert int(error.item()) == 0
+    assert layer._fused_forward(torch.zeros(5, features, device="cuda", dtype=torch.bfloat16)) is None
