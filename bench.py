@@ -474,10 +474,10 @@ def measure_others(ep, device, flush, reps: int) -> dict:
     codes, weight_scale = layer.codes(device), layer.weight_quant_scale.to(device)
     for tokens in (16, 4096):
         x = torch.randn(tokens, 3840, generator=generator, device=device).to(torch.bfloat16)
-        a_codes, a_scale = layer._quantize_rows(x)
+        a_codes, a_scale = layer._quantize_activations(x)
         entry = {
             "compressed_forward_us": timed(lambda: layer(x)) * 1e3,
-            "quantize_activations_us": timed(lambda: layer._quantize_rows(x)) * 1e3,
+            "quantize_activations_us": timed(lambda: layer._quantize_activations(x)) * 1e3,
             "library_fp8_gemm_us": timed(lambda: layer._gemm(a_codes, codes, a_scale, weight_scale, torch.bfloat16)) * 1e3,
             "scaled_mm_us": timed(lambda: torch._scaled_mm(a_codes, codes.t(), scale_a=a_scale.unsqueeze(1),
                                                            scale_b=weight_scale.unsqueeze(0), out_dtype=torch.bfloat16)) * 1e3,

@@ -102,16 +102,17 @@ __global__ void __launch_bounds__(kStreamThreads) linear_stream_kernel(const __n
 }
 
 // ------------------------------------------------------------------------------------------------
-// per-row FP8 quantisation of activations (QuantizedLinear._quantize_rows, entropack/linear/linear.py:286-293)
+// per-row 8-bit quantisation of activations (QuantizedLinear._quantize_rows, entropack/linear/linear.py:286-293)
 // ------------------------------------------------------------------------------------------------
 // scale = max(absmax / 448, eps); code = e4m3(clamp(fl32(x / scale), -448, 448)), round to nearest even.
 __device__ __forceinline__ float as_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ float as_float(__half v) { return __half2float(v); }
 __device__ __forceinline__ float as_float(float v) { return v; }
 
-template <typename T>
-__global__ void __launch_bounds__(256) quantize_rows_fp8_kernel(const T* __restrict__ x, int64_t cols, uint8_t* __restrict__ codes,
-                                                                float* __restrict__ scales) {
+// INT8: scale = max(absmax / 127, eps), code = clamp(rint(x / scale), -127, 127) (round half to even, like torch.round).
+template <typename T, bool INT8>
+__global__ void __launch_bounds__(256) quantize_rows_8bit_kernel(const T* __restrict__ x, int64_t cols, uint8_t* __restrict__ codes,
+                                                                 float* __restrict__ scales) {
   __shared__ float partial[8];
   __shared__ float row_scale;
   const T* row = x + static_cast<int64_t>(blockIdx.x) * cols;
@@ -126,15 +127,20 @@ __global__ void __launch_bounds__(256) quantize_rows_fp8_kernel(const T* __restr
     for (int w = 1; w < 8; ++w) total = fmaxf(total, partial[w]);
     // absmax / 448 the way torch evaluates a division by a host scalar on a GPU: times the fp32 reciprocal;
     // clamped at the float32 epsilon like the reference
-    row_scale = fmaxf(__fmul_rn(total, __fdiv_rn(1.0f, 448.0f)), 1.1920928955078125e-07f);
+    row_scale = fmaxf(__fmul_rn(total, __fdiv_rn(1.0f, INT8 ? 127.0f : 448.0f)), 1.1920928955078125e-07f);
     scales[blockIdx.x] = row_scale;
   }
   __syncthreads();
   const float scale = row_scale;
   uint8_t* out = codes + static_cast<int64_t>(blockIdx.x) * cols;
   for (int64_t c = threadIdx.x; c < cols; c += 256) {
-    const float scaled = fminf(fmaxf(__fdiv_rn(as_float(row[c]), scale), -448.0f), 448.0f);
-    out[c] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3));
+    if (INT8) {
+      const float scaled = fminf(fmaxf(rintf(__fdiv_rn(as_float(row[c]), scale)), -127.0f), 127.0f);
+      out[c] = static_cast<uint8_t>(static_cast<int8_t>(static_cast<int>(scaled)));
+    } else {
+      const float scaled = fminf(fmaxf(__fdiv_rn(as_float(row[c]), scale), -448.0f), 448.0f);
+      out[c] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3));
+    }
   }
 }
 
@@ -175,12 +181,15 @@ template <int TILE_N, int A_ROWS> struct TileShape {
   static constexpr uint32_t kShapeBits = (static_cast<uint32_t>(TILE_N >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
   static constexpr uint32_t kInstructionBf16 = (1u << 4) | (1u << 7) | (1u << 10) | kShapeBits;
   static constexpr uint32_t kInstructionFp8 = (1u << 4) | kShapeBits;
+  // kind::i8: signed 8-bit A and B (format 1), 32-bit integer accumulators (format 2 in bits 4-5)
+  static constexpr uint32_t kInstructionInt8 = (2u << 4) | (1u << 7) | (1u << 10) | kShapeBits;
 };
 
 // Operand kinds of the tensor-core kernel. A shared-memory row is 128 bytes either way: 64 bf16 or 128 fp8
 // elements, consumed by four MMAs of 32 bytes of K each.
 constexpr int kOperandBf16 = 0;
 constexpr int kOperandFp8 = 1;
+constexpr int kOperandInt8 = 2;
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -237,8 +246,10 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   constexpr int kBytesA = Shape::kBytesA;
   constexpr int kBytesB = Shape::kBytesB;
   constexpr uint32_t kTmemColumns = Shape::kTmemColumns;
-  constexpr uint32_t kInstruction = OPERAND == kOperandFp8 ? Shape::kInstructionFp8 : Shape::kInstructionBf16;
-  constexpr int kElementsPerStep = OPERAND == kOperandFp8 ? 128 : 64;   // one 128-byte row of K
+  constexpr uint32_t kInstruction = OPERAND == kOperandFp8 ? Shape::kInstructionFp8
+                                    : (OPERAND == kOperandInt8 ? Shape::kInstructionInt8 : Shape::kInstructionBf16);
+  constexpr bool kScaled = OPERAND != kOperandBf16;                     // 8-bit operands: scaled epilogue
+  constexpr int kElementsPerStep = kScaled ? 128 : 64;                  // one 128-byte row of K
   extern __shared__ uint8_t raw_shared[];
   __shared__ __align__(8) uint64_t full[kStages];
   __shared__ __align__(8) uint64_t empty[kStages];
@@ -324,6 +335,10 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
                 ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          } else if (OPERAND == kOperandInt8) {
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
           } else {
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
@@ -378,7 +393,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         const int col = n0 + chunk * 32;
         if (row < p.m && col < p.n) {
-          if (OPERAND == kOperandFp8) {
+          if (kScaled) {
             // scaled epilogue of the 8-bit layers: the row's activation scale times the column's weight scale
             const float row_scale = p.row_scale[row];
             const int64_t at = static_cast<int64_t>(row) * p.n + col;
@@ -388,7 +403,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
               const bool inside = whole || col + c < p.n;
               const float scale = inside ? row_scale * p.column_scale[col + c] : 0.0f;
               const float b = inside && p.bias_f32 ? p.bias_f32[col + c] : 0.0f;
-              v[c] = __float_as_uint(fmaf(__uint_as_float(v[c]), scale, b));
+              const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(v[c])) : __uint_as_float(v[c]);
+              v[c] = __float_as_uint(fmaf(accumulated, scale, b));
             }
             if (p.y_f32) {
               if (whole) {
@@ -478,12 +494,12 @@ EncodeTiled tensor_map_encoder() {
 bool make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, int box_rows, int operand) {
   EncodeTiled encode = tensor_map_encoder();
   if (!encode) return false;
-  const int element_bytes = operand == kOperandFp8 ? 1 : 2;
+  const int element_bytes = operand == kOperandBf16 ? 2 : 1;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k) * element_bytes};
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / element_bytes), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t element_strides[2] = {1, 1};
-  return encode(map, operand == kOperandFp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+  return encode(map, operand == kOperandBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                 const_cast<void*>(base), dims, strides, box, element_strides,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -582,9 +598,11 @@ extern "C" int ep_linear_forward(const void* x_dev, const void* weight_dev, cons
   return launch_best_tile<kOperandBf16>(x_dev, weight_dev, p, s);
 }
 
-extern "C" int ep_linear_forward_fp8(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev,
-                                     const float* weight_scale_dev, const float* bias_dev, void* y_dev, int y_is_f32, int64_t m,
-                                     int64_t n, int64_t k, int* error_dev, ep_stream_t stream) {
+namespace {
+template <int OPERAND>
+int scaled_forward(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev, const float* weight_scale_dev,
+                   const float* bias_dev, void* y_dev, int y_is_f32, int64_t m, int64_t n, int64_t k, int* error_dev,
+                   ep_stream_t stream) {
   if (!x_codes_dev || !weight_codes_dev || !x_scale_dev || !weight_scale_dev || !y_dev || m <= 0 || n <= 0 || k <= 0 ||
       (k & 15) != 0 || m > 0x7FFFFFFF || n > 0x7FFFFFFF || k > 0x7FFFFFFF) {
     return EP_ERR_INVALID_ARGUMENT;
@@ -603,11 +621,27 @@ extern "C" int ep_linear_forward_fp8(const void* x_codes_dev, const void* weight
   p.bias_f32 = bias_dev;
   if (y_is_f32) p.y_f32 = static_cast<float*>(y_dev);
   else p.y = static_cast<__nv_bfloat16*>(y_dev);
-  return launch_best_tile<kOperandFp8>(x_codes_dev, weight_codes_dev, p, static_cast<cudaStream_t>(stream));
+  return launch_best_tile<OPERAND>(x_codes_dev, weight_codes_dev, p, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+extern "C" int ep_linear_forward_fp8(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev,
+                                     const float* weight_scale_dev, const float* bias_dev, void* y_dev, int y_is_f32, int64_t m,
+                                     int64_t n, int64_t k, int* error_dev, ep_stream_t stream) {
+  return scaled_forward<kOperandFp8>(x_codes_dev, weight_codes_dev, x_scale_dev, weight_scale_dev, bias_dev, y_dev, y_is_f32, m, n, k,
+                                     error_dev, stream);
 }
 
-extern "C" int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
-                                    ep_stream_t stream) {
+extern "C" int ep_linear_forward_int8(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev,
+                                      const float* weight_scale_dev, const float* bias_dev, void* y_dev, int y_is_f32, int64_t m,
+                                      int64_t n, int64_t k, int* error_dev, ep_stream_t stream) {
+  return scaled_forward<kOperandInt8>(x_codes_dev, weight_codes_dev, x_scale_dev, weight_scale_dev, bias_dev, y_dev, y_is_f32, m, n, k,
+                                      error_dev, stream);
+}
+
+namespace {
+template <bool INT8>
+int quantize_rows(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev, ep_stream_t stream) {
   if (!x_dev || !codes_dev || !scales_dev || rows <= 0 || cols <= 0 || rows > 0x7FFFFFFF || x_kind < 0 || x_kind > 2) {
     return EP_ERR_INVALID_ARGUMENT;
   }
@@ -615,9 +649,20 @@ extern "C" int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows,
   const unsigned blocks = static_cast<unsigned>(rows);
   auto* codes = static_cast<uint8_t*>(codes_dev);
   switch (x_kind) {
-    case 0: quantize_rows_fp8_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_dev), cols, codes, scales_dev); break;
-    case 1: quantize_rows_fp8_kernel<<<blocks, 256, 0, s>>>(static_cast<const __half*>(x_dev), cols, codes, scales_dev); break;
-    default: quantize_rows_fp8_kernel<<<blocks, 256, 0, s>>>(static_cast<const float*>(x_dev), cols, codes, scales_dev); break;
+    case 0: quantize_rows_8bit_kernel<__nv_bfloat16, INT8><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x_dev), cols, codes, scales_dev); break;
+    case 1: quantize_rows_8bit_kernel<__half, INT8><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x_dev), cols, codes, scales_dev); break;
+    default: quantize_rows_8bit_kernel<float, INT8><<<blocks, 256, 0, s>>>(static_cast<const float*>(x_dev), cols, codes, scales_dev); break;
   }
-  return check_launch("quantize_rows_fp8_kernel");
+  return check_launch("quantize_rows_8bit_kernel");
+}
+}  // namespace
+
+extern "C" int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
+                                    ep_stream_t stream) {
+  return quantize_rows<false>(x_dev, x_kind, rows, cols, codes_dev, scales_dev, stream);
+}
+
+extern "C" int ep_quantize_rows_int8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
+                                     ep_stream_t stream) {
+  return quantize_rows<true>(x_dev, x_kind, rows, cols, codes_dev, scales_dev, stream);
 }

@@ -24,7 +24,7 @@ from .registry import default_config, get_scheme, name_for_config, require_dtype
 from .schemes import EntroPackLossyConfig, RawConfig
 
 _EPS = torch.finfo(torch.float32).eps
-_FP8_SOURCE_KINDS = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+_SOURCE_KINDS = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 
 
 def _native_gemm_applies(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None) -> bool:
@@ -358,7 +358,7 @@ class QuantizedLinear(CompressedLinear):
 
     def _forward8(self, x: torch.Tensor) -> torch.Tensor:
         flat = x.reshape(-1, x.shape[-1])
-        activation, scale = self._quantize_rows(flat.detach())
+        activation, scale = self._quantize_activations(flat.detach())
         codes = self.codes(x.device)
         weight_scale = self._scale(codes.device)
         tokens = activation.shape[0]
@@ -373,8 +373,41 @@ class QuantizedLinear(CompressedLinear):
         bias = self._bias_on(device)
         return None if bias is None else _pad_to(bias, 0, columns)
 
+    #: names of the library's activation quantiser and scaled 8-bit product for this code type
+    quantize_entry: ClassVar[str]
+    gemm_entry: ClassVar[str]
+
+    def _quantize_activations(self, tensor: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Weights (once, at compression time) go through the torch expression of ``_quantize_rows``; activations on a
+        GPU, every forward, through one kernel that computes the same scale and the same codes."""
+        kind = _SOURCE_KINDS.get(tensor.dtype)
+        if not tensor.is_cuda or kind is None or tensor.numel() == 0:
+            return self._quantize_rows(tensor)
+        flat = tensor.reshape(-1, tensor.shape[-1]).contiguous()
+        codes = torch.empty(flat.shape, dtype=self.code_dtype, device=flat.device)
+        scale = torch.empty(flat.shape[0], dtype=torch.float32, device=flat.device)
+        with torch.cuda.device(flat.device):
+            status = getattr(_native.load(), self.quantize_entry)(
+                _native.ptr(flat), kind, flat.shape[0], flat.shape[1], _native.ptr(codes), _native.ptr(scale),
+                _native.stream_handle(flat.device))
+        _native.check(status, "8-bit activation quantisation")
+        return codes, scale
+
     def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
-        raise NotImplementedError
+        """Scaled 8-bit product on the library's tcgen05 kernel (bf16 or fp32 results; fp16 goes through fp32)."""
+        bias = self._bias_padded(codes.device, weight_scale.shape[0])
+        direct = out_dtype in (torch.bfloat16, torch.float32)
+        out = torch.empty((activation.shape[0], codes.shape[0]), dtype=out_dtype if direct else torch.float32, device=codes.device)
+        activation, codes = activation.contiguous(), codes.contiguous()
+        activation_scale, weight_scale = activation_scale.contiguous(), weight_scale.contiguous()
+        bias32 = None if bias is None else bias.float().contiguous()   # held until after the launch
+        with torch.cuda.device(codes.device):
+            status = getattr(_native.load(), self.gemm_entry)(
+                _native.ptr(activation), _native.ptr(codes), _native.ptr(activation_scale), _native.ptr(weight_scale),
+                _native.ptr(bias32), _native.ptr(out), int(out.dtype == torch.float32), activation.shape[0], codes.shape[0],
+                activation.shape[1], None, _native.stream_handle(codes.device))
+        _native.check(status, "8-bit linear forward")
+        return out if direct else out.to(out_dtype)
 
 
 class CompressedFP8Linear(QuantizedLinear):
@@ -385,50 +418,22 @@ class CompressedFP8Linear(QuantizedLinear):
     rounds_to_integer = False
     code_alignment = 16
     min_tokens = 1
-    min_capability = (8, 9)
+    min_capability = (10, 0)
 
-    def _quantize_rows(self, tensor: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-        """Weights (once, at compression time) go through the torch expression of the base class; activations on a
-        GPU, every forward, through one kernel that computes the same scale and codes."""
-        kind = _FP8_SOURCE_KINDS.get(tensor.dtype)
-        if not tensor.is_cuda or kind is None or tensor.numel() == 0:
-            return super()._quantize_rows(tensor)
-        flat = tensor.reshape(-1, tensor.shape[-1]).contiguous()
-        codes = torch.empty(flat.shape, dtype=torch.float8_e4m3fn, device=flat.device)
-        scale = torch.empty(flat.shape[0], dtype=torch.float32, device=flat.device)
-        with torch.cuda.device(flat.device):
-            status = _native.load().ep_quantize_rows_fp8(_native.ptr(flat), kind, flat.shape[0], flat.shape[1], _native.ptr(codes),
-                                                         _native.ptr(scale), _native.stream_handle(flat.device))
-        _native.check(status, "fp8 activation quantisation")
-        return codes, scale
-
-    def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
-        """Scaled FP8 product on the library's tcgen05 kernel (bf16 or fp32 results; fp16 goes through fp32)."""
-        bias = self._bias_padded(codes.device, weight_scale.shape[0])
-        direct = out_dtype in (torch.bfloat16, torch.float32)
-        out = torch.empty((activation.shape[0], codes.shape[0]), dtype=out_dtype if direct else torch.float32, device=codes.device)
-        activation, codes = activation.contiguous(), codes.contiguous()
-        activation_scale, weight_scale = activation_scale.contiguous(), weight_scale.contiguous()
-        bias32 = None if bias is None else bias.float().contiguous()   # held until after the launch
-        with torch.cuda.device(codes.device):
-            status = _native.load().ep_linear_forward_fp8(
-                _native.ptr(activation), _native.ptr(codes), _native.ptr(activation_scale), _native.ptr(weight_scale),
-                _native.ptr(bias32), _native.ptr(out), int(out.dtype == torch.float32), activation.shape[0], codes.shape[0],
-                activation.shape[1], None, _native.stream_handle(codes.device))
-        _native.check(status, "fp8 linear forward")
-        return out if direct else out.to(out_dtype)
+    quantize_entry = "ep_quantize_rows_fp8"
+    gemm_entry = "ep_linear_forward_fp8"
 
 
 class CompressedINT8Linear(QuantizedLinear):
-    """Symmetric INT8 weights and activations with per-row scales (``torch._int_mm``). The reference's optional
-    ConvRot rotation is not implemented: ``use_convrot=True`` raises."""
+    """Symmetric INT8 weights and activations with per-row scales, multiplied on the library's ``kind::i8`` tensor-core
+    kernel. The reference's optional ConvRot rotation is not implemented: ``use_convrot=True`` raises."""
 
     code_dtype = torch.int8
     code_max = 127.0
     rounds_to_integer = True
-    code_alignment = 8
-    min_tokens = 17
-    min_capability = (8, 0)
+    code_alignment = 16     # the tensor-core kernel takes K in multiples of 16 bytes
+    min_tokens = 1          # (the reference pads to 17 rows for torch._int_mm; this kernel has no such floor)
+    min_capability = (10, 0)
 
     def __init__(self, in_features, out_features, bias=True, *, config=None, device=None, dtype=torch.bfloat16,
                  use_convrot: bool = False, convrot_groupsize: int = 256):
@@ -437,13 +442,8 @@ class CompressedINT8Linear(QuantizedLinear):
         self.use_convrot = False
         super().__init__(in_features, out_features, bias=bias, config=config, device=device, dtype=dtype)
 
-    def _gemm(self, activation, codes, activation_scale, weight_scale, out_dtype):
-        out = torch._int_mm(activation, codes.t()).to(torch.float32)
-        out.mul_(activation_scale.unsqueeze(1))
-        bias = self._bias_padded(codes.device, weight_scale.shape[0])
-        if bias is None:
-            return out.mul_(weight_scale).to(out_dtype)
-        return torch.addcmul(bias.to(torch.float32), out, weight_scale).to(out_dtype)
+    quantize_entry = "ep_quantize_rows_int8"
+    gemm_entry = "ep_linear_forward_int8"
 
 
 __all__ = ["CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "QuantizedLinear"]

@@ -308,6 +308,16 @@ int ep_linear_forward_fp8(const void* x_codes_dev, const void* weight_codes_dev,
 int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
                          ep_stream_t stream);
 
+/* The INT8 layer's counterparts: signed 8-bit codes, kind::i8 product with 32-bit integer accumulators, the same scaled
+ * epilogue; scales_dev[r] = max(absmax / 127, eps32), codes = clamp(rint(x / scale), -127, 127). Stand in for
+ * torch._int_mm plus the scale/bias arithmetic of CompressedINT8Linear (entropack/linear/linear.py:421-490, without the
+ * ConvRot rotation) and for its _quantize_rows. */
+int ep_linear_forward_int8(const void* x_codes_dev, const void* weight_codes_dev, const float* x_scale_dev,
+                           const float* weight_scale_dev, const float* bias_dev, void* y_dev, int y_is_f32, int64_t m, int64_t n,
+                           int64_t k, int* error_dev, ep_stream_t stream);
+int ep_quantize_rows_int8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
+                          ep_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -77,3 +77,48 @@ def test_fp8_gemm_matches_scaled_mm(m, n, k, out_dtype, with_bias):
         library = torch._scaled_mm(a, b.t(), scale_a=a_scale.unsqueeze(1), scale_b=b_scale.unsqueeze(0),
                                    bias=None if bias is None else bias.to(torch.bfloat16), out_dtype=torch.bfloat16)
         assert float((out.float() - library.float()).abs().max() / expected.abs().max()) <= 1e-2
+
+
+def test_int8_row_quantisation_matches_the_torch_expression():
+    from entropack_b200 import _native
+
+    generator = torch.Generator(device="cuda").manual_seed(4)
+    x = (torch.randn(33, 777, generator=generator, device="cuda") * 3).to(torch.bfloat16)
+    x[2] = 0
+    x[3, :8] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 127.0, -127.0], device="cuda").to(torch.bfloat16) * (x[3].abs().max() / 127)
+    codes = torch.empty(x.shape, dtype=torch.int8, device="cuda")
+    scales = torch.empty(x.shape[0], dtype=torch.float32, device="cuda")
+    _native.check(_native.load().ep_quantize_rows_int8(_native.ptr(x), 0, x.shape[0], x.shape[1], _native.ptr(codes), _native.ptr(scales),
+                                                       _native.stream_handle(x.device)), "quantise")
+    flat = x.float()
+    expected_scale = (flat.abs().amax(dim=1) / 127.0).clamp(min=torch.finfo(torch.float32).eps)
+    expected_codes = (flat / expected_scale.unsqueeze(1)).round().clamp(-127.0, 127.0).to(torch.int8)
+    assert torch.equal(scales, expected_scale)
+    assert torch.equal(codes, expected_codes)
+
+
+@pytest.mark.parametrize("m,n,k,out_dtype,with_bias", [
+    (1, 768, 1024, torch.float32, True), (40, 1000, 2048, torch.float32, False), (4096, 3840, 3840, torch.bfloat16, True),
+])
+def test_int8_gemm_is_the_exact_integer_product_scaled(m, n, k, out_dtype, with_bias):
+    """kind::i8 accumulates in 32-bit integers, so the product itself is exact; what remains is one fp32 multiply-add
+    per output (1e-6 relative to the largest output) and, for bf16 results, their rounding (2^-8)."""
+    from entropack_b200 import _native
+
+    generator = torch.Generator(device="cuda").manual_seed(12)
+    a = torch.randint(-127, 128, (m, k), generator=generator, device="cuda", dtype=torch.int8)
+    b = torch.randint(-127, 128, (n, k), generator=generator, device="cuda", dtype=torch.int8)
+    a_scale = torch.rand(m, generator=generator, device="cuda") * 0.01 + 0.001
+    b_scale = torch.rand(n, generator=generator, device="cuda") * 0.01 + 0.001
+    bias = torch.randn(n, generator=generator, device="cuda") if with_bias else None
+    out = torch.empty((m, n), dtype=out_dtype, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _native.check(_native.load().ep_linear_forward_int8(
+        _native.ptr(a), _native.ptr(b), _native.ptr(a_scale), _native.ptr(b_scale), _native.ptr(bias), _native.ptr(out),
+        int(out_dtype == torch.float32), m, n, k, _native.ptr(error), _native.stream_handle(out.device)), "int8 gemm")
+    assert int(error.item()) == 0
+    exact = (a.double() @ b.double().t()) * a_scale.double().unsqueeze(1) * b_scale.double().unsqueeze(0)
+    if bias is not None:
+        exact = exact + bias.double()
+    tolerance = 1e-6 if out_dtype is torch.float32 else 2.0 ** -8
+    assert float((out.double() - exact).abs().max() / exact.abs().max()) <= tolerance
