@@ -52,6 +52,7 @@ _PROTOTYPES = {
     "ep_quantize_rows_fp8": [_ptr, _i32, _i64, _i64, _ptr, _ptr, _ptr],
     "ep_linear_forward_int8": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i64, _ptr, _ptr],
     "ep_quantize_rows_int8": [_ptr, _i32, _i64, _i64, _ptr, _ptr, _ptr],
+    "ep_convrot_rows": [_ptr, _i32, _i64, _i64, _i32, _ptr, _ptr],
     "ep_lattice_row_rms": [_ptr, _i32, _i64, _i64, _ptr, _ptr],
     "ep_lattice_quantize": [_ptr, _i32, _ptr, _i64, _i64, _f32, _ptr, _ptr, _ptr, _ptr],
     "ep_lattice_histogram": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _ptr, _ptr],

@@ -24,6 +24,12 @@ namespace {
 
 constexpr int kMaxLevels = 64;
 constexpr uint32_t kPointerFlag = 0x8000u;
+// Multi-symbol table: indexed by the next kMultiBits bits of the stream, an entry holds up to three whole codewords that
+// fit in those bits: symbols in bytes 0-2, their total length in bits 24-27, their number in bits 28-29 (0: the first
+// codeword is longer than the window, take the one-symbol path). Exponent codes average under three bits, so most
+// look-ups deliver three symbols.
+constexpr int kMultiBits = 10;
+constexpr int kMultiEntries = 1 << kMultiBits;
 
 __device__ __forceinline__ uint32_t byte_swap(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
 
@@ -52,10 +58,12 @@ struct DecodeParams {
 
 __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint32_t shared[];
-  // layout: fused tables u16[levels][256] | scan u32[32] | stream words u32[block_words + 2] | exponents u8[stage_elems + 8]
+  // layout: fused tables u16[levels][256] | multi-symbol table u32[1024] | scan u32[32] | stream words u32[block_words + 2] |
+  //         exponents u8[stage_elems + 8]
   const int levels = p.num_luts - 1;
   uint16_t* const tables = reinterpret_cast<uint16_t*>(shared);
-  uint32_t* const scan = shared + levels * 128;
+  uint32_t* const multi = shared + levels * 128;
+  uint32_t* const scan = multi + kMultiEntries;
   uint32_t* const words = scan + 32;
   const int block_bytes = p.bytes_per_thread * p.threads_per_block;
   const int block_words = ((block_bytes + 3) / 4 + 3) & ~1;  // two look-ahead words, even count keeps what follows 8-byte aligned
@@ -85,6 +93,20 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     words[w] = value;
   }
 
+  __syncthreads();   // level-0 entries are in place
+  for (int v = threadIdx.x; v < kMultiEntries; v += blockDim.x) {
+    uint32_t packed = 0, used = 0, found = 0;
+    while (found < 3u) {
+      const uint32_t rest = (static_cast<uint32_t>(v) << used) & (kMultiEntries - 1);      // bits not yet consumed, left-aligned
+      const uint32_t entry = tables[rest >> (kMultiBits - 8)];
+      const uint32_t length = (entry >> 8) & 0x3Fu;
+      if ((entry & kPointerFlag) || length == 0u || used + length > static_cast<uint32_t>(kMultiBits)) break;
+      packed |= (entry & 0xFFu) << (8 * found);
+      used += length;
+      ++found;
+    }
+    multi[v] = packed | (used << 24) | (found << 28);
+  }
   const bool active = static_cast<int>(threadIdx.x) < p.threads_per_block;
   const int64_t region = static_cast<int64_t>(blockIdx.x) * p.threads_per_block + threadIdx.x;
   const uint32_t meta = active ? p.thread_meta[region] : 0u;
@@ -131,17 +153,29 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   uint32_t word_index = bit >> 5;
   uint32_t current = words[min(word_index, static_cast<uint32_t>(block_words - 2))];
   uint32_t next = words[min(word_index + 1, static_cast<uint32_t>(block_words - 1))];
-  for (int i = 0; i < count; ++i) {
+  for (int i = 0; i < count;) {
     const uint32_t window = __funnelshift_l(next, current, bit & 31u);
-    uint32_t entry = tables[window >> 24];
-    uint32_t peek = window;
+    // three or more symbols to go: whatever the window's first bits hold whole may be taken at once
+    const uint32_t fast = count - i >= 3 ? multi[window >> (32 - kMultiBits)] : 0u;
+    const uint32_t found = fast >> 28;
+    if (found) {
+      exponents[local_base + i] = static_cast<uint8_t>(fast);
+      if (found > 1u) exponents[local_base + i + 1] = static_cast<uint8_t>(fast >> 8);
+      if (found > 2u) exponents[local_base + i + 2] = static_cast<uint8_t>(fast >> 16);
+      i += static_cast<int>(found);
+      bit += (fast >> 24) & 0xFu;
+    } else {
+      uint32_t entry = tables[window >> 24];
+      uint32_t peek = window;
 #pragma unroll 1
-    for (int hop = 0; hop < 3 && (entry & kPointerFlag); ++hop) {  // code longer than this level: the next byte picks in the child level
-      peek <<= 8;
-      entry = tables[(entry & 0xFFu) * 256u + (peek >> 24)];
+      for (int hop = 0; hop < 3 && (entry & kPointerFlag); ++hop) {  // code longer than this level: the next byte picks in the child level
+        peek <<= 8;
+        entry = tables[(entry & 0xFFu) * 256u + (peek >> 24)];
+      }
+      exponents[local_base + i] = static_cast<uint8_t>(entry);
+      bit += (entry >> 8) & 0x3Fu;
+      ++i;
     }
-    exponents[local_base + i] = static_cast<uint8_t>(entry);
-    bit += (entry >> 8) & 0x3Fu;
     if ((bit >> 5) != word_index) {
       word_index = bit >> 5;
       current = next;
@@ -407,7 +441,7 @@ extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const u
   p.error = error_dev;
   const int threads = (threads_per_block + 31) / 32 * 32;
   const size_t block_words = ((block_bytes + 3) / 4 + 3) & ~size_t(1);
-  const size_t shared = static_cast<size_t>(num_luts - 1) * 512 + 128 + block_words * 4 + static_cast<size_t>(max_block_elems) + 16;
+  const size_t shared = static_cast<size_t>(num_luts - 1) * 512 + kMultiEntries * 4 + 128 + block_words * 4 + static_cast<size_t>(max_block_elems) + 16;
   if (shared > 227 * 1024) return EP_ERR_UNSUPPORTED;
   if (shared > 48 * 1024) {
     EP_CUDA_CHECK(cudaFuncSetAttribute(dfloat11_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));

@@ -145,6 +145,42 @@ __global__ void __launch_bounds__(256) quantize_rows_8bit_kernel(const T* __rest
 }
 
 // ------------------------------------------------------------------------------------------------
+// ConvRot: y = x . R per group of `group` consecutive features (entropack/linear/convrot.py:35-61)
+// ------------------------------------------------------------------------------------------------
+// R is the Kronecker power of the 4 x 4 matrix ((1,1,1,-1),(1,1,-1,1),(1,-1,1,1),(-1,1,1,1)) divided by sqrt(group):
+// symmetric and its own inverse, so the same pass rotates activations, rotates weight rows and undoes either. A
+// Kronecker power factors into one radix-4 butterfly pass per base-4 digit of the index, so a row costs
+// log4(group) passes over fp32 values in shared memory instead of a group x group product.
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+
+template <typename T>
+__global__ void __launch_bounds__(256) convrot_rows_kernel(const T* __restrict__ x, int64_t cols, int group, T* __restrict__ y) {
+  extern __shared__ float row_values[];
+  const T* source = x + static_cast<int64_t>(blockIdx.x) * cols;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) row_values[c] = as_float(source[c]);
+  __syncthreads();
+  const int64_t quads = cols / 4;
+  for (int stride = 1; stride < group; stride *= 4) {
+    for (int64_t q = threadIdx.x; q < quads; q += 256) {
+      // the q-th index whose base-4 digit at this stride is zero
+      const int64_t base = (q / stride) * stride * 4 + q % stride;
+      const float a = row_values[base], b = row_values[base + stride], c = row_values[base + 2 * stride], d = row_values[base + 3 * stride];
+      row_values[base] = (a + b) + (c - d);
+      row_values[base + stride] = (a + b) - (c - d);
+      row_values[base + 2 * stride] = (a - b) + (c + d);
+      row_values[base + 3 * stride] = (c + d) - (a - b);
+    }
+    __syncthreads();
+  }
+  const float scale = rsqrtf(static_cast<float>(group));
+  T* target = y + static_cast<int64_t>(blockIdx.x) * cols;
+  for (int64_t c = threadIdx.x; c < cols; c += 256) target[c] = from_float<T>(row_values[c] * scale);
+}
+
+// ------------------------------------------------------------------------------------------------
 // tcgen05 GEMM
 // ------------------------------------------------------------------------------------------------
 constexpr int kTileM = 128;
@@ -665,4 +701,31 @@ extern "C" int ep_quantize_rows_fp8(const void* x_dev, int x_kind, int64_t rows,
 extern "C" int ep_quantize_rows_int8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
                                      ep_stream_t stream) {
   return quantize_rows<true>(x_dev, x_kind, rows, cols, codes_dev, scales_dev, stream);
+}
+
+extern "C" int ep_convrot_rows(const void* x_dev, int x_kind, int64_t rows, int64_t cols, int group, void* y_dev, ep_stream_t stream) {
+  const bool power_of_four = group >= 4 && (group & (group - 1)) == 0 && (__builtin_ctz(static_cast<unsigned>(group)) % 2) == 0;
+  if (!x_dev || !y_dev || rows <= 0 || cols <= 0 || rows > 0x7FFFFFFF || x_kind < 0 || x_kind > 2 || !power_of_four ||
+      cols % group != 0) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  const size_t shared = static_cast<size_t>(cols) * sizeof(float);
+  if (shared > 200 * 1024) return EP_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>(rows);
+  switch (x_kind) {
+    case 0:
+      EP_CUDA_CHECK(cudaFuncSetAttribute(convrot_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+      convrot_rows_kernel<<<blocks, 256, shared, s>>>(static_cast<const __nv_bfloat16*>(x_dev), cols, group, static_cast<__nv_bfloat16*>(y_dev));
+      break;
+    case 1:
+      EP_CUDA_CHECK(cudaFuncSetAttribute(convrot_rows_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+      convrot_rows_kernel<<<blocks, 256, shared, s>>>(static_cast<const __half*>(x_dev), cols, group, static_cast<__half*>(y_dev));
+      break;
+    default:
+      EP_CUDA_CHECK(cudaFuncSetAttribute(convrot_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+      convrot_rows_kernel<<<blocks, 256, shared, s>>>(static_cast<const float*>(x_dev), cols, group, static_cast<float*>(y_dev));
+      break;
+  }
+  return check_launch("convrot_rows_kernel");
 }

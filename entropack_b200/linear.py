@@ -20,6 +20,7 @@ from torch.nn import functional as F
 
 from . import _native
 from .compression import CompressedTensor, compress, decompress
+from .convrot import choose_convrot_group, rotate_activation, rotate_weight
 from .registry import default_config, get_scheme, name_for_config, require_dtype
 from .schemes import EntroPackLossyConfig, RawConfig
 
@@ -326,9 +327,18 @@ class QuantizedLinear(CompressedLinear):
             scaled = scaled.round()
         return scaled.clamp(-self.code_max, self.code_max).to(self.code_dtype), scale
 
+    def _prepare_activation(self, flat: torch.Tensor) -> torch.Tensor:
+        return flat
+
+    def _prepare_weight_source(self, weight: torch.Tensor) -> torch.Tensor:
+        return weight
+
+    def _restore_weight_basis(self, weight: torch.Tensor) -> torch.Tensor:
+        return weight
+
     def compress_weight(self, weight: torch.Tensor) -> None:
         self._check_weight_shape(weight.shape)
-        codes, scale = self._quantize_rows(weight.detach())
+        codes, scale = self._quantize_rows(self._prepare_weight_source(weight.detach()))
         self.weight = torch.nn.Parameter(self._compress_tensor(codes), requires_grad=False)
         self.weight_quant_scale = scale
 
@@ -341,7 +351,7 @@ class QuantizedLinear(CompressedLinear):
 
     def dequantize(self, device: str | torch.device | None = None) -> torch.Tensor:
         codes = self.codes(device)
-        return (codes.float() * self._scale(codes.device).unsqueeze(1)).to(self._init_dtype)
+        return self._restore_weight_basis(codes.float() * self._scale(codes.device).unsqueeze(1)).to(self._init_dtype)
 
     def _require_8bit_gemm(self, device: torch.device) -> None:
         if device.type != "cuda":
@@ -357,7 +367,7 @@ class QuantizedLinear(CompressedLinear):
         return _W8A8Function.apply(x, self) if x.requires_grad else self._forward8(x)
 
     def _forward8(self, x: torch.Tensor) -> torch.Tensor:
-        flat = x.reshape(-1, x.shape[-1])
+        flat = self._prepare_activation(x.reshape(-1, x.shape[-1]))
         activation, scale = self._quantize_activations(flat.detach())
         codes = self.codes(x.device)
         weight_scale = self._scale(codes.device)
@@ -426,7 +436,8 @@ class CompressedFP8Linear(QuantizedLinear):
 
 class CompressedINT8Linear(QuantizedLinear):
     """Symmetric INT8 weights and activations with per-row scales, multiplied on the library's ``kind::i8`` tensor-core
-    kernel. The reference's optional ConvRot rotation is not implemented: ``use_convrot=True`` raises."""
+    kernel. ``use_convrot`` rotates the weight before quantisation and the activations before theirs (the flag is not
+    stored in the checkpoint, as in the reference)."""
 
     code_dtype = torch.int8
     code_max = 127.0
@@ -437,10 +448,21 @@ class CompressedINT8Linear(QuantizedLinear):
 
     def __init__(self, in_features, out_features, bias=True, *, config=None, device=None, dtype=torch.bfloat16,
                  use_convrot: bool = False, convrot_groupsize: int = 256):
-        if use_convrot:
-            raise NotImplementedError("ConvRot rotation is outside this package's scope; construct with use_convrot=False")
-        self.use_convrot = False
+        self.use_convrot = bool(use_convrot)
+        self._convrot_group = choose_convrot_group(in_features, convrot_groupsize) if self.use_convrot else None
+        if self.use_convrot and self._convrot_group is None:
+            raise ValueError(f"use_convrot requires in_features {in_features} to contain a power-of-four group; "
+                             f"got convrot_groupsize={convrot_groupsize}")
         super().__init__(in_features, out_features, bias=bias, config=config, device=device, dtype=dtype)
+
+    def _prepare_activation(self, flat: torch.Tensor) -> torch.Tensor:
+        return rotate_activation(flat, self._convrot_group) if self.use_convrot else flat
+
+    def _prepare_weight_source(self, weight: torch.Tensor) -> torch.Tensor:
+        return rotate_weight(weight, self._convrot_group) if self.use_convrot else weight
+
+    def _restore_weight_basis(self, weight: torch.Tensor) -> torch.Tensor:
+        return rotate_weight(weight, self._convrot_group, inverse=True) if self.use_convrot else weight
 
     quantize_entry = "ep_quantize_rows_int8"
     gemm_entry = "ep_linear_forward_int8"

@@ -318,6 +318,12 @@ int ep_linear_forward_int8(const void* x_codes_dev, const void* weight_codes_dev
 int ep_quantize_rows_int8(const void* x_dev, int x_kind, int64_t rows, int64_t cols, void* codes_dev, float* scales_dev,
                           ep_stream_t stream);
 
+/* y[r] = x[r] . R applied to every group of `group` consecutive features (group a power of four that divides cols), R the
+ * ConvRot matrix of entropack/linear/convrot.py:35-45: symmetric and self-inverse, so this one call stands in for
+ * rotate_activation and for rotate_weight in both directions (convrot.py:48-61). x_kind: 0 bf16, 1 fp16, 2 fp32; the
+ * arithmetic is fp32 with one rounding at the end. */
+int ep_convrot_rows(const void* x_dev, int x_kind, int64_t rows, int64_t cols, int group, void* y_dev, ep_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

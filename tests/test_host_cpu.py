@@ -130,6 +130,19 @@ def test_rate_tradeoff_keeps_the_rate_budget():
     assert distortion[row, choice].sum() <= distortion[:, 2].sum()
 
 
+
+def test_convrot_group_rules():
+    from entropack_b200 import convrot
+
+    assert [convrot.is_convrot_group(v) for v in (4, 16, 64, 256, 1024, 8, 2, 0, 12, 4.0, True)] == [True] * 5 + [False] * 6
+    assert convrot.choose_convrot_group(3840) == 256 and convrot.choose_convrot_group(320) == 64
+    assert convrot.choose_convrot_group(3840, 16) == 16 and convrot.choose_convrot_group(6) is None
+    with pytest.raises(ValueError):
+        convrot.choose_convrot_group(3840, 32)
+    matrix = convrot.build_convrot_matrix(64)
+    assert torch.equal(matrix, matrix.t()) and torch.allclose(matrix @ matrix, torch.eye(64), atol=1e-6)
+
+
 def test_no_cpu_fallback():
     import entropack_b200 as ep
 

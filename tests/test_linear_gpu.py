@@ -94,8 +94,45 @@ def test_int8_linear_forward_and_unsupported_rotation():
     layer = ep.CompressedINT8Linear.from_linear(dense)
     x = torch.randn(32, 512, device="cuda", dtype=torch.bfloat16)
     assert _relative(layer(x), dense(x)) < 0.05
-    with pytest.raises(NotImplementedError):
-        ep.CompressedINT8Linear(512, 256, use_convrot=True)
+
+
+@pytest.mark.parametrize("features,group", [(512, 256), (320, 64), (48, 16), (12, 4)])
+def test_convrot_kernel_is_the_reference_rotation(features, group):
+    """The butterfly passes against the dense Kronecker matrix (fp32: 1e-5 of the largest value), its self-inverse
+    property, and the group chosen for each width."""
+    from entropack_b200 import convrot
+
+    assert convrot.choose_convrot_group(features) == group
+    generator = torch.Generator(device="cuda").manual_seed(8)
+    x = torch.randn(37, features, generator=generator, device="cuda")
+    matrix = convrot.build_convrot_matrix(group, device="cuda")
+    expected = (x.reshape(37, features // group, group) @ matrix).reshape(37, features)
+    rotated = convrot.rotate_activation(x, group)
+    assert float((rotated - expected).abs().max()) <= 1e-5 * float(expected.abs().max())
+    assert float((convrot.rotate_weight(rotated, group, inverse=True) - x).abs().max()) <= 1e-5 * float(x.abs().max())
+    half = convrot.rotate_activation(x.to(torch.bfloat16), group)
+    assert half.dtype == torch.bfloat16 and float((half.float() - expected).abs().max()) <= 2.0 ** -7 * float(expected.abs().max())
+
+
+def test_int8_linear_with_convrot_tames_outlier_channels():
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(9)
+    dense = torch.nn.Linear(1024, 256, bias=True, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        weight = torch.randn(256, 1024, generator=g, device="cuda") * 0.02
+        weight[:, 7] *= 40.0          # one input channel dominates every row's scale
+        dense.weight.copy_(weight.to(torch.bfloat16))
+    x = torch.randn(64, 1024, generator=g, device="cuda").to(torch.bfloat16)
+    plain = ep.CompressedINT8Linear.from_linear(dense)
+    rotated = ep.CompressedINT8Linear.from_linear(dense, use_convrot=True)
+    assert rotated._convrot_group == 256 and set(rotated.state_dict()) == set(plain.state_dict())
+    exact = dense(x)
+    # the rotation spreads the outlier channel over its group: finer weight codes, smaller error
+    assert _relative(rotated(x), exact) < _relative(plain(x), exact) < 0.2
+    assert _relative(rotated.dequantize(), dense.weight) < 0.02
+    with pytest.raises(ValueError):
+        ep.CompressedINT8Linear(514, 256, use_convrot=True)
 
 
 @pytest.mark.parametrize("tokens,features,bias", [(1, 3840, True), (3, 1536, False), (4, 264, True), (2, 1024, True)])
