@@ -30,6 +30,7 @@ constexpr uint32_t kPointerFlag = 0x8000u;
 // look-ups deliver three symbols.
 constexpr int kMultiBits = 10;
 constexpr int kMultiEntries = 1 << kMultiBits;
+constexpr int kMaxFormatBlocks = 4;   // blocks of the format served by one CUDA block, at most
 
 __device__ __forceinline__ uint32_t byte_swap(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
 
@@ -53,24 +54,35 @@ struct DecodeParams {
   int bytes_per_thread;
   int threads_per_block;
   int stage_elems;
+  int64_t blocks;   // blocks of the format (threads_per_block regions each)
+  int groups;       // how many of them one CUDA block serves
   int* error;
 };
 
 __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParams p) {
   extern __shared__ __align__(16) uint32_t shared[];
-  // layout: fused tables u16[levels][256] | multi-symbol table u32[1024] | scan u32[32] | stream words u32[block_words + 2] |
-  //         exponents u8[stage_elems + 8]
+  // A CUDA block serves `p.groups` consecutive blocks of the format side by side, one per group of `group_threads`
+  // threads, so that the code tables are staged and the multi-symbol table built once for all of them.
+  // layout: fused tables u16[levels][256] | multi-symbol table u32[1024] | scan u32[kMaxFormatBlocks][32] |
+  //         per group: stream words u32[block_words] | exponents u8[stage_bytes]
   const int levels = p.num_luts - 1;
   uint16_t* const tables = reinterpret_cast<uint16_t*>(shared);
   uint32_t* const multi = shared + levels * 128;
-  uint32_t* const scan = multi + kMultiEntries;
-  uint32_t* const words = scan + 32;
+  uint32_t* const scan_base = multi + kMultiEntries;
   const int block_bytes = p.bytes_per_thread * p.threads_per_block;
   const int block_words = ((block_bytes + 3) / 4 + 3) & ~1;  // two look-ahead words, even count keeps what follows 8-byte aligned
+  const int stage_bytes = (p.stage_elems + 16 + 15) & ~15;
+  const int group_threads = blockDim.x / p.groups;           // a multiple of 32
+  const int group = threadIdx.x / group_threads;
+  const int member = threadIdx.x - group * group_threads;     // this thread's index inside its format block
+  const int64_t format_block = static_cast<int64_t>(blockIdx.x) * p.groups + group;
+  const bool present = format_block < p.blocks;               // the last CUDA block may have idle groups
+  uint32_t* const scan = scan_base + group * 32;
+  uint32_t* const words = scan_base + kMaxFormatBlocks * 32 + group * (block_words + stage_bytes / 4);
   uint8_t* const exponents_base = reinterpret_cast<uint8_t*>(words + block_words);
   const uint32_t lane = lane_id();
-  const int warp = threadIdx.x >> 5;
-  const int warps = blockDim.x >> 5;
+  const int warp = member >> 5;
+  const int warps = group_threads >> 5;
 
   const uint32_t pointer_min = levels > 1 ? 256u - (levels - 1) : 256u;
   const uint8_t* lengths = p.luts + levels * 256;
@@ -80,8 +92,8 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     tables[i] = entry >= pointer_min ? static_cast<uint16_t>(kPointerFlag | min(256u - entry, static_cast<uint32_t>(levels - 1)))
                                      : static_cast<uint16_t>(entry | (static_cast<uint32_t>(lengths[entry]) << 8));
   }
-  const int64_t block_base = static_cast<int64_t>(blockIdx.x) * block_bytes;
-  for (int w = threadIdx.x; w < block_words; w += blockDim.x) {
+  const int64_t block_base = format_block * block_bytes;
+  for (int w = member; w < block_words && present; w += group_threads) {
     const int64_t byte = block_base + static_cast<int64_t>(w) * 4;
     uint32_t value = 0;
     if (byte + 4 <= p.n_bytes && ((reinterpret_cast<uintptr_t>(p.encoded) + byte) & 3u) == 0) {
@@ -107,12 +119,12 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     }
     multi[v] = packed | (used << 24) | (found << 28);
   }
-  const bool active = static_cast<int>(threadIdx.x) < p.threads_per_block;
-  const int64_t region = static_cast<int64_t>(blockIdx.x) * p.threads_per_block + threadIdx.x;
+  const bool active = present && member < p.threads_per_block;
+  const int64_t region = format_block * p.threads_per_block + member;
   const uint32_t meta = active ? p.thread_meta[region] : 0u;
   int count = static_cast<int>(meta & 2047u);
 
-  // exclusive scan of the counts over the block
+  // exclusive scan of the counts over the format block
   uint32_t inclusive = static_cast<uint32_t>(count);
 #pragma unroll
   for (int step = 1; step < 32; step <<= 1) {
@@ -133,11 +145,11 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   __syncthreads();
   int local_base = static_cast<int>((warp > 0 ? scan[warp - 1] : 0u) + inclusive) - count;
 
-  int64_t out_base = p.output_positions[blockIdx.x];
-  int64_t block_elems = static_cast<int64_t>(p.output_positions[blockIdx.x + 1]) - out_base;
+  int64_t out_base = present ? p.output_positions[format_block] : 0;
+  int64_t block_elems = present ? static_cast<int64_t>(p.output_positions[format_block + 1]) - out_base : 0;
   if (out_base > p.n_elements || block_elems < 0 || block_elems > p.stage_elems || out_base + block_elems > p.n_elements) {
     // inconsistent positions (corrupt container): write nothing for this block
-    if (threadIdx.x == 0) report(p.error, EP_STREAM_BAD_OFFSETS);
+    if (member == 0) report(p.error, EP_STREAM_BAD_OFFSETS);
     out_base = 0;
     block_elems = 0;
     count = 0;
@@ -149,7 +161,7 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   }
 
   // walk this region's codewords
-  uint32_t bit = static_cast<uint32_t>(threadIdx.x) * p.bytes_per_thread * 8u + (meta >> 11);
+  uint32_t bit = static_cast<uint32_t>(member) * p.bytes_per_thread * 8u + (meta >> 11);
   uint32_t word_index = bit >> 5;
   uint32_t current = words[min(word_index, static_cast<uint32_t>(block_words - 2))];
   uint32_t next = words[min(word_index + 1, static_cast<uint32_t>(block_words - 1))];
@@ -186,14 +198,14 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
 
   // write back: 8 elements (16 bytes of bf16) per thread per iteration, aligned on 8-element groups
   const int64_t head = min(block_elems, (8 - (out_base & 7)) & 7);
-  for (int64_t j = threadIdx.x; j < head; j += blockDim.x) {
+  for (int64_t j = member; j < head; j += group_threads) {
     const int64_t g = out_base + j;
     const uint32_t sm = p.sign_mantissa[g];
     p.out[g] = static_cast<uint16_t>(((sm & 0x80u) << 8) | (static_cast<uint32_t>(exponents[j]) << 7) | (sm & 0x7Fu));
   }
   const int64_t groups = (block_elems - head) >> 3;
   const bool wide = (reinterpret_cast<uintptr_t>(p.sign_mantissa) & 7u) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
-  for (int64_t c = threadIdx.x; c < groups; c += blockDim.x) {
+  for (int64_t c = member; c < groups; c += group_threads) {
     const int64_t j = head + (c << 3);
     const int64_t g = out_base + j;
     if (wide) {
@@ -211,7 +223,7 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
       }
     }
   }
-  for (int64_t j = head + (groups << 3) + threadIdx.x; j < block_elems; j += blockDim.x) {
+  for (int64_t j = head + (groups << 3) + member; j < block_elems; j += group_threads) {
     const int64_t g = out_base + j;
     const uint32_t sm = p.sign_mantissa[g];
     p.out[g] = static_cast<uint16_t>(((sm & 0x80u) << 8) | (static_cast<uint32_t>(exponents[j]) << 7) | (sm & 0x7Fu));
@@ -441,12 +453,20 @@ extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const u
   p.error = error_dev;
   const int threads = (threads_per_block + 31) / 32 * 32;
   const size_t block_words = ((block_bytes + 3) / 4 + 3) & ~size_t(1);
-  const size_t shared = static_cast<size_t>(num_luts - 1) * 512 + kMultiEntries * 4 + 128 + block_words * 4 + static_cast<size_t>(max_block_elems) + 16;
+  const size_t stage_bytes = (static_cast<size_t>(max_block_elems) + 16 + 15) & ~size_t(15);
+  const size_t fixed = static_cast<size_t>(num_luts - 1) * 512 + kMultiEntries * 4 + kMaxFormatBlocks * 32 * 4;
+  const size_t per_group = block_words * 4 + stage_bytes;
+  int groups = kMaxFormatBlocks;
+  while (groups > 1 && (threads * groups > 1024 || fixed + groups * per_group > 48 * 1024 || blocks < groups)) groups >>= 1;
+  const size_t shared = fixed + groups * per_group;
   if (shared > 227 * 1024) return EP_ERR_UNSUPPORTED;
   if (shared > 48 * 1024) {
     EP_CUDA_CHECK(cudaFuncSetAttribute(dfloat11_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
   }
-  dfloat11_decode_kernel<<<static_cast<unsigned>(blocks), threads, shared, static_cast<cudaStream_t>(stream)>>>(p);
+  p.blocks = blocks;
+  p.groups = groups;
+  const int64_t grid = (blocks + groups - 1) / groups;
+  dfloat11_decode_kernel<<<static_cast<unsigned>(grid), threads * groups, shared, static_cast<cudaStream_t>(stream)>>>(p);
   return check_launch("dfloat11_decode_kernel");
 }
 
