@@ -348,6 +348,18 @@ tile_ans_decode_kernel(const DecodeParams p) {
   for (int block_lo = ((count - 1) / kBlockElems) * kBlockElems; block_lo >= 0; block_lo -= kBlockElems) {
     const int block_hi = min(block_lo + kBlockElems, count);
     const bool full = block_hi - block_lo == kBlockElems;
+    // The merge phase below reads this block's raw bytes (512 per raw lane) right after the chain phase; asking L2 for
+    // them now takes the DRAM part of that latency off the warp's serial path. Four threads per raw lane, one 128-byte
+    // line each (plus one for a stream that straddles a fifth line).
+    if (NLANES > 1 && raw_mask != 0u) {
+#pragma unroll
+      for (int b = 0; b < NLANES; ++b) {
+        if (((raw_mask >> b) & 1u) && lane < 5u) {
+          const uint8_t* line = payload_bytes + 2 * static_cast<int64_t>(raw_begin[b]) + block_lo + static_cast<int>(lane) * 128;
+          if (line < payload_bytes + 2 * p.payload_words) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
+        }
+      }
+    }
     // ---- chain phase: groups of 32 symbols, back to front; only the tile's last group can be partial
     if (full) {
       static_assert(kBlockElems == 512, "sixteen steps are written out below");
