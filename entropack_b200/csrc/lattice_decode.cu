@@ -225,9 +225,93 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
 
   if (threadIdx.x < kTables) sym_min[threadIdx.x] = p.stream_meta[threadIdx.x * 4 + 1];
   if (SHARED_TABLES) {
-    for (int t = warp; t < kTables; t += kDecodeWarps) {
-      fill_table<uint32_t>(shared_tables + static_cast<size_t>(t) * table_size, p.stream_meta, p.freq_tables, t, table_size, lane,
-                           pack_entry32);
+    // The 17 slot tables are built by the whole block, one work item per (table, run of 32 symbols): first the
+    // frequency total of every run, then, from the totals before it, each run's first slot; inside a run every thread
+    // fills the slots of its own symbol when that symbol is rare and the warp shares the slots of a frequent one. (One
+    // warp per table, symbol after symbol, costs a table of a few hundred mostly rare symbols thousands of cycles while
+    // the rest of the block waits.)
+    constexpr int kRuns = kSharedMaxAlphabet / 32;
+    constexpr int kMaxEntries = kTables * kSharedMaxAlphabet;
+    __shared__ uint32_t run_total[kTables][kRuns];
+    __shared__ uint32_t run_start[kTables][kRuns];
+    __shared__ int meta[kTables * 4];
+    // The stream records and the stored frequencies come to shared memory first, in two passes of the whole block (the
+    // rings' space is free until decoding starts), so the table build below never waits on global memory.
+    if (threadIdx.x < kTables * 4) meta[threadIdx.x] = p.stream_meta[threadIdx.x];
+    for (uint32_t slot = threadIdx.x; slot < kTables * table_size; slot += kDecodeThreads) shared_tables[slot] = 0u;
+    __syncthreads();
+    uint16_t* const staged_freq = reinterpret_cast<uint16_t*>(shared_tables + kTables * table_size);
+    const int entries = max(0, min(meta[(kTables - 1) * 4 + 2] + meta[(kTables - 1) * 4 + 3], kMaxEntries));
+    for (int i = threadIdx.x; i < entries; i += kDecodeThreads) staged_freq[i] = p.freq_tables[i];
+    __syncthreads();
+    auto frequency = [&](int t, int symbol) -> uint32_t {
+      const int alphabet = min(meta[t * 4 + 3], kSharedMaxAlphabet);
+      const int at = meta[t * 4 + 2] + symbol;
+      return symbol < alphabet && at >= 0 && at < entries ? staged_freq[at] : 0u;
+    };
+    // live work items, table after table: first_item[t] .. first_item[t + 1] are table t's runs of 32 symbols
+    __shared__ int first_item[kTables + 1];
+    if (threadIdx.x == 0) {
+      int total = 0;
+      for (int t = 0; t < kTables; ++t) {
+        first_item[t] = total;
+        total += (max(0, min(meta[t * 4 + 3], kSharedMaxAlphabet)) + 31) / 32;
+      }
+      first_item[kTables] = total;
+    }
+    __syncthreads();
+    const int items = first_item[kTables];
+    auto locate = [&](int item, int& t, int& run) {
+      t = 0;
+      while (t + 1 < kTables && first_item[t + 1] <= item) ++t;
+      run = item - first_item[t];
+    };
+    for (int item = warp; item < items; item += kDecodeWarps) {
+      int t, run;
+      locate(item, t, run);
+      const uint32_t freq = frequency(t, run * 32 + static_cast<int>(lane));
+      const uint32_t total = __reduce_add_sync(0xFFFFFFFFu, freq);
+      if (lane == 0) run_total[t][run] = total;
+    }
+    __syncthreads();
+    // each run's first slot: the totals of the runs before it in its table
+    if (threadIdx.x < kTables * kRuns) {
+      const int t = threadIdx.x / kRuns, run = threadIdx.x % kRuns;
+      if (run < first_item[t + 1] - first_item[t]) {
+        uint32_t before = 0;
+        for (int r = 0; r < run; ++r) before += run_total[t][r];
+        run_start[t][run] = before;
+      }
+    }
+    __syncthreads();
+    for (int item = warp; item < items; item += kDecodeWarps) {
+      int t, run;
+      locate(item, t, run);
+      uint32_t* table = shared_tables + static_cast<size_t>(t) * table_size;
+      const int symbol = run * 32 + static_cast<int>(lane);
+      const uint32_t freq = frequency(t, symbol);
+      uint32_t inclusive = freq;
+#pragma unroll
+      for (int step = 1; step < 32; step <<= 1) {
+        const uint32_t below = __shfl_up_sync(0xFFFFFFFFu, inclusive, step);
+        if (lane >= static_cast<uint32_t>(step)) inclusive += below;
+      }
+      const uint32_t first = run_start[t][run] + inclusive - freq;    // this symbol's first slot
+      // rare symbols: every thread fills its own
+      const bool rare = freq < 32u;
+      const uint32_t longest = __reduce_max_sync(0xFFFFFFFFu, rare ? freq : 0u);
+      for (uint32_t j = 0; j < longest; ++j) {
+        if (rare && j < freq && first + j < table_size) table[first + j] = pack_entry32(static_cast<uint32_t>(symbol), freq, j);
+      }
+      // frequent symbols: the warp shares each one's slots
+      uint32_t frequent = __ballot_sync(0xFFFFFFFFu, !rare);
+      while (frequent) {
+        const int k = __ffs(frequent) - 1;
+        frequent &= frequent - 1u;
+        const uint32_t f = __shfl_sync(0xFFFFFFFFu, freq, k);
+        const uint32_t at = __shfl_sync(0xFFFFFFFFu, first, k);
+        for (uint32_t j = lane; j < f && at + j < table_size; j += 32) table[at + j] = pack_entry32(static_cast<uint32_t>(run * 32 + k), f, j);
+      }
     }
   }
   __syncthreads();

@@ -25,6 +25,13 @@ def make_tensor(kind: str, rows: int, cols: int, device, seed: int = 1) -> torch
         return (x * 0.02).to(torch.bfloat16)
     if kind == "fp32":
         return x * 0.02
+    if kind == "bf16_outliers":
+        # 1 % of the rows heavy-tailed (Student-t, 3 degrees of freedom): the lossy benchmark tensor
+        picks = torch.randperm(rows, generator=generator, device=device)[: max(1, rows // 100)]
+        student = torch.randn(picks.numel(), cols, generator=generator, device=device) / \
+            torch.randn(picks.numel(), cols, 3, generator=generator, device=device).square().mean(-1).sqrt()
+        x[picks] = student
+        return (x * 0.02).to(torch.bfloat16)
     if kind == "int16_pair":
         # two independent small-valued bytes per element: both byte lanes are entropy coded
         low = (x * 20).round().clamp(-127, 127).to(torch.int16) & 0xFF
