@@ -422,7 +422,7 @@ def measure_others(ep, device, flush, reps: int) -> dict:
     student = torch.randn(41, 11008, generator=generator, device=device) / torch.randn(41, 11008, 3, generator=generator, device=device).square().mean(-1).sqrt()
     weight[heavy] = student * 0.02
     weight = weight.to(torch.bfloat16)
-    for bpp in (4.0,):
+    for bpp in (2.3, 3.5, 4.0, 6.0):
         config = ep.EntroPackLossyConfig(target_bpp=bpp)
         container = ep.compress(weight, config)
         restored = ep.decompress(container, config)

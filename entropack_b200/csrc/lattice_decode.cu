@@ -30,7 +30,13 @@ constexpr int kTables = 17;
 constexpr int kDecodeWarps = 24;
 constexpr int kDecodeThreads = kDecodeWarps * 32;
 constexpr int kSharedMaxProbBits = 11;
-constexpr int kSharedMaxAlphabet = 512;
+constexpr int kSharedMaxAlphabet = 512;     // 32-bit entries hold 9 bits of symbol
+constexpr int kWideMaxAlphabet = 2048;      // wide shared tables: a byte per slot carries the symbol's high bits
+// Where the 17 slot tables live.
+constexpr int kTablesGlobal = 0;       // 64-bit entries in caller scratch (prob_bits above 11)
+constexpr int kTablesShared = 1;       // packed 32-bit entries in shared memory: symbol | freq << 9 | delta << 21
+constexpr int kTablesSharedWide = 2;   // shared memory, alphabets up to 2048: symbol low 10 bits | (freq - 1) << 10 | delta << 21,
+                                       // plus the symbol's bits above 10 in a byte table behind the 17 word tables
 
 struct LatticeDecodeParams {
   const uint16_t* payload;
@@ -211,9 +217,9 @@ __global__ void __launch_bounds__(32) lattice_build_tables_kernel(uint64_t* tabl
 }
 
 // ---- decode ----------------------------------------------------------------------------------------
-template <bool SHARED_TABLES, int MODE, int TOKENS = 0>
+template <int TABLES, int MODE, int TOKENS = 0>
 __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const LatticeDecodeParams p) {
-  extern __shared__ __align__(16) uint32_t shared_tables[];  // [17][table_size] when SHARED_TABLES
+  extern __shared__ __align__(16) uint32_t shared_tables[];  // [17][table_size] on the shared paths (then [17][table_size] bytes when wide)
   __shared__ int sym_min[kTables + 1];
   const uint32_t lane = lane_id();
   const int warp = threadIdx.x >> 5;
@@ -224,14 +230,20 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
   const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
 
   if (threadIdx.x < kTables) sym_min[threadIdx.x] = p.stream_meta[threadIdx.x * 4 + 1];
-  if (SHARED_TABLES) {
+  if (TABLES != kTablesGlobal) {
     // The 17 slot tables are built by the whole block, one work item per (table, run of 32 symbols): first the
     // frequency total of every run, then, from the totals before it, each run's first slot; inside a run every thread
     // fills the slots of its own symbol when that symbol is rare and the warp shares the slots of a frequent one. (One
     // warp per table, symbol after symbol, costs a table of a few hundred mostly rare symbols thousands of cycles while
     // the rest of the block waits.)
-    constexpr int kRuns = kSharedMaxAlphabet / 32;
-    constexpr int kMaxEntries = kTables * kSharedMaxAlphabet;
+    constexpr bool kWide = TABLES == kTablesSharedWide;
+    constexpr int kAlphabetLimit = kWide ? kWideMaxAlphabet : kSharedMaxAlphabet;
+    constexpr int kRuns = kAlphabetLimit / 32;
+    constexpr int kMaxEntries = kTables * kAlphabetLimit;
+    uint8_t* const high_bits = reinterpret_cast<uint8_t*>(shared_tables + kTables * table_size);   // wide tables only
+    const auto pack = [](uint32_t symbol, uint32_t freq, uint32_t delta) {
+      return kWide ? ((symbol & 0x3FFu) | ((freq - 1u) << 10) | (delta << 21)) : pack_entry32(symbol, freq, delta);
+    };
     __shared__ uint32_t run_total[kTables][kRuns];
     __shared__ uint32_t run_start[kTables][kRuns];
     __shared__ int meta[kTables * 4];
@@ -239,15 +251,26 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     // rings' space is free until decoding starts), so the table build below never waits on global memory.
     if (threadIdx.x < kTables * 4) meta[threadIdx.x] = p.stream_meta[threadIdx.x];
     for (uint32_t slot = threadIdx.x; slot < kTables * table_size; slot += kDecodeThreads) shared_tables[slot] = 0u;
+    if (kWide) {
+      for (uint32_t slot = threadIdx.x; slot < kTables * table_size / 4; slot += kDecodeThreads) {
+        reinterpret_cast<uint32_t*>(high_bits)[slot] = 0u;
+      }
+    }
     __syncthreads();
-    uint16_t* const staged_freq = reinterpret_cast<uint16_t*>(shared_tables + kTables * table_size);
+    // landing area for the frequencies: the rings' space, behind the tables; a container with more entries than fit
+    // there (only possible with wide tables) has them read from global memory instead
+    uint16_t* const staged_freq = reinterpret_cast<uint16_t*>(shared_tables + kTables * table_size) + (kWide ? kTables * table_size / 2 : 0);
     const int entries = max(0, min(meta[(kTables - 1) * 4 + 2] + meta[(kTables - 1) * 4 + 3], kMaxEntries));
-    for (int i = threadIdx.x; i < entries; i += kDecodeThreads) staged_freq[i] = p.freq_tables[i];
+    const bool staged = entries * 2 <= kDecodeWarps * static_cast<int>(kRingWords) * 2;
+    if (staged) {
+      for (int i = threadIdx.x; i < entries; i += kDecodeThreads) staged_freq[i] = p.freq_tables[i];
+    }
     __syncthreads();
     auto frequency = [&](int t, int symbol) -> uint32_t {
-      const int alphabet = min(meta[t * 4 + 3], kSharedMaxAlphabet);
+      const int alphabet = min(meta[t * 4 + 3], kAlphabetLimit);
       const int at = meta[t * 4 + 2] + symbol;
-      return symbol < alphabet && at >= 0 && at < entries ? staged_freq[at] : 0u;
+      if (!(symbol < alphabet && at >= 0 && at < entries)) return 0u;
+      return staged ? staged_freq[at] : __ldg(p.freq_tables + at);
     };
     // live work items, table after table: first_item[t] .. first_item[t + 1] are table t's runs of 32 symbols
     __shared__ int first_item[kTables + 1];
@@ -255,7 +278,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       int total = 0;
       for (int t = 0; t < kTables; ++t) {
         first_item[t] = total;
-        total += (max(0, min(meta[t * 4 + 3], kSharedMaxAlphabet)) + 31) / 32;
+        total += (max(0, min(meta[t * 4 + 3], kAlphabetLimit)) + 31) / 32;
       }
       first_item[kTables] = total;
     }
@@ -275,8 +298,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     }
     __syncthreads();
     // each run's first slot: the totals of the runs before it in its table
-    if (threadIdx.x < kTables * kRuns) {
-      const int t = threadIdx.x / kRuns, run = threadIdx.x % kRuns;
+    for (int index = threadIdx.x; index < kTables * kRuns; index += kDecodeThreads) {
+      const int t = index / kRuns, run = index % kRuns;
       if (run < first_item[t + 1] - first_item[t]) {
         uint32_t before = 0;
         for (int r = 0; r < run; ++r) before += run_total[t][r];
@@ -301,7 +324,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       const bool rare = freq < 32u;
       const uint32_t longest = __reduce_max_sync(0xFFFFFFFFu, rare ? freq : 0u);
       for (uint32_t j = 0; j < longest; ++j) {
-        if (rare && j < freq && first + j < table_size) table[first + j] = pack_entry32(static_cast<uint32_t>(symbol), freq, j);
+        if (rare && j < freq && first + j < table_size) {
+          table[first + j] = pack(static_cast<uint32_t>(symbol), freq, j);
+          if (kWide) high_bits[static_cast<size_t>(t) * table_size + first + j] = static_cast<uint8_t>(symbol >> 10);
+        }
       }
       // frequent symbols: the warp shares each one's slots
       uint32_t frequent = __ballot_sync(0xFFFFFFFFu, !rare);
@@ -310,14 +336,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
         frequent &= frequent - 1u;
         const uint32_t f = __shfl_sync(0xFFFFFFFFu, freq, k);
         const uint32_t at = __shfl_sync(0xFFFFFFFFu, first, k);
-        for (uint32_t j = lane; j < f && at + j < table_size; j += 32) table[at + j] = pack_entry32(static_cast<uint32_t>(run * 32 + k), f, j);
+        for (uint32_t j = lane; j < f && at + j < table_size; j += 32) {
+          table[at + j] = pack(static_cast<uint32_t>(run * 32 + k), f, j);
+          if (kWide) high_bits[static_cast<size_t>(t) * table_size + at + j] = static_cast<uint8_t>((run * 32 + k) >> 10);
+        }
       }
     }
   }
   __syncthreads();
 
   constexpr uint32_t kRingBytes = kRingWords * 2u;
-  const uint32_t table_bytes = SHARED_TABLES ? kTables * table_size * 4u : 0u;
+  const uint32_t table_bytes = TABLES == kTablesGlobal ? 0u : kTables * table_size * (TABLES == kTablesSharedWide ? 5u : 4u);
   const uint32_t ring = ((shared_base + table_bytes + kRingBytes - 1u) & ~(kRingBytes - 1u)) + static_cast<uint32_t>(warp) * kRingBytes;
 
   // tile t goes to block t mod grid: every SM gets its share even when there are fewer tiles than warp slots
@@ -356,10 +385,15 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       uint32_t symbol = 0;
       if (valid) {
         const uint32_t slot = x & slot_mask;
-        if (SHARED_TABLES) {
+        if (TABLES == kTablesShared) {
           const uint32_t entry = shared_tables[table_at + slot];
           symbol = entry & 0x1FFu;
           x = ((entry >> 9) & 0xFFFu) * (x >> prob_bits) + (entry >> 21);
+        } else if (TABLES == kTablesSharedWide) {
+          const uint32_t entry = shared_tables[table_at + slot];
+          const uint32_t high = reinterpret_cast<const uint8_t*>(shared_tables + kTables * table_size)[table_at + slot];
+          symbol = (entry & 0x3FFu) | (high << 10);
+          x = (((entry >> 10) & 0x7FFu) + 1u) * (x >> prob_bits) + (entry >> 21);
         } else {
           const uint64_t entry = __ldg(p.global_tables + table_at + slot);
           symbol = static_cast<uint32_t>(entry) & 0xFFFFu;
@@ -524,7 +558,7 @@ using namespace ep;
 
 extern "C" int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphabet) {
   if (prob_bits < 9 || prob_bits > 15) return EP_ERR_INVALID_ARGUMENT;
-  if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) return 0;
+  if (prob_bits <= kSharedMaxProbBits) return 0;   // both shared-memory layouts together cover every alphabet up to 2^11
   return static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
 }
 
@@ -580,21 +614,34 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   // one persistent block per SM; with fewer tiles than SMs, one block per tile
   const unsigned blocks = static_cast<unsigned>(p.tiles < kSmCount ? p.tiles : kSmCount);
   const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
+  const auto launch = [&](auto kernel, size_t shared) -> int {
+    EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+    kernel<<<blocks, kDecodeThreads, shared, s>>>(p);
+    return EP_OK;
+  };
+  int launched = EP_OK;
   if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) {
     const size_t shared = (static_cast<size_t>(kTables) * sizeof(uint32_t) << prob_bits) + ring_bytes;
     if (products) {
-      auto kernel = tokens == 1 ? lattice_decode_kernel<true, kModeProduct, 1>
-                                : (tokens == 2 ? lattice_decode_kernel<true, kModeProduct, 2> : lattice_decode_kernel<true, kModeProduct, 4>);
-      EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
-      kernel<<<blocks, kDecodeThreads, shared, s>>>(p);
+      launched = tokens == 1 ? launch(lattice_decode_kernel<kTablesShared, kModeProduct, 1>, shared)
+               : tokens == 2 ? launch(lattice_decode_kernel<kTablesShared, kModeProduct, 2>, shared)
+                             : launch(lattice_decode_kernel<kTablesShared, kModeProduct, 4>, shared);
     } else if (store_kind == EP_STORE_BF16) {
-      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, kModeStoreBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(shared)));
-      lattice_decode_kernel<true, kModeStoreBf16><<<blocks, kDecodeThreads, shared, s>>>(p);
+      launched = launch(lattice_decode_kernel<kTablesShared, kModeStoreBf16>, shared);
     } else {
-      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<true, kModeStore>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(shared)));
-      lattice_decode_kernel<true, kModeStore><<<blocks, kDecodeThreads, shared, s>>>(p);
+      launched = launch(lattice_decode_kernel<kTablesShared, kModeStore>, shared);
+    }
+  } else if (prob_bits <= kSharedMaxProbBits) {
+    // alphabets beyond 512 (fine scales, heavy-tailed rows): word tables plus a byte table of high symbol bits
+    const size_t shared = (static_cast<size_t>(kTables) * 5 << prob_bits) + ring_bytes;
+    if (products) {
+      launched = tokens == 1 ? launch(lattice_decode_kernel<kTablesSharedWide, kModeProduct, 1>, shared)
+               : tokens == 2 ? launch(lattice_decode_kernel<kTablesSharedWide, kModeProduct, 2>, shared)
+                             : launch(lattice_decode_kernel<kTablesSharedWide, kModeProduct, 4>, shared);
+    } else if (store_kind == EP_STORE_BF16) {
+      launched = launch(lattice_decode_kernel<kTablesSharedWide, kModeStoreBf16>, shared);
+    } else {
+      launched = launch(lattice_decode_kernel<kTablesSharedWide, kModeStore>, shared);
     }
   } else {
     const int64_t needed = static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
@@ -602,16 +649,16 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
     lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, prob_bits);
     p.global_tables = tables;
     if (products) {
-      auto kernel = tokens == 1 ? lattice_decode_kernel<false, kModeProduct, 1>
-                                : (tokens == 2 ? lattice_decode_kernel<false, kModeProduct, 2> : lattice_decode_kernel<false, kModeProduct, 4>);
-      EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(ring_bytes)));
-      kernel<<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+      launched = tokens == 1 ? launch(lattice_decode_kernel<kTablesGlobal, kModeProduct, 1>, ring_bytes)
+               : tokens == 2 ? launch(lattice_decode_kernel<kTablesGlobal, kModeProduct, 2>, ring_bytes)
+                             : launch(lattice_decode_kernel<kTablesGlobal, kModeProduct, 4>, ring_bytes);
+    } else if (store_kind == EP_STORE_BF16) {
+      launched = launch(lattice_decode_kernel<kTablesGlobal, kModeStoreBf16>, ring_bytes);
     } else {
-      EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<false, kModeStore>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(ring_bytes)));
-      lattice_decode_kernel<false, kModeStore><<<blocks, kDecodeThreads, ring_bytes, s>>>(p);
+      launched = launch(lattice_decode_kernel<kTablesGlobal, kModeStore>, ring_bytes);
     }
   }
+  if (launched != EP_OK) return launched;
   return check_launch("lattice_decode_kernel");
 }
 
@@ -690,7 +737,7 @@ extern "C" int ep_lattice_decode_static(const uint16_t* payload_dev, int64_t pay
                                         const uint16_t* freq_tables_dev, const float* scales_dev, void* output_dev,
                                         int store_kind, int64_t rows, int64_t cols, int prob_bits, int64_t tile_elements,
                                         int max_alphabet, int* error_dev, ep_stream_t stream) {
-  const bool shared_path = prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet;
+  const bool shared_path = prob_bits <= kSharedMaxProbBits;
   if (!shared_path && prob_bits > kStaticMaxProbBits && prob_bits <= 15) return EP_ERR_TOO_LARGE;
   uint64_t* tables = nullptr;
   const int rc = static_tables_for_current_device(&tables);
