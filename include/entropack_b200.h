@@ -118,7 +118,7 @@ int ep_compact_streams(const uint16_t* scratch_dev, const uint32_t* offsets_dev,
 #define EP_STORE_BOOL 13
 
 /* Bytes of table scratch ep_lattice_decode needs for a container: 0 when the slot tables fit in
- * shared memory (prob_bits <= 11 and every alphabet <= 512), else 17 * 2^prob_bits * 8. */
+ * shared memory (prob_bits <= 11, whatever the alphabets), else 17 * 2^prob_bits * 8. */
 int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphabet);
 
 /* Decode + reconstruct + container cast into output_dev[rows][cols] (cols = the padded column count
@@ -156,7 +156,7 @@ int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t payload_words
  * the life of the process), so no scratch is passed and nothing is allocated. Limits and rules:
  *   - a container that needs the global-table path must have prob_bits <= 13
  *     (ep_lattice_decode_static_max_prob_bits()); larger ones return EP_ERR_TOO_LARGE. Containers whose
- *     tables fit in shared memory (prob_bits <= 11, alphabets <= 512) are always accepted;
+ *     tables fit in shared memory (prob_bits <= 11) are always accepted;
  *   - the first call on each device looks up the array's device address (no allocation, but a runtime
  *     query): make that first call outside any stream capture;
  *   - every call on a device shares the one array. It is rewritten in full by each call that uses it,
