@@ -264,7 +264,7 @@ def make_dfloat11(ep, out_dir: Path):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of modelscope/entropack to import the eager lane from")
     parser.add_argument("--only", default="all", choices=("all", "tile_ans", "lattice", "rdo", "dfloat11"))
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
