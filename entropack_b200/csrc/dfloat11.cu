@@ -154,6 +154,11 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     block_elems = 0;
     count = 0;
   }
+  // The write-back after the walk reads this block's sign/mantissa bytes; asking L2 for them now takes the DRAM part of
+  // that latency out of the block's serial path (one 128-byte line per thread).
+  for (int64_t line = static_cast<int64_t>(member) * 128; line < block_elems; line += static_cast<int64_t>(group_threads) * 128) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.sign_mantissa + out_base + line));
+  }
   uint8_t* const exponents = exponents_base + (out_base & 7);  // keeps 8-element output groups aligned in shared memory too
   if (local_base + count > p.stage_elems) {  // only a corrupt container gets here
     count = local_base < p.stage_elems ? p.stage_elems - local_base : 0;
