@@ -87,8 +87,21 @@ def encode(*, weight: torch.Tensor, tile_elements: int, probability_bits: int, r
     tiles = num_tiles(num_elements, tile_elements)
     streams = tiles * num_lanes
     ans_lanes = int((modes == 0).sum())
-    frequencies_dev = torch.from_numpy(frequencies).to(device)
-    cdfs_dev = torch.from_numpy(cdfs).to(device)
+    # the five small host arrays go up in one copy: tables (u32), layout (i64), frequencies and cdfs (u16), modes (u8)
+    layout_host = make_layout(num_elements, num_lanes, tile_elements, prob_bits).numpy()
+    pieces = [tables, layout_host, frequencies, cdfs, modes]
+    starts, cursor = [], 0
+    for piece in pieces:
+        cursor = -(-cursor // 16) * 16
+        starts.append(cursor)
+        cursor += piece.nbytes
+    staging = np.zeros(cursor, dtype=np.uint8)
+    for start, piece in zip(starts, pieces):
+        staging[start:start + piece.nbytes] = np.ascontiguousarray(piece).view(np.uint8).reshape(-1)
+    uploaded = torch.from_numpy(staging).to(device)
+    tables_dev, layout, frequencies_dev, cdfs_dev, modes_dev = (
+        uploaded[start:start + piece.nbytes].view(torch.from_numpy(piece).dtype).view(piece.shape)
+        for start, piece in zip(starts, pieces))
     states = torch.empty((tiles * ans_lanes, NUM_STATES), dtype=torch.uint32, device=device)
     word_counts = torch.empty(streams, dtype=torch.uint32, device=device)
     scratch = torch.empty(streams * tile_elements, dtype=torch.uint16, device=device)
@@ -111,8 +124,4 @@ def encode(*, weight: torch.Tensor, tile_elements: int, probability_bits: int, r
             _native.check(lib.ep_compact_streams(
                 _native.ptr(scratch), _native.ptr(offsets), _native.ptr(payload), tile_elements, streams, stream),
                 "tile_ans compaction")
-    layout = make_layout(num_elements, num_lanes, tile_elements, prob_bits).to(device)
-    return TileBuffers(
-        payload=payload, offsets=offsets, states=states, decode_tables=torch.from_numpy(tables).to(device),
-        lane_modes=torch.from_numpy(modes).to(device), layout=layout,
-    )
+    return TileBuffers(payload=payload, offsets=offsets, states=states, decode_tables=tables_dev, lane_modes=modes_dev, layout=layout)
