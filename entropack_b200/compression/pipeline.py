@@ -5,8 +5,12 @@ runs copy-in, kernel and copy-out one after the other. ``decompress_many`` puts 
 of their own: while tensor *i* is being decoded, tensor *i + 1* is on its way to the GPU and tensor
 *i - 1* on its way back (PCIe moves both directions at once). Headers and the small layout buffers are
 parsed while the container is still in host memory, so nothing is read back from the device in
-between. The reference has no counterpart: its ``decompress`` (entropack/compression/api.py:62-76)
-is the per-tensor call this builds on.
+between. A large container whose scheme can decode independent pieces (Tile-ANS tiles) is not even
+uploaded as a whole: its small buffers go first, then its payload in runs of tiles, each run decoded
+and sent back while the next is on its way, so the download, the longer of the two transfers, starts
+a fraction of a millisecond after the call and never waits for an upload again. The reference has no
+counterpart: its ``decompress`` (entropack/compression/api.py:62-76) is the per-tensor call this
+builds on.
 """
 from __future__ import annotations
 
@@ -37,6 +41,70 @@ def _transfer_order(containers: Sequence[CompressedTensor], *, with_download: bo
     first = sorted((i for i, (up, down) in enumerate(sizes) if up < down), key=lambda i: sizes[i][0])
     second = sorted((i for i, (up, down) in enumerate(sizes) if up >= down), key=lambda i: -sizes[i][1])
     return first + second
+
+
+#: output bytes of one streamed piece, and of the first piece of a call (pieces double from there): large enough for
+#: full PCIe efficiency, small enough that the first download starts early
+PIECE_BYTES = 32 << 20
+FIRST_PIECE_BYTES = 4 << 20
+_COPY_ALIGNMENT = 256
+
+
+def _piece_runs(plan, piece_bytes: int, first_piece_bytes: int) -> list[tuple[int, int]]:
+    """Runs of units ``(first, count)`` whose output is about ``piece_bytes`` each, starting at multiples of the
+    plan's granule; the first run is ``first_piece_bytes`` and the following ones double until they reach the target."""
+    runs, first, wanted = [], 0, min(first_piece_bytes, piece_bytes)
+    while first < plan.units:
+        count = max(1, wanted // plan.unit_output_bytes)
+        count = max(plan.granule, count // plan.granule * plan.granule)
+        count = min(count, plan.units - first)
+        runs.append((first, count))
+        first += count
+        wanted = min(2 * wanted, piece_bytes)
+    return runs
+
+
+def _decode_streamed(host: CompressedTensor, plan, item_config, device, streams, target: torch.Tensor,
+                     first_piece_bytes: int):
+    """Upload, decode and download one container in pieces. Returns (device-resident container, dense result)."""
+    upload, compute, download = streams
+    blob = host.entropack_quant_state
+    streamed = host.buffers[plan.streamed_buffer]
+    streamed_begin = streamed.data_ptr() - blob.data_ptr()
+    streamed_end = streamed_begin + streamed.numel() * streamed.element_size()
+    target_bytes = target.view(torch.uint8).reshape(-1)
+
+    with torch.cuda.stream(upload):
+        device_blob = torch.empty(blob.numel(), dtype=torch.uint8, device=device)
+        for begin, end in ((0, streamed_begin), (streamed_end, blob.numel())):
+            if end > begin:
+                device_blob[begin:end].copy_(blob[begin:end], non_blocking=True)
+    resident = host._remap(lambda _: device_blob)
+    with torch.cuda.stream(compute):
+        dense_bytes = torch.empty(plan.output_bytes, dtype=torch.uint8, device=device)
+    device_blob.record_stream(compute)
+    dense_bytes.record_stream(download)
+
+    for first, count in _piece_runs(plan, PIECE_BYTES, first_piece_bytes):
+        with torch.cuda.stream(upload):
+            for begin, end in plan.byte_ranges(first, count):
+                # whole 256-byte lines: the neighbours' bytes that come along are the same bytes they get anyway
+                begin = streamed_begin + begin // _COPY_ALIGNMENT * _COPY_ALIGNMENT
+                end = min(streamed_end, streamed_begin + -(-end // _COPY_ALIGNMENT) * _COPY_ALIGNMENT)
+                device_blob[begin:end].copy_(blob[begin:end], non_blocking=True)
+            uploaded = torch.cuda.Event()
+            uploaded.record(upload)
+        compute.wait_event(uploaded)
+        with torch.cuda.stream(compute):
+            plan.decode_units(resident.buffers, dense_bytes, first, count, item_config)
+            decoded = torch.cuda.Event()
+            decoded.record(compute)
+        download.wait_event(decoded)
+        begin = first * plan.unit_output_bytes
+        end = min(plan.output_bytes, (first + count) * plan.unit_output_bytes)
+        with torch.cuda.stream(download):
+            target_bytes[begin:end].copy_(dense_bytes[begin:end], non_blocking=True)
+    return resident, dense_bytes.view(host.encoded_dtype).reshape(tuple(host.shape))
 
 
 def decompress_many(blobs: Iterable[torch.Tensor | CompressedTensor], config: CompressionConfig | Sequence[CompressionConfig], *,
@@ -71,10 +139,23 @@ def decompress_many(blobs: Iterable[torch.Tensor | CompressedTensor], config: Co
     containers = [blob if isinstance(blob, CompressedTensor) else CompressedTensor.unpack(blob) for blob in blobs]
     results: list[torch.Tensor | None] = [None] * len(containers)
     keep_alive = []
+    first_piece_bytes = FIRST_PIECE_BYTES
     for index in _transfer_order(containers, with_download=out is not None):
         host, item_config = containers[index], configs[index]
         if host.device.type != "cuda":
             host.scheme.prime_host_metadata(host.buffers)
+        plan = None
+        if (out is not None and host.device.type == "cpu" and host.encoded_dtype == host.dtype and out[index].is_contiguous()
+                and out[index].device.type == "cpu" and out[index].numel() * out[index].element_size() == host.numel() * host.element_size()
+                and host.numel() * host.element_size() >= 2 * PIECE_BYTES):
+            plan = host.scheme.streaming_plan(host.buffers, shape=tuple(host.shape), dtype=host.encoded_dtype)
+        if plan is not None:
+            resident, dense = _decode_streamed(host, plan, item_config, device, (upload, compute, download), out[index],
+                                               first_piece_bytes)
+            first_piece_bytes = PIECE_BYTES
+            results[index] = dense
+            keep_alive.append(resident)
+            continue
         with torch.cuda.stream(upload):
             resident = host.to(device, non_blocking=True)
             uploaded = torch.cuda.Event()

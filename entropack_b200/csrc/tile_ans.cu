@@ -38,6 +38,8 @@ struct DecodeParams {
   int64_t num_elements;
   int64_t tile_elements;
   int64_t tiles;
+  int64_t first_tile;  // this launch decodes tiles [first_tile, tile_end)
+  int64_t tile_end;
   int prob_bits;
   LaneSetup lanes;
   int* error;
@@ -93,8 +95,8 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_simple_kernel(const 
   const uint32_t table_size = 1u << p.prob_bits;
   stage_decode_tables<NLANES>(p, shared_tables, constant_symbol);
 
-  const int64_t tile = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
-  if (tile >= p.tiles) return;
+  const int64_t tile = p.first_tile + static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+  if (tile >= p.tile_end) return;
   const uint32_t lane = lane_id();
   const uint32_t mask_ge = lanemask_ge();
   const uint32_t slot_mask = table_size - 1u;
@@ -220,8 +222,8 @@ tile_ans_decode_kernel(const DecodeParams p) {
   stage_decode_tables<NLANES>(p, shared_tables, constant_symbol);
 
   const int warp = threadIdx.x >> 5;
-  const int64_t tile = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
-  if (tile >= p.tiles) return;
+  const int64_t tile = p.first_tile + static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (tile >= p.tile_end) return;
   const uint32_t lane = lane_id();
   const uint32_t mask_ge = lanemask_ge();
   const uint32_t slot_mask = table_size - 1u;
@@ -744,10 +746,11 @@ int launch_decode(const DecodeParams& p, dim3 grid, size_t table_bytes, bool sta
 
 using namespace ep;
 
-extern "C" int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
-                                  const uint32_t* states_dev, const uint32_t* decode_tables_dev,
-                                  const uint8_t* lane_modes_host, void* output_dev, int64_t num_elements,
-                                  int64_t tile_elements, int prob_bits, int num_lanes, int* error_dev, ep_stream_t stream) {
+extern "C" int ep_tile_ans_decode_tiles(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                        const uint32_t* states_dev, const uint32_t* decode_tables_dev,
+                                        const uint8_t* lane_modes_host, void* output_dev, int64_t num_elements,
+                                        int64_t tile_elements, int prob_bits, int num_lanes, int64_t first_tile,
+                                        int64_t tile_count, int* error_dev, ep_stream_t stream) {
   if (num_elements <= 0 || tile_elements <= 0 || tile_elements > 0x7FFFFFFF || prob_bits < 9 || prob_bits > 12 ||
       payload_words < 0 || offsets_dev == nullptr || output_dev == nullptr) {
     return EP_ERR_INVALID_ARGUMENT;
@@ -766,9 +769,13 @@ extern "C" int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_w
   p.num_elements = num_elements;
   p.tile_elements = tile_elements;
   p.tiles = (num_elements + tile_elements - 1) / tile_elements;
+  if (first_tile < 0 || tile_count < 0 || first_tile > p.tiles || tile_count > p.tiles - first_tile) return EP_ERR_INVALID_ARGUMENT;
+  if (tile_count == 0) return EP_OK;
+  p.first_tile = first_tile;
+  p.tile_end = first_tile + tile_count;
   p.prob_bits = prob_bits;
   p.error = error_dev;
-  const int64_t blocks = (p.tiles + kWarps - 1) / kWarps;
+  const int64_t blocks = (tile_count + kWarps - 1) / kWarps;
   if (blocks > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
   const size_t table_bytes = static_cast<size_t>(p.lanes.ans_lanes) * sizeof(uint32_t) << prob_bits;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -786,6 +793,16 @@ extern "C" int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_w
   }
   if (rc != EP_OK) return rc;
   return check_launch("tile_ans_decode_kernel");
+}
+
+extern "C" int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                                  const uint32_t* states_dev, const uint32_t* decode_tables_dev,
+                                  const uint8_t* lane_modes_host, void* output_dev, int64_t num_elements,
+                                  int64_t tile_elements, int prob_bits, int num_lanes, int* error_dev, ep_stream_t stream) {
+  if (num_elements <= 0 || tile_elements <= 0) return EP_ERR_INVALID_ARGUMENT;
+  const int64_t tiles = (num_elements + tile_elements - 1) / tile_elements;
+  return ep_tile_ans_decode_tiles(payload_dev, payload_words, offsets_dev, states_dev, decode_tables_dev, lane_modes_host,
+                                  output_dev, num_elements, tile_elements, prob_bits, num_lanes, 0, tiles, error_dev, stream);
 }
 
 extern "C" int ep_tile_ans_histogram(const void* input_dev, int64_t num_elements, int num_lanes, uint64_t* histograms_dev,

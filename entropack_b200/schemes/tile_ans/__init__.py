@@ -1,9 +1,38 @@
 """Tile-ANS scheme. Stands in for entropack/schemes/tile_ans/__init__.py:8-50."""
 import torch
 
-from ..base import Scheme, packed_buffers, register_scheme
+from ..base import Scheme, StreamingPlan, packed_buffers, register_scheme
 from ..checks import prepare_weight
-from .format import OPTIONS_BY_DTYPE, PACKED_KEYS, TileANSConfig, TileBuffers, parse_layout_cached, validate_packed
+from .format import OPTIONS_BY_DTYPE, PACKED_KEYS, TileANSConfig, TileBuffers, num_tiles, parse_layout_cached, validate_packed
+
+
+class TileStreamingPlan(StreamingPlan):
+    """Tiles as streaming units: tile ``t`` reads streams ``lane * tiles + t`` of the payload (one byte range per byte
+    lane for a run of tiles) and writes ``tile_elements`` whole elements."""
+
+    streamed_buffer = "payload"
+    granule = 8    # tiles per decode block
+
+    def __init__(self, scheme: "TileANSScheme", buffers: TileBuffers, dtype: torch.dtype):
+        tile_elements, _, num_lanes, num_elements = parse_layout_cached(buffers.layout)
+        self.scheme, self.dtype, self.lanes = scheme, dtype, num_lanes
+        self.units = num_tiles(num_elements, tile_elements)
+        self.unit_output_bytes = tile_elements * num_lanes
+        self.output_bytes = num_elements * num_lanes
+        self.offsets = buffers.offsets.numpy()    # host view, uint32[lanes * tiles + 1], in 16-bit words
+
+    def byte_ranges(self, first: int, count: int) -> list[tuple[int, int]]:
+        ranges = []
+        for lane in range(self.lanes):
+            begin = 2 * int(self.offsets[lane * self.units + first])
+            end = 2 * int(self.offsets[lane * self.units + first + count])
+            if end > begin:
+                ranges.append((begin, end))
+        return ranges
+
+    def decode_units(self, buffers: dict, output: torch.Tensor, first: int, count: int, config: TileANSConfig) -> None:
+        self.scheme.lane().decode(packed_buffers(buffers, TileBuffers), dtype=self.dtype,
+                                  threads_per_block=config.threads_per_block, out=output, tiles=(first, count))
 
 
 class TileANSScheme(Scheme):
@@ -40,6 +69,12 @@ class TileANSScheme(Scheme):
         packed = packed_buffers(buffers, TileBuffers)
         parse_layout_cached(packed.layout)
         _lane_modes_host(packed)
+
+    def streaming_plan(self, buffers: dict, *, shape, dtype):
+        packed = packed_buffers(buffers, TileBuffers)
+        if packed.layout.device.type != "cpu":
+            return None
+        return TileStreamingPlan(self, packed, dtype)
 
     def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: TileANSConfig) -> torch.Tensor:
         buffers = packed_buffers(packed, TileBuffers)

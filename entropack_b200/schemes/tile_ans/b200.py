@@ -25,24 +25,30 @@ def _lane_modes_host(buffers: TileBuffers) -> np.ndarray:
 
 
 def decode(buffers: TileBuffers, *, dtype: torch.dtype, threads_per_block: int | None = None,
-           error: torch.Tensor | None = None) -> torch.Tensor:
+           error: torch.Tensor | None = None, out: torch.Tensor | None = None,
+           tiles: tuple[int, int] | None = None) -> torch.Tensor:
     """Decode to a flat tensor of ``dtype`` on the buffers' device. One kernel launch, no host sync.
 
     ``error``: optional int32[1] device tensor (zeroed by the caller) that receives a non-zero code if
     the bitstream is malformed; without it a malformed stream decodes to garbage silently, as in the
-    reference."""
+    reference. ``out``: the whole tensor's bytes (uint8) to decode into. ``tiles = (first, count)``: decode
+    only those tiles, leaving the rest of ``out`` as it is; only their streams need to be in ``payload``."""
     payload = buffers.payload
     _native.require_cuda(payload)
     tile_elements, prob_bits, num_lanes, num_elements = parse_layout_cached(buffers.layout)
     modes = _lane_modes_host(buffers)
-    output = torch.empty(num_elements * num_lanes, dtype=torch.uint8, device=payload.device)
+    if out is None:
+        out = torch.empty(num_elements * num_lanes, dtype=torch.uint8, device=payload.device)
+    elif out.dtype != torch.uint8 or out.numel() != num_elements * num_lanes or not out.is_contiguous() or out.device != payload.device:
+        raise ValueError(f"tile_ans decode needs a contiguous uint8 output of {num_elements * num_lanes} bytes on {payload.device}")
+    first, count = (0, num_tiles(num_elements, tile_elements)) if tiles is None else tiles
     with torch.cuda.device(payload.device):
-        status = _native_lib().ep_tile_ans_decode(
+        status = _native_lib().ep_tile_ans_decode_tiles(
             _native.ptr(payload), payload.numel(), _native.ptr(buffers.offsets), _native.ptr(buffers.states),
-            _native.ptr(buffers.decode_tables), modes.ctypes.data, _native.ptr(output), num_elements, tile_elements,
-            prob_bits, num_lanes, _native.ptr(error), _native.stream_handle(payload.device))
+            _native.ptr(buffers.decode_tables), modes.ctypes.data, _native.ptr(out), num_elements, tile_elements,
+            prob_bits, num_lanes, first, count, _native.ptr(error), _native.stream_handle(payload.device))
     _native.check(status, "tile_ans decode")
-    return output.view(dtype)
+    return out.view(dtype)
 
 
 def lane_histogram(weight: torch.Tensor) -> np.ndarray:

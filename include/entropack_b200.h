@@ -61,6 +61,17 @@ int ep_tile_ans_decode(const uint16_t* payload_dev, int64_t payload_words, const
                        void* output_dev, int64_t num_elements, int64_t tile_elements, int prob_bits, int num_lanes,
                        int* error_dev, ep_stream_t stream);
 
+/* The same decode for tiles [first_tile, first_tile + tile_count) only: it reads those tiles' streams
+ * (stream = lane * tiles + tile, as in tile_ans.cu:175-469) and writes their elements at their places in
+ * `output_dev`, which is still the whole tensor's buffer. Tiles are independent given the tables, so a
+ * caller that streams a container in from the host can decode and send back each range as soon as its
+ * payload bytes have arrived; offsets, states and tables must be resident in full. No reference
+ * counterpart (its decode() always launches over every tile). */
+int ep_tile_ans_decode_tiles(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
+                             const uint32_t* states_dev, const uint32_t* decode_tables_dev, const uint8_t* lane_modes_host,
+                             void* output_dev, int64_t num_elements, int64_t tile_elements, int prob_bits, int num_lanes,
+                             int64_t first_tile, int64_t tile_count, int* error_dev, ep_stream_t stream);
+
 /* Per-byte-lane 256-bin histogram of the tensor's bytes into histograms_dev[num_lanes][256] (u64,
  * cleared by the call). Stands in for _lane_histogram, entropack/schemes/tile_ans/cuda.py:31-47 /
  * tile_ans_histogram_kernel, tile_ans.cu:27-65. */

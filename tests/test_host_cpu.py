@@ -211,3 +211,21 @@ def test_lattice_host_model_matches_reference():
                                  ctypes.addressof(entries)) == 0
     assert np.array_equal(meta, units["enc_meta"])
     assert np.array_equal(freq[: entries.value], units["enc_freq"])
+
+
+def test_streamed_pieces_cover_every_unit_once_and_ramp_up():
+    """Piece runs of the streamed bulk decode: contiguous, on granule boundaries, doubling from the first piece's size
+    to the target, the last one ragged."""
+    from types import SimpleNamespace
+
+    from entropack_b200.compression.pipeline import _piece_runs
+
+    plan = SimpleNamespace(units=8192 + 5, unit_output_bytes=8192, granule=8)
+    runs = _piece_runs(plan, 16 << 20, 2 << 20)
+    assert runs[0] == (0, 256) and runs[1] == (256, 512) and runs[2] == (768, 1024) and runs[3][1] == 2048 and runs[4][1] == 2048
+    assert all(first % 8 == 0 for first, _ in runs)
+    assert [first for first, _ in runs[1:]] == [first + count for first, count in runs[:-1]]
+    assert runs[-1][0] + runs[-1][1] == plan.units
+    # units larger than a piece: one granule at a time
+    big = SimpleNamespace(units=20, unit_output_bytes=1 << 20, granule=8)
+    assert _piece_runs(big, 1 << 20, 1 << 10) == [(0, 8), (8, 8), (16, 4)]

@@ -157,3 +157,62 @@ def test_decompress_many_matches_decompress_and_fills_pinned_outputs():
             assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
             assert torch.equal(got.view(torch.uint8), source.view(torch.uint8))
             assert torch.equal(host, want.reshape(-1).view(torch.uint8).cpu())
+
+
+@pytest.mark.parametrize("piece_bytes,first_piece_bytes", [(64 << 10, 16 << 10), (1 << 20, 1 << 20)])
+def test_decompress_many_streams_tile_ans_containers_in_pieces(monkeypatch, piece_bytes, first_piece_bytes):
+    """A Tile-ANS container in host memory is uploaded, decoded and sent back in runs of tiles
+    (ep_tile_ans_decode_tiles); the bytes must be those of the whole-tensor decode. Piece sizes are turned down so
+    that small tensors take the path: ragged last tile, raw and coded byte lanes, 1/2/4-byte elements, a tile count
+    that is no multiple of the block's 8."""
+    import entropack_b200 as ep
+    from entropack_b200.compression import pipeline
+
+    monkeypatch.setattr(pipeline, "PIECE_BYTES", piece_bytes)
+    monkeypatch.setattr(pipeline, "FIRST_PIECE_BYTES", first_piece_bytes)
+    taken = []
+    inner = pipeline._decode_streamed
+    monkeypatch.setattr(pipeline, "_decode_streamed", lambda *a, **k: (taken.append(a[1].units), inner(*a, **k))[1])
+
+    generator = torch.Generator(device="cuda").manual_seed(12)
+    tensors = [
+        (torch.randn(531, 4099, generator=generator, device="cuda") * 20).round().clamp(-127, 127).to(torch.int8),
+        (torch.randn(1100, 1111, generator=generator, device="cuda") * 0.02).to(torch.float16),
+        torch.randn(1023, 999, generator=generator, device="cuda") * 0.02,
+        (torch.randn(2048, 1024, generator=generator, device="cuda") * 0.02).to(torch.bfloat16),
+        torch.randn(9, 100, generator=generator, device="cuda"),            # too small to stream
+    ]
+    config = ep.TileANSConfig()
+    containers = [ep.compress(t, config) for t in tensors]
+    blobs = [c.entropack_quant_state.cpu().pin_memory() for c in containers]
+    outputs = [torch.empty_like(t, device="cpu").pin_memory() for t in tensors]
+    for _ in range(2):
+        for host in outputs:
+            host.view(torch.uint8).fill_(0xA5)
+        decoded = ep.decompress_many(blobs, config, device="cuda", out=outputs)
+        for got, source, host in zip(decoded, tensors, outputs):
+            assert got.dtype == source.dtype and got.shape == source.shape
+            assert torch.equal(got.view(torch.uint8), source.view(torch.uint8))
+            assert torch.equal(host.view(torch.uint8), source.cpu().view(torch.uint8))
+    assert len(taken) == 8 and all(units > 8 for units in taken)
+
+
+def test_decode_tiles_rejects_ranges_outside_the_tensor():
+    import entropack_b200 as ep
+    from entropack_b200.schemes.base import packed_buffers
+    from entropack_b200.schemes.tile_ans import b200
+    from entropack_b200.schemes.tile_ans.format import TileBuffers
+
+    tensor = torch.randn(64, 4096, device="cuda").to(torch.bfloat16)
+    container = ep.compress(tensor, ep.TileANSConfig(tile_elements=4096))
+    buffers = packed_buffers(container.buffers, TileBuffers)
+    out = torch.zeros(tensor.numel() * 2, dtype=torch.uint8, device="cuda")
+    b200.decode(buffers, dtype=torch.bfloat16, out=out, tiles=(8, 16))
+    torch.cuda.synchronize()
+    whole = tensor.reshape(-1).view(torch.uint8)
+    span = slice(8 * 4096 * 2, 24 * 4096 * 2)
+    assert torch.equal(out[span], whole[span]) and int(out[: span.start].max()) == 0 and int(out[span.stop :].max()) == 0
+    b200.decode(buffers, dtype=torch.bfloat16, out=out, tiles=(64, 0))     # an empty run at the end is fine
+    for bad in [(-1, 4), (60, 5), (65, 0), (0, -1)]:
+        with pytest.raises(ValueError):
+            b200.decode(buffers, dtype=torch.bfloat16, out=out, tiles=bad)
