@@ -186,7 +186,8 @@ __global__ void __launch_bounds__(256) convrot_rows_kernel(const T* __restrict__
 constexpr int kTileM = 128;
 constexpr int kTileK = 64;               // 64 bf16 = one 128-byte swizzle row
 constexpr int kTileBytesA = kTileM * kTileK * 2;        // 16 KB
-constexpr int kGemmThreads = 192;        // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
+constexpr int kEpilogueWarps = 8;        // two per TMEM lane quadrant, each draining half of the tile's columns
+constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;   // warp 0: TMA, warp 1: MMA + TMEM owner, the rest: epilogue
 constexpr uint32_t kWaitLimit = 1u << 24;
 constexpr int kGemmTimeout = 9;          // value written to the error word when a wait runs out
 
@@ -293,6 +294,12 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   __shared__ __align__(8) uint64_t accumulator_free[2];    // epilogue -> MMA
   __shared__ uint32_t tmem_base_holder;
   __shared__ int failed;
+  // Per epilogue warp, the column factors of its share of the tile (half the columns; all 32 of the narrowest tile)
+  // as fp32: [0] weight scale (8-bit operands), [1] bias; zero outside the matrix. Every thread of a warp needs all of them for its row, so they are read from global memory once per
+  // warp and tile and then come from shared memory as broadcast 16-byte reads. (Wide tiles only: the narrow ones
+  // run three blocks per SM with no shared memory to spare, and store a handful of rows.)
+  constexpr bool kStageColumns = A_ROWS == kTileM;
+  __shared__ __align__(16) float column_factors[kStageColumns ? kEpilogueWarps : 1][2][kStageColumns ? (TILE_N >= 64 ? TILE_N / 2 : 32) : 4];
   // tiles need 1024-byte alignment for the 128-byte swizzle pattern; all A tiles come first, then all B tiles
   uint8_t* tiles_a = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* tiles_b = tiles_a + kStages * kBytesA;
@@ -311,7 +318,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       barrier_init(&accumulator_ready[b], 1);
-      barrier_init(&accumulator_free[b], 4);   // one arrival per epilogue warp
+      barrier_init(&accumulator_free[b], kEpilogueWarps);   // one arrival per epilogue warp
     }
     failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -390,14 +397,37 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       if (!ok) break;
     }
   } else if (warp >= 2) {
-    // ---- epilogue: each warp owns the 32 TMEM lanes of its quadrant (warp index mod 4); it drains one buffer
-    // while the MMA issuer fills the other
+    // ---- epilogue: a warp reaches the 32 TMEM lanes of its quadrant (warp index mod 4); two warps share a quadrant,
+    // one per half of the tile's columns; they drain one buffer while the MMA issuer fills the other
     const int quadrant = warp & 3;
+    const int member = warp - 2;                        // 0..7: which epilogue warp
+    constexpr int kChunks = TILE_N / 32;                // 32 columns at a time
+    constexpr int kChunksPerWarp = kChunks >= 2 ? kChunks / 2 : 1;
+    const int first_chunk = kChunks >= 2 ? (member >> 2) * kChunksPerWarp : 0;
+    const bool has_columns = kChunks >= 2 || member < 4;
     int local = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
       const int buffer = local & 1;
       const int m0 = (tile / n_tiles) * kTileM;
       const int n0 = (tile % n_tiles) * TILE_N;
+      if (kStageColumns && (kScaled || p.bias)) {
+        __syncwarp();   // the previous tile's reads of the factors are over
+        for (int c = static_cast<int>(lane); c < kChunksPerWarp * 32; c += 32) {
+          const int col = n0 + first_chunk * 32 + c;
+          float scale = 0.0f, bias = 0.0f;
+          if (col < p.n) {
+            if (kScaled) {
+              scale = p.column_scale[col];
+              if (p.bias_f32) bias = p.bias_f32[col];
+            } else if (p.bias) {
+              bias = __bfloat162float(p.bias[col]);
+            }
+          }
+          column_factors[member][0][c] = scale;
+          column_factors[member][1][c] = bias;
+        }
+        __syncwarp();
+      }
       const bool ready = barrier_wait(&accumulator_ready[buffer], (local >> 1) & 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (!ready || failed) {
@@ -405,8 +435,15 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         break;
       }
       const int row = m0 + quadrant * 32 + static_cast<int>(lane);
+      if (!has_columns) {   // a 32-column tile has one chunk: the quadrant's second warp only hands the buffer back
+        if (lane == 0) {
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(shared_address(&accumulator_free[buffer])) : "memory");
+        }
+        continue;
+      }
+      const float row_scale = kScaled && row < p.m ? p.row_scale[row] : 1.0f;
 #pragma unroll 1
-      for (int chunk = 0; chunk < TILE_N / 32; ++chunk) {
+      for (int chunk = first_chunk; chunk < first_chunk + kChunksPerWarp; ++chunk) {
         uint32_t v[32];
         const uint32_t address = tmem_base + static_cast<uint32_t>(buffer) * kTmemColumns +
                                  (static_cast<uint32_t>(quadrant * 32) << 16) + static_cast<uint32_t>(chunk * 32);
@@ -419,8 +456,8 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
               "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
             : "r"(address) : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (chunk == TILE_N / 32 - 1) {
-          // the whole buffer is in registers: hand it back before the stores
+        if (chunk == first_chunk + kChunksPerWarp - 1) {
+          // this warp's share of the buffer is in registers: hand it back before the stores
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
@@ -429,11 +466,31 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         const int col = n0 + chunk * 32;
         if (row < p.m && col < p.n) {
-          if (kScaled) {
-            // scaled epilogue of the 8-bit layers: the row's activation scale times the column's weight scale
-            const float row_scale = p.row_scale[row];
-            const int64_t at = static_cast<int64_t>(row) * p.n + col;
-            const bool whole = col + 32 <= p.n && (p.n & 7) == 0;
+          const bool whole = col + 32 <= p.n && (p.n & 7) == 0;
+          const int64_t at = static_cast<int64_t>(row) * p.n + col;
+          // fp32 results in v: accumulator (* row scale * column scale) + bias
+          if (kStageColumns && (kScaled || p.bias)) {
+            const float4* scales = reinterpret_cast<const float4*>(&column_factors[member][0][(chunk - first_chunk) * 32]);
+            const float4* biases = reinterpret_cast<const float4*>(&column_factors[member][1][(chunk - first_chunk) * 32]);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const float4 b = biases[g];
+              const float bias[4] = {b.x, b.y, b.z, b.w};
+              if (kScaled) {
+                const float4 cs = scales[g];
+                const float scale[4] = {row_scale * cs.x, row_scale * cs.y, row_scale * cs.z, row_scale * cs.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t raw = v[g * 4 + j];
+                  const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(raw)) : __uint_as_float(raw);
+                  v[g * 4 + j] = __float_as_uint(fmaf(accumulated, scale[j], bias[j]));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[g * 4 + j] = __float_as_uint(__uint_as_float(v[g * 4 + j]) + bias[j]);
+              }
+            }
+          } else if (kScaled) {
 #pragma unroll
             for (int c = 0; c < 32; ++c) {
               const bool inside = whole || col + c < p.n;
@@ -442,51 +499,34 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
               const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(v[c])) : __uint_as_float(v[c]);
               v[c] = __float_as_uint(fmaf(accumulated, scale, b));
             }
-            if (p.y_f32) {
-              if (whole) {
+          } else if (!kStageColumns && p.bias) {
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                  *reinterpret_cast<uint4*>(p.y_f32 + at + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                }
-              } else {
-                for (int c = 0; c < 32 && col + c < p.n; ++c) p.y_f32[at + c] = __uint_as_float(v[c]);
-              }
-            } else if (whole) {
+            for (int c = 0; c < 32; ++c) {
+              if (whole || col + c < p.n) v[c] = __float_as_uint(__uint_as_float(v[c]) + __bfloat162float(p.bias[col + c]));
+            }
+          }
+          if (kScaled && p.y_f32) {
+            if (whole) {
 #pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + j * 2]), __uint_as_float(v[g * 8 + j * 2 + 1]));
-                  packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
-                }
-                *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              for (int g = 0; g < 8; ++g) {
+                *reinterpret_cast<uint4*>(p.y_f32 + at + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
               }
             } else {
-              for (int c = 0; c < 32 && col + c < p.n; ++c) p.y[at + c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+              for (int c = 0; c < 32 && col + c < p.n; ++c) p.y_f32[at + c] = __uint_as_float(v[c]);
             }
-          } else {
-          __nv_bfloat16* out = p.y + static_cast<int64_t>(row) * p.n + col;
-          if (col + 32 <= p.n && (p.n & 7) == 0) {
+          } else if (whole) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint32_t packed[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const int c = g * 8 + j * 2;
-                const float b0 = p.bias ? __bfloat162float(p.bias[col + c]) : 0.0f;
-                const float b1 = p.bias ? __bfloat162float(p.bias[col + c + 1]) : 0.0f;
-                const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[c]) + b0, __uint_as_float(v[c + 1]) + b1);
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + j * 2]), __uint_as_float(v[g * 8 + j * 2 + 1]));
                 packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
               }
-              *reinterpret_cast<uint4*>(out + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
           } else {
-            for (int c = 0; c < 32 && col + c < p.n; ++c) {
-              const float b = p.bias ? __bfloat162float(p.bias[col + c]) : 0.0f;
-              out[c] = __float2bfloat16_rn(__uint_as_float(v[c]) + b);
-            }
-          }
+            for (int c = 0; c < 32 && col + c < p.n; ++c) p.y[at + c] = __float2bfloat16_rn(__uint_as_float(v[c]));
           }
         }
       }

@@ -52,6 +52,7 @@ def main() -> None:
     parser.add_argument("--reps", type=int, default=3)
     parser.add_argument("--tile-elements", type=int, default=0, help="tile-ANS tile size (0 = automatic)")
     parser.add_argument("--inner", type=int, default=3840, help="linear: K (rows = tokens M, cols = features N)")
+    parser.add_argument("--operand", default="bf16", choices=("bf16", "fp8", "int8"), help="linear: operand type of the product")
     args = parser.parse_args()
 
     import entropack_b200 as ep
@@ -63,10 +64,27 @@ def main() -> None:
 
         weight = make_tensor("bf16", args.cols, args.inner, device)
         tokens = make_tensor("bf16", args.rows, args.inner, device, seed=2) * 50
-        for _ in range(args.reps):
-            out = linear_forward(tokens, weight)
+        if args.operand == "bf16":
+            for _ in range(args.reps):
+                out = linear_forward(tokens, weight)
+        else:
+            # 8-bit codes with per-row scales, as the quantised layers hand them to the kernel
+            from entropack_b200 import _native
+
+            lib = _native.load()
+            if args.operand == "fp8":
+                entry, codes_x, codes_w = lib.ep_linear_forward_fp8, tokens.to(torch.float8_e4m3fn), (weight * 50).to(torch.float8_e4m3fn)
+            else:
+                entry, codes_x, codes_w = lib.ep_linear_forward_int8, tokens.round().clamp(-127, 127).to(torch.int8), (weight * 2000).round().clamp(-127, 127).to(torch.int8)
+            scale_x = torch.full((args.rows,), 0.02, device=device)
+            scale_w = torch.full((args.cols,), 0.01, device=device)
+            out = torch.empty((args.rows, args.cols), dtype=torch.bfloat16, device=device)
+            for _ in range(args.reps):
+                _native.check(entry(_native.ptr(codes_x), _native.ptr(codes_w), _native.ptr(scale_x), _native.ptr(scale_w), None,
+                                    _native.ptr(out), 0, args.rows, args.cols, args.inner, None, _native.stream_handle(device)),
+                              "8-bit linear forward")
         torch.cuda.synchronize()
-        print(f"linear M={args.rows} N={args.cols} K={args.inner}: {args.reps} launches")
+        print(f"linear {args.operand} M={args.rows} N={args.cols} K={args.inner}: {args.reps} launches")
         return
     tensor = make_tensor(args.kind, args.rows, args.cols, device)
     config = ep.TileANSConfig(tile_elements=args.tile_elements)
