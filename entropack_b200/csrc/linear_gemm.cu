@@ -275,6 +275,113 @@ struct GemmParams {
   float* y_f32;
 };
 
+// Loads 32 consecutive accumulator columns of this thread's TMEM lane and waits for them.
+__device__ __forceinline__ void load_accumulator_chunk(uint32_t (&v)[32], uint32_t address) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(address) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Epilogue arithmetic and stores of one thread's 32 accumulator values: row `row`, columns col .. col + 31 (the
+// caller has checked row < m and col < n). bf16 operands: + bias; 8-bit operands: accumulator * row scale *
+// column scale + bias. `staged_scale` / `staged_bias` point at the 32 columns' factors in shared memory (zero
+// outside the matrix), or are null, in which case the factors come from global memory.
+template <int OPERAND>
+__device__ __forceinline__ void finish_chunk(uint32_t (&v)[32], const GemmParams& p, int row, int col, float row_scale,
+                                             const float* staged_scale, const float* staged_bias) {
+  constexpr bool kScaled = OPERAND != kOperandBf16;
+  const bool whole = col + 32 <= p.n && (p.n & 7) == 0;
+  const int64_t at = static_cast<int64_t>(row) * p.n + col;
+  if (staged_bias != nullptr) {
+    const float4* scales = reinterpret_cast<const float4*>(staged_scale);
+    const float4* biases = reinterpret_cast<const float4*>(staged_bias);
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      const float4 b = biases[g];
+      const float bias[4] = {b.x, b.y, b.z, b.w};
+      if (kScaled) {
+        const float4 cs = scales[g];
+        const float scale[4] = {row_scale * cs.x, row_scale * cs.y, row_scale * cs.z, row_scale * cs.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t raw = v[g * 4 + j];
+          const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(raw)) : __uint_as_float(raw);
+          v[g * 4 + j] = __float_as_uint(fmaf(accumulated, scale[j], bias[j]));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[g * 4 + j] = __float_as_uint(__uint_as_float(v[g * 4 + j]) + bias[j]);
+      }
+    }
+  } else if (kScaled) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const bool inside = whole || col + c < p.n;
+      const float scale = inside ? row_scale * p.column_scale[col + c] : 0.0f;
+      const float b = inside && p.bias_f32 ? p.bias_f32[col + c] : 0.0f;
+      const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(v[c])) : __uint_as_float(v[c]);
+      v[c] = __float_as_uint(fmaf(accumulated, scale, b));
+    }
+  } else if (p.bias) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      if (whole || col + c < p.n) v[c] = __float_as_uint(__uint_as_float(v[c]) + __bfloat162float(p.bias[col + c]));
+    }
+  }
+  if (kScaled && p.y_f32) {
+    if (whole) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        *reinterpret_cast<uint4*>(p.y_f32 + at + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+      }
+    } else {
+      for (int c = 0; c < 32 && col + c < p.n; ++c) p.y_f32[at + c] = __uint_as_float(v[c]);
+    }
+  } else if (whole) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t packed[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + j * 2]), __uint_as_float(v[g * 8 + j * 2 + 1]));
+        packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
+      }
+      *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+  } else {
+    for (int c = 0; c < 32 && col + c < p.n; ++c) p.y[at + c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+  }
+}
+
+// Per-warp staging of the column factors of `columns` consecutive columns starting at `first_col`.
+template <int OPERAND>
+__device__ __forceinline__ void stage_column_factors(const GemmParams& p, float* scales, float* biases, int first_col, int columns,
+                                                     uint32_t lane) {
+  constexpr bool kScaled = OPERAND != kOperandBf16;
+  __syncwarp();   // the previous tile's reads of the factors are over
+  for (int c = static_cast<int>(lane); c < columns; c += 32) {
+    const int col = first_col + c;
+    float scale = 0.0f, bias = 0.0f;
+    if (col < p.n) {
+      if (kScaled) {
+        scale = p.column_scale[col];
+        if (p.bias_f32) bias = p.bias_f32[col];
+      } else if (p.bias) {
+        bias = __bfloat162float(p.bias[col]);
+      }
+    }
+    scales[c] = scale;
+    biases[c] = bias;
+  }
+  __syncwarp();
+}
+
 template <int TILE_N, int A_ROWS, int OPERAND>
 __global__ void __launch_bounds__(kGemmThreads, TileShape<TILE_N, A_ROWS>::kBlocksPerSm)
 linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
@@ -411,22 +518,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
       const int m0 = (tile / n_tiles) * kTileM;
       const int n0 = (tile % n_tiles) * TILE_N;
       if (kStageColumns && (kScaled || p.bias)) {
-        __syncwarp();   // the previous tile's reads of the factors are over
-        for (int c = static_cast<int>(lane); c < kChunksPerWarp * 32; c += 32) {
-          const int col = n0 + first_chunk * 32 + c;
-          float scale = 0.0f, bias = 0.0f;
-          if (col < p.n) {
-            if (kScaled) {
-              scale = p.column_scale[col];
-              if (p.bias_f32) bias = p.bias_f32[col];
-            } else if (p.bias) {
-              bias = __bfloat162float(p.bias[col]);
-            }
-          }
-          column_factors[member][0][c] = scale;
-          column_factors[member][1][c] = bias;
-        }
-        __syncwarp();
+        stage_column_factors<OPERAND>(p, column_factors[member][0], column_factors[member][1], n0 + first_chunk * 32, kChunksPerWarp * 32, lane);
       }
       const bool ready = barrier_wait(&accumulator_ready[buffer], (local >> 1) & 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -447,15 +539,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         uint32_t v[32];
         const uint32_t address = tmem_base + static_cast<uint32_t>(buffer) * kTmemColumns +
                                  (static_cast<uint32_t>(quadrant * 32) << 16) + static_cast<uint32_t>(chunk * 32);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-              "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-              "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-              "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(address) : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        load_accumulator_chunk(v, address);
         if (chunk == first_chunk + kChunksPerWarp - 1) {
           // this warp's share of the buffer is in registers: hand it back before the stores
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -466,68 +550,9 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         const int col = n0 + chunk * 32;
         if (row < p.m && col < p.n) {
-          const bool whole = col + 32 <= p.n && (p.n & 7) == 0;
-          const int64_t at = static_cast<int64_t>(row) * p.n + col;
-          // fp32 results in v: accumulator (* row scale * column scale) + bias
-          if (kStageColumns && (kScaled || p.bias)) {
-            const float4* scales = reinterpret_cast<const float4*>(&column_factors[member][0][(chunk - first_chunk) * 32]);
-            const float4* biases = reinterpret_cast<const float4*>(&column_factors[member][1][(chunk - first_chunk) * 32]);
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              const float4 b = biases[g];
-              const float bias[4] = {b.x, b.y, b.z, b.w};
-              if (kScaled) {
-                const float4 cs = scales[g];
-                const float scale[4] = {row_scale * cs.x, row_scale * cs.y, row_scale * cs.z, row_scale * cs.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint32_t raw = v[g * 4 + j];
-                  const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(raw)) : __uint_as_float(raw);
-                  v[g * 4 + j] = __float_as_uint(fmaf(accumulated, scale[j], bias[j]));
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) v[g * 4 + j] = __float_as_uint(__uint_as_float(v[g * 4 + j]) + bias[j]);
-              }
-            }
-          } else if (kScaled) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              const bool inside = whole || col + c < p.n;
-              const float scale = inside ? row_scale * p.column_scale[col + c] : 0.0f;
-              const float b = inside && p.bias_f32 ? p.bias_f32[col + c] : 0.0f;
-              const float accumulated = OPERAND == kOperandInt8 ? static_cast<float>(static_cast<int>(v[c])) : __uint_as_float(v[c]);
-              v[c] = __float_as_uint(fmaf(accumulated, scale, b));
-            }
-          } else if (!kStageColumns && p.bias) {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) {
-              if (whole || col + c < p.n) v[c] = __float_as_uint(__uint_as_float(v[c]) + __bfloat162float(p.bias[col + c]));
-            }
-          }
-          if (kScaled && p.y_f32) {
-            if (whole) {
-#pragma unroll
-              for (int g = 0; g < 8; ++g) {
-                *reinterpret_cast<uint4*>(p.y_f32 + at + g * 4) = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-              }
-            } else {
-              for (int c = 0; c < 32 && col + c < p.n; ++c) p.y_f32[at + c] = __uint_as_float(v[c]);
-            }
-          } else if (whole) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint32_t packed[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + j * 2]), __uint_as_float(v[g * 8 + j * 2 + 1]));
-                packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
-              }
-              *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            }
-          } else {
-            for (int c = 0; c < 32 && col + c < p.n; ++c) p.y[at + c] = __float2bfloat16_rn(__uint_as_float(v[c]));
-          }
+          const bool staged = kStageColumns && (kScaled || p.bias);
+          finish_chunk<OPERAND>(v, p, row, col, row_scale, staged ? &column_factors[member][0][(chunk - first_chunk) * 32] : nullptr,
+                                staged ? &column_factors[member][1][(chunk - first_chunk) * 32] : nullptr);
         }
       }
     }
@@ -536,6 +561,225 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * kTmemColumns) : "memory");
+  }
+  if (threadIdx.x == 0 && failed) report(p.error, kGemmTimeout);
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// Two-block tiles (tcgen05 cta_group::2). A pair of blocks on neighbouring SMs, launched as a cluster of two,
+// computes a 256 x 256 output tile: each block stages its own 128 rows of activations and its own 128 weight rows
+// (half of the tile's columns) per K step, and one MMA instruction issued by the pair's first block multiplies all
+// 256 rows by all 256 columns, reading both blocks' shared memory and writing each block's 128 rows of fp32
+// accumulators into that block's TMEM. Per block and K step that is 32 KB of operands for a 128 x 256 slice of the
+// tile, against 48 KB when a block works alone: the single-block kernel is bound by what one SM can pull through
+// its shared memory (TMA writes plus the MMA's reads), and this one by the tensor cores.
+//   * Both blocks run a producer thread; the loads of both land on the first block's `full` barrier
+//     (cp.async.bulk.tensor with cta_group::2 may signal the partner's barrier), which expects the bytes of both.
+//   * tcgen05.commit with a two-block multicast mask hands a stage back to both producers and tells both
+//     blocks' epilogue warps that an accumulator buffer is complete.
+//   * The epilogue warps of both blocks arrive on the first block's `accumulator_free` barrier.
+//   * The cluster barrier brackets the kernel: no block signals a partner whose barriers are not initialised yet,
+//     and none leaves while its partner may still read its shared memory or write its barriers.
+// Every mbarrier wait is bounded as in the single-block kernel; a block that gives up stops signalling, its
+// partner's waits run out in turn, and both report the timeout.
+constexpr int kPairTileM = 2 * kTileM;
+constexpr int kPairTileN = 256;
+constexpr int kPairBytesA = kTileM * kTileK * 2;              // this block's 128 activation rows: 16 KB
+constexpr int kPairBytesB = (kPairTileN / 2) * kTileK * 2;    // this block's 128 weight rows: 16 KB
+constexpr int kPairStages = 6;
+constexpr int kPairSharedBytes = kPairStages * (kPairBytesA + kPairBytesB) + 1024;
+constexpr uint32_t kPairShapeBits = (static_cast<uint32_t>(kPairTileN >> 3) << 17) | (static_cast<uint32_t>(kPairTileM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+// Address, in the cluster's shared window, of the first block's copy of a shared variable of this block.
+__device__ __forceinline__ uint32_t first_block_address(uint32_t local) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(0));
+  return remote;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// One box into this block's shared memory; the bytes are counted on a barrier that may belong to the partner.
+__device__ __forceinline__ void tma_load_2d_pair(void* target, const CUtensorMap* map, uint32_t barrier_address, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(shared_address(target)), "l"(map), "r"(barrier_address), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void commit_to_pair(uint64_t* bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(shared_address(bar)), "h"(both) : "memory");
+}
+
+template <int OPERAND>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+  constexpr uint32_t kInstruction = OPERAND == kOperandFp8 ? ((1u << 4) | kPairShapeBits)
+                                    : (OPERAND == kOperandInt8 ? ((2u << 4) | (1u << 7) | (1u << 10) | kPairShapeBits)
+                                                               : ((1u << 4) | (1u << 7) | (1u << 10) | kPairShapeBits));
+  constexpr bool kScaled = OPERAND != kOperandBf16;
+  constexpr int kElementsPerStep = kScaled ? 128 : 64;
+  constexpr uint32_t kColumns = kPairTileN;              // TMEM columns per accumulator buffer
+  extern __shared__ uint8_t raw_shared[];
+  __shared__ __align__(8) uint64_t full[kPairStages];        // used in the first block: operands of both blocks have landed
+  __shared__ __align__(8) uint64_t empty[kPairStages];       // in each block: the MMAs that read the stage are done
+  __shared__ __align__(8) uint64_t accumulator_ready[2];     // in each block: this block's rows of the buffer are complete
+  __shared__ __align__(8) uint64_t accumulator_free[2];      // used in the first block: both blocks have drained the buffer
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int failed;
+  __shared__ __align__(16) float column_factors[kEpilogueWarps][2][kPairTileN / 2];
+  uint8_t* tiles_a = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* tiles_b = tiles_a + kPairStages * kPairBytesA;
+  const int warp = threadIdx.x >> 5;
+  const uint32_t lane = lane_id();
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1;
+  const int pairs = gridDim.x >> 1;
+  const int k_steps = (p.k + kElementsPerStep - 1) / kElementsPerStep;
+  const int n_tiles = (p.n + kPairTileN - 1) / kPairTileN;
+  const int total_tiles = n_tiles * ((p.m + kPairTileM - 1) / kPairTileM);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      barrier_init(&full[s], 1);
+      barrier_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      barrier_init(&accumulator_ready[b], 1);
+      barrier_init(&accumulator_free[b], 2 * kEpilogueWarps);   // one arrival per epilogue warp of either block
+    }
+    failed = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    // the same warp of both blocks allocates (and later frees) the pair's accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(shared_address(&tmem_base_holder)),
+                 "r"(2u * kColumns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_holder;
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer (both blocks): this block's rows of the activations and of the weight, counted on the first
+    // block's barrier
+    const uint32_t full_first = first_block_address(shared_address(&full[0]));
+    int step = 0;
+    for (int tile = pair; tile < total_tiles && !failed; tile += pairs) {
+      const int m0 = (tile / n_tiles) * kPairTileM + static_cast<int>(rank) * kTileM;
+      const int n0 = (tile % n_tiles) * kPairTileN + static_cast<int>(rank) * (kPairTileN / 2);
+      for (int ks = 0; ks < k_steps; ++ks, ++step) {
+        const int s = step % kPairStages;
+        if (step >= kPairStages && !barrier_wait(&empty[s], ((step / kPairStages) - 1) & 1)) {
+          failed = 1;
+          break;
+        }
+        if (rank == 0) barrier_expect(&full[s], 2 * (kPairBytesA + kPairBytesB));
+        tma_load_2d_pair(tiles_a + s * kPairBytesA, &map_x, full_first + 8u * s, ks * kElementsPerStep, m0);
+        tma_load_2d_pair(tiles_b + s * kPairBytesB, &map_w, full_first + 8u * s, ks * kElementsPerStep, n0);
+      }
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---- MMA issuer (first block only): four K-slices per stage, 256 rows x 256 columns each
+    int step = 0;
+    int local = 0;
+    for (int tile = pair; tile < total_tiles && !failed; tile += pairs, ++local) {
+      const int buffer = local & 1;
+      if (!barrier_wait(&accumulator_free[buffer], ((local >> 1) & 1) ^ 1)) {
+        failed = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t accumulator = tmem_base + static_cast<uint32_t>(buffer) * kColumns;
+      bool ok = true;
+      for (int ks = 0; ks < k_steps; ++ks, ++step) {
+        const int s = step % kPairStages;
+        ok = barrier_wait(&full[s], (step / kPairStages) & 1);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t a = matrix_descriptor(shared_address(tiles_a + s * kPairBytesA));
+        const uint64_t b = matrix_descriptor(shared_address(tiles_b + s * kPairBytesB));
+#pragma unroll
+        for (int kk = 0; kk < kTileK / 16; ++kk) {
+          const uint32_t accumulate = (ks | kk) ? 1u : 0u;
+          if (OPERAND == kOperandFp8) {
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          } else if (OPERAND == kOperandInt8) {
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}"
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          } else {
+            asm volatile(
+                "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+          }
+        }
+        commit_to_pair(&empty[s]);
+      }
+      if (!ok) failed = 1;
+      commit_to_pair(&accumulator_ready[buffer]);   // also on the failure path, so that the epilogue warps wake
+      if (!ok) break;
+    }
+  } else if (warp >= 2) {
+    // ---- epilogue (both blocks): as in the single-block kernel, on this block's 128 rows of the tile
+    const int quadrant = warp & 3;
+    const int member = warp - 2;
+    constexpr int kChunksPerWarp = kPairTileN / 64;
+    const int first_chunk = (member >> 2) * kChunksPerWarp;
+    const uint32_t free_first = first_block_address(shared_address(&accumulator_free[0]));
+    int local = 0;
+    for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
+      const int buffer = local & 1;
+      const int m0 = (tile / n_tiles) * kPairTileM + static_cast<int>(rank) * kTileM;
+      const int n0 = (tile % n_tiles) * kPairTileN;
+      const bool staged = kScaled || p.bias;
+      if (staged) {
+        stage_column_factors<OPERAND>(p, column_factors[member][0], column_factors[member][1], n0 + first_chunk * 32, kChunksPerWarp * 32, lane);
+      }
+      const bool ready = barrier_wait(&accumulator_ready[buffer], (local >> 1) & 1);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!ready || failed) {
+        if (lane == 0) failed = 1;
+        break;
+      }
+      const int row = m0 + quadrant * 32 + static_cast<int>(lane);
+      const float row_scale = kScaled && row < p.m ? p.row_scale[row] : 1.0f;
+#pragma unroll 1
+      for (int chunk = first_chunk; chunk < first_chunk + kChunksPerWarp; ++chunk) {
+        uint32_t v[32];
+        load_accumulator_chunk(v, tmem_base + static_cast<uint32_t>(buffer) * kColumns + (static_cast<uint32_t>(quadrant * 32) << 16) +
+                                      static_cast<uint32_t>(chunk * 32));
+        if (chunk == first_chunk + kChunksPerWarp - 1) {
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(free_first + 8u * buffer) : "memory");
+          }
+        }
+        const int col = n0 + chunk * 32;
+        if (row < p.m && col < p.n) {
+          finish_chunk<OPERAND>(v, p, row, col, row_scale, staged ? &column_factors[member][0][(chunk - first_chunk) * 32] : nullptr,
+                                staged ? &column_factors[member][1][(chunk - first_chunk) * 32] : nullptr);
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2u * kColumns) : "memory");
   }
   if (threadIdx.x == 0 && failed) report(p.error, kGemmTimeout);
 }
@@ -612,10 +856,75 @@ int launch_narrow(const void* x_dev, const void* weight_dev, const GemmParams& p
   return launch_tcgen05<TILE_N, 128, OPERAND>(x_dev, weight_dev, p, s);
 }
 
+// Pairs of blocks that can be resident at once (0 when clusters of two cannot be launched here); asked once per
+// operand type.
+template <int OPERAND>
+int resident_pairs() {
+  static std::once_flag once;
+  static int pairs = 0;
+  std::call_once(once, [] {
+    if (cudaFuncSetAttribute(linear_tcgen05_pair_kernel<OPERAND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSharedBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = 2;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * kSmCount);
+    config.blockDim = dim3(kGemmThreads);
+    config.dynamicSmemBytes = kPairSharedBytes;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, linear_tcgen05_pair_kernel<OPERAND>, &config) != cudaSuccess) {
+      cudaGetLastError();
+      return;
+    }
+    pairs = clusters;
+  });
+  return pairs;
+}
+
+template <int OPERAND>
+int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& p, int pairs, cudaStream_t s) {
+  CUtensorMap map_x, map_w;
+  if (!make_tile_map(&map_x, x_dev, p.m, p.k, kTileM, OPERAND) || !make_tile_map(&map_w, weight_dev, p.n, p.k, kPairTileN / 2, OPERAND)) {
+    return EP_ERR_UNSUPPORTED;
+  }
+  const int64_t tiles = static_cast<int64_t>((p.n + kPairTileN - 1) / kPairTileN) * ((p.m + kPairTileM - 1) / kPairTileM);
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 2;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(2u * static_cast<unsigned>(tiles < pairs ? tiles : pairs));
+  config.blockDim = dim3(kGemmThreads);
+  config.dynamicSmemBytes = kPairSharedBytes;
+  config.stream = s;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  EP_CUDA_CHECK(cudaLaunchKernelEx(&config, linear_tcgen05_pair_kernel<OPERAND>, map_x, map_w, p));
+  return EP_OK;
+}
+
 // Tile width. A block's time goes with the bytes it pulls through L2 per K step (activation box + weight box);
 // blocks beyond what the SMs hold at once run in further rounds. Take the width with the least rounds x bytes.
 template <int OPERAND>
 int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
+  // Large products go to the two-block tiles: at least two rounds of 256 x 256 tiles over the resident pairs.
+  if (p.m > kTileM) {
+    const int pairs = resident_pairs<OPERAND>();
+    const int64_t pair_tiles = static_cast<int64_t>((p.n + kPairTileN - 1) / kPairTileN) * ((p.m + kPairTileM - 1) / kPairTileM);
+    if (pairs >= 32 && pair_tiles >= 2 * static_cast<int64_t>(pairs)) {
+      const int rc = launch_pair<OPERAND>(x_dev, weight_dev, p, pairs, s);
+      if (rc != EP_OK) return rc;
+      return check_launch("linear_tcgen05_pair_kernel");
+    }
+  }
   const int64_t row_tiles = (p.m + kTileM - 1) / kTileM;
   const int a_rows = p.m <= 16 ? 16 : (p.m <= 32 ? 32 : (p.m <= 64 ? 64 : 128));
   int tile_n = 32;

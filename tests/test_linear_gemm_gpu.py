@@ -9,6 +9,7 @@ pytestmark = pytest.mark.gpu
     (1, 512, 1024, True), (4, 384, 3840, False), (16, 1000, 264, True),          # CUDA-core kernel
     (17, 128, 64, False), (128, 128, 128, True), (256, 384, 1024, True),         # tensor-core kernel
     (300, 1000, 264, True), (130, 136, 3840, False), (1024, 3840, 3840, True),
+    (4096, 3840, 3840, True), (1500, 10000, 1088, True), (2100, 4600, 1152, False),   # two-block tiles, whole and ragged
 ])
 def test_matches_fp32_reference(m, n, k, bias):
     from entropack_b200.linear import linear_forward
@@ -49,7 +50,7 @@ def test_fp8_row_quantisation_matches_the_torch_expression(dtype):
 
 @pytest.mark.parametrize("m,n,k,out_dtype,with_bias", [
     (1, 768, 1024, torch.bfloat16, True), (16, 3840, 3840, torch.bfloat16, False), (200, 1000, 2048, torch.float32, True),
-    (4096, 3840, 3840, torch.bfloat16, True), (300, 520, 4096, torch.bfloat16, False),
+    (4096, 3840, 3840, torch.bfloat16, True), (300, 520, 4096, torch.bfloat16, False), (1500, 10000, 1152, torch.float32, True),
 ])
 def test_fp8_gemm_matches_scaled_mm(m, n, k, out_dtype, with_bias):
     """tcgen05 kind::f8f6f4 kernel against torch._scaled_mm on the same codes and scales. Products of e4m3 values are
@@ -99,6 +100,7 @@ def test_int8_row_quantisation_matches_the_torch_expression():
 
 @pytest.mark.parametrize("m,n,k,out_dtype,with_bias", [
     (1, 768, 1024, torch.float32, True), (40, 1000, 2048, torch.float32, False), (4096, 3840, 3840, torch.bfloat16, True),
+    (2100, 4600, 1152, torch.float32, False),
 ])
 def test_int8_gemm_is_the_exact_integer_product_scaled(m, n, k, out_dtype, with_bias):
     """kind::i8 accumulates in 32-bit integers, so the product itself is exact; what remains is one fp32 multiply-add
