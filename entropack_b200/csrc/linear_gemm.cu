@@ -273,6 +273,7 @@ struct GemmParams {
   const float* column_scale;
   const float* bias_f32;
   float* y_f32;
+  int pair_tile_n;               // two-block kernel: columns per tile (a multiple of 32, 128..256)
 };
 
 // Loads 32 consecutive accumulator columns of this thread's TMEM lane and waits for them.
@@ -583,13 +584,16 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 //     and none leaves while its partner may still read its shared memory or write its barriers.
 // Every mbarrier wait is bounded as in the single-block kernel; a block that gives up stops signalling, its
 // partner's waits run out in turn, and both report the timeout.
+// The tile is 256 rows by `pair_tile_n` columns, 256 at most. Narrower tiles (224, 192) are for products whose
+// count of 256-wide tiles leaves most pairs idle in the last round: 4096 x 3840 is 240 such tiles for 74 pairs,
+// 3.24 rounds that take 4, and 288 tiles of 224 columns, 3.9 rounds that take 4 x 224/256 = 3.5.
 constexpr int kPairTileM = 2 * kTileM;
-constexpr int kPairTileN = 256;
+constexpr int kPairTileN = 256;                               // widest tile: sizes shared memory and TMEM
 constexpr int kPairBytesA = kTileM * kTileK * 2;              // this block's 128 activation rows: 16 KB
-constexpr int kPairBytesB = (kPairTileN / 2) * kTileK * 2;    // this block's 128 weight rows: 16 KB
+constexpr int kPairBytesB = (kPairTileN / 2) * kTileK * 2;    // this block's weight rows (half the tile's columns): up to 16 KB
 constexpr int kPairStages = 6;
 constexpr int kPairSharedBytes = kPairStages * (kPairBytesA + kPairBytesB) + 1024;
-constexpr uint32_t kPairShapeBits = (static_cast<uint32_t>(kPairTileN >> 3) << 17) | (static_cast<uint32_t>(kPairTileM >> 4) << 24);
+constexpr uint32_t kPairShapeBits = static_cast<uint32_t>(kPairTileM >> 4) << 24;   // the column count is added per launch
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t rank;
@@ -642,7 +646,8 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
   const int pair = blockIdx.x >> 1;
   const int pairs = gridDim.x >> 1;
   const int k_steps = (p.k + kElementsPerStep - 1) / kElementsPerStep;
-  const int n_tiles = (p.n + kPairTileN - 1) / kPairTileN;
+  const int tile_n = p.pair_tile_n;
+  const int n_tiles = (p.n + tile_n - 1) / tile_n;
   const int total_tiles = n_tiles * ((p.m + kPairTileM - 1) / kPairTileM);
 
   if (threadIdx.x == 0) {
@@ -676,20 +681,21 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     int step = 0;
     for (int tile = pair; tile < total_tiles && !failed; tile += pairs) {
       const int m0 = (tile / n_tiles) * kPairTileM + static_cast<int>(rank) * kTileM;
-      const int n0 = (tile % n_tiles) * kPairTileN + static_cast<int>(rank) * (kPairTileN / 2);
+      const int n0 = (tile % n_tiles) * tile_n + static_cast<int>(rank) * (tile_n / 2);
       for (int ks = 0; ks < k_steps; ++ks, ++step) {
         const int s = step % kPairStages;
         if (step >= kPairStages && !barrier_wait(&empty[s], ((step / kPairStages) - 1) & 1)) {
           failed = 1;
           break;
         }
-        if (rank == 0) barrier_expect(&full[s], 2 * (kPairBytesA + kPairBytesB));
+        if (rank == 0) barrier_expect(&full[s], 2 * (kPairBytesA + (tile_n / 2) * kTileK * 2));
         tma_load_2d_pair(tiles_a + s * kPairBytesA, &map_x, full_first + 8u * s, ks * kElementsPerStep, m0);
         tma_load_2d_pair(tiles_b + s * kPairBytesB, &map_w, full_first + 8u * s, ks * kElementsPerStep, n0);
       }
     }
   } else if (warp == 1 && lane == 0 && rank == 0) {
-    // ---- MMA issuer (first block only): four K-slices per stage, 256 rows x 256 columns each
+    // ---- MMA issuer (first block only): four K-slices per stage, 256 rows x tile_n columns each
+    const uint32_t instruction = kInstruction | (static_cast<uint32_t>(tile_n >> 3) << 17);
     int step = 0;
     int local = 0;
     for (int tile = pair; tile < total_tiles && !failed; tile += pairs, ++local) {
@@ -714,15 +720,15 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
           if (OPERAND == kOperandFp8) {
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
-                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(instruction), "r"(accumulate) : "memory");
           } else if (OPERAND == kOperandInt8) {
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}"
-                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(instruction), "r"(accumulate) : "memory");
           } else {
             asm volatile(
                 "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
-                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(kInstruction), "r"(accumulate) : "memory");
+                ::"r"(accumulator), "l"(a + 2u * kk), "l"(b + 2u * kk), "r"(instruction), "r"(accumulate) : "memory");
           }
         }
         commit_to_pair(&empty[s]);
@@ -735,17 +741,19 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     // ---- epilogue (both blocks): as in the single-block kernel, on this block's 128 rows of the tile
     const int quadrant = warp & 3;
     const int member = warp - 2;
-    constexpr int kChunksPerWarp = kPairTileN / 64;
-    const int first_chunk = (member >> 2) * kChunksPerWarp;
+    // the quadrant's first warp takes the larger half of the tile's 32-column chunks (4 to 8 of them)
+    const int chunks = tile_n / 32;
+    const int first_chunk = (member >> 2) * ((chunks + 1) / 2);
+    const int chunks_here = (member >> 2) ? chunks / 2 : (chunks + 1) / 2;
     const uint32_t free_first = first_block_address(shared_address(&accumulator_free[0]));
     int local = 0;
     for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
       const int buffer = local & 1;
       const int m0 = (tile / n_tiles) * kPairTileM + static_cast<int>(rank) * kTileM;
-      const int n0 = (tile % n_tiles) * kPairTileN;
+      const int n0 = (tile % n_tiles) * tile_n;
       const bool staged = kScaled || p.bias;
       if (staged) {
-        stage_column_factors<OPERAND>(p, column_factors[member][0], column_factors[member][1], n0 + first_chunk * 32, kChunksPerWarp * 32, lane);
+        stage_column_factors<OPERAND>(p, column_factors[member][0], column_factors[member][1], n0 + first_chunk * 32, chunks_here * 32, lane);
       }
       const bool ready = barrier_wait(&accumulator_ready[buffer], (local >> 1) & 1);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -756,11 +764,11 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
       const int row = m0 + quadrant * 32 + static_cast<int>(lane);
       const float row_scale = kScaled && row < p.m ? p.row_scale[row] : 1.0f;
 #pragma unroll 1
-      for (int chunk = first_chunk; chunk < first_chunk + kChunksPerWarp; ++chunk) {
+      for (int chunk = first_chunk; chunk < first_chunk + chunks_here; ++chunk) {
         uint32_t v[32];
         load_accumulator_chunk(v, tmem_base + static_cast<uint32_t>(buffer) * kColumns + (static_cast<uint32_t>(quadrant * 32) << 16) +
                                       static_cast<uint32_t>(chunk * 32));
-        if (chunk == first_chunk + kChunksPerWarp - 1) {
+        if (chunk == first_chunk + chunks_here - 1) {
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) {
@@ -889,12 +897,14 @@ int resident_pairs() {
 }
 
 template <int OPERAND>
-int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& p, int pairs, cudaStream_t s) {
+int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& problem, int tile_n, int pairs, cudaStream_t s) {
+  GemmParams p = problem;
+  p.pair_tile_n = tile_n;
   CUtensorMap map_x, map_w;
-  if (!make_tile_map(&map_x, x_dev, p.m, p.k, kTileM, OPERAND) || !make_tile_map(&map_w, weight_dev, p.n, p.k, kPairTileN / 2, OPERAND)) {
+  if (!make_tile_map(&map_x, x_dev, p.m, p.k, kTileM, OPERAND) || !make_tile_map(&map_w, weight_dev, p.n, p.k, tile_n / 2, OPERAND)) {
     return EP_ERR_UNSUPPORTED;
   }
-  const int64_t tiles = static_cast<int64_t>((p.n + kPairTileN - 1) / kPairTileN) * ((p.m + kPairTileM - 1) / kPairTileM);
+  const int64_t tiles = static_cast<int64_t>((p.n + tile_n - 1) / tile_n) * ((p.m + kPairTileM - 1) / kPairTileM);
   cudaLaunchAttribute attribute;
   attribute.id = cudaLaunchAttributeClusterDimension;
   attribute.val.clusterDim.x = 2;
@@ -918,9 +928,21 @@ int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams
   // Large products go to the two-block tiles: at least two rounds of 256 x 256 tiles over the resident pairs.
   if (p.m > kTileM) {
     const int pairs = resident_pairs<OPERAND>();
-    const int64_t pair_tiles = static_cast<int64_t>((p.n + kPairTileN - 1) / kPairTileN) * ((p.m + kPairTileM - 1) / kPairTileM);
+    const int64_t row_pairs = (p.m + kPairTileM - 1) / kPairTileM;
+    const int64_t pair_tiles = static_cast<int64_t>((p.n + kPairTileN - 1) / kPairTileN) * row_pairs;
     if (pairs >= 32 && pair_tiles >= 2 * static_cast<int64_t>(pairs)) {
-      const int rc = launch_pair<OPERAND>(x_dev, weight_dev, p, pairs, s);
+      // tile width: rounds x columns is what the tensor cores spend; the widest of the cheapest
+      int tile_n = kPairTileN;
+      int64_t best = -1;
+      for (int candidate = kPairTileN; candidate >= 192; candidate -= 32) {
+        const int64_t tiles = static_cast<int64_t>((p.n + candidate - 1) / candidate) * row_pairs;
+        const int64_t cost = ((tiles + pairs - 1) / pairs) * candidate;
+        if (best < 0 || cost < best) {
+          best = cost;
+          tile_n = candidate;
+        }
+      }
+      const int rc = launch_pair<OPERAND>(x_dev, weight_dev, p, tile_n, pairs, s);
       if (rc != EP_OK) return rc;
       return check_launch("linear_tcgen05_pair_kernel");
     }
