@@ -27,13 +27,14 @@ def test_matches_fp32_reference(m, n, k, bias):
     assert float((out.float() - expected).abs().max() / expected.abs().max()) <= 1e-2
 
 
+@pytest.mark.parametrize("cols", [1000, 1001, 3840])       # 16-byte row reads, element-wise fallback, more than one read per thread
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-def test_fp8_row_quantisation_matches_the_torch_expression(dtype):
+def test_fp8_row_quantisation_matches_the_torch_expression(dtype, cols):
     """Same scale and the same e4m3 codes, bit for bit, as QuantizedLinear._quantize_rows computes with torch ops."""
     from entropack_b200 import _native
 
     generator = torch.Generator(device="cuda").manual_seed(3)
-    x = (torch.randn(37, 1000, generator=generator, device="cuda") * 3).to(dtype)
+    x = (torch.randn(37, cols, generator=generator, device="cuda") * 3).to(dtype)
     x[5] = 0          # an all-zero row takes the epsilon scale
     x[6, 10] = 7e4 if dtype is not torch.float16 else 6e4
     codes = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device="cuda")
@@ -80,11 +81,12 @@ def test_fp8_gemm_matches_scaled_mm(m, n, k, out_dtype, with_bias):
         assert float((out.float() - library.float()).abs().max() / expected.abs().max()) <= 1e-2
 
 
-def test_int8_row_quantisation_matches_the_torch_expression():
+@pytest.mark.parametrize("cols", [777, 2048])
+def test_int8_row_quantisation_matches_the_torch_expression(cols):
     from entropack_b200 import _native
 
     generator = torch.Generator(device="cuda").manual_seed(4)
-    x = (torch.randn(33, 777, generator=generator, device="cuda") * 3).to(torch.bfloat16)
+    x = (torch.randn(33, cols, generator=generator, device="cuda") * 3).to(torch.bfloat16)
     x[2] = 0
     x[3, :8] = torch.tensor([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 127.0, -127.0], device="cuda").to(torch.bfloat16) * (x[3].abs().max() / 127)
     codes = torch.empty(x.shape, dtype=torch.int8, device="cuda")
