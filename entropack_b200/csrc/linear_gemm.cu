@@ -307,7 +307,7 @@ struct GemmParams {
   const float* column_scale;
   const float* bias_f32;
   float* y_f32;
-  int pair_tile_n;               // two-block kernel: columns per tile (a multiple of 32, 128..256)
+  int pair_tile_n;               // two-block kernel: columns per tile (a multiple of 32, 64..256)
 };
 
 // Loads 32 consecutive accumulator columns of this thread's TMEM lane and waits for them.
@@ -775,7 +775,7 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     // ---- epilogue (both blocks): as in the single-block kernel, on this block's 128 rows of the tile
     const int quadrant = warp & 3;
     const int member = warp - 2;
-    // the quadrant's first warp takes the larger half of the tile's 32-column chunks (4 to 8 of them)
+    // the quadrant's first warp takes the larger half of the tile's 32-column chunks (2 to 8 of them)
     const int chunks = tile_n / 32;
     const int first_chunk = (member >> 2) * ((chunks + 1) / 2);
     const int chunks_here = (member >> 2) ? chunks / 2 : (chunks + 1) / 2;
@@ -955,46 +955,48 @@ int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& pro
   return EP_OK;
 }
 
-// Tile width. A block's time goes with the bytes it pulls through L2 per K step (activation box + weight box);
-// blocks beyond what the SMs hold at once run in further rounds. Take the width with the least rounds x bytes.
+// Tile shape. What a K step costs an SM, in clocks: the tensor cores need 2 x columns (four MMAs of 128 rows), and
+// the shared memory, which takes the TMA's writes and feeds the MMA's reads at 128 bytes per clock, needs
+// 2 x (rows staged for A + rows staged for B). A single block stages 128 (or fewer) + columns rows; a block of a pair
+// stages 128 + columns / 2 for the same 128 x columns slice of the output. Tiles beyond what is resident at once run
+// in further rounds: take the shape with the least rounds x clocks, the two-block tiles first among equals.
 template <int OPERAND>
 int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
-  // Large products go to the two-block tiles: at least two rounds of 256 x 256 tiles over the resident pairs.
-  if (p.m > kTileM) {
-    const int pairs = resident_pairs<OPERAND>();
-    const int64_t row_pairs = (p.m + kPairTileM - 1) / kPairTileM;
-    const int64_t pair_tiles = static_cast<int64_t>((p.n + kPairTileN - 1) / kPairTileN) * row_pairs;
-    if (pairs >= 32 && pair_tiles >= 2 * static_cast<int64_t>(pairs)) {
-      // tile width: rounds x columns is what the tensor cores spend; the widest of the cheapest
-      int tile_n = kPairTileN;
-      int64_t best = -1;
-      for (int candidate = kPairTileN; candidate >= 192; candidate -= 32) {
-        const int64_t tiles = static_cast<int64_t>((p.n + candidate - 1) / candidate) * row_pairs;
-        const int64_t cost = ((tiles + pairs - 1) / pairs) * candidate;
-        if (best < 0 || cost < best) {
-          best = cost;
-          tile_n = candidate;
-        }
-      }
-      const int rc = launch_pair<OPERAND>(x_dev, weight_dev, p, tile_n, pairs, s);
-      if (rc != EP_OK) return rc;
-      return check_launch("linear_tcgen05_pair_kernel");
-    }
-  }
   const int64_t row_tiles = (p.m + kTileM - 1) / kTileM;
   const int a_rows = p.m <= 16 ? 16 : (p.m <= 32 ? 32 : (p.m <= 64 ? 64 : 128));
   int tile_n = 32;
+  bool two_blocks = false;
   int64_t best = -1;
+  const int pairs = p.m > kTileM ? resident_pairs<OPERAND>() : 0;
+  if (pairs >= 32) {
+    const int64_t row_pairs = (p.m + kPairTileM - 1) / kPairTileM;
+    for (int candidate = kPairTileN; candidate >= 64; candidate -= 32) {
+      const int64_t tiles = static_cast<int64_t>((p.n + candidate - 1) / candidate) * row_pairs;
+      const int64_t clocks = 2 * candidate > 256 + candidate ? 2 * candidate : 256 + candidate;
+      const int64_t cost = ((tiles + pairs - 1) / pairs) * clocks;
+      if (best < 0 || cost < best) {
+        best = cost;
+        tile_n = candidate;
+        two_blocks = true;
+      }
+    }
+  }
   for (int candidate = 256; candidate >= 32; candidate >>= 1) {
     const bool narrow = candidate <= 64;
     const int box_a = narrow ? a_rows : 128;
     const int64_t blocks = row_tiles * ((p.n + candidate - 1) / candidate);
     const int64_t resident = static_cast<int64_t>(kSmCount) * (box_a < 128 ? 3 : 1);
-    const int64_t cost = ((blocks + resident - 1) / resident) * (box_a + candidate);
+    const int64_t cost = ((blocks + resident - 1) / resident) * 2 * (box_a + candidate);
     if (best < 0 || cost < best) {
       best = cost;
       tile_n = candidate;
+      two_blocks = false;
     }
+  }
+  if (two_blocks) {
+    const int rc = launch_pair<OPERAND>(x_dev, weight_dev, p, tile_n, pairs, s);
+    if (rc != EP_OK) return rc;
+    return check_launch("linear_tcgen05_pair_kernel");
   }
   int rc = EP_ERR_UNSUPPORTED;
   switch (tile_n) {
