@@ -288,7 +288,8 @@ def run_b200(args) -> None:
     others = measure_others(ep, device, flush, args.steps) if not args.headline_only else {}
 
     # whole-model encode: this rank's share of the synthetic 276-linear DiT at 4 bpp (layers sharded, no collectives)
-    model = measure_model_encode(ep, device, rank, world) if not args.headline_only else {"seconds": 0.0, "layers": 0, "bpp": 0.0}
+    model = measure_model_encode(ep, device, rank, world) if not args.headline_only else {
+        "seconds": 0.0, "layers": 0, "bpp": 0.0, "decode_seconds": 0.0, "forward_seconds": 0.0, "mixed_seconds": 0.0, "mixed_bpp": 0.0}
 
     # end to end through the public API from pinned host blobs
     host_blobs = [c.entropack_quant_state.cpu().pin_memory() for c in containers]
@@ -314,9 +315,12 @@ def run_b200(args) -> None:
     assert torch.equal(host_outputs[0], launches[0][4].view(torch.uint8).reshape(-1).cpu())
 
     if distributed:
-        times = torch.tensor([total_ms, e2e_seconds, model["seconds"]], dtype=torch.float64, device=device)
+        timed_keys = ("seconds", "decode_seconds", "forward_seconds", "mixed_seconds")
+        times = torch.tensor([total_ms, e2e_seconds] + [model[key] for key in timed_keys], dtype=torch.float64, device=device)
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-        total_ms, e2e_seconds, model["seconds"] = float(times[0]), float(times[1]), float(times[2])
+        total_ms, e2e_seconds = float(times[0]), float(times[1])
+        for position, key in enumerate(timed_keys):
+            model[key] = float(times[2 + position])
     if rank != 0:
         if distributed:
             dist.destroy_process_group()
@@ -349,7 +353,9 @@ def run_b200(args) -> None:
         "others": others,
         "model_encode": {"workload": "synthetic DiT, 276 linears (hidden 3840, mlp 10240), bf16 N(0,0.02^2), 4 bpp, layers sharded "
                                      "largest-first over the ranks", "seconds": model["seconds"], "layers_on_rank0": model["layers"],
-                         "mean_bpp_rank0": model["bpp"]},
+                         "mean_bpp_rank0": model["bpp"], "decode_all_seconds": model["decode_seconds"],
+                         "forward_4096_tokens_seconds": model["forward_seconds"], "mixed_2p3_bpp_encode_seconds": model["mixed_seconds"],
+                         "mixed_mean_bpp_rank0": model["mixed_bpp"]},
         "gpu_launches": len(launches) * args.steps,
         "clocks": clocks,
     }
@@ -359,26 +365,71 @@ def run_b200(args) -> None:
 
 
 def measure_model_encode(ep, device, rank: int, world: int) -> dict:
+    """This rank's share of the synthetic 276-linear DiT: every layer compressed at 4 bpp, then decoded, then run on
+    4096 tokens (decode + product per layer, every layer fed its own width of seeded activations), then compressed
+    again at the mixed per-layer targets that average 2.3 bpp. Wall-clock seconds around device-synchronised loops."""
     from entropack_b200 import sharding
 
     shapes = sharding.dit_layer_shapes()
     mine = sharding.partition_layers([r * c for r, c in shapes], world)[rank]
+    targets = sharding.mixed_bit_targets(shapes)
     config = ep.EntroPackLossyConfig(target_bpp=4.0)
-    generator = torch.Generator(device=device).manual_seed(1000 + rank)
-    seconds, stored, elements = 0.0, 0, 0
-    warm = (torch.randn(3840, 3840, generator=generator, device=device) * 0.02).to(torch.bfloat16)
+    warm = (torch.randn(3840, 3840, generator=torch.Generator(device=device).manual_seed(999), device=device) * 0.02).to(torch.bfloat16)
     ep.compress(warm, config)
-    for index in mine:
-        rows, cols = shapes[index]
-        weight = (torch.randn(rows, cols, generator=generator, device=device) * 0.02).to(torch.bfloat16)
+
+    def layer_weights():
+        generator = torch.Generator(device=device).manual_seed(1000 + rank)
+        for index in mine:
+            rows, cols = shapes[index]
+            yield index, (torch.randn(rows, cols, generator=generator, device=device) * 0.02).to(torch.bfloat16)
+
+    seconds, stored, elements, layers = 0.0, 0, 0, []
+    for index, weight in layer_weights():
         torch.cuda.synchronize(device)
         begin = time.perf_counter()
         container = ep.compress(weight, config)
         torch.cuda.synchronize(device)
         seconds += time.perf_counter() - begin
         stored += container.storage_nbytes()
-        elements += rows * cols
-    return {"seconds": seconds, "layers": len(mine), "bpp": stored * 8 / max(1, elements)}
+        elements += weight.numel()
+        layer = ep.CompressedLinear(weight.shape[1], weight.shape[0], bias=False, config=config, device=device)
+        layer.load_state_dict({"weight.entropack_quant_state": container.entropack_quant_state})
+        layers.append(layer)
+
+    for layer in layers[:4]:
+        layer.dequantize()
+    torch.cuda.synchronize(device)
+    begin = time.perf_counter()
+    for layer in layers:
+        layer.dequantize()
+    torch.cuda.synchronize(device)
+    decode_seconds = time.perf_counter() - begin
+
+    generator = torch.Generator(device=device).manual_seed(2000 + rank)
+    tokens = {width: torch.randn(4096, width, generator=generator, device=device).to(torch.bfloat16)
+              for width in sorted({layer.in_features for layer in layers})}
+    with torch.no_grad():
+        for layer in layers[:4]:
+            layer(tokens[layer.in_features])
+        torch.cuda.synchronize(device)
+        begin = time.perf_counter()
+        for layer in layers:
+            layer(tokens[layer.in_features])
+        torch.cuda.synchronize(device)
+    forward_seconds = time.perf_counter() - begin
+    del layers, tokens
+
+    mixed_seconds, mixed_stored = 0.0, 0
+    for index, weight in layer_weights():
+        mixed = ep.EntroPackLossyConfig(target_bpp=targets[index])
+        torch.cuda.synchronize(device)
+        begin = time.perf_counter()
+        container = ep.compress(weight, mixed)
+        torch.cuda.synchronize(device)
+        mixed_seconds += time.perf_counter() - begin
+        mixed_stored += container.storage_nbytes()
+    return {"seconds": seconds, "layers": len(mine), "bpp": stored * 8 / max(1, elements), "decode_seconds": decode_seconds,
+            "forward_seconds": forward_seconds, "mixed_seconds": mixed_seconds, "mixed_bpp": mixed_stored * 8 / max(1, elements)}
 
 
 def measure_others(ep, device, flush, reps: int) -> dict:
