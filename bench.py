@@ -205,6 +205,12 @@ def run_b200(args) -> None:
     distributed = world > 1
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    # keep this rank's host thread, and the pinned buffers it allocates, on the socket its GPU hangs off (undone before the
+    # CPU baseline, which uses every host thread)
+    from entropack_b200 import sharding
+
+    original_cpus = os.sched_getaffinity(0)
+    bound_cpus = sharding.bind_host_thread_near(device)
     if distributed:
         import torch.distributed as dist
 
@@ -331,6 +337,7 @@ def run_b200(args) -> None:
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
     kernel_seconds = sum(kernel_ms) * 1e-3
     achieved = bytes_per_step / kernel_seconds / 1e9
+    os.sched_setaffinity(0, original_cpus)
     if args.headline_only:
         cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": "skipped (--headline-only)"}
     else:
@@ -349,7 +356,8 @@ def run_b200(args) -> None:
                      "per_launch_GBps": {k: b / (ms * 1e-3) / 1e9 for k, b, ms in zip(KINDS, per_kind_bytes, kernel_ms)}},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": world * bytes_per_step * e2e_steps / e2e_seconds / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
+                "host_cpus_near_gpu": None if bound_cpus is None else len(bound_cpus)},
         "others": others,
         "model_encode": {"workload": "synthetic DiT, 276 linears (hidden 3840, mlp 10240), bf16 N(0,0.02^2), 4 bpp, layers sharded "
                                      "largest-first over the ranks", "seconds": model["seconds"], "layers_on_rank0": model["layers"],

@@ -46,6 +46,37 @@ def mixed_bit_targets(shapes, mean_bpp: float = 2.3, seed: int = 0) -> list[floa
     return [round(float(v), 3) for v in raw]
 
 
+def bind_host_thread_near(device: torch.device | int) -> list[int] | None:
+    """Restrict the calling process to the CPUs that NVML reports as local to ``device`` (the cores of the socket its
+    PCIe root hangs off), so that pinned staging buffers allocated afterwards sit in that socket's memory and uploads
+    and downloads do not cross the inter-socket link. With one rank per GPU on a two-socket host this is what keeps
+    the ranks' host traffic apart. Returns the CPUs now in use, or None when nothing was changed (no NVML, no
+    affinity information, or none of the local CPUs is available to this process). Only the process's own CPU
+    affinity is touched; no GPU setting is."""
+    import os
+
+    try:
+        import pynvml
+    except ImportError:
+        return None
+    index = device if isinstance(device, int) else (device.index if device.index is not None else torch.cuda.current_device())
+    try:
+        pynvml.nvmlInit()
+        properties = torch.cuda.get_device_properties(index)
+        bus = f"{properties.pci_domain_id:08x}:{properties.pci_bus_id:02x}:{properties.pci_device_id:02x}.0"
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+    except Exception:    # NVML missing on the host, an unknown bus id, an old driver: leave the process where it is
+        return None
+    local = {64 * word + bit for word, bits in enumerate(mask) for bit in range(64) if (bits >> bit) & 1}
+    usable = sorted(local & os.sched_getaffinity(0))
+    if not usable:
+        return None
+    os.sched_setaffinity(0, usable)
+    return usable
+
+
 def partition_layers(sizes, world_size: int) -> list[list[int]]:
     """Greedy longest-processing-time assignment: layers by decreasing size onto the least-loaded rank.
     Deterministic (ties go to the lower layer index, then the lower rank)."""

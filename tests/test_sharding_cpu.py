@@ -65,3 +65,14 @@ def test_two_ranks_share_layers_and_gather_outputs():
     for r in range(world):
         assert results[r][1] == {i: float((4 + i) * 8 * i) for i in range(7)}
         assert results[r][2]
+
+
+def test_binding_near_a_gpu_is_a_no_op_without_one():
+    """No NVML device here: the helper reports that it changed nothing and leaves the affinity as it was."""
+    import os
+
+    from entropack_b200 import sharding
+
+    before = os.sched_getaffinity(0)
+    assert sharding.bind_host_thread_near(0) is None
+    assert os.sched_getaffinity(0) == before
