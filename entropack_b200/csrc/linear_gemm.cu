@@ -939,6 +939,8 @@ int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& pro
     return EP_ERR_UNSUPPORTED;
   }
   const int64_t tiles = static_cast<int64_t>((p.n + tile_n - 1) / tile_n) * ((p.m + kPairTileM - 1) / kPairTileM);
+  // per device, so on every launch (the occupancy query above ran on whichever device came first)
+  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_pair_kernel<OPERAND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSharedBytes));
   cudaLaunchAttribute attribute;
   attribute.id = cudaLaunchAttributeClusterDimension;
   attribute.val.clusterDim.x = 2;

@@ -64,3 +64,22 @@ def test_column_sharded_linear_all_gathers_outputs():
     for rank in range(world):
         shape, identical, relative = results[rank]
         assert shape == (48, 768) and identical and relative < 0.12
+
+
+def test_one_process_can_drive_the_product_on_two_devices():
+    """Kernel attributes (the dynamic shared memory limit) are per device: a process that multiplies on cuda:0 and then
+    on cuda:1 must get the large-tile kernels on both."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from entropack_b200.linear import linear_forward
+
+    generator = torch.Generator().manual_seed(3)
+    x = torch.randn(2048, 1024, generator=generator).to(torch.bfloat16)
+    w = (torch.randn(4608, 1024, generator=generator) * 0.02).to(torch.bfloat16)
+    expected = x.float() @ w.float().t()
+    for index in (0, 1):
+        device = torch.device("cuda", index)
+        with torch.cuda.device(device):
+            out = linear_forward(x.to(device), w.to(device))
+            torch.cuda.synchronize(device)
+        assert float((out.float().cpu() - expected).abs().max() / expected.abs().max()) <= 1e-2
