@@ -629,6 +629,22 @@ constexpr int kPairStages = 6;
 constexpr int kPairSharedBytes = kPairStages * (kPairBytesA + kPairBytesB) + 1024;
 constexpr uint32_t kPairShapeBits = static_cast<uint32_t>(kPairTileM >> 4) << 24;   // the column count is added per launch
 
+// Order of the pairs' tiles. The tiles at work at any moment are consecutive in this order, and what they read
+// together is what has to stay in L2: with rows of tiles taken one after the other, 74 tiles of a wide layer span
+// every weight row and the whole weight streams through L2 once per round. Here the order runs down bands of
+// kPairBandRows tile rows, column by column, so 74 consecutive tiles cover about 8 x 9 tiles: a ninth of the
+// weight and an eighth of the activations.
+constexpr int kPairBandRows = 8;
+__device__ __forceinline__ void pair_tile_position(int tile, int n_tiles, int m_tiles, int* m_index, int* n_index) {
+  const int band_tiles = kPairBandRows * n_tiles;
+  const int band = tile / band_tiles;
+  const int first_row = band * kPairBandRows;
+  const int rows = min(kPairBandRows, m_tiles - first_row);
+  const int within = tile - band * band_tiles;
+  *m_index = first_row + within % rows;
+  *n_index = within / rows;
+}
+
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t rank;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -682,7 +698,8 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
   const int k_steps = (p.k + kElementsPerStep - 1) / kElementsPerStep;
   const int tile_n = p.pair_tile_n;
   const int n_tiles = (p.n + tile_n - 1) / tile_n;
-  const int total_tiles = n_tiles * ((p.m + kPairTileM - 1) / kPairTileM);
+  const int m_tiles = (p.m + kPairTileM - 1) / kPairTileM;
+  const int total_tiles = n_tiles * m_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -714,8 +731,10 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     const uint32_t full_first = first_block_address(shared_address(&full[0]));
     int step = 0;
     for (int tile = pair; tile < total_tiles && !failed; tile += pairs) {
-      const int m0 = (tile / n_tiles) * kPairTileM + static_cast<int>(rank) * kTileM;
-      const int n0 = (tile % n_tiles) * tile_n + static_cast<int>(rank) * (tile_n / 2);
+      int m_index, n_index;
+      pair_tile_position(tile, n_tiles, m_tiles, &m_index, &n_index);
+      const int m0 = m_index * kPairTileM + static_cast<int>(rank) * kTileM;
+      const int n0 = n_index * tile_n + static_cast<int>(rank) * (tile_n / 2);
       for (int ks = 0; ks < k_steps; ++ks, ++step) {
         const int s = step % kPairStages;
         if (step >= kPairStages && !barrier_wait(&empty[s], ((step / kPairStages) - 1) & 1)) {
@@ -783,8 +802,10 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
     int local = 0;
     for (int tile = pair; tile < total_tiles; tile += pairs, ++local) {
       const int buffer = local & 1;
-      const int m0 = (tile / n_tiles) * kPairTileM + static_cast<int>(rank) * kTileM;
-      const int n0 = (tile % n_tiles) * tile_n;
+      int m_index, n_index;
+      pair_tile_position(tile, n_tiles, m_tiles, &m_index, &n_index);
+      const int m0 = m_index * kPairTileM + static_cast<int>(rank) * kTileM;
+      const int n0 = n_index * tile_n;
       const bool staged = kScaled || p.bias;
       if (staged) {
         stage_column_factors<OPERAND>(p, column_factors[member][0], column_factors[member][1], n0 + first_chunk * 32, chunks_here * 32, lane);
