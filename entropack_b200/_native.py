@@ -60,6 +60,7 @@ _PROTOTYPES = {
     "ep_lattice_bins_needed": [_ptr],
     "ep_lattice_max_alphabet": [_ptr],
     "ep_lattice_coded_bytes": [_ptr, _ptr, _i64, _i32, _i64, _ptr],
+    "ep_lattice_search_scale": [_ptr, _i32, _ptr, _i64, _i64, _ptr, _ptr, _ptr, _i64, _f64, _i32, _i64, _i32, _f64, _f64, _f64, _ptr, _ptr, _ptr],
     "ep_lattice_tables": [_ptr, _ptr, _i64, _i32, _ptr, _ptr, _i64, _ptr],
     "ep_lattice_refit_scales": [_ptr, _i32, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr, _ptr],
     "ep_lattice_refit_rows": [_ptr, _i32, _ptr, _ptr, _ptr, _f32, _i64, _i64, _ptr, _ptr, _ptr],

@@ -10,6 +10,9 @@
 // taking the row's 8-element vectors t, t+256, ... in order, then a halving tree. No fused multiply-add.
 #include <cuda_bf16.h>
 
+#include <cmath>
+#include <vector>
+
 #include "ep_common.cuh"
 
 namespace ep {
@@ -576,6 +579,64 @@ extern "C" int ep_lattice_histogram(const int16_t* fields_dev, const uint8_t* co
   histogram_kernel<<<blocks, kThreads, kSharedBins * sizeof(int), s>>>(fields_dev, cosets_dev, vectors, minmax_dev, bins_dev,
                                                                        static_cast<int>(bins_capacity), kSharedBins, bins_used_dev);
   return check_launch("histogram_kernel");
+}
+
+// Layout of the statistics buffer the search and the encoder share: the min/max record, the count of bins it
+// implies, one pad word (keeps the bins 16-byte aligned), then the bins.
+constexpr int kStatsUsedAt = kMinMaxLen;
+constexpr int kStatsHeaderWords = kMinMaxLen + 2;
+
+extern "C" int ep_lattice_search_scale(const void* weight_dev, int is_bf16, const float* rms_dev, int64_t rows, int64_t cols,
+                                       int16_t* fields_dev, uint8_t* cosets_dev, int32_t* stats_dev, int64_t bins_capacity,
+                                       double target_bpp, int prob_bits, int64_t tile_elements, int iterations, double low,
+                                       double high, double fixed_bytes, double* scale_host, int64_t* bins_needed_host,
+                                       ep_stream_t stream) {
+  const int rc = check_matrix(weight_dev, rows, cols);
+  if (rc != EP_OK) return rc;
+  if (!stats_dev || !scale_host || !bins_needed_host || bins_capacity <= 0 || iterations < 0 || !(low > 0.0) || !(high >= low)) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t vectors = rows * (cols / 8);
+  const double elements = static_cast<double>(rows) * static_cast<double>(cols);
+  // Most searches use a few thousand bins: the header and that many come back in one copy, the rest only when needed.
+  const int64_t first_bins = bins_capacity < 4096 ? bins_capacity : 4096;
+  std::vector<int32_t> host(static_cast<size_t>(kStatsHeaderWords + bins_capacity));
+  *bins_needed_host = 0;
+  for (int step = 0; step < iterations; ++step) {
+    const double middle = std::sqrt(low * high);
+    int status = ep_lattice_quantize(weight_dev, is_bf16, rms_dev, rows, cols, static_cast<float>(middle), fields_dev, cosets_dev,
+                                     stats_dev, stream);
+    if (status != EP_OK) return status;
+    status = ep_lattice_histogram(fields_dev, cosets_dev, vectors, stats_dev, stats_dev + kStatsHeaderWords, bins_capacity,
+                                  stats_dev + kStatsUsedAt, stream);
+    if (status != EP_OK) return status;
+    EP_CUDA_CHECK(cudaMemcpyAsync(host.data(), stats_dev, sizeof(int32_t) * (kStatsHeaderWords + first_bins), cudaMemcpyDeviceToHost, s));
+    EP_CUDA_CHECK(cudaStreamSynchronize(s));
+    const int64_t used = host[kStatsUsedAt];
+    if (used > bins_capacity) {
+      *bins_needed_host = used;
+      return EP_MORE_BINS;
+    }
+    if (used > first_bins) {
+      EP_CUDA_CHECK(cudaMemcpyAsync(host.data() + kStatsHeaderWords + first_bins, stats_dev + kStatsHeaderWords + first_bins,
+                                    sizeof(int32_t) * (used - first_bins), cudaMemcpyDeviceToHost, s));
+      EP_CUDA_CHECK(cudaStreamSynchronize(s));
+    }
+    double total = HUGE_VAL;   // a field that left the int16 range: far too fine a scale for any table
+    if (host[kMinMaxLen - 1] == 0) {
+      status = ep_lattice_coded_bytes(host.data(), host.data() + kStatsHeaderWords, vectors, prob_bits, tile_elements, &total);
+      if (status != EP_OK) return status;
+    }
+    total += static_cast<double>(rows) * 4.0 + fixed_bytes;
+    if (8.0 * total / elements > target_bpp) {
+      low = middle;
+    } else {
+      high = middle;
+    }
+  }
+  *scale_host = std::sqrt(low * high);
+  return EP_OK;
 }
 
 extern "C" int ep_lattice_refit_scales(const void* weight_dev, int is_bf16, const int16_t* fields_dev, const uint8_t* cosets_dev,

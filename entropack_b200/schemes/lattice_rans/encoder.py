@@ -22,6 +22,7 @@ from .format import (
     subsample_index, vector_tile_elements,
 )
 
+EP_MORE_BINS = 1            # status of ep_lattice_search_scale: retry with the capacity it reports
 _MINMAX_WORDS = 34
 _HEADER_WORDS = 36          # min/max record, bins_used, one pad word: keeps the bins 16-byte aligned
 _DEFAULT_BINS = 16384
@@ -117,17 +118,21 @@ def _bisect_scale(work, rms, target_bpp, prob_bits, tile_elements, iterations, m
         index = index.to(work.device)
         work, rms = work.index_select(0, index).contiguous(), rms.index_select(0, index).contiguous()
     search = _Pass(work, rms)
-    elements = sub_rows * cols
-    lo, hi = 0.001, 8.0
-    for _ in range(iterations):
-        mid = math.sqrt(lo * hi)
-        minmax, bins = search.quantize(mid)
-        total = search.coded_bytes(minmax, bins, prob_bits, tile_elements) + sub_rows * 4 + MODEL_FIXED_BYTES
-        if 8 * total / elements > target_bpp:
-            lo = mid
-        else:
-            hi = mid
-    return math.sqrt(lo * hi)
+    # The bisection itself runs in the library (quantise, count, read back, price, halve the interval; one call instead
+    # of a dozen round trips through Python): per step the midpoint sqrt(lo * hi) is kept when
+    # 8 * (coded bytes + 4 bytes per row scale + fixed bytes) / elements stays within the target.
+    scale, needed = ctypes.c_double(0.0), ctypes.c_int64(0)
+    while True:
+        status = _native.load().ep_lattice_search_scale(
+            _native.ptr(search.work), search.is_bf16, _native.ptr(search.rms), search.rows, search.cols, _native.ptr(search.fields),
+            _native.ptr(search.cosets), search.stats.data_ptr(), search.capacity, float(target_bpp), int(prob_bits), int(tile_elements),
+            int(iterations), 0.001, 8.0, float(MODEL_FIXED_BYTES), ctypes.addressof(scale), ctypes.addressof(needed),
+            _native.stream_handle(search.device))
+        if status != EP_MORE_BINS:
+            break
+        search._allocate_stats(int(needed.value))   # alphabets wider than the bins: again with room for them
+    _native.check(status, "lattice_rans rate search")
+    return scale.value
 
 
 # ---- per-row rate-distortion refinement (entropack/schemes/lattice_rans/rdo.py) -----------------------------

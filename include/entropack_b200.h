@@ -32,6 +32,8 @@ extern "C" {
 #define EP_ERR_NORMALIZE (-4)
 #define EP_ERR_ALPHABET (-5)
 #define EP_ERR_TOO_LARGE (-6)
+/* not an error: the call stopped because a caller-sized buffer is too small; the size it needs is in an output argument */
+#define EP_MORE_BINS 1
 
 /* codes written to error_dev by decode kernels */
 #define EP_STREAM_BAD_OFFSETS 1
@@ -192,6 +194,18 @@ int ep_lattice_row_rms(const void* weight_dev, int is_bf16, int64_t rows, int64_
  * e8_quantize_fields_kernel, lattice_rans.cu:149-241 (call site cuda.py:115-139). */
 int ep_lattice_quantize(const void* weight_dev, int is_bf16, const float* rms_dev, int64_t rows, int64_t cols, float scale,
                         int16_t* fields_dev, uint8_t* cosets_dev, int32_t* minmax_dev, ep_stream_t stream);
+
+/* The rate search as one call: `iterations` steps of geometric bisection of the global scale between `low` and `high`
+ * on the (sub-sampled) operand, each step = ep_lattice_quantize + ep_lattice_histogram into `stats_dev`
+ * (int32[36 + bins_capacity]: min/max record[34], bins used, pad, bins), the statistics read back and priced with
+ * ep_lattice_coded_bytes + rows * 4 + fixed_bytes against target_bpp. Writes sqrt(low * high) after the last step
+ * to *scale_host. Returns EP_MORE_BINS with the needed capacity in *bins_needed_host when a step's alphabets do
+ * not fit `bins_capacity` (call again with a larger buffer). Stands in for _bisect_scale_cuda / _SearchState.total_at,
+ * entropack/schemes/lattice_rans/cuda.py:315-478; synchronises `stream` once or twice per step. */
+int ep_lattice_search_scale(const void* weight_dev, int is_bf16, const float* rms_dev, int64_t rows, int64_t cols,
+                            int16_t* fields_dev, uint8_t* cosets_dev, int32_t* stats_dev, int64_t bins_capacity,
+                            double target_bpp, int prob_bits, int64_t tile_elements, int iterations, double low, double high,
+                            double fixed_bytes, double* scale_host, int64_t* bins_needed_host, ep_stream_t stream);
 
 /* Exact per-stream symbol counts into compact bins (2 coset bins, then max - min + 1 bins per live
  * stream, in table order); bins_used_dev[0] receives the number of bins the min/max record implies and
