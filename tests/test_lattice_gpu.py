@@ -254,3 +254,33 @@ def test_row_refinement_reaches_the_reference_rate_and_error(oracle_module, name
     assert abs(container.actual_bpp - float(record["rdo_actual_bpp"])) <= 0.01
     assert relative <= float(record["rdo_rel_l2"]) * 1.005
     assert relative < float(record["plain_rel_l2"])
+
+
+def test_rate_search_in_the_library_equals_the_step_by_step_loop(monkeypatch):
+    """ep_lattice_search_scale against the same twelve bisection steps driven from Python with the single-step entry
+    points (quantise, count, read back, price), and its retry path when the alphabets outgrow the bins it was given."""
+    import math
+
+    from entropack_b200.schemes.lattice_rans import encoder
+    from entropack_b200.schemes.lattice_rans.format import MODEL_FIXED_BYTES
+
+    generator = torch.Generator(device="cuda").manual_seed(31)
+    work = (torch.randn(96, 1024, generator=generator, device="cuda") * 0.02).to(torch.bfloat16)
+    work[5] *= 30.0          # a wide row: large alphabets at fine scales
+    rms = encoder._row_rms(work)
+    for target, prob_bits, tile_elements in [(4.0, 11, 16384), (2.3, 11, 16384), (6.5, 12, 8192)]:
+        stepwise = encoder._Pass(work, rms)
+        lo, hi = 0.001, 8.0
+        for _ in range(12):
+            mid = math.sqrt(lo * hi)
+            minmax, bins = stepwise.quantize(mid)
+            total = stepwise.coded_bytes(minmax, bins, prob_bits, tile_elements) + work.shape[0] * 4 + MODEL_FIXED_BYTES
+            if 8 * total / work.numel() > target:
+                lo = mid
+            else:
+                hi = mid
+        expected = math.sqrt(lo * hi)
+        assert encoder._bisect_scale(work, rms, target, prob_bits, tile_elements, 12, 1 << 30) == expected
+        monkeypatch.setattr(encoder, "_DEFAULT_BINS", 48)     # far too few bins: the search has to ask for more
+        assert encoder._bisect_scale(work, rms, target, prob_bits, tile_elements, 12, 1 << 30) == expected
+        monkeypatch.undo()
