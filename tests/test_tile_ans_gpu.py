@@ -44,6 +44,36 @@ def test_decode_reference_bitstreams(name):
 
 
 @pytest.mark.parametrize("name", golden_names("tile_ans_"))
+def test_reference_bitstreams_decode_in_runs_of_tiles(name):
+    """ep_tile_ans_decode_tiles over three runs (a first tile alone, a middle run, the rest) writes the bytes of the
+    whole-tensor decode; with only the payload words of each run's streams present in the payload buffer."""
+    from entropack_b200.schemes.tile_ans import b200
+    from entropack_b200.schemes.tile_ans.format import num_tiles, parse_layout
+
+    record = load_golden(f"tile_ans_{name}")
+    host = buffers_of(record)
+    itemsize = int(record["itemsize"])
+    buffers = _to_device(host)
+    tile_elements, _, lanes, elements = parse_layout(buffers.layout)
+    tiles = num_tiles(elements, tile_elements)
+    cuts = sorted({0, min(1, tiles), (tiles + 1) // 2, tiles})
+    out = torch.full((elements * lanes,), 0xA5, dtype=torch.uint8, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    offsets = host["offsets"].astype(np.int64)
+    whole_payload = np.ascontiguousarray(host["payload"])
+    for first, last in zip(cuts, cuts[1:]):
+        # a payload buffer that holds this run's words only; everything else is poison
+        partial = np.full_like(whole_payload, 0xDEAD)
+        for lane in range(lanes):
+            begin, end = int(offsets[lane * tiles + first]), int(offsets[lane * tiles + last])
+            partial[begin:end] = whole_payload[begin:end]
+        b200.decode(buffers._replace(payload=torch.from_numpy(partial).cuda()), dtype=DTYPES[itemsize], error=error, out=out,
+                    tiles=(first, last - first))
+    assert int(error.item()) == 0
+    assert np.array_equal(out.cpu().numpy(), record["input_bytes"])
+
+
+@pytest.mark.parametrize("name", golden_names("tile_ans_"))
 def test_encode_reproduces_reference_bitstreams(name):
     record = load_golden(f"tile_ans_{name}")
     reference = buffers_of(record)
