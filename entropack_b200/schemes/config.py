@@ -73,14 +73,27 @@ def config_fields(cls: type) -> dict:
     return _field_cache[cls]
 
 
-def _validate_field(name: str, value, hint) -> None:
+def _field_rule(hint) -> tuple:
+    """(base type, nullable, markers) of an annotated field type such as ``Annotated[int | None, Range(1, None)]``."""
     markers = []
     if get_origin(hint) is Annotated:
         hint, *markers = get_args(hint)
     members = get_args(hint) if get_origin(hint) is not None else (hint,)
     kinds = [kind for kind in members if kind is not type(None)]
-    nullable = len(kinds) < len(members)
-    base = kinds[0]
+    return kinds[0], len(kinds) < len(members), tuple(markers)
+
+
+_rule_cache: dict[type, list] = {}
+
+
+def _field_rules(cls: type) -> list:
+    """The rules of a config class, worked out from its type hints once (decode paths validate on every call)."""
+    if cls not in _rule_cache:
+        _rule_cache[cls] = [(name, *_field_rule(hint)) for name, hint in config_fields(cls).items()]
+    return _rule_cache[cls]
+
+
+def _validate_field(name: str, value, base, nullable: bool, markers) -> None:
     noun = "an integer" if base is int else "a bool" if base is bool else "a real number"
     if value is None:
         if nullable:
@@ -100,5 +113,5 @@ def _validate_field(name: str, value, hint) -> None:
 
 
 def validate_config(config) -> None:
-    for name, hint in config_fields(type(config)).items():
-        _validate_field(name, getattr(config, name), hint)
+    for name, base, nullable, markers in _field_rules(type(config)):
+        _validate_field(name, getattr(config, name), base, nullable, markers)
