@@ -2,6 +2,7 @@
 """Benchmark of the compression hot path: lossless Tile-ANS decode throughput.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+    python bench.py --only <kernel> [--kind ...] [--rows R] [--cols C] [--bpp B] [--reps N]     (see run_only)
 
 Workload ("c2_tile_ans_decode"): the four 8192 x 8192 tensors of the lossless benchmark config --
 fp8 e4m3 (N(0,1) scaled to amax 448), int8 (round(N(0,20^2)) clipped to +-127), fp16 and fp32
@@ -20,7 +21,8 @@ containers. Bytes per step = container bytes (header excluded) read once + dense
              quarter-height sample of the same four tensors on the host cores.
 
 With N > 1 (torchrun, one rank per GPU) every rank decodes its own copy of the workload (weak
-scaling, no collective on the data path); the time is the max over ranks.
+scaling, no collective on the data path); the time is the max over ranks. The one collective of the
+package, the output all-gather of the column-sharded linear, is timed beside it ("sharded_linear").
 """
 import argparse
 import json
@@ -44,9 +46,12 @@ ROWS, COLS = 8192, 8192
 METRIC = "decode GB/s/GPU (HBM frac)"
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the four decode launches of one step, from one ncu capture per
-# tensor kind (profiles/tile_ans_decode_traffic.md): fp8 82.06 MB, int8 80.77 MB, fp16 213.04 MB, fp32 475.13 MB
-DRAM_TRAFFIC_BYTES = 851.0e6
+# dram__bytes_read.sum + dram__bytes_write.sum of the four decode launches of one step, one ncu capture per tensor
+# kind (`ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:tile_ans_decode_kernel
+# -s 1 -c 1 python bench.py --only tile_ans_decode --kind <kind> --reps 2`). A capture, not a live measurement: it is
+# dated, and goes stale when the decode kernel's memory behaviour changes.
+DRAM_TRAFFIC = {"captured": "2026-11-25", "bytes": {"fp8_e4m3": 82.06e6, "int8": 80.77e6, "fp16": 213.04e6, "fp32": 475.13e6}}
+DRAM_TRAFFIC_BYTES = float(sum(DRAM_TRAFFIC["bytes"].values()))
 
 
 def make_tensor(kind: str, rows: int, cols: int, device) -> torch.Tensor:
@@ -136,6 +141,128 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
+# --only: one kernel of the hot path, a few launches on a seeded synthetic case (the command that
+# goes under a profiler: `ncu -k regex:<kernel> -c <reps> ... python bench.py --only <op> ...`)
+# ------------------------------------------------------------------------------------------------
+ONLY_OPS = ("tile_ans_decode", "tile_ans_encode", "lattice_decode", "lattice_encode", "dfloat11_decode", "dfloat11_encode",
+            "linear", "layer_forward")
+
+
+def make_case(kind: str, rows: int, cols: int, device, seed: int = 1) -> torch.Tensor:
+    generator = torch.Generator(device=device).manual_seed(seed)
+    x = torch.randn(rows, cols, generator=generator, device=device)
+    if kind == "fp8_e4m3":
+        return (x * (448.0 / x.abs().max())).to(torch.float8_e4m3fn)
+    if kind == "int8":
+        return (x * 20).round().clamp(-127, 127).to(torch.int8)
+    if kind == "int8_narrow":
+        return (x * 2).round().clamp(-127, 127).to(torch.int8)
+    if kind == "fp16":
+        return (x * 0.02).to(torch.float16)
+    if kind == "bf16":
+        return (x * 0.02).to(torch.bfloat16)
+    if kind == "fp32":
+        return x * 0.02
+    if kind == "bf16_outliers":
+        # 1 % of the rows heavy-tailed (Student-t, 3 degrees of freedom): the lossy benchmark tensor
+        picks = torch.randperm(rows, generator=generator, device=device)[: max(1, rows // 100)]
+        student = torch.randn(picks.numel(), cols, generator=generator, device=device) / \
+            torch.randn(picks.numel(), cols, 3, generator=generator, device=device).square().mean(-1).sqrt()
+        x[picks] = student
+        return (x * 0.02).to(torch.bfloat16)
+    if kind == "int16_pair":
+        # two independent small-valued bytes per element: both byte lanes are entropy coded
+        low = (x * 20).round().clamp(-127, 127).to(torch.int16) & 0xFF
+        high = (torch.randn(rows, cols, generator=generator, device=device) * 20).round().clamp(-127, 127).to(torch.int16)
+        return low | (high << 8)
+    raise ValueError(kind)
+
+
+def run_only(args) -> None:
+    """Set-up (tensor generation, encoding) first; then the chosen kernel runs ``--reps`` times back to back, each launch
+    timed with CUDA events after a 512 MB L2 flush (a profiler's `-k regex:<kernel> -c <reps>` captures exactly those)."""
+    import entropack_b200 as ep
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    stream = torch.cuda.current_stream(device)
+    flush = L2Flush(device)
+    rows, cols = args.rows, args.cols
+
+    def repeat(fn):
+        times = []
+        for _ in range(args.reps):
+            flush()
+            torch.cuda._sleep(1_000_000)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            out = fn()
+            end.record(stream)
+            end.synchronize()
+            times.append(begin.elapsed_time(end) * 1e3)
+        return out, times
+
+    report = {"op": args.only, "kind": args.kind, "rows": rows, "cols": cols, "reps": args.reps}
+    if args.only == "linear":
+        from entropack_b200 import _native
+        from entropack_b200.linear import linear_forward
+
+        weight = make_case("bf16", cols, args.inner, device)
+        tokens = make_case("bf16", rows, args.inner, device, seed=2) * 50
+        if args.operand == "bf16":
+            _, times = repeat(lambda: linear_forward(tokens, weight))
+        else:
+            # 8-bit codes with per-row scales, as the quantised layers hand them to the kernel
+            lib = _native.load()
+            if args.operand == "fp8":
+                entry, codes_x, codes_w = lib.ep_linear_forward_fp8, tokens.to(torch.float8_e4m3fn), (weight * 50).to(torch.float8_e4m3fn)
+            else:
+                entry, codes_x, codes_w = (lib.ep_linear_forward_int8, tokens.round().clamp(-127, 127).to(torch.int8),
+                                           (weight * 2000).round().clamp(-127, 127).to(torch.int8))
+            scale_x = torch.full((rows,), 0.02, device=device)
+            scale_w = torch.full((cols,), 0.01, device=device)
+            out = torch.empty((rows, cols), dtype=torch.bfloat16, device=device)
+            _, times = repeat(lambda: _native.check(entry(
+                _native.ptr(codes_x), _native.ptr(codes_w), _native.ptr(scale_x), _native.ptr(scale_w), None, _native.ptr(out), 0, rows,
+                cols, args.inner, None, _native.stream_handle(device)), "8-bit linear forward"))
+        report.update(operand=args.operand, inner=args.inner, us=times)
+    elif args.only == "layer_forward":
+        # CompressedLinear.forward (decode + product, or the fused kernel up to 4 tokens): rows = tokens, cols = out features
+        dense = torch.nn.Linear(args.inner, cols, bias=False, device=device, dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_(make_case("bf16", cols, args.inner, device))
+        options = {"tile_elements": args.tile_elements} if args.tile_elements else {}
+        layer = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=args.bpp, **options))
+        x = make_case("bf16", rows, args.inner, device, seed=2) * 50
+        with torch.no_grad():
+            _, times = repeat(lambda: layer(x))
+        report.update(inner=args.inner, bits=layer.compressed_bits, us=times)
+    else:
+        tensor = make_case(args.kind, rows, cols, device)
+        if args.only.startswith("lattice"):
+            options = {"tile_elements": args.tile_elements} if args.tile_elements else {}
+            config = ep.EntroPackLossyConfig(target_bpp=args.bpp, **options)
+        elif args.only.startswith("dfloat11"):
+            config = ep.DFloat11Config()
+        else:
+            config = ep.TileANSConfig(tile_elements=args.tile_elements)
+        if args.only.endswith("_decode"):
+            container = ep.compress(tensor, config)
+            torch.cuda.synchronize(device)
+            out, times = repeat(lambda: ep.decompress(container, config))
+            if container.lossless:
+                assert torch.equal(out.view(torch.uint8), tensor.view(torch.uint8))
+            nbytes = container.storage_nbytes(include_header=False) + tensor.numel() * tensor.element_size()
+        else:
+            container, times = repeat(lambda: ep.compress(tensor, config))
+            nbytes = container.storage_nbytes(include_header=False) + tensor.numel() * tensor.element_size()
+        report.update(bpp=container.actual_bpp, algorithmic_bytes=nbytes, us=times,
+                      GBps=[nbytes / (t * 1e-6) / 1e9 for t in times])
+    torch.cuda.synchronize(device)
+    print(json.dumps(report))
+
+
+# ------------------------------------------------------------------------------------------------
 # reference arm / CPU baseline: the oracle port on host cores
 # ------------------------------------------------------------------------------------------------
 def cpu_workload(sample_rows: int):
@@ -155,6 +282,8 @@ def cpu_workload(sample_rows: int):
 def time_cpu(steps: int, warmup: int, sample_rows: int) -> dict:
     oracle, work = cpu_workload(sample_rows)
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks; the CPU arm is meant to use every host thread it may run on
+    oracle.set_threads(cores)
     total_bytes = sum(nbytes for _, _, nbytes in work)
     for _ in range(warmup):
         for buffers, _, _ in work:
@@ -297,6 +426,9 @@ def run_b200(args) -> None:
     model = measure_model_encode(ep, device, rank, world) if not args.headline_only else {
         "seconds": 0.0, "layers": 0, "bpp": 0.0, "decode_seconds": 0.0, "forward_seconds": 0.0, "mixed_seconds": 0.0, "mixed_bpp": 0.0}
 
+    # the package's one collective: the output all-gather of a column-sharded layer (every rank takes part)
+    sharded = measure_sharded_linear(ep, device, rank, world, args.steps) if distributed and not args.headline_only else {}
+
     # end to end through the public API from pinned host blobs
     host_blobs = [c.entropack_quant_state.cpu().pin_memory() for c in containers]
     host_outputs = [torch.empty(c.numel() * c.element_size(), dtype=torch.uint8).pin_memory() for c in containers]
@@ -351,14 +483,17 @@ def run_b200(args) -> None:
                    "l2": "inputs larger than L2, plus a 512 MB write-then-read flush between timed steps", "per_gpu_GBps": value / world,
                    "hbm_frac_of_" + peak_kind: value / world / peak},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_kind, "traffic": DRAM_TRAFFIC_BYTES, "kernel": "tile_ans_decode_kernel",
+                     "peak_source": peak_kind, "traffic": DRAM_TRAFFIC_BYTES, "traffic_captured": DRAM_TRAFFIC["captured"],
+                     "kernel": "tile_ans_decode_kernel",
                      "per_launch_ms": dict(zip(KINDS, kernel_ms)),
                      "per_launch_GBps": {k: b / (ms * 1e-3) / 1e9 for k, b, ms in zip(KINDS, per_kind_bytes, kernel_ms)}},
         "cpu_baseline": {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": world * bytes_per_step * e2e_steps / e2e_seconds / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
+                "per_gpu_GBps": bytes_per_step * e2e_steps / e2e_seconds / 1e9,
                 "host_cpus_near_gpu": None if bound_cpus is None else len(bound_cpus)},
         "others": others,
+        "sharded_linear": sharded,
         "model_encode": {"workload": "synthetic DiT, 276 linears (hidden 3840, mlp 10240), bf16 N(0,0.02^2), 4 bpp, layers sharded "
                                      "largest-first over the ranks", "seconds": model["seconds"], "layers_on_rank0": model["layers"],
                          "mean_bpp_rank0": model["bpp"], "decode_all_seconds": model["decode_seconds"],
@@ -370,6 +505,74 @@ def run_b200(args) -> None:
     print(json.dumps(line))
     if distributed:
         dist.destroy_process_group()
+
+
+def measure_sharded_linear(ep, device, rank: int, world: int, reps: int) -> dict:
+    """Column-sharded CompressedLinear at 4096 tokens on two of the model's layer shapes: each rank holds N / G rows of
+    the weight at 4 bpp, runs decode + product on its slice and the ranks all-gather the [M, N / G] outputs (the
+    package's one collective). Device times (CUDA events, max over ranks) of the local forward, of the gather alone and
+    of both; the gathered output is checked, bit for bit, against the same shards computed on one GPU."""
+    import torch.distributed as dist
+
+    from entropack_b200 import sharding
+
+    stream = torch.cuda.current_stream(device)
+    reps = max(3, min(reps, 10))
+    results = {}
+
+    def timed(fn):
+        fn()
+        total = 0.0
+        for _ in range(reps):
+            dist.barrier()
+            torch.cuda.synchronize(device)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            fn()
+            end.record(stream)
+            end.synchronize()
+            total += begin.elapsed_time(end)
+        worst = torch.tensor([total / reps], dtype=torch.float64, device=device)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        return float(worst[0]) * 1e3
+
+    config = ep.EntroPackLossyConfig(target_bpp=4.0)
+    tokens = 4096
+    for out_features, in_features in ((3840, 3840), (10240, 3840)):
+        if out_features % world:
+            continue
+        generator = torch.Generator(device=device).manual_seed(77)       # the same weight and activations on every rank
+        dense = torch.nn.Linear(in_features, out_features, bias=False, device=device, dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_((torch.randn(out_features, in_features, generator=generator, device=device) * 0.02).to(torch.bfloat16))
+        x = torch.randn(tokens, in_features, generator=generator, device=device).to(torch.bfloat16)
+        layer = sharding.ColumnShardedLinear(dense, config=config)
+        with torch.no_grad():
+            out = layer(x)
+            local = layer.local(x).contiguous()
+            staging = torch.empty((world, *local.shape), dtype=local.dtype, device=device)
+            entry = {
+                "local_forward_us": timed(lambda: layer.local(x)),
+                "all_gather_us": timed(lambda: sharding.gather_columns(local, None, staging)),
+                "forward_us": timed(lambda: layer(x)),
+            }
+            # the same row shards, compressed and multiplied one after the other on this GPU
+            pieces = []
+            for r in range(world):
+                rows = sharding.row_slice(out_features, r, world)
+                shard = torch.nn.Linear(in_features, rows.end - rows.begin, bias=False, device=device, dtype=torch.bfloat16)
+                shard.weight.copy_(dense.weight[rows.begin:rows.end])
+                pieces.append(ep.CompressedLinear.from_linear(shard, config=config)(x))
+            identical = bool(torch.equal(out.view(torch.int16), torch.cat(pieces, dim=-1).view(torch.int16)))
+        agree = torch.tensor([int(identical)], device=device)
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        received = (world - 1) * tokens * (out_features // world) * 2          # bytes each GPU receives = (G-1)/G * M * N * 2
+        entry.update(matches_single_gpu=bool(int(agree[0])), bytes_received_per_gpu=received,
+                     all_gather_GBps_per_gpu=received / entry["all_gather_us"] / 1e3,
+                     nvlink_frac_of_770=received / entry["all_gather_us"] / 1e3 / 770.0)
+        results[f"{in_features}x{out_features}_M{tokens}"] = entry
+        del layer, dense, pieces, staging
+    return results
 
 
 def measure_model_encode(ep, device, rank: int, world: int) -> dict:
@@ -534,7 +737,10 @@ def measure_others(ep, device, flush, reps: int) -> dict:
     for tokens in (16, 4096):
         x = torch.randn(tokens, 3840, generator=generator, device=device).to(torch.bfloat16)
         a_codes, a_scale = layer._quantize_activations(x)
+        expected = (a_codes.float() @ codes.float().t()) * a_scale.unsqueeze(1) * weight_scale.unsqueeze(0)
+        produced = layer(x)
         entry = {
+            "max_rel_err": float((produced.float() - expected).abs().max() / expected.abs().max()),
             "compressed_forward_us": timed(lambda: layer(x)) * 1e3,
             "quantize_activations_us": timed(lambda: layer._quantize_activations(x)) * 1e3,
             "library_fp8_gemm_us": timed(lambda: layer._gemm(a_codes, codes, a_scale, weight_scale, torch.bfloat16)) * 1e3,
@@ -558,8 +764,19 @@ def main() -> None:
     parser.add_argument("--headline-only", action="store_true",
                         help="time the headline workload and e2e only (no secondary kernels, model encode or CPU baseline): "
                              "the short command whose launch list goes under a profiler")
+    parser.add_argument("--only", choices=ONLY_OPS, default=None, help="run one kernel a few times and print its timings (see run_only)")
+    parser.add_argument("--kind", default="fp8_e4m3", help="--only: tensor kind (fp8_e4m3, int8, fp16, bf16, fp32, bf16_outliers, int16_pair)")
+    parser.add_argument("--rows", type=int, default=8192, help="--only: rows (linear / layer_forward: tokens)")
+    parser.add_argument("--cols", type=int, default=8192, help="--only: columns (linear / layer_forward: output features)")
+    parser.add_argument("--inner", type=int, default=3840, help="--only linear / layer_forward: input features")
+    parser.add_argument("--operand", default="bf16", choices=("bf16", "fp8", "int8"), help="--only linear: operand type")
+    parser.add_argument("--bpp", type=float, default=4.0, help="--only lattice_* / layer_forward: target rate")
+    parser.add_argument("--tile-elements", type=int, default=0, help="--only: tile size of the encoder (0 = automatic)")
+    parser.add_argument("--reps", type=int, default=3, help="--only: timed launches")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.only:
+        run_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

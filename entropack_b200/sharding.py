@@ -116,15 +116,20 @@ def compress_layers(weights, configs, group=None, compress_fn=None) -> dict:
     return result
 
 
-def gather_columns(local: torch.Tensor, group=None) -> torch.Tensor:
-    """All-gather ``[..., N / G]`` shards along the last dimension into ``[..., N]`` (rank order)."""
+def gather_columns(local: torch.Tensor, group=None, staging: torch.Tensor | None = None) -> torch.Tensor:
+    """All-gather ``[..., N / G]`` shards along the last dimension into ``[..., N]`` (rank order): one
+    ``all_gather_into_tensor`` into a ``[G, ..., N / G]`` buffer (``staging``, when the caller keeps one) and one
+    strided copy that interleaves the ranks' column blocks."""
     _rank, world = _rank_and_world(group)
     if world == 1:
         return local
     local = local.contiguous()
-    pieces = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(pieces, local, group=group)
-    return torch.cat(pieces, dim=-1)
+    shape = (world, *local.shape)
+    if staging is None or tuple(staging.shape) != shape or staging.dtype != local.dtype or staging.device != local.device:
+        staging = torch.empty(shape, dtype=local.dtype, device=local.device)
+    # the collective wants the ranks' pieces stacked along the first dimension: [G * M, N / G] is the same memory
+    dist.all_gather_into_tensor(staging.view(world * local.shape[0], *local.shape[1:]), local, group=group)
+    return staging.movedim(0, -2).reshape(*local.shape[:-1], world * local.shape[-1])
 
 
 @dataclass
@@ -163,6 +168,13 @@ class ColumnShardedLinear(torch.nn.Module):
         self.rows = rows
         self.out_features = linear.out_features
         self.local = layer_cls.from_linear(shard, **layer_kwargs)
+        self._staging = None      # the all-gather's landing buffer, kept between calls of the same shape
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return gather_columns(self.local(x), self.group)
+        local = self.local(x).contiguous()
+        _rank, world = _rank_and_world(self.group)
+        shape = (world, *local.shape)
+        if world > 1 and (self._staging is None or tuple(self._staging.shape) != shape or self._staging.dtype != local.dtype
+                          or self._staging.device != local.device):
+            self._staging = torch.empty(shape, dtype=local.dtype, device=local.device)
+        return gather_columns(local, self.group, self._staging)

@@ -240,6 +240,45 @@ def make_rdo(ep, out_dir: Path):
     np.savez_compressed(out_dir / "rdo_ratio_ladders.npz", **ladders)
 
 
+def baseline_lossy_weight(rows, cols, seed, outliers):
+    """The lossy benchmark tensor: bf16 N(0, 0.02^2) rows, `outliers` of them (seeded pick) Student-t(3) x 0.02 built
+    from the same CPU generator. tests/test_baseline_sizes_gpu.py builds the same tensor; the record's checksum ties
+    the two together."""
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(rows, cols, generator=g) * 0.02
+    if outliers:
+        picks = torch.randperm(rows, generator=g)[:outliers]
+        heavy = torch.randn(outliers, cols, generator=g) / torch.sqrt(torch.randn(outliers, cols, 3, generator=g).square().mean(-1))
+        w[picks] = heavy * 0.02
+    return w.to(torch.bfloat16)
+
+
+def make_baseline_scalars(ep, out_dir: Path):
+    """The reference's stored rate and relative error on the full-size lossy benchmark tensor (4096 x 11008 bf16, 41
+    heavy-tailed rows) at the four benchmark rates: scalars only, the containers are tens of megabytes."""
+    import hashlib
+    import json
+
+    tensor = baseline_lossy_weight(4096, 11008, 5, 41)
+    record = {"rows": 4096, "cols": 11008, "seed": 5, "outliers": 41,
+              "input_sha256": hashlib.sha256(raw_bytes(tensor).tobytes()).hexdigest(), "rates": {}}
+    for bpp in (2.3, 3.5, 4.0, 6.0):
+        config = ep.EntroPackLossyConfig(target_bpp=bpp, execution_backend="eager")
+        compressed = ep.compress(tensor, config)
+        assert compressed.compress_method == "lattice_rans", compressed.header
+        restored = ep.decompress(compressed, config)
+        rel = ((restored.float() - tensor.float()).norm() / tensor.float().norm()).item()
+        buffers = as_numpy(compressed.buffers)
+        record["rates"][str(bpp)] = {
+            "actual_bpp": compressed.actual_bpp, "rel_l2": rel, "prob_bits": int(buffers["layout"][1]),
+            "tile_elements": int(buffers["layout"][2]), "max_alphabet": int(buffers["stream_meta"][:, 3].max()),
+            "payload_words": int(buffers["payload"].size),
+            "decoded_sha256": hashlib.sha256(raw_bytes(restored).tobytes()).hexdigest(),
+        }
+        print(f"baseline lossy {bpp}: {record['rates'][str(bpp)]}", flush=True)
+        (out_dir / "baseline_lossy_scalars.json").write_text(json.dumps(record, indent=1, sort_keys=True) + "\n")
+
+
 def make_dfloat11(ep, out_dir: Path):
     g = torch.Generator().manual_seed(77)
     cases = {
@@ -265,7 +304,7 @@ def make_dfloat11(ep, out_dir: Path):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference", required=True, help="checkout of modelscope/entropack to import the eager lane from")
-    parser.add_argument("--only", default="all", choices=("all", "tile_ans", "lattice", "rdo", "dfloat11"))
+    parser.add_argument("--only", default="all", choices=("all", "tile_ans", "lattice", "rdo", "dfloat11", "baseline"))
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     install_huffman_stand_in()
@@ -279,6 +318,8 @@ def main():
         make_rdo(ep, HERE)
     if args.only in ("all", "dfloat11"):
         make_dfloat11(ep, HERE)
+    if args.only == "baseline":      # minutes of single-threaded reference code: only on request
+        make_baseline_scalars(ep, HERE)
 
 
 if __name__ == "__main__":

@@ -39,18 +39,30 @@ def test_decode_reference_bitstreams(name):
     assert _bytes(decoded) == record["decoded_bytes"].tobytes()
 
 
-@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.float8_e4m3fn, torch.float8_e5m2, torch.int8, torch.uint8,
-                                   torch.int16, torch.int32, torch.int64, torch.bool, torch.float8_e4m3fnuz])
+# container dtype -> factor on the stored row scales that pushes the largest values past the type's range
+_CAST_CASES = {
+    torch.float16: 3.0e5, torch.float32: 3000.0, torch.float8_e4m3fn: 3000.0, torch.float8_e5m2: 3.0e6, torch.int8: 3000.0,
+    torch.uint8: 3000.0, torch.int16: 3.0e5, torch.uint16: 3.0e5, torch.int32: 3.0e10, torch.uint32: 3.0e10, torch.int64: 3.0e20,
+    torch.uint64: 3.0e20, torch.bool: 30.0, torch.float8_e4m3fnuz: 3000.0, torch.float8_e5m2fnuz: 3.0e6,
+}
+
+
+@pytest.mark.parametrize("dtype", list(_CAST_CASES), ids=lambda d: str(d).removeprefix("torch."))
 def test_every_container_cast_matches_oracle(oracle_module, dtype):
     """One reference bitstream decoded into every container dtype, with scales blown up so the
-    saturating casts are exercised."""
+    saturating casts are exercised (both ends for the signed types, the upper end and zero for the unsigned)."""
     record = load_golden("lattice_bf16_6p0_outliers")
     buffers = buffers_of(record)
-    buffers["scales"] = (buffers["scales"] * np.float32(3000.0 if dtype not in (torch.bool,) else 30.0)).astype(np.float32)
+    buffers["scales"] = (buffers["scales"] * np.float32(_CAST_CASES[dtype])).astype(np.float32)
     shape = tuple(int(v) for v in record["shape"])
     expected = oracle_module.lattice_decode(buffers, shape, dtype)
     decoded = _gpu_decode(buffers, shape, dtype)
+    assert decoded.dtype == dtype
     assert _bytes(decoded) == _bytes(expected)
+    if dtype not in (torch.float32, torch.bool):
+        # the case does saturate: the type's largest value occurs in the decoded tensor
+        top = torch.finfo(dtype).max if dtype.is_floating_point else torch.iinfo(dtype).max
+        assert bool((expected.cpu().double() if dtype.is_floating_point else expected.cpu().to(torch.float64)).max() >= float(top) * 0.999)
 
 
 @pytest.mark.parametrize("name", golden_names("lattice_"))
@@ -80,7 +92,7 @@ def test_encode_matches_oracle_bit_for_bit(oracle_module, name):
     reference = buffers_of(record)
     elements = shape[0] * shape[1]
     size = lambda b: sum(np.asarray(b[k]).nbytes for k in reference)  # noqa: E731
-    assert abs(size({k: getattr(ours, k).cpu().numpy() for k in reference}) - size(reference)) * 8 / elements <= 0.01 + 512 / elements
+    assert abs(size({k: getattr(ours, k).cpu().numpy() for k in reference}) - size(reference)) * 8 / elements <= 0.01
 
 
 def _weights(rows, cols, seed, outliers):
@@ -104,7 +116,7 @@ def test_public_api_round_trip_against_oracle(oracle_module, bpp):
     compressed = ep.compress(weight.cuda(), config)
     assert compressed.compress_method == "lattice_rans"
     compressed.scheme.validate_buffers(compressed.buffers, tuple(weight.shape), weight.dtype)
-    assert abs(compressed.actual_bpp - bpp) < 0.06
+    assert abs(compressed.actual_bpp - bpp) < 0.06    # 1 M elements: the header and the fixed per-tile costs are 0.02 bpp of it
     restored = ep.decompress(compressed, config)
     assert restored.shape == weight.shape and restored.dtype == weight.dtype
     ours = {key: value.cpu().numpy() for key, value in compressed.buffers.items()}
@@ -115,23 +127,6 @@ def test_public_api_round_trip_against_oracle(oracle_module, bpp):
     assert _bytes(_gpu_decode(theirs, tuple(weight.shape), weight.dtype)) == _bytes(oracle_module.lattice_decode(theirs, tuple(weight.shape), weight.dtype))
     relative = ((restored.float().cpu() - weight.float()).norm() / weight.float().norm()).item()
     assert relative < {2.3: 0.30, 3.5: 0.13, 4.0: 0.09, 6.0: 0.03}[bpp]
-
-
-def test_full_size_lossy_round_trip():
-    """4096 x 11008 bf16 at 4 bpp: encode and decode on the GPU; re-encoding the decoded symbols is not
-    possible without the oracle at this size, so check rate, distortion and a second decode's determinism."""
-    import entropack_b200 as ep
-
-    g = torch.Generator(device="cuda").manual_seed(5)
-    weight = (torch.randn(4096, 11008, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
-    config = ep.EntroPackLossyConfig(target_bpp=4.0)
-    compressed = ep.compress(weight, config)
-    assert abs(compressed.actual_bpp - 4.0) < 0.03
-    first = ep.decompress(compressed, config)
-    second = ep.decompress(compressed, config)
-    assert torch.equal(first.view(torch.int16), second.view(torch.int16))
-    relative = ((first.float() - weight.float()).norm() / weight.float().norm()).item()
-    assert 0.05 < relative < 0.09
 
 
 def test_malformed_lossy_stream_is_reported():
