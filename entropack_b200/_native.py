@@ -13,7 +13,8 @@ LIBRARY_PATH = Path(__file__).resolve().parent / "lib" / "libentropack_b200.so"
 EP_OK = 0
 STREAM_ERRORS = {
     1: "stream offsets are out of range", 2: "payload is truncated", 3: "payload contains unread words",
-    4: "raw lane payload length is invalid", 5: "symbol count exceeds the staging buffer",
+    4: "raw lane payload length is invalid", 5: "a decoded table selector is out of range (corrupt coset table)",
+    9: "a bounded wait inside a tensor-core product ran out",
 }
 
 
@@ -35,11 +36,13 @@ _PROTOTYPES = {
     "ep_tile_ans_encode": [_ptr, _i64, _i32, _i64, _i32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "ep_exclusive_scan_u32": [_ptr, _i64, _ptr, _ptr, _ptr],
     "ep_compact_streams": [_ptr, _ptr, _ptr, _i64, _i64, _ptr],
-    "ep_lattice_decode": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _ptr, _ptr],
-    "ep_lattice_linear_forward": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _ptr, _ptr, _i32,
-                                  _ptr, _ptr, _ptr, _ptr],
+    "ep_lattice_decode": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _i32, _ptr, _ptr],
+    "ep_lattice_linear_forward": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _i64, _i64, _i32, _i64, _i32, _ptr, _i64, _i32, _ptr, _ptr,
+                                  _i32, _ptr, _ptr, _ptr, _ptr],
+    "ep_lattice_slot_tables_bytes": [_i32, _i32],
+    "ep_lattice_build_slot_tables": [_ptr, _ptr, _i64, _i32, _i32, _ptr, _i64, _ptr],
     "ep_lattice_decode_scratch_bytes": [_i32, _i32],
-    "ep_lattice_decode_static": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _ptr],
+    "ep_lattice_decode_static": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _ptr],
     "ep_lattice_decode_static_max_prob_bits": [],
     "ep_dfloat11_decode": [_ptr, _i32, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _i32, _ptr, _ptr],
     "ep_dfloat11_histogram": [_ptr, _i64, _ptr, _ptr],
@@ -71,7 +74,7 @@ _PROTOTYPES = {
     "ep_lattice_encode": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _i32, _i64, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
 _RESTYPES = {"ep_status_string": ctypes.c_char_p, "ep_last_cuda_error": ctypes.c_char_p}
-_INT64_RESULTS = ("ep_lattice_decode_scratch_bytes", "ep_lattice_bins_needed", "ep_lattice_encode_scratch_words",
+_INT64_RESULTS = ("ep_lattice_decode_scratch_bytes", "ep_lattice_slot_tables_bytes", "ep_lattice_bins_needed", "ep_lattice_encode_scratch_words",
                   "ep_dfloat11_chunks")
 
 

@@ -297,7 +297,7 @@ extern "C" const char* ep_status_string(int status) {
   }
 }
 
-extern "C" int ep_abi_version(void) { return 1; }
+extern "C" int ep_abi_version(void) { return 2; }
 
 extern "C" const char* ep_last_cuda_error(void) { return ep::g_last_cuda_error.c_str(); }
 

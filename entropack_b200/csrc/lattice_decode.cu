@@ -10,7 +10,7 @@
 // One warp decodes one tile at a time; a persistent block walks the tile list. The slot tables are
 // rebuilt from the stored frequencies inside the kernel -- no host-side plan, no cached side tables:
 //   * shared path (prob_bits <= 11, every alphabet <= 512): each block builds all 17 tables as packed
-//     32-bit entries (symbol | freq << 9 | (slot - cdf) << 21) in its own shared memory;
+//     32-bit entries (symbol | (slot - cdf) << 9 | freq << 20) in its own shared memory;
 //   * global path (anything else): a small kernel first writes 64-bit entries
 //     (symbol | freq << 16 | (slot - cdf) << 32) into caller-provided scratch, read through L1.
 // Payload words reach the chain through the per-warp cp.async ring of rans_ring.cuh.
@@ -19,6 +19,7 @@
 #include <cuda_fp8.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "ep_common.cuh"
 #include "rans_ring.cuh"
@@ -34,7 +35,7 @@ constexpr int kSharedMaxAlphabet = 512;     // 32-bit entries hold 9 bits of sym
 constexpr int kWideMaxAlphabet = 2048;      // wide shared tables: a byte per slot carries the symbol's high bits
 // Where the 17 slot tables live.
 constexpr int kTablesGlobal = 0;       // 64-bit entries in caller scratch (prob_bits above 11)
-constexpr int kTablesShared = 1;       // packed 32-bit entries in shared memory: symbol | freq << 9 | delta << 21
+constexpr int kTablesShared = 1;       // packed 32-bit entries in shared memory: symbol | delta << 9 | freq << 20
 constexpr int kTablesSharedWide = 2;   // shared memory, alphabets up to 2048: symbol low 10 bits | (freq - 1) << 10 | delta << 21,
                                        // plus the symbol's bits above 10 in a byte table behind the 17 word tables
 
@@ -45,9 +46,12 @@ struct LatticeDecodeParams {
   const uint32_t* states;
   const int32_t* stream_meta;   // [17][4]: n_symbols, sym_min, freq_offset, alphabet
   const uint16_t* freq_tables;
+  int64_t freq_entries;         // length of freq_tables: no table record can make a read go past it
   const float* scales;
   void* output;
   const uint64_t* global_tables;  // [17][1 << prob_bits], global path only
+  const uint32_t* slot_tables;    // shared paths: the tables as an earlier launch exported them (null: build them here)
+  uint32_t* export_tables;        // kModeExport: where the freshly built tables go
   int64_t vectors;
   int64_t tiles;
   int tile_vectors;
@@ -68,6 +72,7 @@ struct LatticeDecodeParams {
 constexpr int kModeStore = 0;       // any container dtype (store_kind)
 constexpr int kModeStoreBf16 = 1;   // bf16, one 16-byte store
 constexpr int kModeProduct = 2;     // nothing is stored: the vector is multiplied into up to kMaxTokens dot products
+constexpr int kModeExport = 3;      // no decoding: the block builds the slot tables and writes them to global memory
 constexpr int kMaxTokens = 4;    // instantiated for 1, 2 and 4 tokens: every token costs its instructions whether used or not
 
 // ---- container cast (entropack/schemes/lattice_rans/format.py:153-168) ---------------------------
@@ -181,19 +186,23 @@ __device__ __forceinline__ void store_vector(void* output, int64_t vector, const
 
 // ---- slot tables -----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack_entry32(uint32_t symbol, uint32_t freq, uint32_t delta) {
-  return symbol | (freq << 9) | (delta << 21);
+  return symbol | (delta << 9) | (freq << 20);
 }
 __device__ __forceinline__ uint64_t pack_entry64(uint32_t symbol, uint32_t freq, uint32_t delta) {
   return static_cast<uint64_t>(symbol) | (static_cast<uint64_t>(freq) << 16) | (static_cast<uint64_t>(delta) << 32);
 }
 
 // One warp fills table `t`: symbols in order, the 32 threads sharing each symbol's run of slots. Slots
-// the stored frequencies do not cover (a corrupt table) keep entry 0, which decodes to symbol 0.
+// the stored frequencies do not cover (a corrupt table) keep entry 0, which decodes to symbol 0; a table
+// record that points outside the `freq_entries` stored frequencies, or claims more symbols than slots, is
+// cut to what exists.
 template <typename Entry, typename Pack>
-__device__ __forceinline__ void fill_table(Entry* table, const int32_t* stream_meta, const uint16_t* freq_tables, int t,
-                                           uint32_t table_size, uint32_t lane, Pack pack) {
-  const int offset = stream_meta[t * 4 + 2];
-  const int alphabet = stream_meta[t * 4 + 3];
+__device__ __forceinline__ void fill_table(Entry* table, const int32_t* stream_meta, const uint16_t* freq_tables,
+                                           int64_t freq_entries, int t, uint32_t table_size, uint32_t lane, Pack pack) {
+  const int64_t offset = stream_meta[t * 4 + 2];
+  int alphabet = min(stream_meta[t * 4 + 3], static_cast<int>(table_size));
+  if (offset < 0 || offset >= freq_entries) alphabet = 0;
+  else alphabet = static_cast<int>(min(static_cast<int64_t>(alphabet), freq_entries - offset));
   for (uint32_t slot = lane; slot < table_size; slot += 32) table[slot] = Entry(0);
   __syncwarp();
   uint32_t running = 0;
@@ -210,27 +219,43 @@ __device__ __forceinline__ void fill_table(Entry* table, const int32_t* stream_m
 }
 
 __global__ void __launch_bounds__(32) lattice_build_tables_kernel(uint64_t* tables, const int32_t* stream_meta,
-                                                                  const uint16_t* freq_tables, int prob_bits) {
+                                                                  const uint16_t* freq_tables, int64_t freq_entries, int prob_bits) {
   const uint32_t table_size = 1u << prob_bits;
-  fill_table<uint64_t>(tables + static_cast<size_t>(blockIdx.x) * table_size, stream_meta, freq_tables, blockIdx.x, table_size,
-                       lane_id(), pack_entry64);
+  fill_table<uint64_t>(tables + static_cast<size_t>(blockIdx.x) * table_size, stream_meta, freq_tables, freq_entries, blockIdx.x,
+                       table_size, lane_id(), pack_entry64);
 }
 
 // ---- decode ----------------------------------------------------------------------------------------
-template <int TABLES, int MODE, int TOKENS = 0>
+// TABLES: where the slot tables live. MODE: what happens to a reconstructed vector. TOKENS: kModeProduct only.
+// PB: the container's prob_bits when it is the usual 11 (shifts, masks and table offsets become literals), 0 = read
+// it from the parameters.
+template <int TABLES, int MODE, int TOKENS = 0, int PB = 0>
 __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const LatticeDecodeParams p) {
+  // 256-word ring chunks (upkeep twice per group of nine steps) wherever shared memory has the room: everywhere but
+  // beside the wide tables
+  using Ring = WordRing<TABLES == kTablesSharedWide ? 7 : 8>;
   extern __shared__ __align__(16) uint32_t shared_tables[];  // [17][table_size] on the shared paths (then [17][table_size] bytes when wide)
-  __shared__ int sym_min[kTables + 1];
+  // smallest value of every field for either coset: field_min[c][f] = sym_min of table 1 + 2 f + c
+  __shared__ __align__(16) int field_min[2][8];
   const uint32_t lane = lane_id();
   const int warp = threadIdx.x >> 5;
-  const uint32_t table_size = 1u << p.prob_bits;
+  const int prob_bits = PB ? PB : p.prob_bits;
+  const uint32_t table_size = 1u << prob_bits;
   const uint32_t slot_mask = table_size - 1u;
-  const int prob_bits = p.prob_bits;
   const uint32_t mask_ge = lanemask_ge();
   const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
 
-  if (threadIdx.x < kTables) sym_min[threadIdx.x] = p.stream_meta[threadIdx.x * 4 + 1];
-  if (TABLES != kTablesGlobal) {
+  if (threadIdx.x < 16) field_min[threadIdx.x & 1][threadIdx.x >> 1] = p.stream_meta[(1 + threadIdx.x) * 4 + 1];
+  if (TABLES != kTablesGlobal && p.slot_tables != nullptr) {
+    // The tables were built once for this container (kModeExport) and come in as they are: 16-byte asynchronous
+    // copies, all in flight at once.
+    const uint32_t words = kTables * table_size + (TABLES == kTablesSharedWide ? kTables * table_size / 4 : 0u);
+    for (uint32_t at = threadIdx.x * 4u; at < words; at += kDecodeThreads * 4u) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(shared_base + at * 4u), "l"(p.slot_tables + at) : "memory");
+    }
+    ring_commit();
+    ring_wait_all();
+  } else if (TABLES != kTablesGlobal) {
     // The 17 slot tables are built by the whole block, one work item per (table, run of 32 symbols): first the
     // frequency total of every run, then, from the totals before it, each run's first slot; inside a run every thread
     // fills the slots of its own symbol when that symbol is rare and the warp shares the slots of a frequent one. (One
@@ -260,8 +285,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     // landing area for the frequencies: the rings' space, behind the tables; a container with more entries than fit
     // there (only possible with wide tables) has them read from global memory instead
     uint16_t* const staged_freq = reinterpret_cast<uint16_t*>(shared_tables + kTables * table_size) + (kWide ? kTables * table_size / 2 : 0);
-    const int entries = max(0, min(meta[(kTables - 1) * 4 + 2] + meta[(kTables - 1) * 4 + 3], kMaxEntries));
-    const bool staged = entries * 2 <= kDecodeWarps * static_cast<int>(kRingWords) * 2;
+    const int entries = static_cast<int>(max(int64_t(0), min(static_cast<int64_t>(min(meta[(kTables - 1) * 4 + 2] + meta[(kTables - 1) * 4 + 3], kMaxEntries)),
+                                                             p.freq_entries)));
+    const bool staged = entries * 2 <= kDecodeWarps * static_cast<int>(Ring::kBytes);
     if (staged) {
       for (int i = threadIdx.x; i < entries; i += kDecodeThreads) staged_freq[i] = p.freq_tables[i];
     }
@@ -344,10 +370,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     }
   }
   __syncthreads();
+  if (MODE == kModeExport) {
+    const uint32_t words = kTables * table_size + (TABLES == kTablesSharedWide ? kTables * table_size / 4 : 0u);
+    for (uint32_t at = threadIdx.x; at < words; at += kDecodeThreads) p.export_tables[at] = shared_tables[at];
+    return;
+  }
 
-  constexpr uint32_t kRingBytes = kRingWords * 2u;
   const uint32_t table_bytes = TABLES == kTablesGlobal ? 0u : kTables * table_size * (TABLES == kTablesSharedWide ? 5u : 4u);
-  const uint32_t ring = ((shared_base + table_bytes + kRingBytes - 1u) & ~(kRingBytes - 1u)) + static_cast<uint32_t>(warp) * kRingBytes;
+  const uint32_t ring = ((shared_base + table_bytes + Ring::kBytes - 1u) & ~(Ring::kBytes - 1u)) + static_cast<uint32_t>(warp) * Ring::kBytes;
+  // a row holds at least a group's 32 vectors: stepping back one group crosses at most one row boundary
+  const bool long_rows = p.vecs_per_row >= 32;
 
   // tile t goes to block t mod grid: every SM gets its share even when there are fewer tiles than warp slots
   for (int64_t tile = static_cast<int64_t>(warp) * gridDim.x + blockIdx.x; tile < p.tiles;
@@ -362,59 +394,68 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       continue;
     }
     uint32_t x = p.states[tile * kNumStates + lane];
-    const int origin = 2 * static_cast<int>(begin & (kRingWords - 1));
+    const int origin = 2 * static_cast<int>(begin & (Ring::kWords - 1));
     int cursor = origin + 2 * static_cast<int>(end - begin);
-    int chunk = end > begin ? static_cast<int>((end - 1u) >> kChunkLog) : -1;
-    int refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(chunk) << kChunkLog) - static_cast<int64_t>(begin));
+    int chunk = end > begin ? static_cast<int>((end - 1u) >> Ring::kLog) : -1;
+    int refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(chunk) << Ring::kLog) - static_cast<int64_t>(begin));
     // the previous tile's last prefetch may still be in flight and every thread must be past its reads
     // of the old ring contents before the ring is refilled
     ring_wait_all();
     __syncwarp();
-    ring_fetch_clipped(p.payload, p.payload_words, ring, chunk, lane);
-    ring_fetch_clipped(p.payload, p.payload_words, ring, chunk - 1, lane);
-    ring_fetch_clipped(p.payload, p.payload_words, ring, chunk - 2, lane);
+    Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk, lane);
+    Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk - 1, lane);
+    Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk - 2, lane);
     ring_commit();
     ring_wait_all();
     __syncwarp();
-    ring_fetch_interior(p.payload, ring, chunk - 3, lane);
+    Ring::fetch_interior(p.payload, ring, chunk - 3, lane);
     ring_commit();
 
-    // One symbol from the table that starts `table_at` entries into the table array. Same chain as the
-    // Tile-ANS decoder; `valid` is a literal in the main loop, so its tests fold away there.
-    auto step = [&](uint32_t table_at, bool valid) -> uint32_t {
+    // One symbol from the table that starts `table_first` entries into the table array, `coset_at` entries further for
+    // the tables of coset 1 (a multiple of the table size, so it can be or-ed into the slot). Same chain as the Tile-ANS
+    // decoder; `valid` is a literal in the main loop, so its tests fold away there.
+    auto step = [&](uint32_t table_first, uint32_t coset_at, auto valid) -> uint32_t {
+      constexpr bool kWholeGroup = std::is_same<decltype(valid), std::true_type>::value;
       uint32_t symbol = 0;
       if (valid) {
-        const uint32_t slot = x & slot_mask;
+        const uint32_t slot = (x & slot_mask) | coset_at;
         if (TABLES == kTablesShared) {
-          const uint32_t entry = shared_tables[table_at + slot];
+          // entry = symbol | delta << 9 | freq << 20, so entry >> 9 = freq * 2048 + delta and
+          // freq * (x >> prob_bits) + delta = freq * ((x >> prob_bits) - 2048) + (entry >> 9): one shift between the
+          // table read and the multiply-add
+          const uint32_t entry = shared_tables[table_first + slot];
           symbol = entry & 0x1FFu;
-          x = ((entry >> 9) & 0xFFFu) * (x >> prob_bits) + (entry >> 21);
+          x = (entry >> 20) * ((x >> prob_bits) - 2048u) + (entry >> 9);
         } else if (TABLES == kTablesSharedWide) {
-          const uint32_t entry = shared_tables[table_at + slot];
-          const uint32_t high = reinterpret_cast<const uint8_t*>(shared_tables + kTables * table_size)[table_at + slot];
+          const uint32_t entry = shared_tables[table_first + slot];
+          const uint32_t high = reinterpret_cast<const uint8_t*>(shared_tables + kTables * table_size)[table_first + slot];
           symbol = (entry & 0x3FFu) | (high << 10);
           x = (((entry >> 10) & 0x7FFu) + 1u) * (x >> prob_bits) + (entry >> 21);
         } else {
-          const uint64_t entry = __ldg(p.global_tables + table_at + slot);
+          const uint64_t entry = __ldg(p.global_tables + table_first + slot);
           symbol = static_cast<uint32_t>(entry) & 0xFFFFu;
           x = ((static_cast<uint32_t>(entry) >> 16) & 0xFFFFu) * (x >> prob_bits) + static_cast<uint32_t>(entry >> 32);
         }
       }
-      const bool need = valid && x < kStateMin;
-      const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
-      const int below = cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
-      const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingBytes - 2u)) | ring), x, 0x5410);
-      x = need ? merged : x;
-      cursor = __reduce_min_sync(0xFFFFFFFFu, below);   // thread 0's position, as a value the compiler knows is warp-uniform
+      if constexpr (kWholeGroup) {
+        renormalize_from_ring<Ring::kBytes>(x, cursor, ring, mask_ge);
+      } else {
+        const bool need = valid && x < kStateMin;
+        const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
+        const int below = cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
+        const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (Ring::kBytes - 2u)) | ring), x, 0x5410);
+        x = need ? merged : x;
+        cursor = __shfl_sync(0xFFFFFFFFu, below, 0);   // thread 0 counted every reader
+      }
       return symbol;
     };
     auto upkeep = [&]() {
-      if (cursor <= refill_at) {
-        refill_at -= 2 * kChunkWords;
+      while (cursor <= refill_at) {    // at most once where the stream is intact
+        refill_at -= 2 * Ring::kChunk;
         chunk -= 1;
         ring_wait_all();
         __syncwarp();
-        ring_fetch_interior(p.payload, ring, chunk - 3, lane);
+        Ring::fetch_interior(p.payload, ring, chunk - 3, lane);
         ring_commit();
       }
     };
@@ -425,6 +466,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     // row and column (in vectors) of this thread's vector in the current group, stepped back 32 per group
     int row = static_cast<int>(static_cast<uint32_t>(tile_begin + offset + lane) / static_cast<uint32_t>(p.vecs_per_row));
     int col = static_cast<int>(static_cast<uint32_t>(tile_begin + offset + lane) - static_cast<uint32_t>(row) * p.vecs_per_row);
+    uint32_t seen_cosets = 0;     // every coset symbol or-ed together: anything above 1 is a corrupt table
     // kModeProduct: this thread's running dot products for the weight row it is in, flushed with one atomic add per
     // token whenever its vectors move on to another row, and at the end of the tile
     constexpr int kTokens = TOKENS > 0 ? TOKENS : 1;
@@ -441,9 +483,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
         }
       }
     };
-    auto decode_group = [&](bool valid) {
-      // kModeProduct: the activations this vector will meet are requested before its nine chain steps, so that
-      // their latency (an L2 round trip once the payload stream has pushed them out of L1) hides behind the chain
+    auto decode_group = [&](auto valid) {
+      // the row's scale, and in kModeProduct the activations this vector will meet, are requested before the vector's
+      // nine chain steps, so that their latency (an L2 round trip once the payload stream has pushed them out of L1)
+      // hides behind the chain
+      const float scale = valid ? __ldg(p.scales + row) : 0.0f;
       uint4 early[kTokens];
       if (MODE == kModeProduct && valid) {
 #pragma unroll
@@ -451,21 +495,27 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
           if (t < p.tokens) early[t] = __ldg(reinterpret_cast<const uint4*>(p.activations + (static_cast<int64_t>(t) * p.vecs_per_row + col) * 8));
         }
       }
-      const uint32_t coset = step(0, valid);
-      const uint32_t coset_at = coset * table_size;
-      int value[8];
+      uint32_t coset = step(0u, 0u, valid);
+      seen_cosets |= coset;
+      coset = min(coset, 1u);      // a corrupt coset table must not steer the look-ups past the 17 tables
+      const uint32_t coset_at = coset << prob_bits;
+      uint32_t symbol[8];
 #pragma unroll
       for (int field = 0; field < 8; ++field) {
-        value[field] = static_cast<int>(step((1 + 2 * field) * table_size + coset_at, valid)) + sym_min[1 + 2 * field + coset];
-        if (field == 1 || field == 4 || field == 7) upkeep();  // every three steps: at most 96 words
+        symbol[field] = step((1 + 2 * field) * table_size, coset_at, valid);
+        // upkeep every kStepsPerUpkeep steps at most: after fields 3 and 7 (five and four steps), or 1, 4 and 7
+        if (Ring::kStepsPerUpkeep >= 8 ? (field == 3 || field == 7) : (field == 1 || field == 4 || field == 7)) upkeep();
       }
       if (valid) {
-        int parity = 0;
-#pragma unroll
-        for (int field = 0; field < 7; ++field) parity += value[field];
+        const int4 low = *reinterpret_cast<const int4*>(&field_min[coset][0]);
+        const int4 high = *reinterpret_cast<const int4*>(&field_min[coset][4]);
+        int value[8] = {static_cast<int>(symbol[0]) + low.x,  static_cast<int>(symbol[1]) + low.y,  static_cast<int>(symbol[2]) + low.z,
+                        static_cast<int>(symbol[3]) + low.w,  static_cast<int>(symbol[4]) + high.x, static_cast<int>(symbol[5]) + high.y,
+                        static_cast<int>(symbol[6]) + high.z, static_cast<int>(symbol[7]) + high.w};
+        // z7 = 2 m + (z0 + ... + z6 mod 2); the parity of a sum is the exclusive-or of the low bits
+        const int parity = (value[0] ^ value[1] ^ value[2]) ^ (value[3] ^ value[4] ^ value[5]) ^ value[6];
         value[7] = 2 * value[7] + (parity & 1);
         const int64_t vector = tile_begin + offset + lane;
-        const float scale = __ldg(p.scales + row);
         const float half = coset ? 0.5f : 0.0f;
         float v[8];
 #pragma unroll
@@ -512,21 +562,29 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       }
       offset -= 32;
       col -= 32;
-      while (col < 0) {
-        col += p.vecs_per_row;
-        row -= 1;
+      if (long_rows) {
+        const bool wrapped = col < 0;
+        col += wrapped ? p.vecs_per_row : 0;
+        row -= wrapped ? 1 : 0;
+      } else {
+        while (col < 0) {
+          col += p.vecs_per_row;
+          row -= 1;
+        }
       }
     };
     if (count & 31) decode_group(lane < static_cast<uint32_t>(count & 31));
-    while (offset >= 0) decode_group(true);
+    while (offset >= 0) decode_group(std::true_type{});
     if (MODE == kModeProduct) {
       flush_products();
       running_row = -1;
     }
     const bool dirty = __any_sync(0xFFFFFFFFu, x != kStateMin);
+    const bool bad_coset = __any_sync(0xFFFFFFFFu, seen_cosets > 1u);
     const int left = (cursor - origin) / 2;
     if (lane == 0) {
-      if (left < 0) report(p.error, EP_STREAM_UNDERRUN);
+      if (bad_coset) report(p.error, EP_STREAM_BAD_SYMBOL);
+      else if (left < 0) report(p.error, EP_STREAM_UNDERRUN);
       else if (left != 0 || dirty) report(p.error, EP_STREAM_NOT_CONSUMED);
     }
   }
@@ -562,22 +620,87 @@ extern "C" int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphab
   return static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
 }
 
+extern "C" int64_t ep_lattice_slot_tables_bytes(int prob_bits, int max_alphabet) {
+  if (prob_bits < 9 || prob_bits > 15 || max_alphabet < 0 || max_alphabet > (1 << prob_bits)) return EP_ERR_INVALID_ARGUMENT;
+  const int64_t slots = static_cast<int64_t>(kTables) << prob_bits;
+  if (prob_bits > kSharedMaxProbBits) return slots * 8;
+  return max_alphabet <= kSharedMaxAlphabet ? slots * 4 : slots * 5;
+}
+
+extern "C" int ep_lattice_build_slot_tables(const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev, int64_t freq_entries,
+                                            int prob_bits, int max_alphabet, void* slot_tables_dev, int64_t slot_tables_bytes,
+                                            ep_stream_t stream) {
+  const int64_t needed = ep_lattice_slot_tables_bytes(prob_bits, max_alphabet);
+  if (needed < 0) return static_cast<int>(needed);
+  if (!stream_meta_dev || !freq_tables_dev || freq_entries < 0 || !slot_tables_dev || slot_tables_bytes < needed ||
+      (reinterpret_cast<uintptr_t>(slot_tables_dev) & 15u)) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (prob_bits > kSharedMaxProbBits) {
+    lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(static_cast<uint64_t*>(slot_tables_dev), stream_meta_dev, freq_tables_dev,
+                                                       freq_entries, prob_bits);
+    return check_launch("lattice_build_tables_kernel");
+  }
+  // one block of the decode kernel in its export mode: it builds the tables exactly as a decode would and writes them out
+  LatticeDecodeParams p = {};
+  p.stream_meta = stream_meta_dev;
+  p.freq_tables = freq_tables_dev;
+  p.freq_entries = freq_entries;
+  p.prob_bits = prob_bits;
+  p.export_tables = static_cast<uint32_t*>(slot_tables_dev);
+  const bool wide = max_alphabet > kSharedMaxAlphabet;
+  const size_t shared = static_cast<size_t>(needed) + static_cast<size_t>(kDecodeWarps + 1) * (wide ? WordRing<7>::kBytes : WordRing<8>::kBytes);
+  if (wide) {
+    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<kTablesSharedWide, kModeExport, 0, 0>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+    lattice_decode_kernel<kTablesSharedWide, kModeExport, 0, 0><<<1, kDecodeThreads, shared, s>>>(p);
+  } else {
+    EP_CUDA_CHECK(cudaFuncSetAttribute(lattice_decode_kernel<kTablesShared, kModeExport, 0, 0>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+    lattice_decode_kernel<kTablesShared, kModeExport, 0, 0><<<1, kDecodeThreads, shared, s>>>(p);
+  }
+  return check_launch("lattice_decode_kernel (table export)");
+}
+
 namespace ep {
 namespace {
+
+// Size of a container's slot tables as the decode kernel wants them: 32-bit entries (plus a byte per slot behind them
+// for alphabets beyond 512) when they go to shared memory, 64-bit entries when they stay in global memory.
+int64_t slot_table_bytes(int prob_bits, int max_alphabet) {
+  const int64_t slots = static_cast<int64_t>(kTables) << prob_bits;
+  if (prob_bits > kSharedMaxProbBits) return slots * 8;
+  return max_alphabet <= kSharedMaxAlphabet ? slots * 4 : slots * 5;
+}
+
+// The kernel for one table layout and prob_bits specialisation, picked by what is done with a vector.
+template <int TABLES, int PB, typename Launch>
+int launch_for_mode(Launch&& launch, size_t shared, bool product, int tokens, int store_kind) {
+  if (product) {
+    return tokens == 1 ? launch(lattice_decode_kernel<TABLES, kModeProduct, 1, PB>, shared)
+         : tokens == 2 ? launch(lattice_decode_kernel<TABLES, kModeProduct, 2, PB>, shared)
+                       : launch(lattice_decode_kernel<TABLES, kModeProduct, 4, PB>, shared);
+  }
+  if (store_kind == EP_STORE_BF16) return launch(lattice_decode_kernel<TABLES, kModeStoreBf16, 0, PB>, shared);
+  return launch(lattice_decode_kernel<TABLES, kModeStore, 0, PB>, shared);
+}
 
 // Validates the arguments, fills the parameter block and launches the decode (plus the table-build
 // kernel on the global path). `tables` must hold 17 * 2^prob_bits 64-bit entries when the container
 // needs the global path; it is ignored otherwise.
 int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                           const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
-                          const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols, int prob_bits,
-                          int64_t tile_elements, int max_alphabet, uint64_t* tables, int64_t table_bytes, int* error_dev,
-                          cudaStream_t s, const __nv_bfloat16* activations = nullptr, float* products = nullptr, int tokens = 0,
-                          const __nv_bfloat16* bias = nullptr, __nv_bfloat16* product_out = nullptr) {
+                          int64_t freq_entries, const float* scales_dev, void* output_dev, int store_kind, int64_t rows,
+                          int64_t cols, int prob_bits, int64_t tile_elements, int max_alphabet, uint64_t* tables,
+                          int64_t table_bytes, bool tables_ready, int* error_dev, cudaStream_t s,
+                          const __nv_bfloat16* activations = nullptr,
+                          float* products = nullptr, int tokens = 0, const __nv_bfloat16* bias = nullptr,
+                          __nv_bfloat16* product_out = nullptr) {
   if (rows <= 0 || cols <= 0 || (cols & 7) != 0 || prob_bits < 9 || prob_bits > 15 || tile_elements <= 0 ||
       store_kind < 0 || store_kind > EP_STORE_BOOL || max_alphabet < 0 || max_alphabet > (1 << prob_bits) ||
-      payload_words < 0 || !offsets_dev || !states_dev || !stream_meta_dev || !freq_tables_dev || !scales_dev ||
-      (!output_dev && !products)) {
+      payload_words < 0 || freq_entries < 0 || !offsets_dev || !states_dev || !stream_meta_dev || !freq_tables_dev ||
+      !scales_dev || (!output_dev && !products)) {
     return EP_ERR_INVALID_ARGUMENT;
   }
   if (payload_words > 0 && !payload_dev) return EP_ERR_INVALID_ARGUMENT;
@@ -593,9 +716,12 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   p.states = states_dev;
   p.stream_meta = stream_meta_dev;
   p.freq_tables = freq_tables_dev;
+  p.freq_entries = freq_entries;
   p.scales = scales_dev;
   p.output = output_dev;
   p.global_tables = nullptr;
+  p.slot_tables = nullptr;
+  p.export_tables = nullptr;
   p.vectors = vectors;
   const int64_t tile_vectors = tile_elements / 9 < 32 ? 32 : tile_elements / 9;
   if (tile_vectors > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
@@ -613,50 +739,39 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   p.rows = static_cast<int>(rows);
   // one persistent block per SM; with fewer tiles than SMs, one block per tile
   const unsigned blocks = static_cast<unsigned>(p.tiles < kSmCount ? p.tiles : kSmCount);
-  const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * kRingWords * sizeof(uint16_t);
+  // one ring per warp, plus one ring's worth of slack for aligning the first to its size
+  const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * WordRing<8>::kBytes;
+  const size_t narrow_ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * WordRing<7>::kBytes;
   const auto launch = [&](auto kernel, size_t shared) -> int {
     EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
     kernel<<<blocks, kDecodeThreads, shared, s>>>(p);
     return EP_OK;
   };
+  const bool product = products != nullptr;
   int launched = EP_OK;
+  if (tables_ready) {
+    // tables built for this container by ep_lattice_build_slot_tables: the shared paths copy them in, the global path reads them
+    if (!tables || table_bytes < slot_table_bytes(prob_bits, max_alphabet) || (reinterpret_cast<uintptr_t>(tables) & 15u)) {
+      return EP_ERR_INVALID_ARGUMENT;
+    }
+    p.slot_tables = reinterpret_cast<const uint32_t*>(tables);
+  }
   if (prob_bits <= kSharedMaxProbBits && max_alphabet <= kSharedMaxAlphabet) {
     const size_t shared = (static_cast<size_t>(kTables) * sizeof(uint32_t) << prob_bits) + ring_bytes;
-    if (products) {
-      launched = tokens == 1 ? launch(lattice_decode_kernel<kTablesShared, kModeProduct, 1>, shared)
-               : tokens == 2 ? launch(lattice_decode_kernel<kTablesShared, kModeProduct, 2>, shared)
-                             : launch(lattice_decode_kernel<kTablesShared, kModeProduct, 4>, shared);
-    } else if (store_kind == EP_STORE_BF16) {
-      launched = launch(lattice_decode_kernel<kTablesShared, kModeStoreBf16>, shared);
-    } else {
-      launched = launch(lattice_decode_kernel<kTablesShared, kModeStore>, shared);
-    }
+    launched = prob_bits == 11 ? launch_for_mode<kTablesShared, 11>(launch, shared, product, tokens, store_kind)
+                               : launch_for_mode<kTablesShared, 0>(launch, shared, product, tokens, store_kind);
   } else if (prob_bits <= kSharedMaxProbBits) {
     // alphabets beyond 512 (fine scales, heavy-tailed rows): word tables plus a byte table of high symbol bits
-    const size_t shared = (static_cast<size_t>(kTables) * 5 << prob_bits) + ring_bytes;
-    if (products) {
-      launched = tokens == 1 ? launch(lattice_decode_kernel<kTablesSharedWide, kModeProduct, 1>, shared)
-               : tokens == 2 ? launch(lattice_decode_kernel<kTablesSharedWide, kModeProduct, 2>, shared)
-                             : launch(lattice_decode_kernel<kTablesSharedWide, kModeProduct, 4>, shared);
-    } else if (store_kind == EP_STORE_BF16) {
-      launched = launch(lattice_decode_kernel<kTablesSharedWide, kModeStoreBf16>, shared);
-    } else {
-      launched = launch(lattice_decode_kernel<kTablesSharedWide, kModeStore>, shared);
-    }
+    const size_t shared = (static_cast<size_t>(kTables) * 5 << prob_bits) + narrow_ring_bytes;
+    launched = prob_bits == 11 ? launch_for_mode<kTablesSharedWide, 11>(launch, shared, product, tokens, store_kind)
+                               : launch_for_mode<kTablesSharedWide, 0>(launch, shared, product, tokens, store_kind);
   } else {
     const int64_t needed = static_cast<int64_t>(kTables) * sizeof(uint64_t) << prob_bits;
     if (!tables || table_bytes < needed || (reinterpret_cast<uintptr_t>(tables) & 7u)) return EP_ERR_INVALID_ARGUMENT;
-    lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, prob_bits);
+    if (!tables_ready) lattice_build_tables_kernel<<<kTables, 32, 0, s>>>(tables, stream_meta_dev, freq_tables_dev, freq_entries, prob_bits);
     p.global_tables = tables;
-    if (products) {
-      launched = tokens == 1 ? launch(lattice_decode_kernel<kTablesGlobal, kModeProduct, 1>, ring_bytes)
-               : tokens == 2 ? launch(lattice_decode_kernel<kTablesGlobal, kModeProduct, 2>, ring_bytes)
-                             : launch(lattice_decode_kernel<kTablesGlobal, kModeProduct, 4>, ring_bytes);
-    } else if (store_kind == EP_STORE_BF16) {
-      launched = launch(lattice_decode_kernel<kTablesGlobal, kModeStoreBf16>, ring_bytes);
-    } else {
-      launched = launch(lattice_decode_kernel<kTablesGlobal, kModeStore>, ring_bytes);
-    }
+    p.slot_tables = nullptr;
+    launched = launch_for_mode<kTablesGlobal, 0>(launch, ring_bytes, product, tokens, store_kind);
   }
   if (launched != EP_OK) return launched;
   return check_launch("lattice_decode_kernel");
@@ -667,9 +782,11 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
 
 extern "C" int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                                          const uint32_t* states_dev, const int32_t* stream_meta_dev,
-                                         const uint16_t* freq_tables_dev, const float* scales_dev, int64_t rows, int64_t cols,
+                                         const uint16_t* freq_tables_dev, int64_t freq_entries, const float* scales_dev,
+                                         int64_t rows, int64_t cols,
                                          int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
-                                         int64_t table_scratch_bytes, const void* x_dev, const void* bias_dev, int tokens,
+                                         int64_t table_scratch_bytes, int tables_ready, const void* x_dev, const void* bias_dev,
+                                         int tokens,
                                          float* products_dev, void* y_dev, int* error_dev, ep_stream_t stream) {
   if (!x_dev || !products_dev || !y_dev || tokens < 1 || tokens > ep::kMaxTokens || rows <= 0 || rows > 0x7FFFFFFF) {
     return EP_ERR_INVALID_ARGUMENT;
@@ -678,21 +795,21 @@ extern "C" int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t pa
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t total = static_cast<int64_t>(tokens) * rows;
   EP_CUDA_CHECK(cudaMemsetAsync(products_dev, 0, sizeof(float) * (total + 1), s));   // accumulators and the block counter
-  return ep::launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, scales_dev,
-                                   nullptr, EP_STORE_BF16, rows, cols, prob_bits, tile_elements, max_alphabet,
-                                   static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, error_dev, s,
+  return ep::launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev,
+                                   freq_entries, scales_dev, nullptr, EP_STORE_BF16, rows, cols, prob_bits, tile_elements, max_alphabet,
+                                   static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, tables_ready != 0, error_dev, s,
                                    static_cast<const __nv_bfloat16*>(x_dev), products_dev, tokens,
                                    static_cast<const __nv_bfloat16*>(bias_dev), static_cast<__nv_bfloat16*>(y_dev));
 }
 
 extern "C" int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                                  const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
-                                 const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
+                                 int64_t freq_entries, const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
                                  int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
-                                 int64_t table_scratch_bytes, int* error_dev, ep_stream_t stream) {
-  return launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, scales_dev,
-                               output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet,
-                               static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, error_dev,
+                                 int64_t table_scratch_bytes, int tables_ready, int* error_dev, ep_stream_t stream) {
+  return launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, freq_entries,
+                               scales_dev, output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet,
+                               static_cast<uint64_t*>(table_scratch_dev), table_scratch_bytes, tables_ready != 0, error_dev,
                                static_cast<cudaStream_t>(stream));
 }
 
@@ -734,15 +851,15 @@ extern "C" int ep_lattice_decode_static_max_prob_bits(void) { return kStaticMaxP
 
 extern "C" int ep_lattice_decode_static(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                                         const uint32_t* states_dev, const int32_t* stream_meta_dev,
-                                        const uint16_t* freq_tables_dev, const float* scales_dev, void* output_dev,
-                                        int store_kind, int64_t rows, int64_t cols, int prob_bits, int64_t tile_elements,
+                                        const uint16_t* freq_tables_dev, int64_t freq_entries, const float* scales_dev,
+                                        void* output_dev, int store_kind, int64_t rows, int64_t cols, int prob_bits, int64_t tile_elements,
                                         int max_alphabet, int* error_dev, ep_stream_t stream) {
   const bool shared_path = prob_bits <= kSharedMaxProbBits;
   if (!shared_path && prob_bits > kStaticMaxProbBits && prob_bits <= 15) return EP_ERR_TOO_LARGE;
   uint64_t* tables = nullptr;
   const int rc = static_tables_for_current_device(&tables);
   if (rc != EP_OK) return rc;
-  return launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, scales_dev,
-                               output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet, tables,
-                               static_cast<int64_t>(kStaticTableBytes), error_dev, static_cast<cudaStream_t>(stream));
+  return launch_lattice_decode(payload_dev, payload_words, offsets_dev, states_dev, stream_meta_dev, freq_tables_dev, freq_entries,
+                               scales_dev, output_dev, store_kind, rows, cols, prob_bits, tile_elements, max_alphabet, tables,
+                               static_cast<int64_t>(kStaticTableBytes), false, error_dev, static_cast<cudaStream_t>(stream));
 }

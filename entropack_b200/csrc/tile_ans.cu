@@ -12,6 +12,8 @@
 //
 // Encode: one warp owns one tile across all byte lanes as well, so the input is read once as whole
 // elements. Division by the symbol frequency uses a per-symbol 32-bit reciprocal with one correction.
+#include <type_traits>
+
 #include "ep_common.cuh"
 #include "rans_ring.cuh"
 
@@ -51,8 +53,11 @@ template <> struct Element<2> { using type = uint16_t; };
 template <> struct Element<4> { using type = uint32_t; };
 template <> struct Element<8> { using type = uint64_t; };
 
-// Shared table entry: symbol | frequency << 8 | (slot - cdf) << 20. A frequency field of 0 can only
-// mean "the whole table" (one symbol, 4096 slots): such a lane decodes to a constant and never reads.
+// Shared table entry: symbol | (slot - cdf) << 8 | frequency << 20, so that entry >> 8 is
+// frequency * 4096 + (slot - cdf) and the state update frequency * (x >> prob_bits) + (slot - cdf) becomes
+// (entry >> 20) * ((x >> prob_bits) - 4096) + (entry >> 8): one shift between the table read and the
+// multiply-add. A frequency field of 0 can only mean "the whole table" (one symbol, 4096 slots): such a
+// lane decodes to a constant and never reads.
 template <int NLANES>
 __device__ __forceinline__ void stage_decode_tables(const DecodeParams& p, uint32_t* shared_tables, int* constant_symbol) {
   const uint32_t table_size = 1u << p.prob_bits;
@@ -63,7 +68,9 @@ __device__ __forceinline__ void stage_decode_tables(const DecodeParams& p, uint3
     if ((p.lanes.raw_mask >> b) & 1u) continue;
     const uint32_t* source = p.tables + static_cast<size_t>(b) * table_size;
     uint32_t* staged = shared_tables + static_cast<size_t>(p.lanes.ans_rank[b]) * table_size;
-    const auto repack = [](uint32_t entry, uint32_t slot) { return (entry & 0xFFFFFu) | ((slot - (entry >> 20)) << 20); };
+    const auto repack = [](uint32_t entry, uint32_t slot) {
+      return (entry & 0xFFu) | (((slot - (entry >> 20)) & 0xFFFu) << 8) | ((entry >> 8) << 20);
+    };
     if (threadIdx.x == 0) {
       const uint32_t entry = source[0];
       if (((entry >> 8) & 0xFFFu) == 0u) constant_symbol[b] = static_cast<int>(entry & 0xFFu);
@@ -158,7 +165,7 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_simple_kernel(const 
           const uint32_t slot = x & slot_mask;
           const uint32_t entry = table[b][slot];
           byte = entry & 0xFFu;
-          state[b] = ((entry >> 8) & 0xFFFu) * (x >> p.prob_bits) + (entry >> 20);
+          state[b] = (entry >> 20) * ((x >> p.prob_bits) - 4096u) + (entry >> 8);
         }
         renormalize(valid, state[b], words[b], position[b], mask_ge);
       }
@@ -207,10 +214,12 @@ struct CodedLane {
 };
 
 // RAW_MASK >= 0 fixes the lane pattern at compile time (dead per-lane state disappears from the register file);
-// RAW_MASK < 0 reads it from the parameters.
-template <int NLANES, int RAW_MASK>
+// RAW_MASK < 0 reads it from the parameters. CHUNK_LOG picks the ring: 256-word chunks (upkeep every eight steps)
+// where seven blocks' shared memory still fits an SM, 128-word chunks otherwise.
+template <int NLANES, int RAW_MASK, int CHUNK_LOG>
 __global__ void __launch_bounds__(kThreads, (NLANES <= 2 || (NLANES == 4 && RAW_MASK == 7)) ? kDecodeBlocksPerSm : (NLANES == 4 ? 3 : 1))
 tile_ans_decode_kernel(const DecodeParams p) {
+  using Ring = WordRing<CHUNK_LOG>;
   extern __shared__ __align__(16) uint32_t shared_tables[];
   __shared__ int constant_symbol[kMaxLanes];
   __shared__ uint32_t raw_begins[kWarps][kMaxLanes];
@@ -233,8 +242,8 @@ tile_ans_decode_kernel(const DecodeParams p) {
   const int ans_lanes = p.lanes.ans_lanes;
   const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
 
-  // dynamic shared memory: tables | pad to 1 KB | rings[warp][rank] | staging[warp][rank]
-  constexpr uint32_t kRingBytes = kRingWords * 2u;
+  // dynamic shared memory: tables | pad to the ring size | rings[warp][rank] | staging[warp][rank]
+  constexpr uint32_t kRingBytes = Ring::kBytes;
   const uint32_t rings_address = (shared_base + static_cast<uint32_t>(ans_lanes) * table_size * 4u + kRingBytes - 1u) & ~(kRingBytes - 1u);
   const uint32_t staging_at = (rings_address - shared_base) + static_cast<uint32_t>(kWarps * ans_lanes) * kRingBytes;  // in bytes
 
@@ -259,10 +268,10 @@ tile_ans_decode_kernel(const DecodeParams p) {
     c.table = rank * table_size;
     c.ring = rings_address + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kRingBytes;
     c.stage = staging_at + (static_cast<uint32_t>(warp * ans_lanes) + rank) * kBlockElems + lane;
-    const int origin = 2 * static_cast<int>(begin & (kRingWords - 1));
+    const int origin = 2 * static_cast<int>(begin & (Ring::kWords - 1));
     c.cursor = origin + 2 * static_cast<int>(end - begin);
-    c.chunk = end > begin ? static_cast<int>((end - 1u) >> kChunkLog) : -1;
-    c.refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(c.chunk) << kChunkLog) - static_cast<int64_t>(begin));
+    c.chunk = end > begin ? static_cast<int>((end - 1u) >> Ring::kLog) : -1;
+    c.refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(c.chunk) << Ring::kLog) - static_cast<int64_t>(begin));
     c.state = kStateMin;
     if ((raw_mask >> b) & 1u) {
       if (!failure && end - begin != static_cast<uint32_t>((count + 1) >> 1)) failure = EP_STREAM_BAD_RAW_LENGTH;
@@ -280,9 +289,9 @@ tile_ans_decode_kernel(const DecodeParams p) {
   for (int b = 0; b < NLANES; ++b) {
     if ((raw_mask >> b) & 1u) continue;
     const uint32_t ring_address = coded[b].ring;
-    ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk, lane);
-    ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 1, lane);
-    ring_fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 2, lane);
+    Ring::fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk, lane);
+    Ring::fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 1, lane);
+    Ring::fetch_clipped(p.payload, p.payload_words, ring_address, coded[b].chunk - 2, lane);
   }
   ring_commit();
   ring_wait_all();
@@ -290,16 +299,18 @@ tile_ans_decode_kernel(const DecodeParams p) {
 #pragma unroll
   for (int b = 0; b < NLANES; ++b) {
     if ((raw_mask >> b) & 1u) continue;
-    ring_fetch_interior(p.payload, coded[b].ring, coded[b].chunk - 3, lane);
+    Ring::fetch_interior(p.payload, coded[b].ring, coded[b].chunk - 3, lane);
   }
   ring_commit();
 
+  element_t* out = static_cast<element_t*>(p.output) + tile_begin;
   // One decode step of every coded lane for the group at `in_block` (offset inside the staging block).
   // Branch-free: every thread loads a ring word and only the threads that need it merge it in. A
   // single-symbol lane (frequency field 0) runs through the same code: its table yields the right
   // symbol for every slot, its state and cursor become meaningless, all ring reads stay inside the
   // ring, and its final consistency check is skipped.
-  auto chain_step = [&](int in_block, bool valid) {
+  auto chain_step = [&](int in_block, auto valid) {
+    constexpr bool kWholeGroup = std::is_same<decltype(valid), std::true_type>::value;
 #pragma unroll
     for (int b = 0; b < NLANES; ++b) {
       if ((raw_mask >> b) & 1u) continue;
@@ -308,21 +319,25 @@ tile_ans_decode_kernel(const DecodeParams p) {
       if (valid) {
         const uint32_t entry = shared_tables[c.table + (x & slot_mask)];
         shared_bytes[c.stage + in_block] = static_cast<uint8_t>(entry);
-        x = ((entry >> 8) & 0xFFFu) * (x >> prob_bits) + (entry >> 20);
+        x = (entry >> 20) * ((x >> prob_bits) - 4096u) + (entry >> 8);
       }
-      const bool need = valid && x < kStateMin;
-      const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
-      // this thread's word sits 2 * (readers at or above this lane) bytes below the cursor; thread 0 counts every
-      // reader, so the lowest position in the warp is the cursor for the next step (a reduction, whose result
-      // the compiler knows to be warp-uniform)
-      const int below = c.cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
-      const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingWords * 2u - 2u)) | c.ring), x, 0x5410);
-      c.state = need ? merged : x;
-      c.cursor = __reduce_min_sync(0xFFFFFFFFu, below);
+      if constexpr (kWholeGroup) {
+        renormalize_from_ring<kRingBytes>(x, c.cursor, c.ring, mask_ge);
+        c.state = x;
+      } else {
+        const bool need = valid && x < kStateMin;
+        const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
+        // this thread's word sits 2 * (readers at or above this lane) bytes below the cursor; thread 0 counts every
+        // reader, so its position is the cursor for the next step
+        const int below = c.cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
+        const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (kRingBytes - 2u)) | c.ring), x, 0x5410);
+        c.state = need ? merged : x;
+        c.cursor = __shfl_sync(0xFFFFFFFFu, below, 0);
+      }
     }
   };
-  // Ring upkeep, run once every four steps. Three chunks at and below the cursor's chunk are resident
-  // and a fourth is in flight; four steps consume at most 128 words = one chunk, so at most one chunk
+  // Ring upkeep, run once every Ring::kStepsPerUpkeep steps. Three chunks at and below the cursor's chunk are
+  // resident and a fourth is in flight; that many steps consume at most one chunk, so at most one chunk
   // boundary is crossed between two calls and every read in between stays inside resident chunks.
   // On a crossing, the chunk requested one crossing ago is made visible to the warp and the next one
   // down is requested into the ring slot that has just been vacated.
@@ -332,17 +347,22 @@ tile_ans_decode_kernel(const DecodeParams p) {
       if ((raw_mask >> b) & 1u) continue;
       CodedLane& c = coded[b];
       if (c.cursor <= c.refill_at) {
-        c.refill_at -= 2 * kChunkWords;
+        c.refill_at -= 2 * Ring::kChunk;
         c.chunk -= 1;
         ring_wait_all();
         __syncwarp();
-        ring_fetch_interior(p.payload, c.ring, c.chunk - 3, lane);
+        Ring::fetch_interior(p.payload, c.ring, c.chunk - 3, lane);
         ring_commit();
       }
     }
   };
+  // `steps` consecutive full groups ending at offset `first` (the highest group first), then one upkeep
+  auto chain_run = [&](int first) {
+#pragma unroll
+    for (int k = Ring::kStepsPerUpkeep - 1; k >= 0; --k) chain_step(first + 32 * k, std::true_type{});
+    ring_upkeep();
+  };
 
-  element_t* out = static_cast<element_t*>(p.output) + tile_begin;
   const uint8_t* payload_bytes = reinterpret_cast<const uint8_t*>(p.payload);
   // kGroup elements = 16 bytes of output per thread; needs every tile to start on a 16-byte boundary
   constexpr int kGroup = 16 / NLANES;
@@ -364,18 +384,9 @@ tile_ans_decode_kernel(const DecodeParams p) {
     }
     // ---- chain phase: groups of 32 symbols, back to front; only the tile's last group can be partial
     if (full) {
-      static_assert(kBlockElems == 512, "sixteen steps are written out below");
-#define EP_FOUR_STEPS(first)          \
-  chain_step((first) * 32 + 96, true); \
-  chain_step((first) * 32 + 64, true); \
-  chain_step((first) * 32 + 32, true); \
-  chain_step((first) * 32, true);      \
-  ring_upkeep();
-      EP_FOUR_STEPS(12)
-      EP_FOUR_STEPS(8)
-      EP_FOUR_STEPS(4)
-      EP_FOUR_STEPS(0)
-#undef EP_FOUR_STEPS
+      static_assert(kBlockElems % (32 * Ring::kStepsPerUpkeep) == 0, "a staging block is a whole number of runs");
+#pragma unroll
+      for (int first = kBlockElems - 32 * Ring::kStepsPerUpkeep; first >= 0; first -= 32 * Ring::kStepsPerUpkeep) chain_run(first);
     } else {
       const int tail = (block_hi - block_lo) & 31;
       for (int offset = block_hi - (tail ? tail : 32); offset >= block_lo; offset -= 32) {
@@ -480,11 +491,132 @@ tile_ans_decode_kernel(const DecodeParams p) {
     const bool dirty = __any_sync(0xFFFFFFFFu, coded[b].state != kStateMin);
     // words left = (cursor - 2 * (stream begin mod ring size)) / 2; the begin is read again rather than kept in a register
     const uint32_t begin = __reduce_min_sync(0xFFFFFFFFu, p.offsets[static_cast<int64_t>(b) * p.tiles + tile]);
-    const int left = (coded[b].cursor - 2 * static_cast<int>(begin & (kRingWords - 1))) / 2;
+    const int left = (coded[b].cursor - 2 * static_cast<int>(begin & (Ring::kWords - 1))) / 2;
     if (left < 0) failure = EP_STREAM_UNDERRUN;
     else if (left != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
   }
   if (failure && lane == 0) report(p.error, failure);
+}
+
+// ------------------------------------------------------------------------------------------------
+// One-byte elements with their single lane coded (fp8, int8, uint8): there is nothing to merge, so
+// each step stores its 32 symbols straight to the output (32 consecutive bytes per warp: one full
+// sector) and the step shrinks to its chain -- table read, store, multiply-add, renormalisation.
+// Runs of Ring::kStepsPerUpkeep steps are written out with the stores at literal offsets from one
+// base pointer per run. Needs tiles of whole 32-byte groups (tile_elements a multiple of 32).
+// ------------------------------------------------------------------------------------------------
+template <int OFFSET>
+__device__ __forceinline__ void store_low_byte(uint8_t* base, uint32_t value) {
+  asm volatile("st.global.u8 [%0 + %1], %2;" ::"l"(base), "n"(OFFSET), "r"(value) : "memory");
+}
+
+template <int CHUNK_LOG>
+__global__ void __launch_bounds__(kThreads, kDecodeBlocksPerSm) tile_ans_decode_bytes_kernel(const DecodeParams p) {
+  using Ring = WordRing<CHUNK_LOG>;
+  static_assert(Ring::kStepsPerUpkeep == 4 || Ring::kStepsPerUpkeep == 8, "runs are written out for four or eight steps");
+  extern __shared__ __align__(16) uint32_t shared_tables[];
+  __shared__ int constant_symbol[kMaxLanes];
+  const uint32_t table_size = 1u << p.prob_bits;
+  stage_decode_tables<1>(p, shared_tables, constant_symbol);
+
+  const int warp = threadIdx.x >> 5;
+  const int64_t tile = p.first_tile + static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  if (tile >= p.tile_end) return;
+  const uint32_t lane = lane_id();
+  const uint32_t mask_ge = lanemask_ge();
+  const uint32_t slot_mask = table_size - 1u;
+  const int prob_bits = p.prob_bits;
+  const int64_t tile_begin = tile * p.tile_elements;
+  const int count = static_cast<int>(min(p.tile_elements, p.num_elements - tile_begin));
+  const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared_tables));
+  const uint32_t ring = ((shared_base + table_size * 4u + Ring::kBytes - 1u) & ~(Ring::kBytes - 1u)) + static_cast<uint32_t>(warp) * Ring::kBytes;
+
+  // through a warp reduction: the compiler then knows the bounds, and the cursor arithmetic built on them, to be
+  // the same in all 32 threads
+  const uint32_t begin = __reduce_min_sync(0xFFFFFFFFu, p.offsets[tile]);
+  const uint32_t end = __reduce_min_sync(0xFFFFFFFFu, p.offsets[tile + 1]);
+  if (end < begin || static_cast<int64_t>(end) > p.payload_words) {
+    if (lane == 0) report(p.error, EP_STREAM_BAD_OFFSETS);
+    return;
+  }
+  uint32_t x = p.states[tile * kNumStates + lane];
+  const int origin = 2 * static_cast<int>(begin & (Ring::kWords - 1));
+  int cursor = origin + 2 * static_cast<int>(end - begin);
+  int chunk = end > begin ? static_cast<int>((end - 1u) >> Ring::kLog) : -1;
+  int refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(chunk) << Ring::kLog) - static_cast<int64_t>(begin));
+  // three chunks resident, the fourth on its way
+  Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk, lane);
+  Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk - 1, lane);
+  Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk - 2, lane);
+  ring_commit();
+  ring_wait_all();
+  __syncwarp();
+  Ring::fetch_interior(p.payload, ring, chunk - 3, lane);
+  ring_commit();
+
+  const auto upkeep = [&]() {
+    if (cursor <= refill_at) {
+      refill_at -= 2 * Ring::kChunk;
+      chunk -= 1;
+      ring_wait_all();
+      __syncwarp();
+      Ring::fetch_interior(p.payload, ring, chunk - 3, lane);
+      ring_commit();
+    }
+  };
+  uint8_t* const out = static_cast<uint8_t*>(p.output) + tile_begin + lane;
+  // a single group, possibly partial (the tensor's last tile), with its own upkeep
+  const auto single_step = [&](int offset, bool valid) {
+    if (valid) {
+      const uint32_t entry = shared_tables[x & slot_mask];
+      out[offset] = static_cast<uint8_t>(entry);
+      x = (entry >> 20) * ((x >> prob_bits) - 4096u) + (entry >> 8);
+    }
+    const bool need = valid && x < kStateMin;
+    const uint32_t vote = __ballot_sync(0xFFFFFFFFu, need);
+    const int below = cursor - 2 * static_cast<int>(__popc(vote & mask_ge));
+    const uint32_t merged = __byte_perm(load_shared_u16((static_cast<uint32_t>(below) & (Ring::kBytes - 2u)) | ring), x, 0x5410);
+    x = need ? merged : x;
+    cursor = __shfl_sync(0xFFFFFFFFu, below, 0);
+    upkeep();
+  };
+  int offset = count;
+  if (count & 31) {
+    offset -= count & 31;
+    single_step(offset, lane < static_cast<uint32_t>(count & 31));
+  }
+  constexpr int kRun = 32 * Ring::kStepsPerUpkeep;
+  while (offset % kRun) {
+    offset -= 32;
+    single_step(offset, true);
+  }
+#define EP_BYTE_STEP(K)                                                        \
+  {                                                                            \
+    const uint32_t entry = shared_tables[x & slot_mask];                       \
+    store_low_byte<(K) * 32>(run, entry);                                      \
+    x = (entry >> 20) * ((x >> prob_bits) - 4096u) + (entry >> 8);             \
+    renormalize_from_ring<Ring::kBytes>(x, cursor, ring, mask_ge);             \
+  }
+  uint8_t* run = out + offset;
+  while (offset > 0) {
+    offset -= kRun;
+    run -= kRun;
+    if (Ring::kStepsPerUpkeep == 8) {
+      EP_BYTE_STEP(7) EP_BYTE_STEP(6) EP_BYTE_STEP(5) EP_BYTE_STEP(4)
+    }
+    EP_BYTE_STEP(3) EP_BYTE_STEP(2) EP_BYTE_STEP(1) EP_BYTE_STEP(0)
+    upkeep();
+  }
+#undef EP_BYTE_STEP
+
+  if (constant_symbol[0] < 0) {
+    const bool dirty = __any_sync(0xFFFFFFFFu, x != kStateMin);
+    const int left = (cursor - origin) / 2;
+    int failure = 0;
+    if (left < 0) failure = EP_STREAM_UNDERRUN;
+    else if (left != 0 || dirty) failure = EP_STREAM_NOT_CONSUMED;
+    if (failure && lane == 0) report(p.error, failure);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -712,26 +844,57 @@ int allow_shared(Kernel kernel, size_t bytes) {
   return EP_OK;
 }
 
+// Shared memory of one block of the staged decoder.
+template <int CHUNK_LOG>
+size_t staged_shared_bytes(size_t table_bytes, int ans_lanes) {
+  const size_t per_warp_lane = WordRing<CHUNK_LOG>::kBytes + kBlockElems;
+  // one ring's worth of padding lets the kernel align the rings to their own size
+  return table_bytes + WordRing<CHUNK_LOG>::kBytes + static_cast<size_t>(kWarps) * ans_lanes * per_warp_lane;
+}
+
+template <int NLANES, int RAW_MASK, int CHUNK_LOG>
+int launch_staged(const DecodeParams& p, dim3 grid, size_t shared, cudaStream_t stream) {
+  const int rc = allow_shared(tile_ans_decode_kernel<NLANES, RAW_MASK, CHUNK_LOG>, shared);
+  if (rc != EP_OK) return rc;
+  tile_ans_decode_kernel<NLANES, RAW_MASK, CHUNK_LOG><<<grid, kThreads, shared, stream>>>(p);
+  return EP_OK;
+}
+
+// kDecodeBlocksPerSm blocks of `bytes` shared memory each fit one SM (227 KB, 1 KB of it reserved per block, plus the
+// kernels' few static words)
+inline bool fits_all_blocks(size_t bytes) { return (bytes + 1024 + 64) * kDecodeBlocksPerSm <= 227 * 1024; }
+
 template <int NLANES>
 int launch_decode(const DecodeParams& p, dim3 grid, size_t table_bytes, bool staged, cudaStream_t stream) {
+  if (staged && NLANES == 1 && p.lanes.raw_mask == 0u && p.tile_elements % 32 == 0) {
+    // one coded byte lane in tiles of whole 32-byte groups: the dedicated kernel (rings only, no staging block)
+    const size_t wide_ring = table_bytes + WordRing<8>::kBytes * (kWarps + 1), narrow_ring = table_bytes + WordRing<7>::kBytes * (kWarps + 1);
+    if (fits_all_blocks(wide_ring)) {
+      const int rc = allow_shared(tile_ans_decode_bytes_kernel<8>, wide_ring);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_bytes_kernel<8><<<grid, kThreads, wide_ring, stream>>>(p);
+    } else {
+      const int rc = allow_shared(tile_ans_decode_bytes_kernel<7>, narrow_ring);
+      if (rc != EP_OK) return rc;
+      tile_ans_decode_bytes_kernel<7><<<grid, kThreads, narrow_ring, stream>>>(p);
+    }
+    return EP_OK;
+  }
   if (staged) {
-    const size_t per_warp_lane = kRingWords * sizeof(uint16_t) + kBlockElems;
-    // one ring's worth of padding lets the kernel align the rings to their own size
-    const size_t shared = table_bytes + kRingWords * sizeof(uint16_t) + static_cast<size_t>(kWarps) * p.lanes.ans_lanes * per_warp_lane;
+    // 256-word ring chunks halve the ring upkeep; they are used for one- and two-byte elements where kDecodeBlocksPerSm
+    // blocks still fit an SM's shared memory, which keeps a tensor of 8192 tiles resident at once (four-byte elements
+    // measured no better with them)
+    const size_t wide_ring = staged_shared_bytes<8>(table_bytes, p.lanes.ans_lanes);
+    const bool wide = NLANES <= 2 && fits_all_blocks(wide_ring);
+    const size_t shared = wide ? wide_ring : staged_shared_bytes<7>(table_bytes, p.lanes.ans_lanes);
     // common patterns get their own instantiation: everything coded, or only the top byte coded
     constexpr int top_only = (1 << (NLANES - 1)) - 1;
     if (p.lanes.raw_mask == 0u && NLANES <= 2) {
-      const int rc = allow_shared(tile_ans_decode_kernel<NLANES, 0>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<NLANES, 0><<<grid, kThreads, shared, stream>>>(p);
+      return wide ? launch_staged<NLANES, 0, 8>(p, grid, shared, stream) : launch_staged<NLANES, 0, 7>(p, grid, shared, stream);
     } else if (NLANES > 1 && p.lanes.raw_mask == static_cast<uint32_t>(top_only)) {
-      const int rc = allow_shared(tile_ans_decode_kernel<NLANES, top_only>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<NLANES, top_only><<<grid, kThreads, shared, stream>>>(p);
+      return wide ? launch_staged<NLANES, top_only, 8>(p, grid, shared, stream) : launch_staged<NLANES, top_only, 7>(p, grid, shared, stream);
     } else {
-      const int rc = allow_shared(tile_ans_decode_kernel<NLANES, -1>, shared);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_kernel<NLANES, -1><<<grid, kThreads, shared, stream>>>(p);
+      return wide ? launch_staged<NLANES, -1, 8>(p, grid, shared, stream) : launch_staged<NLANES, -1, 7>(p, grid, shared, stream);
     }
   } else {
     const int rc = allow_shared(tile_ans_decode_simple_kernel<NLANES>, table_bytes);

@@ -28,6 +28,47 @@ def max_alphabet(buffers: LatticeBuffers) -> int:
     return cached
 
 
+def slot_tables(buffers: LatticeBuffers, prob_bits: int, alphabet: int, device: torch.device) -> torch.Tensor | None:
+    """The container's decode plan: its 17 slot tables, built on the device once and kept on the layout tensor (as the
+    reference keeps its plan, entropack/schemes/lattice_rans/cuda.py:697-741) so that later decodes copy them into
+    shared memory instead of rebuilding them from the stored frequencies at the head of every launch. A container
+    that is decoded only once never gets one: the first decode builds its tables inside the kernel and this returns
+    None; the second builds the kept copy (139 KB at prob_bits 11). Must not be first reached during a stream capture."""
+    layout = buffers.layout
+    cached = getattr(layout, "_lattice_rans_slot_tables", None)
+    if cached is not None and cached.device == device:
+        return cached
+    seen = getattr(layout, "_lattice_rans_decodes", 0)
+    layout._lattice_rans_decodes = seen + 1
+    if seen == 0:
+        return None
+    lib = _native.load()
+    nbytes = lib.ep_lattice_slot_tables_bytes(prob_bits, alphabet)
+    if nbytes < 0:
+        _native.check(int(nbytes), "lattice_rans slot tables")
+    tables = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        status = lib.ep_lattice_build_slot_tables(
+            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), buffers.freq_tables.numel(), prob_bits, alphabet,
+            _native.ptr(tables), nbytes, _native.stream_handle(device))
+    _native.check(status, "lattice_rans slot tables")
+    layout._lattice_rans_slot_tables = tables
+    return tables
+
+
+def _tables_or_scratch(buffers: LatticeBuffers, prob_bits: int, alphabet: int, device: torch.device, what: str):
+    """(buffer, bytes, ready) for the decode entry points: the kept slot tables when there are any, else scratch for the
+    kernels that keep their tables in global memory, else nothing."""
+    tables = slot_tables(buffers, prob_bits, alphabet, device)
+    if tables is not None:
+        return tables, tables.numel(), 1
+    scratch_bytes = _native.load().ep_lattice_decode_scratch_bytes(prob_bits, alphabet)
+    if scratch_bytes < 0:
+        _native.check(int(scratch_bytes), what)
+    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=device) if scratch_bytes else None
+    return scratch, scratch_bytes, 0
+
+
 def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_block=None, l2_prefetch=True,
            error: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Decode to ``[rows, cols_padded]`` of ``dtype`` on the buffers' device (one or two launches, no host sync
@@ -43,16 +84,14 @@ def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_bl
         out = torch.empty((rows, cols), dtype=out_dtype, device=device)
     alphabet = max_alphabet(buffers)
     lib = _native.load()
-    scratch_bytes = lib.ep_lattice_decode_scratch_bytes(prob_bits, alphabet)
-    if scratch_bytes < 0:
-        _native.check(int(scratch_bytes), "lattice_rans decode")
-    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=device) if scratch_bytes else None
+    scratch, scratch_bytes, ready = _tables_or_scratch(buffers, prob_bits, alphabet, device, "lattice_rans decode")
     with torch.cuda.device(device):
         status = lib.ep_lattice_decode(
             _native.ptr(payload), payload.numel(), _native.ptr(buffers.offsets), _native.ptr(buffers.states),
-            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), _native.ptr(buffers.scales), _native.ptr(out),
+            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), buffers.freq_tables.numel(), _native.ptr(buffers.scales),
+            _native.ptr(out),
             STORE_KINDS[out_dtype], rows, cols, prob_bits, info["tile_elements"], alphabet, _native.ptr(scratch),
-            scratch_bytes, _native.ptr(error), _native.stream_handle(device))
+            scratch_bytes, ready, _native.ptr(error), _native.stream_handle(device))
     _native.check(status, "lattice_rans decode")
     return snap_to_container(out, dtype) if via_float else out
 
@@ -80,15 +119,13 @@ def linear_forward(buffers: LatticeBuffers, *, shape, x: torch.Tensor, bias: tor
     out = torch.empty((tokens, rows), dtype=torch.bfloat16, device=device)
     alphabet = max_alphabet(buffers)
     lib = _native.load()
-    scratch_bytes = lib.ep_lattice_decode_scratch_bytes(prob_bits, alphabet)
-    if scratch_bytes < 0:
-        _native.check(int(scratch_bytes), "lattice_rans fused forward")
-    scratch = torch.empty(scratch_bytes, dtype=torch.uint8, device=device) if scratch_bytes else None
+    scratch, scratch_bytes, ready = _tables_or_scratch(buffers, prob_bits, alphabet, device, "lattice_rans fused forward")
     with torch.cuda.device(device):
         status = lib.ep_lattice_linear_forward(
             _native.ptr(payload), payload.numel(), _native.ptr(buffers.offsets), _native.ptr(buffers.states),
-            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), _native.ptr(buffers.scales), rows, cols, prob_bits,
-            info["tile_elements"], alphabet, _native.ptr(scratch), scratch_bytes, _native.ptr(x), _native.ptr(bias), tokens,
+            _native.ptr(buffers.stream_meta), _native.ptr(buffers.freq_tables), buffers.freq_tables.numel(), _native.ptr(buffers.scales),
+            rows, cols, prob_bits,
+            info["tile_elements"], alphabet, _native.ptr(scratch), scratch_bytes, ready, _native.ptr(x), _native.ptr(bias), tokens,
             _native.ptr(products), _native.ptr(out), _native.ptr(error), _native.stream_handle(device))
     _native.check(status, "lattice_rans fused forward")
     return out

@@ -40,6 +40,8 @@ extern "C" {
 #define EP_STREAM_UNDERRUN 2
 #define EP_STREAM_NOT_CONSUMED 3
 #define EP_STREAM_BAD_RAW_LENGTH 4
+#define EP_STREAM_BAD_SYMBOL 5   /* a decoded symbol that selects a table lies outside the tables (lossy: a coset above 1) */
+#define EP_KERNEL_TIMEOUT 9      /* a bounded wait inside a tensor-core product ran out; its output is incomplete */
 
 typedef void* ep_stream_t;
 
@@ -130,22 +132,39 @@ int ep_compact_streams(const uint16_t* scratch_dev, const uint32_t* offsets_dev,
 #define EP_STORE_U64 12
 #define EP_STORE_BOOL 13
 
-/* Bytes of table scratch ep_lattice_decode needs for a container: 0 when the slot tables fit in
- * shared memory (prob_bits <= 11, whatever the alphabets), else 17 * 2^prob_bits * 8. */
+/* Bytes of table scratch ep_lattice_decode needs for a container when it builds the slot tables itself
+ * (tables_ready = 0): 0 when they fit in shared memory (prob_bits <= 11, whatever the alphabets), else
+ * 17 * 2^prob_bits * 8. */
 int64_t ep_lattice_decode_scratch_bytes(int prob_bits, int max_alphabet);
+
+/* A container's slot tables, built once and kept by the caller for every later decode of that container
+ * -- the decode plan that the reference caches per container (entropack/schemes/lattice_rans/cuda.py:697-741).
+ * ep_lattice_slot_tables_bytes gives the size (17 * 2^prob_bits entries of 4, 5 or 8 bytes, by table
+ * layout), ep_lattice_build_slot_tables fills a 16-byte aligned device buffer of that size from the
+ * container's stream_meta and freq_tables (one small launch). Passing the buffer to ep_lattice_decode /
+ * ep_lattice_linear_forward as table_scratch_dev with tables_ready = 1 replaces the table build at the head
+ * of every decode (13 us at 4 bpp, 30 us with alphabets beyond 512) by a copy into shared memory. */
+int64_t ep_lattice_slot_tables_bytes(int prob_bits, int max_alphabet);
+int ep_lattice_build_slot_tables(const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev, int64_t freq_entries,
+                                 int prob_bits, int max_alphabet, void* slot_tables_dev, int64_t slot_tables_bytes,
+                                 ep_stream_t stream);
 
 /* Decode + reconstruct + container cast into output_dev[rows][cols] (cols = the padded column count
  * stored in the layout, a multiple of 8). Stands in for decode() of
  * entropack/schemes/lattice_rans/cuda.py:781-805 together with its host-side _decode_plan (:697-741)
- * and the e8_decode_vector_* kernels (lattice_rans.cu:732-1141): the slot tables are rebuilt on the
- * device from freq_tables, so there is no plan to cache. `max_alphabet` is the largest alphabet in
- * stream_meta (the caller reads that 17x4 buffer once). bf16 output saturates at the largest finite
- * value, as the reference's eager lane does. */
+ * and the e8_decode_vector_* kernels (lattice_rans.cu:732-1141). With tables_ready = 0 the slot tables
+ * are rebuilt on the device from freq_tables inside the call (table_scratch_dev is plain scratch, see
+ * ep_lattice_decode_scratch_bytes); with tables_ready = 1 table_scratch_dev holds tables that
+ * ep_lattice_build_slot_tables made for this container. `max_alphabet` is the largest alphabet in
+ * stream_meta (the caller reads that 17x4 buffer once); `freq_entries` is the length of freq_tables_dev
+ * and bounds every read of it, whatever the table records claim. bf16 output saturates at the largest
+ * finite value, as the reference's eager lane does. A coset symbol above 1 (only a corrupt coset table
+ * yields one) is decoded as 1 and reported as EP_STREAM_BAD_SYMBOL. */
 int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                       const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
-                      const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols, int prob_bits,
-                      int64_t tile_elements, int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes,
-                      int* error_dev, ep_stream_t stream);
+                      int64_t freq_entries, const float* scales_dev, void* output_dev, int store_kind, int64_t rows,
+                      int64_t cols, int prob_bits, int64_t tile_elements, int max_alphabet, void* table_scratch_dev,
+                      int64_t table_scratch_bytes, int tables_ready, int* error_dev, ep_stream_t stream);
 
 /* Fused forward of a lossy-coded bf16 layer for 1..4 tokens: y[t][r] = bf16(sum_c x[t][c] * W[r][c] + bias[r]) with
  * W the decoded weight rounded to bf16, which is never written out: the decode kernel multiplies every
@@ -157,10 +176,11 @@ int ep_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, const 
  * (entropack/linear/linear.py:125-130, 163-165) at decode-time batch sizes. */
 int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                               const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
-                              const float* scales_dev, int64_t rows, int64_t cols, int prob_bits, int64_t tile_elements,
-                              int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes, const void* x_dev,
-                              const void* bias_dev, int tokens, float* products_dev, void* y_dev, int* error_dev,
-                              ep_stream_t stream);
+                              int64_t freq_entries, const float* scales_dev, int64_t rows, int64_t cols, int prob_bits,
+                              int64_t tile_elements,
+                              int max_alphabet, void* table_scratch_dev, int64_t table_scratch_bytes, int tables_ready,
+                              const void* x_dev, const void* bias_dev, int tokens, float* products_dev, void* y_dev,
+                              int* error_dev, ep_stream_t stream);
 
 /* Same decode for callers that cannot allocate device memory when they need it -- for example a
  * serving process that has given all of HBM to its own pool, or code running inside an allocator
@@ -170,16 +190,19 @@ int ep_lattice_linear_forward(const uint16_t* payload_dev, int64_t payload_words
  *   - a container that needs the global-table path must have prob_bits <= 13
  *     (ep_lattice_decode_static_max_prob_bits()); larger ones return EP_ERR_TOO_LARGE. Containers whose
  *     tables fit in shared memory (prob_bits <= 11) are always accepted;
- *   - the first call on each device looks up the array's device address (no allocation, but a runtime
- *     query): make that first call outside any stream capture;
+ *   - the first call on each device looks up the array's device address (a runtime query), and if the
+ *     library's code has not been loaded onto that device yet, that first call is also when the CUDA
+ *     runtime loads it together with the fixed array: make that first call outside any stream capture
+ *     and before the host's own pool takes the rest of the device's memory;
  *   - every call on a device shares the one array. It is rewritten in full by each call that uses it,
  *     so stale contents never matter, but two such calls in flight at once on the same device
  *     (different streams or threads) race; serialise them. */
 int ep_lattice_decode_static_max_prob_bits(void);
 int ep_lattice_decode_static(const uint16_t* payload_dev, int64_t payload_words, const uint32_t* offsets_dev,
                              const uint32_t* states_dev, const int32_t* stream_meta_dev, const uint16_t* freq_tables_dev,
-                             const float* scales_dev, void* output_dev, int store_kind, int64_t rows, int64_t cols,
-                             int prob_bits, int64_t tile_elements, int max_alphabet, int* error_dev, ep_stream_t stream);
+                             int64_t freq_entries, const float* scales_dev, void* output_dev, int store_kind, int64_t rows,
+                             int64_t cols, int prob_bits, int64_t tile_elements, int max_alphabet, int* error_dev,
+                             ep_stream_t stream);
 
 /* --- encode. Work tensors are bf16 or fp32 [rows][cols], cols a multiple of 8 (is_bf16 selects);
  * quantised symbols travel as fields_dev int16[vectors][8] (z0..z6, m) and cosets_dev u8[vectors].

@@ -39,6 +39,24 @@ def test_decode_reference_bitstreams(name):
     assert _bytes(decoded) == record["decoded_bytes"].tobytes()
 
 
+@pytest.mark.parametrize("name", golden_names("lattice_"))
+def test_kept_slot_tables_decode_like_tables_built_in_the_kernel(name):
+    """The first decode of a container builds its slot tables inside the kernel; the second builds the copy that is
+    kept on the container (its decode plan) and every later one copies that in. All must give the reference's bytes."""
+    from entropack_b200.schemes.lattice_rans import b200
+
+    record = load_golden(f"lattice_{name}")
+    dtype = getattr(torch, str(record["dtype"]))
+    shape = tuple(int(v) for v in record["shape"])
+    device_buffers = _to_device(buffers_of(record))
+    for call in range(3):
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = b200.decode(device_buffers, shape=shape, dtype=dtype, error=error)
+        assert int(error.item()) == 0
+        assert _bytes(out[:, : shape[1]]) == record["decoded_bytes"].tobytes(), f"decode {call + 1} differs"
+        assert (getattr(device_buffers.layout, "_lattice_rans_slot_tables", None) is not None) == (call >= 1)
+
+
 # container dtype -> factor on the stored row scales that pushes the largest values past the type's range
 _CAST_CASES = {
     torch.float16: 3.0e5, torch.float32: 3000.0, torch.float8_e4m3fn: 3000.0, torch.float8_e5m2: 3.0e6, torch.int8: 3000.0,
@@ -140,6 +158,33 @@ def test_malformed_lossy_stream_is_reported():
     b200.decode(_to_device(bad), shape=tuple(int(v) for v in record["shape"]), dtype=torch.bfloat16, error=error)
     torch.cuda.synchronize()
     assert int(error.item()) in (2, 3)
+
+
+def test_coset_table_with_a_third_symbol_is_refused_and_cannot_steer_lookups_out_of_the_tables():
+    """A coset is 0 or 1. A crafted container whose coset table carries a third symbol fails validation; decoded anyway,
+    the kernel treats the symbol as 1, stays inside its tables, finishes, and reports the bad selector."""
+    from entropack_b200.schemes.lattice_rans import b200
+    from entropack_b200.schemes.lattice_rans.format import validate_packed
+
+    record = load_golden("lattice_bf16_4p0")
+    buffers = buffers_of(record)
+    shape = tuple(int(v) for v in record["shape"])
+    meta = buffers["stream_meta"].copy()
+    freq = buffers["freq_tables"].astype(np.uint16)
+    assert meta[0, 3] == 2 and freq[1] > 8
+    crafted = np.concatenate([[freq[0], freq[1] - 8, 8], freq[2:]]).astype(np.uint16)     # same total, one more symbol
+    meta[0, 3] = 3
+    meta[1:, 2] += 1
+    bad = dict(buffers, stream_meta=meta, freq_tables=crafted)
+    with pytest.raises(ValueError, match="coset"):
+        validate_packed({key: torch.from_numpy(np.ascontiguousarray(value)) for key, value in bad.items()}, shape, torch.bfloat16)
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = b200.decode(_to_device(bad), shape=shape, dtype=torch.bfloat16, error=error)
+    torch.cuda.synchronize()
+    assert int(error.item()) == 5      # EP_STREAM_BAD_SYMBOL
+    assert out.shape[0] == shape[0]
+    # the device is intact: the untouched container still decodes to the reference's bytes
+    assert _bytes(_gpu_decode(buffers, shape, torch.bfloat16)) == record["decoded_bytes"].tobytes()
 
 
 # ---- per-row rate-distortion refinement ------------------------------------------------------------------
