@@ -528,6 +528,9 @@ def measure_sharded_linear(ep, device, rank: int, world: int, reps: int) -> dict
         for _ in range(reps):
             dist.barrier()
             torch.cuda.synchronize(device)
+            # a spin of about a millisecond lets the host queue the whole call behind it, so that the events bracket
+            # device work only and not the Python time between the two records
+            torch.cuda._sleep(2_000_000)
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record(stream)
             fn()
@@ -548,16 +551,27 @@ def measure_sharded_linear(ep, device, rank: int, world: int, reps: int) -> dict
         with torch.no_grad():
             dense.weight.copy_((torch.randn(out_features, in_features, generator=generator, device=device) * 0.02).to(torch.bfloat16))
         x = torch.randn(tokens, in_features, generator=generator, device=device).to(torch.bfloat16)
-        layer = sharding.ColumnShardedLinear(dense, config=config)
+        layer = sharding.ColumnShardedLinear(dense, config=config, exchange="gather")
+        fused = sharding.ColumnShardedLinear(dense, config=config, exchange="auto")
+        fused.local = layer.local          # one compressed shard serves both
         with torch.no_grad():
             out = layer(x)
             local = layer.local(x).contiguous()
             staging = torch.empty((world, *local.shape), dtype=local.dtype, device=device)
             entry = {
                 "local_forward_us": timed(lambda: layer.local(x)),
-                "all_gather_us": timed(lambda: sharding.gather_columns(local, None, staging)),
-                "forward_us": timed(lambda: layer(x)),
+                "all_gather_us": timed(lambda: dist.all_gather_into_tensor(staging.view(world * local.shape[0], local.shape[1]), local)),
+                "all_gather_and_interleave_us": timed(lambda: sharding.gather_columns(local, None, staging)),
+                "forward_gather_us": timed(lambda: layer(x)),
             }
+            # the exchange folded into the product's epilogue: peer stores over NVLink + one bounded flag barrier
+            scattered = fused(x).clone()
+            fused.check()
+            entry["scatter_unavailable"] = fused.scatter_unavailable
+            if fused.scatter_unavailable is None:
+                entry["forward_scatter_us"] = timed(lambda: fused(x))
+                fused.check()
+                entry["scatter_matches_gather"] = bool(torch.equal(scattered.view(torch.int16), out.view(torch.int16)))
             # the same row shards, compressed and multiplied one after the other on this GPU
             pieces = []
             for r in range(world):
@@ -573,7 +587,7 @@ def measure_sharded_linear(ep, device, rank: int, world: int, reps: int) -> dict
                      all_gather_GBps_per_gpu=received / entry["all_gather_us"] / 1e3,
                      nvlink_frac_of_770=received / entry["all_gather_us"] / 1e3 / 770.0)
         results[f"{in_features}x{out_features}_M{tokens}"] = entry
-        del layer, dense, pieces, staging
+        del layer, fused, dense, pieces, staging
     return results
 
 

@@ -52,6 +52,8 @@ _PROTOTYPES = {
     "ep_dfloat11_chunk_bits": [_ptr, _i64, _ptr, _ptr, _ptr],
     "ep_dfloat11_pack": [_ptr, _i64, _ptr, _ptr, _ptr, ctypes.c_uint64, _i32, _i32, _i32, ctypes.c_uint32, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr],
     "ep_linear_forward": [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _i64, _ptr, _ptr],
+    "ep_linear_forward_scatter": [_ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i64, _i64, _i64, _ptr, _ptr],
+    "ep_peer_barrier": [_ptr, _i32, _i32, ctypes.c_uint32, _i64, _ptr, _ptr],
     "ep_linear_forward_fp8": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i64, _ptr, _ptr],
     "ep_quantize_rows_fp8": [_ptr, _i32, _i64, _i64, _ptr, _ptr, _ptr],
     "ep_linear_forward_int8": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _i32, _i64, _i64, _i64, _ptr, _ptr],

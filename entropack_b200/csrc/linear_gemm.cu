@@ -297,6 +297,8 @@ __device__ __forceinline__ uint64_t matrix_descriptor(uint32_t tile_address) {
   d |= static_cast<uint64_t>(2) << 61;            // 128-byte swizzle
   return d;
 }
+constexpr int kMaxOutputCopies = 7;   // peers of an eight-GPU node
+
 struct GemmParams {
   const __nv_bfloat16* bias;     // bf16 operands: optional bias in bf16
   __nv_bfloat16* y;
@@ -308,6 +310,13 @@ struct GemmParams {
   const float* bias_f32;
   float* y_f32;
   int pair_tile_n;               // two-block kernel: columns per tile (a multiple of 32, 64..256)
+  // Column-sharded output (bf16 results only): this product is columns y_col0 .. y_col0 + n of rows that are y_ld
+  // elements apart (0: the rows are n elements apart), and every tile is stored to y and to y_copy[0 .. y_copies) --
+  // the same rows in the other GPUs' output buffers, written with ordinary stores through peer mappings.
+  int64_t y_ld;
+  int y_col0;
+  int y_copies;
+  __nv_bfloat16* y_copy[kMaxOutputCopies];
 };
 
 // Loads 32 consecutive accumulator columns of this thread's TMEM lane and waits for them.
@@ -327,12 +336,22 @@ __device__ __forceinline__ void load_accumulator_chunk(uint32_t (&v)[32], uint32
 // caller has checked row < m and col < n). bf16 operands: + bias; 8-bit operands: accumulator * row scale *
 // column scale + bias. `staged_scale` / `staged_bias` point at the 32 columns' factors in shared memory (zero
 // outside the matrix), or are null, in which case the factors come from global memory.
-template <int OPERAND>
+// `scatter_stage` (per warp, 32 rows of kScatterRowPieces 16-byte pieces; may be null) is used for the copies into the
+// other GPUs' buffers: a thread holds 64 bytes of one row, and stored as they are, each store instruction would carry
+// 32 separate 16-byte pieces across NVLink. Staged through shared memory, four threads share a row and an instruction
+// carries eight contiguous 64-byte runs.
+constexpr int kScatterRowPieces = 5;   // four pieces of data, one of padding against bank conflicts
+
+template <int OPERAND, bool SCATTER = false>
 __device__ __forceinline__ void finish_chunk(uint32_t (&v)[32], const GemmParams& p, int row, int col, float row_scale,
-                                             const float* staged_scale, const float* staged_bias) {
+                                             const float* staged_scale, const float* staged_bias, uint4* scatter_stage = nullptr) {
   constexpr bool kScaled = OPERAND != kOperandBf16;
-  const bool whole = col + 32 <= p.n && (p.n & 7) == 0;
-  const int64_t at = static_cast<int64_t>(row) * p.n + col;
+  // the plain product (SCATTER false) knows nothing of row pitches, column offsets and copies
+  const int64_t ld = SCATTER && p.y_ld ? p.y_ld : p.n;
+  const int col0 = SCATTER ? p.y_col0 : 0;
+  const int copies = SCATTER ? p.y_copies : 0;
+  const bool whole = col + 32 <= p.n && ((ld | col0) & 7) == 0;
+  const int64_t at = static_cast<int64_t>(row) * ld + col0 + col;
   if (staged_bias != nullptr) {
     const float4* scales = reinterpret_cast<const float4*>(staged_scale);
     const float4* biases = reinterpret_cast<const float4*>(staged_bias);
@@ -379,18 +398,54 @@ __device__ __forceinline__ void finish_chunk(uint32_t (&v)[32], const GemmParams
       for (int c = 0; c < 32 && col + c < p.n; ++c) p.y_f32[at + c] = __uint_as_float(v[c]);
     }
   } else if (whole) {
+    uint32_t packed[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[j * 2]), __uint_as_float(v[j * 2 + 1]));
+      packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      uint32_t packed[4];
+      *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+    }
+    if (copies > 0 && scatter_stage == nullptr) {
+      for (int copy = 0; copy < copies; ++copy) {
+        __nv_bfloat16* const target = p.y_copy[copy] + at;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(v[g * 8 + j * 2]), __uint_as_float(v[g * 8 + j * 2 + 1]));
-        packed[j] = *reinterpret_cast<const uint32_t*>(&pair);
+        for (int g = 0; g < 4; ++g) {
+          *reinterpret_cast<uint4*>(target + g * 8) = make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+        }
       }
-      *reinterpret_cast<uint4*>(p.y + at + g * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    } else if (copies > 0) {
+      const uint32_t lane = lane_id();
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        scatter_stage[lane * kScatterRowPieces + g] = make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+      }
     }
   } else {
-    for (int c = 0; c < 32 && col + c < p.n; ++c) p.y[at + c] = __float2bfloat16_rn(__uint_as_float(v[c]));
+    for (int c = 0; c < 32 && col + c < p.n; ++c) {
+      const __nv_bfloat16 value = __float2bfloat16_rn(__uint_as_float(v[c]));
+      p.y[at + c] = value;
+      for (int copy = 0; copy < copies; ++copy) p.y_copy[copy][at + c] = value;
+    }
+  }
+}
+
+// Second half of the staged scatter, run by the whole warp: the 32 rows x 32 columns that finish_chunk left in
+// `scatter_stage` go to every copy, four threads to a row, rows past the matrix skipped.
+__device__ __forceinline__ void scatter_rows(const GemmParams& p, const uint4* scatter_stage, int first_row, int col, uint32_t lane) {
+  const int64_t ld = p.y_ld ? p.y_ld : p.n;
+  const int piece = static_cast<int>(lane & 3u);
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int in_tile = pass * 8 + static_cast<int>(lane >> 2);
+    const int row = first_row + in_tile;
+    if (row < p.m) {
+      const uint4 value = scatter_stage[in_tile * kScatterRowPieces + piece];
+      const int64_t at = static_cast<int64_t>(row) * ld + p.y_col0 + col + piece * 8;
+      for (int copy = 0; copy < p.y_copies; ++copy) *reinterpret_cast<uint4*>(p.y_copy[copy] + at) = value;
+    }
   }
 }
 
@@ -435,7 +490,7 @@ linear_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
   __shared__ __align__(8) uint64_t accumulator_ready[2];   // MMA -> epilogue, one per accumulator buffer
   __shared__ __align__(8) uint64_t accumulator_free[2];    // epilogue -> MMA
   __shared__ uint32_t tmem_base_holder;
-  __shared__ int failed;
+  __shared__ volatile int failed;   // polled by the other warps' loops: volatile, so the reads are not hoisted out of them
   // Per epilogue warp, the column factors of its share of the tile (half the columns; all 32 of the narrowest tile)
   // as fp32: [0] weight scale (8-bit operands), [1] bias; zero outside the matrix. Every thread of a warp needs all of them for its row, so they are read from global memory once per
   // warp and tile and then come from shared memory as broadcast 16-byte reads. (Wide tiles only: the narrow ones
@@ -671,7 +726,7 @@ __device__ __forceinline__ void commit_to_pair(uint64_t* bar) {
                ::"r"(shared_address(bar)), "h"(both) : "memory");
 }
 
-template <int OPERAND>
+template <int OPERAND, bool SCATTER = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
   constexpr uint32_t kInstruction = OPERAND == kOperandFp8 ? ((1u << 4) | kPairShapeBits)
@@ -686,8 +741,9 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
   __shared__ __align__(8) uint64_t accumulator_ready[2];     // in each block: this block's rows of the buffer are complete
   __shared__ __align__(8) uint64_t accumulator_free[2];      // used in the first block: both blocks have drained the buffer
   __shared__ uint32_t tmem_base_holder;
-  __shared__ int failed;
+  __shared__ volatile int failed;   // polled by the other warps' loops: volatile, so the reads are not hoisted out of them
   __shared__ __align__(16) float column_factors[kEpilogueWarps][2][kPairTileN / 2];
+  __shared__ __align__(16) uint4 scatter_stage[SCATTER ? kEpilogueWarps : 1][SCATTER ? 32 * kScatterRowPieces : 1];   // column-sharded output only
   uint8_t* tiles_a = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw_shared) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* tiles_b = tiles_a + kPairStages * kPairBytesA;
   const int warp = threadIdx.x >> 5;
@@ -831,9 +887,17 @@ linear_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
           }
         }
         const int col = n0 + chunk * 32;
+        // the copies of a whole, 16-byte aligned chunk leave through the warp's staging area (the same test as in finish_chunk)
+        const bool through_stage = SCATTER && p.y_copies > 0 && col + 32 <= p.n && (((p.y_ld ? p.y_ld : p.n) | p.y_col0) & 7) == 0;
         if (row < p.m && col < p.n) {
-          finish_chunk<OPERAND>(v, p, row, col, row_scale, staged ? &column_factors[member][0][(chunk - first_chunk) * 32] : nullptr,
-                                staged ? &column_factors[member][1][(chunk - first_chunk) * 32] : nullptr);
+          finish_chunk<OPERAND, SCATTER>(v, p, row, col, row_scale, staged ? &column_factors[member][0][(chunk - first_chunk) * 32] : nullptr,
+                                         staged ? &column_factors[member][1][(chunk - first_chunk) * 32] : nullptr,
+                                         through_stage ? scatter_stage[SCATTER ? member : 0] : nullptr);
+        }
+        if (through_stage) {
+          __syncwarp();
+          scatter_rows(p, scatter_stage[SCATTER ? member : 0], m0 + quadrant * 32, col, lane);
+          __syncwarp();
         }
       }
     }
@@ -951,7 +1015,7 @@ int resident_pairs() {
   return pairs;
 }
 
-template <int OPERAND>
+template <int OPERAND, bool SCATTER = false>
 int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& problem, int tile_n, int pairs, cudaStream_t s) {
   GemmParams p = problem;
   p.pair_tile_n = tile_n;
@@ -961,7 +1025,7 @@ int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& pro
   }
   const int64_t tiles = static_cast<int64_t>((p.n + tile_n - 1) / tile_n) * ((p.m + kPairTileM - 1) / kPairTileM);
   // per device, so on every launch (the occupancy query above ran on whichever device came first)
-  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_pair_kernel<OPERAND>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSharedBytes));
+  EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_pair_kernel<OPERAND, SCATTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSharedBytes));
   cudaLaunchAttribute attribute;
   attribute.id = cudaLaunchAttributeClusterDimension;
   attribute.val.clusterDim.x = 2;
@@ -974,7 +1038,7 @@ int launch_pair(const void* x_dev, const void* weight_dev, const GemmParams& pro
   config.stream = s;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  EP_CUDA_CHECK(cudaLaunchKernelEx(&config, linear_tcgen05_pair_kernel<OPERAND>, map_x, map_w, p));
+  EP_CUDA_CHECK(cudaLaunchKernelEx(&config, linear_tcgen05_pair_kernel<OPERAND, SCATTER>, map_x, map_w, p));
   return EP_OK;
 }
 
@@ -1032,6 +1096,27 @@ int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams
   return check_launch("linear_tcgen05_kernel");
 }
 
+// The column-sharded product: two-block tiles only (more than 128 rows of activations), tile width by the same cost.
+int launch_scatter(const void* x_dev, const void* weight_dev, const GemmParams& p, cudaStream_t s) {
+  const int pairs = p.m > kTileM ? resident_pairs<kOperandBf16>() : 0;
+  if (pairs < 1) return EP_ERR_UNSUPPORTED;
+  const int64_t row_pairs = (p.m + kPairTileM - 1) / kPairTileM;
+  int tile_n = kPairTileN;
+  int64_t best = -1;
+  for (int candidate = kPairTileN; candidate >= 64; candidate -= 32) {
+    const int64_t tiles = static_cast<int64_t>((p.n + candidate - 1) / candidate) * row_pairs;
+    const int64_t clocks = 2 * candidate > 256 + candidate ? 2 * candidate : 256 + candidate;
+    const int64_t cost = ((tiles + pairs - 1) / pairs) * clocks;
+    if (best < 0 || cost < best) {
+      best = cost;
+      tile_n = candidate;
+    }
+  }
+  const int rc = launch_pair<kOperandBf16, true>(x_dev, weight_dev, p, tile_n, pairs, s);
+  if (rc != EP_OK) return rc;
+  return check_launch("linear_tcgen05_pair_kernel (column-sharded)");
+}
+
 }  // namespace
 }  // namespace ep
 
@@ -1062,6 +1147,95 @@ extern "C" int ep_linear_forward(const void* x_dev, const void* weight_dev, cons
   p.k = ki;
   p.error = error_dev;
   return launch_best_tile<kOperandBf16>(x_dev, weight_dev, p, s);
+}
+
+extern "C" int ep_linear_forward_scatter(const void* x_dev, const void* weight_dev, const void* bias_dev, void* y_dev,
+                                         void* const* y_peers_host, int peers, int64_t y_ld, int64_t y_col0, int64_t m, int64_t n,
+                                         int64_t k, int* error_dev, ep_stream_t stream) {
+  if (!x_dev || !weight_dev || !y_dev || m <= 0 || n <= 0 || k <= 0 || (k & 7) != 0 || m > 0x7FFFFFFF || n > 0x7FFFFFFF ||
+      k > 0x7FFFFFFF || peers < 0 || peers > kMaxOutputCopies || (peers > 0 && !y_peers_host) || y_col0 < 0 || y_ld < y_col0 + n ||
+      y_ld > 0x7FFFFFFF) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  if (m <= kTileM) return EP_ERR_UNSUPPORTED;   // the two-block tensor-core kernel only: a few tokens' outputs are cheaper to gather
+  if ((reinterpret_cast<uintptr_t>(x_dev) & 15u) || (reinterpret_cast<uintptr_t>(weight_dev) & 15u) ||
+      (reinterpret_cast<uintptr_t>(y_dev) & 15u)) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  GemmParams p = {};
+  p.bias = static_cast<const __nv_bfloat16*>(bias_dev);
+  p.y = static_cast<__nv_bfloat16*>(y_dev);
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.error = error_dev;
+  p.y_ld = y_ld;
+  p.y_col0 = static_cast<int>(y_col0);
+  p.y_copies = peers;
+  for (int copy = 0; copy < peers; ++copy) {
+    if (!y_peers_host[copy] || (reinterpret_cast<uintptr_t>(y_peers_host[copy]) & 15u)) return EP_ERR_INVALID_ARGUMENT;
+    p.y_copy[copy] = static_cast<__nv_bfloat16*>(y_peers_host[copy]);
+  }
+  return launch_scatter(x_dev, weight_dev, p, static_cast<cudaStream_t>(stream));
+}
+
+// ---- barrier between the GPUs of a column-sharded layer ---------------------------------------------------------
+// Each rank owns a row of `world` 32-bit flags that its peers can write (a peer mapping of the same allocation on every
+// rank). Thread r of the one block tells peer r "rank `rank` has arrived at `epoch`" with a system-scope release store
+// into the peer's row and then polls its own row's slot r until that peer's arrival shows, for at most `timeout_ns`:
+// a peer that never arrives costs that long and an error word, never a hang.
+namespace ep {
+namespace {
+struct PeerBarrierParams {
+  uint32_t* flags[kMaxOutputCopies + 1];   // flags[r]: rank r's row, as mapped on this GPU
+  int rank;
+  int world;
+  uint32_t epoch;
+  unsigned long long timeout_ns;
+  int* error;
+};
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerBarrierParams p) {
+  const int peer = threadIdx.x;
+  if (peer >= p.world || peer == p.rank) return;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[peer] + p.rank), "r"(p.epoch) : "memory");
+  const uint32_t* mine = p.flags[p.rank] + peer;
+  unsigned long long begin, now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(begin));
+  for (;;) {
+    uint32_t seen;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(seen - p.epoch) >= 0) return;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    if (now - begin > p.timeout_ns) {
+      report(p.error, EP_KERNEL_TIMEOUT);
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+}  // namespace
+}  // namespace ep
+
+extern "C" int ep_peer_barrier(void* const* flag_rows_host, int rank, int world, uint32_t epoch, int64_t timeout_us, int* error_dev,
+                               ep_stream_t stream) {
+  if (!flag_rows_host || world < 1 || world > kMaxOutputCopies + 1 || rank < 0 || rank >= world || timeout_us <= 0 ||
+      timeout_us > 60 * 1000 * 1000) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
+  PeerBarrierParams p = {};
+  for (int r = 0; r < world; ++r) {
+    if (!flag_rows_host[r] || (reinterpret_cast<uintptr_t>(flag_rows_host[r]) & 3u)) return EP_ERR_INVALID_ARGUMENT;
+    p.flags[r] = static_cast<uint32_t*>(flag_rows_host[r]);
+  }
+  p.rank = rank;
+  p.world = world;
+  p.epoch = epoch;
+  p.timeout_ns = static_cast<unsigned long long>(timeout_us) * 1000ull;
+  p.error = error_dev;
+  if (world == 1) return EP_OK;
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("peer_barrier_kernel");
 }
 
 namespace {

@@ -7,9 +7,13 @@ work shards without any exchange on the data path:
 * :func:`compress_layers` compresses this rank's share (one process per GPU, ``torch.distributed`` only
   to learn rank and world size) and returns ``{layer index: CompressedTensor}``;
 * :class:`ColumnShardedLinear` keeps rows ``[rank * N / G, (rank + 1) * N / G)`` of a weight on each rank
-  (row scales and whole E8 vectors stay local) and all-gathers only the ``[M, N / G]`` outputs -- the one
-  collective of the package (NCCL over NVLink on GPUs).
+  (row scales and whole E8 vectors stay local) and exchanges only the ``[M, N / G]`` outputs -- the one
+  exchange of the package. Above 128 tokens on GPUs with peer access the exchange is folded into the product: the
+  tensor-core kernel's epilogue stores every finished tile into all ranks' ``[M, N]`` buffers (ordinary stores through
+  peer mappings of symmetric memory), followed by one bounded flag barrier; otherwise it is an NCCL all-gather.
 """
+import ctypes
+import os
 from dataclasses import dataclass
 
 import torch
@@ -145,18 +149,66 @@ def row_slice(out_features: int, rank: int, world: int) -> RowSlice:
     return RowSlice(rank * rows, (rank + 1) * rows)
 
 
+#: how long a rank waits at the barrier behind a scattered product for a peer that does not arrive, in microseconds
+PEER_BARRIER_TIMEOUT_US = 2_000_000
+
+
+class _PeerOutputs:
+    """Two ``[M, N]`` bf16 output buffers in symmetric memory (used alternately, so that a forward never writes into
+    rows a peer may still be reading from the forward before) and one row of arrival flags per rank, with every
+    rank's copies mapped into this process. Creating one is a collective over the group."""
+
+    def __init__(self, rows: int, cols: int, device: torch.device, group, rank: int, world: int):
+        # no multicast object is bound to these allocations: peers are reached with plain stores only
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symmetric_memory
+
+        group = dist.group.WORLD if group is None else group
+        self.rank, self.world = rank, world
+        self.buffers, self.handles, self.peer_pointers = [], [], []
+        for _ in range(2):
+            buffer = symmetric_memory.empty((rows, cols), dtype=torch.bfloat16, device=device)
+            handle = symmetric_memory.rendezvous(buffer, group)
+            peers = [int(handle.buffer_ptrs[r]) for r in range(world) if r != rank]
+            self.buffers.append(buffer)
+            self.handles.append(handle)
+            self.peer_pointers.append((ctypes.c_void_p * len(peers))(*peers))
+        self.flags = symmetric_memory.empty((max(world, 4),), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        torch.cuda.synchronize(device)
+        self.flag_handle = symmetric_memory.rendezvous(self.flags, group)
+        self.flag_rows = (ctypes.c_void_p * world)(*[int(self.flag_handle.buffer_ptrs[r]) for r in range(world)])
+        dist.barrier(group)      # every rank's flags are zero before anyone's first arrival is stored
+        self.epoch = 0
+        self.turn = 0
+
+
 class ColumnShardedLinear(torch.nn.Module):
     """A compressed linear whose output features are split over the ranks of a process group.
 
-    Each rank compresses and decodes only its own rows of the weight; activations are replicated; the
-    forward computes ``x @ W_rank^T`` locally and all-gathers the outputs."""
+    Each rank compresses and decodes only its own rows of the weight; activations are replicated; the forward
+    computes ``x @ W_rank^T`` locally and the ranks exchange the outputs. ``exchange="scatter"`` (tried first under
+    ``"auto"``) writes every output tile straight into all ranks' ``[M, N]`` buffers from the product's epilogue and
+    ends with one bounded barrier; it needs bf16 activations of more than 128 rows, the plain :class:`CompressedLinear`
+    and symmetric memory with peer access. ``exchange="gather"`` is the NCCL all-gather plus one interleaving copy.
+    A scattered forward returns a view of one of two alternating buffers, valid until the layer's next forward but one
+    (``copy_output=True`` returns a private copy instead). ``check()`` reads the layer's error word (a peer that did
+    not arrive, a wait that ran out inside the product) and raises."""
 
-    def __init__(self, linear: torch.nn.Linear, layer_cls=None, group=None, **layer_kwargs):
+    def __init__(self, linear: torch.nn.Linear, layer_cls=None, group=None, exchange: str = "auto", copy_output: bool = False,
+                 **layer_kwargs):
         super().__init__()
         from .linear import CompressedLinear
 
+        if exchange not in ("auto", "scatter", "gather"):
+            raise ValueError(f"exchange must be 'auto', 'scatter' or 'gather', got {exchange!r}")
         layer_cls = layer_cls or CompressedLinear
         self.group = group
+        self.exchange = exchange
+        self.copy_output = copy_output
+        self.scatter_unavailable = None if layer_cls is CompressedLinear else f"{layer_cls.__name__} has no scattered product"
+        self._peer_outputs: dict[int, _PeerOutputs] = {}
+        self._error = None
         rank, world = _rank_and_world(group)
         rows = row_slice(linear.out_features, rank, world)
         shard = torch.nn.Linear(linear.in_features, rows.end - rows.begin, bias=linear.bias is not None,
@@ -170,9 +222,61 @@ class ColumnShardedLinear(torch.nn.Module):
         self.local = layer_cls.from_linear(shard, **layer_kwargs)
         self._staging = None      # the all-gather's landing buffer, kept between calls of the same shape
 
+    def _scatter_applies(self, x: torch.Tensor, world: int) -> bool:
+        return (self.exchange != "gather" and self.scatter_unavailable is None and world > 1 and world <= 8 and x.is_cuda
+                and x.dtype == torch.bfloat16 and x.numel() // max(1, x.shape[-1]) > 128 and x.shape[-1] % 8 == 0
+                and (self.out_features // world) % 8 == 0 and not (torch.is_grad_enabled() and x.requires_grad))
+
+    def _scattered_forward(self, x: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+        from . import _native
+
+        flat = x.reshape(-1, x.shape[-1]).contiguous()
+        tokens = flat.shape[0]
+        outputs = self._peer_outputs.get(tokens)
+        if outputs is None:
+            outputs = self._peer_outputs[tokens] = _PeerOutputs(tokens, self.out_features, x.device, self.group, rank, world)
+        if self._error is None:
+            self._error = torch.zeros(1, dtype=torch.int32, device=x.device)
+        weight = self.local.dequantize(x.device)
+        bias = self.local._bias_on(x.device)
+        target = outputs.buffers[outputs.turn]
+        lib = _native.load()
+        columns = self.out_features // world
+        with torch.cuda.device(x.device):
+            stream = _native.stream_handle(x.device)
+            _native.check(lib.ep_linear_forward_scatter(
+                _native.ptr(flat), _native.ptr(weight), _native.ptr(None if bias is None else bias.contiguous()), target.data_ptr(),
+                outputs.peer_pointers[outputs.turn], world - 1, self.out_features, rank * columns, tokens, columns, flat.shape[1],
+                _native.ptr(self._error), stream), "scattered linear forward")
+            outputs.epoch += 1
+            _native.check(lib.ep_peer_barrier(outputs.flag_rows, rank, world, outputs.epoch & 0xFFFFFFFF, PEER_BARRIER_TIMEOUT_US,
+                                              _native.ptr(self._error), stream), "peer barrier")
+        outputs.turn ^= 1
+        result = target.clone() if self.copy_output else target
+        return result.reshape(*x.shape[:-1], self.out_features)
+
+    def check(self) -> None:
+        """Raise if a scattered forward of this layer reported a failure on the device (synchronises)."""
+        if self._error is not None:
+            code = int(self._error.item())
+            if code:
+                from . import _native
+
+                self._error.zero_()
+                _native.raise_stream_error(code, "column-sharded linear forward")
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        rank, world = _rank_and_world(self.group)
+        if self._scatter_applies(x, world):
+            try:
+                return self._scattered_forward(x, rank, world)
+            except (RuntimeError, ImportError, AttributeError) as error:
+                if self.exchange == "scatter":
+                    raise
+                # no symmetric memory or no peer access on this machine: every rank fails the same collective set-up the
+                # same way, and the layer gathers from here on
+                self.scatter_unavailable = f"{type(error).__name__}: {error}"
         local = self.local(x).contiguous()
-        _rank, world = _rank_and_world(self.group)
         shape = (world, *local.shape)
         if world > 1 and (self._staging is None or tuple(self._staging.shape) != shape or self._staging.dtype != local.dtype
                           or self._staging.device != local.device):

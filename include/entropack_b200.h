@@ -342,6 +342,26 @@ int ep_dfloat11_pack(const void* bf16_dev, int64_t n_elements, const int32_t* co
 int ep_linear_forward(const void* x_dev, const void* weight_dev, const void* bias_dev, void* y_dev, int64_t m, int64_t n,
                       int64_t k, int* error_dev, ep_stream_t stream);
 
+/* ep_linear_forward for a column-sharded layer, with the all-gather of the outputs folded into the epilogue: this
+ * rank's product is columns [y_col0, y_col0 + n) of output rows that are y_ld elements long, and every finished tile
+ * is stored to y_dev and, with ordinary stores through peer mappings, to the same place in each of the `peers`
+ * buffers of y_peers_host (a host array of device pointers: the other GPUs' output buffers as mapped on this GPU, at
+ * most 7). y_ld and y_col0 must be multiples of 8 for 16-byte stores (else element stores). The two-block tensor-core
+ * kernel only: m <= 128 returns EP_ERR_UNSUPPORTED (gather those few rows instead). The reference has no multi-GPU code; this is
+ * the NVLink half of CompressedLinear.forward (entropack/linear/linear.py:163-165) on a column shard. */
+int ep_linear_forward_scatter(const void* x_dev, const void* weight_dev, const void* bias_dev, void* y_dev,
+                              void* const* y_peers_host, int peers, int64_t y_ld, int64_t y_col0, int64_t m, int64_t n, int64_t k,
+                              int* error_dev, ep_stream_t stream);
+
+/* Barrier between the `world` GPUs (at most 8) that write into one another's buffers, as one small launch on `stream`:
+ * flag_rows_host[r] is rank r's row of `world` uint32 flags as mapped on this GPU (zero before the first use). The
+ * kernel stores `epoch` (use 1, 2, 3, ... per barrier) into slot `rank` of every peer's row with a system-scope
+ * release and polls slot r of its own row until peer r's epoch shows, for at most timeout_us microseconds; a peer
+ * that does not arrive in time sets *error_dev to EP_KERNEL_TIMEOUT and the kernel returns -- no trap, no endless
+ * wait. Stream order makes everything this rank launched before the barrier visible to the peers that pass it. */
+int ep_peer_barrier(void* const* flag_rows_host, int rank, int world, uint32_t epoch, int64_t timeout_us, int* error_dev,
+                    ep_stream_t stream);
+
 /* The 8-bit layer's product: y[m][n] = (x_codes[m][k] . weight_codes[n][k]^T) * x_scale[m] * weight_scale[n]
  * (+ bias[n], fp32), both code matrices fp8 e4m3, accumulation in fp32 on the tcgen05 kernel
  * (kind::f8f6f4), y written as bf16 (y_is_f32 = 0) or fp32. k must be a multiple of 16. Stands in for

@@ -126,3 +126,66 @@ def test_int8_gemm_is_the_exact_integer_product_scaled(m, n, k, out_dtype, with_
         exact = exact + bias.double()
     tolerance = 1e-6 if out_dtype is torch.float32 else 2.0 ** -8
     assert float((out.double() - exact).abs().max() / exact.abs().max()) <= tolerance
+
+
+def test_scattered_product_writes_its_columns_into_every_destination():
+    """ep_linear_forward_scatter on one GPU: the product lands in columns [col0, col0 + n) of rows that are ld elements
+    long, in the local destination and in a second one standing in for a peer's buffer; everything else stays as it was,
+    and the values equal ep_linear_forward's."""
+    import ctypes
+
+    from entropack_b200 import _native
+    from entropack_b200.linear import linear_forward
+
+    lib = _native.load()
+    generator = torch.Generator(device="cuda").manual_seed(17)
+    stream = torch.cuda.current_stream().cuda_stream
+    for tokens, columns, inner, ld, col0 in ((300, 480, 1024, 3840, 960), (4096, 256, 512, 1032, 8), (129, 72, 64, 100, 20), (1000, 200, 256, 404, 4)):
+        x = torch.randn(tokens, inner, generator=generator, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(columns, inner, generator=generator, device="cuda") * 0.05).to(torch.bfloat16)
+        bias = torch.randn(columns, generator=generator, device="cuda").to(torch.bfloat16)
+        expected = linear_forward(x, w, bias)
+        local = torch.full((tokens, ld), 7.0, dtype=torch.bfloat16, device="cuda")
+        peer = torch.full((tokens, ld), 7.0, dtype=torch.bfloat16, device="cuda")
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        peers = (ctypes.c_void_p * 1)(peer.data_ptr())
+        status = lib.ep_linear_forward_scatter(x.data_ptr(), w.data_ptr(), bias.data_ptr(), local.data_ptr(), peers, 1, ld, col0, tokens,
+                                               columns, inner, error.data_ptr(), stream)
+        assert status == 0, lib.ep_status_string(status)
+        torch.cuda.synchronize()
+        assert int(error.item()) == 0
+        for destination in (local, peer):
+            assert torch.equal(destination[:, col0:col0 + columns].view(torch.int16), expected.view(torch.int16))
+            untouched = torch.cat([destination[:, :col0], destination[:, col0 + columns:]], dim=1)
+            assert bool((untouched == 7.0).all())
+    few = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda")
+    assert lib.ep_linear_forward_scatter(few.data_ptr(), few.data_ptr(), None, out.data_ptr(), None, 0, 64, 0, 128, 64, 64, None, stream) == -2
+
+
+def test_peer_barrier_passes_on_arrival_and_gives_up_on_a_peer_that_never_arrives():
+    """The barrier's wait is bounded: with the peer's arrival already in this rank's flag row it returns at once and
+    leaves its own arrival in the peer's row; with a flag that nothing sets it gives up after the time limit, records
+    the timeout in the error word and returns -- the context stays usable."""
+    import ctypes
+    import time
+
+    from entropack_b200 import _native
+
+    lib = _native.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    mine = torch.zeros(4, dtype=torch.int32, device="cuda")      # rank 0's row
+    theirs = torch.zeros(4, dtype=torch.int32, device="cuda")    # rank 1's row, standing in for a peer mapping
+    rows = (ctypes.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    mine[1] = 5                                                   # the peer arrived at epoch 5 already
+    assert lib.ep_peer_barrier(rows, 0, 2, 5, 50_000, error.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    assert int(error.item()) == 0 and int(theirs[0].item()) == 5
+    begin = time.perf_counter()
+    assert lib.ep_peer_barrier(rows, 0, 2, 6, 20_000, error.data_ptr(), stream) == 0    # epoch 6 never comes: 20 ms limit
+    torch.cuda.synchronize()
+    assert time.perf_counter() - begin < 2.0
+    assert int(error.item()) == 9 and int(theirs[0].item()) == 6
+    assert torch.equal(mine.cpu(), torch.tensor([0, 5, 0, 0], dtype=torch.int32))
+    assert lib.ep_peer_barrier(rows, 0, 9, 1, 1000, None, stream) == -1 and lib.ep_peer_barrier(rows, 2, 2, 1, 1000, None, stream) == -1

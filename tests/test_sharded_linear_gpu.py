@@ -22,7 +22,7 @@ def _dense(device):
     with torch.no_grad():
         layer.weight.copy_((torch.randn(768, 1024, generator=g) * 0.02).to(torch.bfloat16))
         layer.bias.copy_(torch.randn(768, generator=g).to(torch.bfloat16))
-    x = torch.randn(48, 1024, generator=g).to(torch.bfloat16)
+    x = torch.randn(304, 1024, generator=g).to(torch.bfloat16)
     return layer.to(device), x.to(device)
 
 
@@ -36,9 +36,16 @@ def _worker(rank: int, world: int, port: int, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         dense, x = _dense(device)
-        layer = sharding.ColumnShardedLinear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
+        layer = sharding.ColumnShardedLinear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0), exchange="gather")
         out = layer(x)
         torch.cuda.synchronize()
+        # the same layer with the exchange folded into the product's epilogue (peer stores + bounded barrier), three
+        # forwards in a row so that both of its alternating output buffers and a reused one are read
+        fused = sharding.ColumnShardedLinear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0), exchange="auto")
+        scattered = [fused(x).clone() for _ in range(3)]
+        fused.check()
+        torch.cuda.synchronize()
+        results[f"scatter{rank}"] = (fused.scatter_unavailable, [bool(torch.equal(s.view(torch.int16), out.view(torch.int16))) for s in scattered])
         # what a single device computes for the same two row shards, each compressed on its own
         pieces = []
         for r in range(world):
@@ -63,7 +70,10 @@ def test_column_sharded_linear_all_gathers_outputs():
     mp.spawn(_worker, args=(world, _free_port(), results), nprocs=world, join=True)
     for rank in range(world):
         shape, identical, relative = results[rank]
-        assert shape == (48, 768) and identical and relative < 0.12
+        assert shape == (304, 768) and identical and relative < 0.12
+        unavailable, same = results[f"scatter{rank}"]
+        assert unavailable is None, f"the scattered exchange fell back to the all-gather: {unavailable}"
+        assert same == [True, True, True]
 
 
 def test_one_process_can_drive_the_product_on_two_devices():
