@@ -48,9 +48,22 @@ def _store_raw(tensor: torch.Tensor, requested: str, error: Exception) -> Compre
         buffers=get_scheme("raw").encode(tensor, RawConfig()), shape=tuple(tensor.shape), dtype=tensor.dtype)
 
 
-def decompress(compressed: CompressedTensor, config: CompressionConfig) -> torch.Tensor:
-    """Restore the dense tensor (container's shape and dtype, on the device holding its buffers)."""
+def decompress(compressed: CompressedTensor, config: CompressionConfig, *, check: bool = False) -> torch.Tensor:
+    """Restore the dense tensor (container's shape and dtype, on the device holding its buffers).
+
+    The decode kernels never fault on a malformed bitstream: they decode what they can and record what they saw in
+    an error word. ``check=True`` (not part of the reference's signature) passes such a word, waits for the decode
+    and raises ``ValueError`` if the kernels found bad stream offsets, a truncated or over-long payload or a corrupt
+    table; without it a damaged container decodes to garbage silently, as it does in the reference."""
     validate_config(config)
-    restored = compressed.scheme.decode(
-        compressed.buffers, shape=tuple(compressed.shape), dtype=compressed.encoded_dtype, config=config)
+    scheme = compressed.scheme
+    if not check or scheme.name == "raw":
+        restored = scheme.decode(compressed.buffers, shape=tuple(compressed.shape), dtype=compressed.encoded_dtype, config=config)
+        return restored.to(compressed.dtype)
+    from .. import _native
+
+    device = next(iter(compressed.buffers.values())).device
+    error = torch.zeros(1, dtype=torch.int32, device=device)
+    restored = scheme.decode(compressed.buffers, shape=tuple(compressed.shape), dtype=compressed.encoded_dtype, config=config, error=error)
+    _native.raise_stream_error(int(error.item()), f"{scheme.name} decode")
     return restored.to(compressed.dtype)

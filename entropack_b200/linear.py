@@ -8,8 +8,9 @@ state_dict written by either implementation loads into the other.
 
 Forward: the weight is decoded by the fused sm_100a decode kernel (entropy decode, dequantisation and
 the container cast in one pass, straight from the packed blob) into a dense operand that a GEMM consumes
-while it is still resident in the 126 MB L2. The INT8 layer's optional ConvRot rotation is not part of
-this package.
+while it is still resident in the 126 MB L2. The INT8 layer's optional ConvRot rotation runs on the
+library's butterfly kernel (``convrot.py``). Activations that are not bf16, and calls that need gradients,
+fall back to ``torch.nn.functional.linear`` on the decoded weight.
 """
 import dataclasses
 from numbers import Real
@@ -36,12 +37,42 @@ def _native_gemm_applies(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tens
             and x.shape[-1] % 8 == 0 and x.numel() > 0 and not (torch.is_grad_enabled() and x.requires_grad))
 
 
+#: one int32 error word per device, zeroed when it is made and handed to every product this module launches: a bounded
+#: wait that runs out inside a tensor-core kernel leaves its code there instead of passing unnoticed
+_error_words: dict[torch.device, torch.Tensor] = {}
+
+
+def kernel_error_word(device: torch.device) -> torch.Tensor:
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    word = _error_words.get(device)
+    if word is None:
+        word = _error_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return word
+
+
+def check_kernel_errors(device: torch.device | None = None) -> None:
+    """Read the error words of the products launched so far (``device``, or every device used) and raise if a kernel
+    reported a failure -- a wait inside a tensor-core product that ran out leaves an incomplete output. Reading the
+    word waits for the device, so this is for the end of a step or a test, not for every forward."""
+    for where, word in list(_error_words.items()):
+        if device is not None and torch.device(device) != where:
+            continue
+        code = int(word.item())
+        if code:
+            word.zero_()
+            _native.raise_stream_error(code, f"a product on {where}")
+
+
 def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                    error: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T + bias`` in bf16 through ``ep_linear_forward`` (CUDA-core kernel for up to 16 tokens,
-    tcgen05 tensor-core kernel above)."""
+    tcgen05 tensor-core kernel above). ``error`` defaults to the device's shared error word (``check_kernel_errors``)."""
     flat = x.reshape(-1, x.shape[-1]).contiguous()
     weight = weight.contiguous()
+    if error is None:
+        error = kernel_error_word(x.device)
     out = torch.empty((flat.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
         status = _native.load().ep_linear_forward(
@@ -415,7 +446,7 @@ class QuantizedLinear(CompressedLinear):
             status = getattr(_native.load(), self.gemm_entry)(
                 _native.ptr(activation), _native.ptr(codes), _native.ptr(activation_scale), _native.ptr(weight_scale),
                 _native.ptr(bias32), _native.ptr(out), int(out.dtype == torch.float32), activation.shape[0], codes.shape[0],
-                activation.shape[1], None, _native.stream_handle(codes.device))
+                activation.shape[1], _native.ptr(kernel_error_word(codes.device)), _native.stream_handle(codes.device))
         _native.check(status, "8-bit linear forward")
         return out if direct else out.to(out_dtype)
 
@@ -468,4 +499,4 @@ class CompressedINT8Linear(QuantizedLinear):
     gemm_entry = "ep_linear_forward_int8"
 
 
-__all__ = ["CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "QuantizedLinear"]
+__all__ = ["CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "QuantizedLinear", "check_kernel_errors"]

@@ -32,13 +32,14 @@ class DFloat11Scheme(Scheme):
 
         parse_layout_cached(buffers["layout"])
 
-    def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: DFloat11Config) -> torch.Tensor:
+    def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: DFloat11Config,
+               error: torch.Tensor | None = None) -> torch.Tensor:
         buffers = packed_buffers(packed, DFloat11Buffers)
         source = buffers.layout.device
         lane, run_on = self.lane_for(buffers.layout, config.execution_backend, gate_dtype=False)
         if source != run_on:
             buffers = DFloat11Buffers._make(value.to(run_on) for value in buffers)
-        out = lane.decode(buffers).reshape(shape)
+        out = lane.decode(buffers, error=error).reshape(shape)
         return out if out.device == source else out.to(source)
 
 

@@ -22,6 +22,14 @@ def decode(buffers: DFloat11Buffers, *, error: torch.Tensor | None = None) -> to
     _native.require_cuda(sign_mantissa)
     bpt, tpb, widest = parse_layout_cached(buffers.layout)
     n = sign_mantissa.numel()
+    # the kernel indexes the position and region records by block: their lengths are checked here, on the host, for free
+    blocks = -(-buffers.encoded_exponent.numel() // (bpt * tpb))
+    if buffers.output_positions.numel() != blocks + 1:
+        raise ValueError(f"dfloat11 output_positions hold {buffers.output_positions.numel()} entries, the layout needs {blocks + 1}")
+    if buffers.thread_meta.numel() != blocks * tpb:
+        raise ValueError(f"dfloat11 thread_meta holds {buffers.thread_meta.numel()} entries, the layout needs {blocks * tpb}")
+    if buffers.luts.ndim != 2 or buffers.luts.shape[1] != 256 or buffers.luts.shape[0] < 2:
+        raise ValueError(f"dfloat11 luts must be [levels + 1, 256], got {tuple(buffers.luts.shape)}")
     out = torch.empty(n, dtype=torch.bfloat16, device=sign_mantissa.device)
     with torch.cuda.device(sign_mantissa.device):
         status = _native.load().ep_dfloat11_decode(

@@ -47,14 +47,15 @@ class LatticeRANSScheme(Scheme):
         cached_parse(buffers["layout"], parse_layout, "_lattice_rans_layout")
         max_alphabet(packed_buffers(buffers, LatticeBuffers))
 
-    def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: EntroPackLossyConfig) -> torch.Tensor:
+    def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: EntroPackLossyConfig,
+               error: torch.Tensor | None = None) -> torch.Tensor:
         buffers = packed_buffers(packed, LatticeBuffers)
         source = buffers.layout.device
         lane, run_on = self.lane_for(buffers.layout, config.execution_backend, gate_dtype=False)
         if source != run_on:
             buffers = LatticeBuffers._make(value.to(run_on) for value in buffers)
         out = lane.decode(buffers, shape=shape, dtype=dtype, threads_per_block=config.threads_per_block,
-                          l2_prefetch=config.l2_prefetch)
+                          l2_prefetch=config.l2_prefetch, error=error)
         if shape and tuple(out.shape) != tuple(shape):
             out = out[: shape[0], : shape[1]]
         return out if out.device == source else out.to(source)

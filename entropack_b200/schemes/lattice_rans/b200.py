@@ -69,6 +69,20 @@ def _tables_or_scratch(buffers: LatticeBuffers, prob_bits: int, alphabet: int, d
     return scratch, scratch_bytes, 0
 
 
+def _check_lengths(buffers: LatticeBuffers, info: dict) -> None:
+    """The kernels index offsets, states, scales and the table records by tile, row and table: their lengths are checked
+    here, on the host, without reading anything back from the device."""
+    tiles, rows = info["total_tiles"], info["rows"]
+    if buffers.offsets.numel() != tiles + 1:
+        raise ValueError(f"lattice_rans offsets hold {buffers.offsets.numel()} entries, the layout needs {tiles + 1}")
+    if buffers.states.numel() != tiles * 32:
+        raise ValueError(f"lattice_rans states hold {buffers.states.numel()} words, the layout needs {tiles * 32}")
+    if buffers.scales.numel() != rows:
+        raise ValueError(f"lattice_rans scales hold {buffers.scales.numel()} entries for {rows} rows")
+    if buffers.stream_meta.numel() != 17 * 4:
+        raise ValueError(f"lattice_rans stream_meta holds {buffers.stream_meta.numel()} entries instead of 17 x 4")
+
+
 def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_block=None, l2_prefetch=True,
            error: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """Decode to ``[rows, cols_padded]`` of ``dtype`` on the buffers' device (one or two launches, no host sync
@@ -82,6 +96,7 @@ def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_bl
     out_dtype = torch.float32 if via_float else dtype
     if out is None:
         out = torch.empty((rows, cols), dtype=out_dtype, device=device)
+    _check_lengths(buffers, info)
     alphabet = max_alphabet(buffers)
     lib = _native.load()
     scratch, scratch_bytes, ready = _tables_or_scratch(buffers, prob_bits, alphabet, device, "lattice_rans decode")
@@ -117,6 +132,7 @@ def linear_forward(buffers: LatticeBuffers, *, shape, x: torch.Tensor, bias: tor
     bias = None if bias is None else bias.to(torch.bfloat16).contiguous()
     products = torch.empty(tokens * rows + 1, dtype=torch.float32, device=device)   # accumulators + the kernel's block counter
     out = torch.empty((tokens, rows), dtype=torch.bfloat16, device=device)
+    _check_lengths(buffers, info)
     alphabet = max_alphabet(buffers)
     lib = _native.load()
     scratch, scratch_bytes, ready = _tables_or_scratch(buffers, prob_bits, alphabet, device, "lattice_rans fused forward")

@@ -76,13 +76,14 @@ class TileANSScheme(Scheme):
             return None
         return TileStreamingPlan(self, packed, dtype)
 
-    def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: TileANSConfig) -> torch.Tensor:
+    def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: TileANSConfig,
+               error: torch.Tensor | None = None) -> torch.Tensor:
         buffers = packed_buffers(packed, TileBuffers)
         source = buffers.layout.device
         lane, run_on = self.lane_for(buffers.layout, config.execution_backend, gate_dtype=False)
         if source != run_on:
             buffers = TileBuffers._make(value.to(run_on) for value in buffers)
-        out = lane.decode(buffers, dtype=dtype, threads_per_block=config.threads_per_block).reshape(shape)
+        out = lane.decode(buffers, dtype=dtype, threads_per_block=config.threads_per_block, error=error).reshape(shape)
         return out if out.device == source else out.to(source)
 
 

@@ -41,7 +41,16 @@ def decode(buffers: TileBuffers, *, dtype: torch.dtype, threads_per_block: int |
         out = torch.empty(num_elements * num_lanes, dtype=torch.uint8, device=payload.device)
     elif out.dtype != torch.uint8 or out.numel() != num_elements * num_lanes or not out.is_contiguous() or out.device != payload.device:
         raise ValueError(f"tile_ans decode needs a contiguous uint8 output of {num_elements * num_lanes} bytes on {payload.device}")
-    first, count = (0, num_tiles(num_elements, tile_elements)) if tiles is None else tiles
+    total_tiles = num_tiles(num_elements, tile_elements)
+    first, count = (0, total_tiles) if tiles is None else tiles
+    # the kernels index offsets and states by tile and lane: their lengths are checked here, on the host, for free
+    coded_lanes = int((modes == 0).sum())
+    if buffers.offsets.numel() != total_tiles * num_lanes + 1:
+        raise ValueError(f"tile_ans offsets hold {buffers.offsets.numel()} entries, the layout needs {total_tiles * num_lanes + 1}")
+    if buffers.states.numel() != total_tiles * coded_lanes * NUM_STATES:
+        raise ValueError(f"tile_ans states hold {buffers.states.numel()} words, the layout needs {total_tiles * coded_lanes * NUM_STATES}")
+    if buffers.decode_tables.numel() != num_lanes << prob_bits:
+        raise ValueError(f"tile_ans decode_tables hold {buffers.decode_tables.numel()} entries, the layout needs {num_lanes << prob_bits}")
     with torch.cuda.device(payload.device):
         status = _native_lib().ep_tile_ans_decode_tiles(
             _native.ptr(payload), payload.numel(), _native.ptr(buffers.offsets), _native.ptr(buffers.states),

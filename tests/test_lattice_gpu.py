@@ -160,6 +160,32 @@ def test_malformed_lossy_stream_is_reported():
     assert int(error.item()) in (2, 3)
 
 
+def test_checked_decompress_raises_on_a_damaged_container_and_lanes_check_buffer_lengths():
+    """``decompress(..., check=True)`` reads the kernels' error word and raises; the unchecked call decodes the same
+    container silently, as the reference does. Buffers that are too short for the layout are refused on the host."""
+    import entropack_b200 as ep
+    from entropack_b200.schemes.lattice_rans import b200
+
+    weight = _weights(96, 512, 5, 2).cuda()
+    config = ep.EntroPackLossyConfig(target_bpp=4.0)
+    compressed = ep.compress(weight, config)
+    good = ep.decompress(compressed, config, check=True)
+    assert torch.equal(good.view(torch.int16), ep.decompress(compressed, config).view(torch.int16))
+    damaged = ep.compress(weight, config)
+    damaged.buffers["states"].view(torch.int32)[0, 3] ^= 0x1234
+    ep.decompress(damaged, config)                      # silent
+    with pytest.raises(ValueError, match="payload"):
+        ep.decompress(damaged, config, check=True)
+    record = load_golden("lattice_bf16_4p0")
+    buffers = buffers_of(record)
+    shape = tuple(int(v) for v in record["shape"])
+    for key in ("offsets", "states", "scales"):
+        short = dict(buffers)
+        short[key] = buffers[key].reshape(-1)[:-1].copy() if key != "states" else buffers[key][:-1].copy()
+        with pytest.raises(ValueError, match=key):
+            b200.decode(_to_device(short), shape=shape, dtype=torch.bfloat16)
+
+
 def test_coset_table_with_a_third_symbol_is_refused_and_cannot_steer_lookups_out_of_the_tables():
     """A coset is 0 or 1. A crafted container whose coset table carries a third symbol fails validation; decoded anyway,
     the kernel treats the symbol as 1, stays inside its tables, finishes, and reports the bad selector."""
