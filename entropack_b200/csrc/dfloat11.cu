@@ -24,10 +24,11 @@ namespace {
 
 constexpr int kMaxLevels = 64;
 constexpr uint32_t kPointerFlag = 0x8000u;
-// Multi-symbol table: indexed by the next kMultiBits bits of the stream, an entry holds up to three whole codewords that
-// fit in those bits: symbols in bytes 0-2, their total length in bits 24-27, their number in bits 28-29 (0: the first
-// codeword is longer than the window, take the one-symbol path). Exponent codes average under three bits, so most
-// look-ups deliver three symbols.
+// Multi-symbol table: indexed by the next kMultiBits bits of the stream, a 64-bit entry holds up to three whole codewords
+// that fit in those bits: .x = symbols in bytes 0-2 and their number in bits 24-25 (0: the first codeword is longer than
+// the window, take the one-symbol path), .y = the bits consumed after one, two and three of them in bytes 0-2. A thread
+// with fewer symbols left than the entry holds takes only those and advances by their length, so the end of a region
+// needs no path of its own. Exponent codes average under three bits, so most look-ups deliver three symbols.
 constexpr int kMultiBits = 10;
 constexpr int kMultiEntries = 1 << kMultiBits;
 constexpr int kMaxFormatBlocks = 4;   // blocks of the format served by one CUDA block, at most
@@ -67,8 +68,8 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   //         per group: stream words u32[block_words] | exponents u8[stage_bytes]
   const int levels = p.num_luts - 1;
   uint16_t* const tables = reinterpret_cast<uint16_t*>(shared);
-  uint32_t* const multi = shared + levels * 128;
-  uint32_t* const scan_base = multi + kMultiEntries;
+  uint2* const multi = reinterpret_cast<uint2*>(shared + ((levels * 128 + 1) & ~1));     // 8-byte aligned
+  uint32_t* const scan_base = reinterpret_cast<uint32_t*>(multi + kMultiEntries);
   const int block_bytes = p.bytes_per_thread * p.threads_per_block;
   const int block_words = ((block_bytes + 3) / 4 + 3) & ~1;  // two look-ahead words, even count keeps what follows 8-byte aligned
   const int stage_bytes = (p.stage_elems + 16 + 15) & ~15;
@@ -107,7 +108,7 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
 
   __syncthreads();   // level-0 entries are in place
   for (int v = threadIdx.x; v < kMultiEntries; v += blockDim.x) {
-    uint32_t packed = 0, used = 0, found = 0;
+    uint32_t packed = 0, lengths = 0, used = 0, found = 0;
     while (found < 3u) {
       const uint32_t rest = (static_cast<uint32_t>(v) << used) & (kMultiEntries - 1);      // bits not yet consumed, left-aligned
       const uint32_t entry = tables[rest >> (kMultiBits - 8)];
@@ -115,9 +116,10 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
       if ((entry & kPointerFlag) || length == 0u || used + length > static_cast<uint32_t>(kMultiBits)) break;
       packed |= (entry & 0xFFu) << (8 * found);
       used += length;
+      lengths |= used << (8 * found);
       ++found;
     }
-    multi[v] = packed | (used << 24) | (found << 28);
+    multi[v] = make_uint2(packed | (found << 24), lengths);
   }
   const bool active = present && member < p.threads_per_block;
   const int64_t region = format_block * p.threads_per_block + member;
@@ -172,15 +174,15 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   uint32_t next = words[min(word_index + 1, static_cast<uint32_t>(block_words - 1))];
   for (int i = 0; i < count;) {
     const uint32_t window = __funnelshift_l(next, current, bit & 31u);
-    // three or more symbols to go: whatever the window's first bits hold whole may be taken at once
-    const uint32_t fast = count - i >= 3 ? multi[window >> (32 - kMultiBits)] : 0u;
-    const uint32_t found = fast >> 28;
+    // whatever whole codewords the window's first bits hold are taken at once, as many as this region still wants
+    const uint2 fast = multi[window >> (32 - kMultiBits)];
+    const uint32_t found = min(fast.x >> 24, static_cast<uint32_t>(count - i));
     if (found) {
-      exponents[local_base + i] = static_cast<uint8_t>(fast);
-      if (found > 1u) exponents[local_base + i + 1] = static_cast<uint8_t>(fast >> 8);
-      if (found > 2u) exponents[local_base + i + 2] = static_cast<uint8_t>(fast >> 16);
+      exponents[local_base + i] = static_cast<uint8_t>(fast.x);
+      if (found > 1u) exponents[local_base + i + 1] = static_cast<uint8_t>(fast.x >> 8);
+      if (found > 2u) exponents[local_base + i + 2] = static_cast<uint8_t>(fast.x >> 16);
       i += static_cast<int>(found);
-      bit += (fast >> 24) & 0xFu;
+      bit += (fast.y >> (8u * found - 8u)) & 0xFFu;
     } else {
       uint32_t entry = tables[window >> 24];
       uint32_t peek = window;
@@ -459,7 +461,7 @@ extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const u
   const int threads = (threads_per_block + 31) / 32 * 32;
   const size_t block_words = ((block_bytes + 3) / 4 + 3) & ~size_t(1);
   const size_t stage_bytes = (static_cast<size_t>(max_block_elems) + 16 + 15) & ~size_t(15);
-  const size_t fixed = static_cast<size_t>(num_luts - 1) * 512 + kMultiEntries * 4 + kMaxFormatBlocks * 32 * 4;
+  const size_t fixed = ((static_cast<size_t>(num_luts - 1) * 512 + 7) & ~size_t(7)) + kMultiEntries * 8 + kMaxFormatBlocks * 32 * 4;
   const size_t per_group = block_words * 4 + stage_bytes;
   int groups = kMaxFormatBlocks;
   while (groups > 1 && (threads * groups > 1024 || fixed + groups * per_group > 48 * 1024 || blocks < groups)) groups >>= 1;

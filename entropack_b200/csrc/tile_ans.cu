@@ -79,13 +79,13 @@ __device__ __forceinline__ void stage_decode_tables(const DecodeParams& p, uint3
       // four entries per load and store (the table has at least 512 entries)
       const uint4* source4 = reinterpret_cast<const uint4*>(source);
       uint4* staged4 = reinterpret_cast<uint4*>(staged);
-      for (uint32_t quad = threadIdx.x; quad < table_size / 4; quad += kThreads) {
+      for (uint32_t quad = threadIdx.x; quad < table_size / 4; quad += blockDim.x) {
         const uint4 e = __ldg(source4 + quad);
         const uint32_t slot = quad * 4;
         staged4[quad] = make_uint4(repack(e.x, slot), repack(e.y, slot + 1), repack(e.z, slot + 2), repack(e.w, slot + 3));
       }
     } else {
-      for (uint32_t slot = threadIdx.x; slot < table_size; slot += kThreads) staged[slot] = repack(source[slot], slot);
+      for (uint32_t slot = threadIdx.x; slot < table_size; slot += blockDim.x) staged[slot] = repack(source[slot], slot);
     }
   }
   __syncthreads();
@@ -202,6 +202,10 @@ __global__ void __launch_bounds__(kThreads) tile_ans_decode_simple_kernel(const 
 // ------------------------------------------------------------------------------------------------
 constexpr int kBlockElems = 512;   // elements staged per warp between merges (16 groups of 32)
 constexpr int kDecodeBlocksPerSm = 7;   // 56 warps of 32 registers: a tensor of 8192 tiles is resident all at once
+// The other block shape: 14 warps, four blocks to an SM (the same 56 resident warps). Four table copies instead of
+// seven leave room for the 256-word ring chunks at every probability width, and a block's table is staged for 14 tiles.
+constexpr int kByteWarps = 14;
+constexpr int kByteBlocksPerSm = 4;
 // State of one coded byte lane of the tile a warp is decoding.
 struct CodedLane {
   uint32_t state;       // this thread's rANS state
@@ -215,11 +219,13 @@ struct CodedLane {
 
 // RAW_MASK >= 0 fixes the lane pattern at compile time (dead per-lane state disappears from the register file);
 // RAW_MASK < 0 reads it from the parameters. CHUNK_LOG picks the ring: 256-word chunks (upkeep every eight steps)
-// where seven blocks' shared memory still fits an SM, 128-word chunks otherwise.
-template <int NLANES, int RAW_MASK, int CHUNK_LOG>
-__global__ void __launch_bounds__(kThreads, (NLANES <= 2 || (NLANES == 4 && RAW_MASK == 7)) ? kDecodeBlocksPerSm : (NLANES == 4 ? 3 : 1))
+// where shared memory has the room, 128-word chunks otherwise. WARPS: eight warps to a block and seven blocks to an SM,
+// or fourteen and four (the same 56 resident warps with four table copies instead of seven).
+template <int NLANES, int RAW_MASK, int CHUNK_LOG, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, (NLANES <= 2 || (NLANES == 4 && RAW_MASK == 7)) ? 56 / WARPS : (NLANES == 4 && WARPS == 8 ? 3 : 1))
 tile_ans_decode_kernel(const DecodeParams p) {
   using Ring = WordRing<CHUNK_LOG>;
+  constexpr int kWarps = WARPS;     // shadows the file-wide block shape of the other kernels
   extern __shared__ __align__(16) uint32_t shared_tables[];
   __shared__ int constant_symbol[kMaxLanes];
   __shared__ uint32_t raw_begins[kWarps][kMaxLanes];
@@ -511,7 +517,7 @@ __device__ __forceinline__ void store_low_byte(uint8_t* base, uint32_t value) {
 }
 
 template <int CHUNK_LOG>
-__global__ void __launch_bounds__(kThreads, kDecodeBlocksPerSm) tile_ans_decode_bytes_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kByteWarps * 32, kByteBlocksPerSm) tile_ans_decode_bytes_kernel(const DecodeParams p) {
   using Ring = WordRing<CHUNK_LOG>;
   static_assert(Ring::kStepsPerUpkeep == 4 || Ring::kStepsPerUpkeep == 8, "runs are written out for four or eight steps");
   extern __shared__ __align__(16) uint32_t shared_tables[];
@@ -520,7 +526,7 @@ __global__ void __launch_bounds__(kThreads, kDecodeBlocksPerSm) tile_ans_decode_
   stage_decode_tables<1>(p, shared_tables, constant_symbol);
 
   const int warp = threadIdx.x >> 5;
-  const int64_t tile = p.first_tile + static_cast<int64_t>(blockIdx.x) * kWarps + warp;
+  const int64_t tile = p.first_tile + static_cast<int64_t>(blockIdx.x) * kByteWarps + warp;
   if (tile >= p.tile_end) return;
   const uint32_t lane = lane_id();
   const uint32_t mask_ge = lanemask_ge();
@@ -846,56 +852,60 @@ int allow_shared(Kernel kernel, size_t bytes) {
 
 // Shared memory of one block of the staged decoder.
 template <int CHUNK_LOG>
-size_t staged_shared_bytes(size_t table_bytes, int ans_lanes) {
+size_t staged_shared_bytes(size_t table_bytes, int ans_lanes, int warps) {
   const size_t per_warp_lane = WordRing<CHUNK_LOG>::kBytes + kBlockElems;
   // one ring's worth of padding lets the kernel align the rings to their own size
-  return table_bytes + WordRing<CHUNK_LOG>::kBytes + static_cast<size_t>(kWarps) * ans_lanes * per_warp_lane;
+  return table_bytes + WordRing<CHUNK_LOG>::kBytes + static_cast<size_t>(warps) * ans_lanes * per_warp_lane;
 }
 
-template <int NLANES, int RAW_MASK, int CHUNK_LOG>
-int launch_staged(const DecodeParams& p, dim3 grid, size_t shared, cudaStream_t stream) {
-  const int rc = allow_shared(tile_ans_decode_kernel<NLANES, RAW_MASK, CHUNK_LOG>, shared);
+template <int NLANES, int RAW_MASK, int CHUNK_LOG, int WARPS>
+int launch_staged(const DecodeParams& p, size_t shared, cudaStream_t stream) {
+  const int rc = allow_shared(tile_ans_decode_kernel<NLANES, RAW_MASK, CHUNK_LOG, WARPS>, shared);
   if (rc != EP_OK) return rc;
-  tile_ans_decode_kernel<NLANES, RAW_MASK, CHUNK_LOG><<<grid, kThreads, shared, stream>>>(p);
+  const int64_t tiles = p.tile_end - p.first_tile;
+  const dim3 grid(static_cast<unsigned>((tiles + WARPS - 1) / WARPS));
+  tile_ans_decode_kernel<NLANES, RAW_MASK, CHUNK_LOG, WARPS><<<grid, WARPS * 32, shared, stream>>>(p);
   return EP_OK;
 }
 
-// kDecodeBlocksPerSm blocks of `bytes` shared memory each fit one SM (227 KB, 1 KB of it reserved per block, plus the
-// kernels' few static words)
-inline bool fits_all_blocks(size_t bytes) { return (bytes + 1024 + 64) * kDecodeBlocksPerSm <= 227 * 1024; }
+// `blocks` blocks of `bytes` shared memory each fit one SM (227 KB, 1 KB of it reserved per block, plus the kernels'
+// static words)
+inline bool fits_sm(size_t bytes, int blocks) { return (bytes + 1024 + 512) * blocks <= 227 * 1024; }
+
+// Block shape and ring of the staged decoder for one lane pattern: fourteen warps and 256-word chunks where four such
+// blocks fit an SM, else eight warps with 256-word chunks where seven fit, else eight warps and 128-word chunks.
+// Four-byte elements measured no better with the wider chunks and keep eight warps and 128 words.
+template <int NLANES, int RAW_MASK>
+int launch_staged_shape(const DecodeParams& p, size_t table_bytes, cudaStream_t stream) {
+  const int lanes = p.lanes.ans_lanes;
+  if (NLANES <= 2) {
+    const size_t big = staged_shared_bytes<8>(table_bytes, lanes, kByteWarps);
+    if (fits_sm(big, kByteBlocksPerSm)) return launch_staged<NLANES, RAW_MASK, 8, kByteWarps>(p, big, stream);
+    const size_t wide = staged_shared_bytes<8>(table_bytes, lanes, kWarps);
+    if (fits_sm(wide, kDecodeBlocksPerSm)) return launch_staged<NLANES, RAW_MASK, 8, kWarps>(p, wide, stream);
+  }
+  return launch_staged<NLANES, RAW_MASK, 7, kWarps>(p, staged_shared_bytes<7>(table_bytes, lanes, kWarps), stream);
+}
 
 template <int NLANES>
 int launch_decode(const DecodeParams& p, dim3 grid, size_t table_bytes, bool staged, cudaStream_t stream) {
   if (staged && NLANES == 1 && p.lanes.raw_mask == 0u && p.tile_elements % 32 == 0) {
-    // one coded byte lane in tiles of whole 32-byte groups: the dedicated kernel (rings only, no staging block)
-    const size_t wide_ring = table_bytes + WordRing<8>::kBytes * (kWarps + 1), narrow_ring = table_bytes + WordRing<7>::kBytes * (kWarps + 1);
-    if (fits_all_blocks(wide_ring)) {
-      const int rc = allow_shared(tile_ans_decode_bytes_kernel<8>, wide_ring);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_bytes_kernel<8><<<grid, kThreads, wide_ring, stream>>>(p);
-    } else {
-      const int rc = allow_shared(tile_ans_decode_bytes_kernel<7>, narrow_ring);
-      if (rc != EP_OK) return rc;
-      tile_ans_decode_bytes_kernel<7><<<grid, kThreads, narrow_ring, stream>>>(p);
-    }
+    // one coded byte lane in tiles of whole 32-byte groups: the dedicated kernel (rings only, no staging block), 14
+    // tiles to a block; 16 KB of table and 30 KB of rings at most, four blocks to an SM
+    const size_t shared = table_bytes + WordRing<8>::kBytes * (kByteWarps + 1);
+    const int64_t tiles = p.tile_end - p.first_tile;
+    const dim3 byte_grid(static_cast<unsigned>((tiles + kByteWarps - 1) / kByteWarps));
+    const int rc = allow_shared(tile_ans_decode_bytes_kernel<8>, shared);
+    if (rc != EP_OK) return rc;
+    tile_ans_decode_bytes_kernel<8><<<byte_grid, kByteWarps * 32, shared, stream>>>(p);
     return EP_OK;
   }
   if (staged) {
-    // 256-word ring chunks halve the ring upkeep; they are used for one- and two-byte elements where kDecodeBlocksPerSm
-    // blocks still fit an SM's shared memory, which keeps a tensor of 8192 tiles resident at once (four-byte elements
-    // measured no better with them)
-    const size_t wide_ring = staged_shared_bytes<8>(table_bytes, p.lanes.ans_lanes);
-    const bool wide = NLANES <= 2 && fits_all_blocks(wide_ring);
-    const size_t shared = wide ? wide_ring : staged_shared_bytes<7>(table_bytes, p.lanes.ans_lanes);
     // common patterns get their own instantiation: everything coded, or only the top byte coded
     constexpr int top_only = (1 << (NLANES - 1)) - 1;
-    if (p.lanes.raw_mask == 0u && NLANES <= 2) {
-      return wide ? launch_staged<NLANES, 0, 8>(p, grid, shared, stream) : launch_staged<NLANES, 0, 7>(p, grid, shared, stream);
-    } else if (NLANES > 1 && p.lanes.raw_mask == static_cast<uint32_t>(top_only)) {
-      return wide ? launch_staged<NLANES, top_only, 8>(p, grid, shared, stream) : launch_staged<NLANES, top_only, 7>(p, grid, shared, stream);
-    } else {
-      return wide ? launch_staged<NLANES, -1, 8>(p, grid, shared, stream) : launch_staged<NLANES, -1, 7>(p, grid, shared, stream);
-    }
+    if (p.lanes.raw_mask == 0u && NLANES <= 2) return launch_staged_shape<NLANES, 0>(p, table_bytes, stream);
+    if (NLANES > 1 && p.lanes.raw_mask == static_cast<uint32_t>(top_only)) return launch_staged_shape<NLANES, top_only>(p, table_bytes, stream);
+    return launch_staged_shape<NLANES, -1>(p, table_bytes, stream);
   } else {
     const int rc = allow_shared(tile_ans_decode_simple_kernel<NLANES>, table_bytes);
     if (rc != EP_OK) return rc;
