@@ -44,7 +44,9 @@ _PROTOTYPES = {
     "ep_lattice_decode_scratch_bytes": [_i32, _i32],
     "ep_lattice_decode_static": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _ptr, _ptr, _i32, _i64, _i64, _i32, _i64, _i32, _ptr, _ptr],
     "ep_lattice_decode_static_max_prob_bits": [],
-    "ep_dfloat11_decode": [_ptr, _i32, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _i32, _ptr, _ptr],
+    "ep_dfloat11_decode": [_ptr, _i32, _ptr, _i64, _ptr, _ptr, _ptr, _ptr, _i64, _i32, _i32, _i32, _ptr, _i64, _ptr, _ptr],
+    "ep_dfloat11_decode_tables_bytes": [_i32],
+    "ep_dfloat11_build_decode_tables": [_ptr, _i32, _ptr, _i64, _ptr],
     "ep_dfloat11_histogram": [_ptr, _i64, _ptr, _ptr],
     "ep_dfloat11_build_code": [_ptr, _ptr, _ptr],
     "ep_dfloat11_build_luts": [_ptr, _ptr, _ptr, _i32, _ptr],
@@ -76,7 +78,7 @@ _PROTOTYPES = {
     "ep_lattice_encode": [_ptr, _ptr, _i64, _ptr, _ptr, _i64, _i32, _i64, _ptr, _ptr, _ptr, _ptr, _ptr],
 }
 _RESTYPES = {"ep_status_string": ctypes.c_char_p, "ep_last_cuda_error": ctypes.c_char_p}
-_INT64_RESULTS = ("ep_lattice_decode_scratch_bytes", "ep_lattice_slot_tables_bytes", "ep_lattice_bins_needed", "ep_lattice_encode_scratch_words",
+_INT64_RESULTS = ("ep_lattice_decode_scratch_bytes", "ep_lattice_slot_tables_bytes", "ep_dfloat11_decode_tables_bytes", "ep_lattice_bins_needed", "ep_lattice_encode_scratch_words",
                   "ep_dfloat11_chunks")
 
 

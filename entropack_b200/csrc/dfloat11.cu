@@ -24,13 +24,15 @@ namespace {
 
 constexpr int kMaxLevels = 64;
 constexpr uint32_t kPointerFlag = 0x8000u;
-// Multi-symbol table: indexed by the next kMultiBits bits of the stream, a 64-bit entry holds up to three whole codewords
-// that fit in those bits: .x = symbols in bytes 0-2 and their number in bits 24-25 (0: the first codeword is longer than
-// the window, take the one-symbol path), .y = the bits consumed after one, two and three of them in bytes 0-2. A thread
-// with fewer symbols left than the entry holds takes only those and advances by their length, so the end of a region
-// needs no path of its own. Exponent codes average under three bits, so most look-ups deliver three symbols.
-constexpr int kMultiBits = 10;
-constexpr int kMultiEntries = 1 << kMultiBits;
+// Multi-symbol table: indexed by the next MULTI_BITS bits of the stream, a 64-bit entry holds up to four whole codewords
+// that fit in those bits: .x = their symbols, one per byte; .y = the bits consumed after one, two, three and four of
+// them in four 4-bit fields, and their number in bits 16-18 (0: the first codeword is longer than the window or than a
+// level-0 look-up, take the one-symbol path). A thread with fewer symbols left than the entry holds takes only those
+// and advances by their length, so the end of a region needs no path of its own. Exponent codes average under three
+// bits, so most look-ups deliver three or four symbols. The table is built inside the kernel with a 10-bit window, or
+// once per container with an 11-bit window (ep_dfloat11_build_decode_tables) and copied in by every later decode.
+constexpr int kBuiltMultiBits = 10;
+constexpr int kKeptMultiBits = 11;
 constexpr int kMaxFormatBlocks = 4;   // blocks of the format served by one CUDA block, at most
 
 __device__ __forceinline__ uint32_t byte_swap(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
@@ -58,9 +60,17 @@ struct DecodeParams {
   int64_t blocks;   // blocks of the format (threads_per_block regions each)
   int groups;       // how many of them one CUDA block serves
   int* error;
+  const uint32_t* kept_tables;   // fused level tables + multi-symbol table as an earlier launch exported them, or null
+  uint32_t* export_tables;       // EXPORT: where the freshly built tables go
 };
 
+// Words of the fused level tables (u16[levels][256], padded to 16 bytes) in front of the multi-symbol table.
+__host__ __device__ inline uint32_t level_table_words(int levels) { return (static_cast<uint32_t>(levels) * 128u + 3u) & ~3u; }
+
+template <int MULTI_BITS, bool EXPORT>
 __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParams p) {
+  constexpr int kMultiBits = MULTI_BITS;
+  constexpr int kMultiEntries = 1 << MULTI_BITS;
   extern __shared__ __align__(16) uint32_t shared[];
   // A CUDA block serves `p.groups` consecutive blocks of the format side by side, one per group of `group_threads`
   // threads, so that the code tables are staged and the multi-symbol table built once for all of them.
@@ -68,7 +78,7 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   //         per group: stream words u32[block_words] | exponents u8[stage_bytes]
   const int levels = p.num_luts - 1;
   uint16_t* const tables = reinterpret_cast<uint16_t*>(shared);
-  uint2* const multi = reinterpret_cast<uint2*>(shared + ((levels * 128 + 1) & ~1));     // 8-byte aligned
+  uint2* const multi = reinterpret_cast<uint2*>(shared + level_table_words(levels));
   uint32_t* const scan_base = reinterpret_cast<uint32_t*>(multi + kMultiEntries);
   const int block_bytes = p.bytes_per_thread * p.threads_per_block;
   const int block_words = ((block_bytes + 3) / 4 + 3) & ~1;  // two look-ahead words, even count keeps what follows 8-byte aligned
@@ -85,16 +95,26 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
   const int warp = member >> 5;
   const int warps = group_threads >> 5;
 
+  const bool kept = !EXPORT && p.kept_tables != nullptr;
+  if (kept) {
+    // both tables as they were exported: 16-byte asynchronous copies, waited for together with nothing else
+    const uint32_t words = level_table_words(levels) + 2u * kMultiEntries;
+    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
+    for (uint32_t at = threadIdx.x * 4u; at < words; at += blockDim.x * 4u) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + at * 4u), "l"(p.kept_tables + at) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
   const uint32_t pointer_min = levels > 1 ? 256u - (levels - 1) : 256u;
   const uint8_t* lengths = p.luts + levels * 256;
-  for (int i = threadIdx.x; i < levels * 256; i += blockDim.x) {
+  for (int i = threadIdx.x; i < levels * 256 && !kept; i += blockDim.x) {
     const uint32_t entry = p.luts[i];
     // a pointer names a child level; clamp it into the staged tables so a corrupt row cannot index outside them
     tables[i] = entry >= pointer_min ? static_cast<uint16_t>(kPointerFlag | min(256u - entry, static_cast<uint32_t>(levels - 1)))
                                      : static_cast<uint16_t>(entry | (static_cast<uint32_t>(lengths[entry]) << 8));
   }
   const int64_t block_base = format_block * block_bytes;
-  for (int w = member; w < block_words && present; w += group_threads) {
+  for (int w = member; w < block_words && present && !EXPORT; w += group_threads) {
     const int64_t byte = block_base + static_cast<int64_t>(w) * 4;
     uint32_t value = 0;
     if (byte + 4 <= p.n_bytes && ((reinterpret_cast<uintptr_t>(p.encoded) + byte) & 3u) == 0) {
@@ -106,20 +126,27 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     words[w] = value;
   }
 
+  if (kept) asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();   // level-0 entries are in place
-  for (int v = threadIdx.x; v < kMultiEntries; v += blockDim.x) {
+  for (int v = threadIdx.x; v < kMultiEntries && !kept; v += blockDim.x) {
     uint32_t packed = 0, lengths = 0, used = 0, found = 0;
-    while (found < 3u) {
+    while (found < 4u) {
       const uint32_t rest = (static_cast<uint32_t>(v) << used) & (kMultiEntries - 1);      // bits not yet consumed, left-aligned
       const uint32_t entry = tables[rest >> (kMultiBits - 8)];
       const uint32_t length = (entry >> 8) & 0x3Fu;
       if ((entry & kPointerFlag) || length == 0u || used + length > static_cast<uint32_t>(kMultiBits)) break;
       packed |= (entry & 0xFFu) << (8 * found);
       used += length;
-      lengths |= used << (8 * found);
+      lengths |= used << (4 * found);
       ++found;
     }
-    multi[v] = make_uint2(packed | (found << 24), lengths);
+    multi[v] = make_uint2(packed, lengths | (found << 16));
+  }
+  if (EXPORT) {
+    __syncthreads();
+    const uint32_t words = level_table_words(levels) + 2u * kMultiEntries;
+    for (uint32_t at = threadIdx.x; at < words; at += blockDim.x) p.export_tables[at] = shared[at];
+    return;
   }
   const bool active = present && member < p.threads_per_block;
   const int64_t region = format_block * p.threads_per_block + member;
@@ -167,39 +194,50 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     if (active) report(p.error, EP_STREAM_NOT_CONSUMED);
   }
 
-  // walk this region's codewords
+  // Walk this region's codewords. Every thread of the warp runs the same instruction stream, without branches that could
+  // split it: a thread that is done (or idle) takes zero symbols, the four staging stores are predicated on how many
+  // symbols the look-up delivered, the window's second word is re-read every round (the first one moves up when the
+  // cursor crossed into it), and the one-symbol path for codewords longer than the window is entered by the whole
+  // warp, and only in rounds where some thread needs it.
   uint32_t bit = static_cast<uint32_t>(member) * p.bytes_per_thread * 8u + (meta >> 11);
   uint32_t word_index = bit >> 5;
-  uint32_t current = words[min(word_index, static_cast<uint32_t>(block_words - 2))];
-  uint32_t next = words[min(word_index + 1, static_cast<uint32_t>(block_words - 1))];
-  for (int i = 0; i < count;) {
+  const uint32_t last_word = static_cast<uint32_t>(block_words - 1);
+  uint32_t current = words[min(word_index, last_word - 1u)];
+  uint32_t next = words[min(word_index + 1u, last_word)];
+  int i = 0;
+  while (__any_sync(0xFFFFFFFFu, i < count)) {
+    const bool active = i < count;
     const uint32_t window = __funnelshift_l(next, current, bit & 31u);
-    // whatever whole codewords the window's first bits hold are taken at once, as many as this region still wants
     const uint2 fast = multi[window >> (32 - kMultiBits)];
-    const uint32_t found = min(fast.x >> 24, static_cast<uint32_t>(count - i));
-    if (found) {
-      exponents[local_base + i] = static_cast<uint8_t>(fast.x);
-      if (found > 1u) exponents[local_base + i + 1] = static_cast<uint8_t>(fast.x >> 8);
-      if (found > 2u) exponents[local_base + i + 2] = static_cast<uint8_t>(fast.x >> 16);
-      i += static_cast<int>(found);
-      bit += (fast.y >> (8u * found - 8u)) & 0xFFu;
-    } else {
-      uint32_t entry = tables[window >> 24];
-      uint32_t peek = window;
+    const uint32_t held = fast.y >> 16;                       // whole codewords in the window's first bits
+    uint32_t found = active ? min(held, static_cast<uint32_t>(count - i)) : 0u;
+    uint32_t advance = found ? (fast.y >> (4u * found - 4u)) & 0xFu : 0u;
+    uint32_t symbols = fast.x;
+    if (__any_sync(0xFFFFFFFFu, active && held == 0u)) {
+      if (active && held == 0u) {
+        uint32_t entry = tables[window >> 24];
+        uint32_t peek = window;
 #pragma unroll 1
-      for (int hop = 0; hop < 3 && (entry & kPointerFlag); ++hop) {  // code longer than this level: the next byte picks in the child level
-        peek <<= 8;
-        entry = tables[(entry & 0xFFu) * 256u + (peek >> 24)];
+        for (int hop = 0; hop < 3 && (entry & kPointerFlag); ++hop) {  // code longer than this level: the next byte picks in the child level
+          peek <<= 8;
+          entry = tables[(entry & 0xFFu) * 256u + (peek >> 24)];
+        }
+        symbols = entry & 0xFFu;
+        found = 1u;
+        advance = (entry >> 8) & 0x3Fu;
       }
-      exponents[local_base + i] = static_cast<uint8_t>(entry);
-      bit += (entry >> 8) & 0x3Fu;
-      ++i;
     }
-    if ((bit >> 5) != word_index) {
-      word_index = bit >> 5;
-      current = next;
-      next = words[min(word_index + 1, static_cast<uint32_t>(block_words - 1))];
-    }
+    uint8_t* const target = exponents + local_base + i;
+    if (found > 0u) target[0] = static_cast<uint8_t>(symbols);
+    if (found > 1u) target[1] = static_cast<uint8_t>(symbols >> 8);
+    if (found > 2u) target[2] = static_cast<uint8_t>(symbols >> 16);
+    if (found > 3u) target[3] = static_cast<uint8_t>(symbols >> 24);
+    i += static_cast<int>(found);
+    bit += advance;
+    const uint32_t now = bit >> 5;
+    current = now != word_index ? next : current;      // at most one word further: a codeword has 32 bits at most
+    word_index = now;
+    next = words[min(now + 1u, last_word)];
   }
   __syncthreads();
 
@@ -429,10 +467,36 @@ __global__ void fill_u32_kernel(uint32_t* target, int64_t count, uint32_t value)
 
 using namespace ep;
 
+extern "C" int64_t ep_dfloat11_decode_tables_bytes(int num_luts) {
+  if (num_luts < 2 || num_luts > kMaxLevels + 1) return EP_ERR_INVALID_ARGUMENT;
+  return static_cast<int64_t>(level_table_words(num_luts - 1) + 2u * (1u << kKeptMultiBits)) * 4;
+}
+
+extern "C" int ep_dfloat11_build_decode_tables(const uint8_t* luts_dev, int num_luts, void* tables_dev, int64_t tables_bytes,
+                                               ep_stream_t stream) {
+  const int64_t needed = ep_dfloat11_decode_tables_bytes(num_luts);
+  if (needed < 0) return static_cast<int>(needed);
+  if (!luts_dev || !tables_dev || tables_bytes < needed || (reinterpret_cast<uintptr_t>(tables_dev) & 15u)) return EP_ERR_INVALID_ARGUMENT;
+  DecodeParams p = {};
+  p.luts = luts_dev;
+  p.num_luts = num_luts;
+  p.bytes_per_thread = 16;
+  p.threads_per_block = 128;
+  p.groups = 1;
+  p.export_tables = static_cast<uint32_t*>(tables_dev);
+  if (needed > 48 * 1024) {
+    EP_CUDA_CHECK(cudaFuncSetAttribute(dfloat11_decode_kernel<kKeptMultiBits, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(needed)));
+  }
+  dfloat11_decode_kernel<kKeptMultiBits, true><<<1, 512, static_cast<size_t>(needed), static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("dfloat11_decode_kernel (table export)");
+}
+
 extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const uint8_t* encoded_dev, int64_t n_bytes,
                                   const uint8_t* sign_mantissa_dev, const uint32_t* output_positions_dev,
                                   const uint16_t* thread_meta_dev, void* output_dev, int64_t n_elements, int bytes_per_thread,
-                                  int threads_per_block, int max_block_elems, int* error_dev, ep_stream_t stream) {
+                                  int threads_per_block, int max_block_elems, const void* decode_tables_dev,
+                                  int64_t decode_tables_bytes, int* error_dev, ep_stream_t stream) {
   if (!luts_dev || !sign_mantissa_dev || !output_positions_dev || !thread_meta_dev || !output_dev || n_elements <= 0 ||
       n_bytes < 0 || num_luts < 2 || num_luts > kMaxLevels + 1 || bytes_per_thread <= 0 || threads_per_block <= 0 ||
       max_block_elems < 0) {
@@ -440,11 +504,15 @@ extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const u
   }
   if (n_bytes > 0 && !encoded_dev) return EP_ERR_INVALID_ARGUMENT;
   if (threads_per_block > 1024) return EP_ERR_UNSUPPORTED;
+  const bool kept = decode_tables_dev != nullptr;
+  if (kept && (decode_tables_bytes < ep_dfloat11_decode_tables_bytes(num_luts) || (reinterpret_cast<uintptr_t>(decode_tables_dev) & 15u))) {
+    return EP_ERR_INVALID_ARGUMENT;
+  }
   const int64_t block_bytes = static_cast<int64_t>(bytes_per_thread) * threads_per_block;
   const int64_t blocks = (n_bytes + block_bytes - 1) / block_bytes;
   if (blocks == 0) return EP_OK;
   if (blocks > 0x7FFFFFFF) return EP_ERR_TOO_LARGE;
-  DecodeParams p;
+  DecodeParams p = {};
   p.luts = luts_dev;
   p.encoded = encoded_dev;
   p.sign_mantissa = sign_mantissa_dev;
@@ -458,22 +526,28 @@ extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const u
   p.threads_per_block = threads_per_block;
   p.stage_elems = max_block_elems;
   p.error = error_dev;
+  p.kept_tables = static_cast<const uint32_t*>(decode_tables_dev);
   const int threads = (threads_per_block + 31) / 32 * 32;
   const size_t block_words = ((block_bytes + 3) / 4 + 3) & ~size_t(1);
   const size_t stage_bytes = (static_cast<size_t>(max_block_elems) + 16 + 15) & ~size_t(15);
-  const size_t fixed = ((static_cast<size_t>(num_luts - 1) * 512 + 7) & ~size_t(7)) + kMultiEntries * 8 + kMaxFormatBlocks * 32 * 4;
+  const size_t multi_bytes = static_cast<size_t>(8) << (kept ? kKeptMultiBits : kBuiltMultiBits);
+  const size_t fixed = static_cast<size_t>(level_table_words(num_luts - 1)) * 4 + multi_bytes + kMaxFormatBlocks * 32 * 4;
   const size_t per_group = block_words * 4 + stage_bytes;
+  // four blocks of the format to a CUDA block while four such CUDA blocks still fit an SM's shared memory
   int groups = kMaxFormatBlocks;
-  while (groups > 1 && (threads * groups > 1024 || fixed + groups * per_group > 48 * 1024 || blocks < groups)) groups >>= 1;
+  while (groups > 1 && (threads * groups > 1024 || fixed + groups * per_group > 55 * 1024 || blocks < groups)) groups >>= 1;
   const size_t shared = fixed + groups * per_group;
   if (shared > 227 * 1024) return EP_ERR_UNSUPPORTED;
-  if (shared > 48 * 1024) {
-    EP_CUDA_CHECK(cudaFuncSetAttribute(dfloat11_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
-  }
   p.blocks = blocks;
   p.groups = groups;
   const int64_t grid = (blocks + groups - 1) / groups;
-  dfloat11_decode_kernel<<<static_cast<unsigned>(grid), threads * groups, shared, static_cast<cudaStream_t>(stream)>>>(p);
+  const auto launch = [&](auto kernel) -> int {
+    if (shared > 48 * 1024) EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+    kernel<<<static_cast<unsigned>(grid), threads * groups, shared, static_cast<cudaStream_t>(stream)>>>(p);
+    return EP_OK;
+  };
+  const int rc = kept ? launch(dfloat11_decode_kernel<kKeptMultiBits, false>) : launch(dfloat11_decode_kernel<kBuiltMultiBits, false>);
+  if (rc != EP_OK) return rc;
   return check_launch("dfloat11_decode_kernel");
 }
 

@@ -16,6 +16,35 @@ from .format import DFloat11Buffers, make_layout, parse_layout_cached
 _MAX_LUT_ROWS = 65
 
 
+def decode_tables(buffers: DFloat11Buffers) -> torch.Tensor | None:
+    """The container's decode tables (fused level tables + an 11-bit multi-symbol table, 17 KB), built on the device once
+    and kept on the layout tensor so that later decodes copy them into shared memory instead of rebuilding a smaller
+    table at the head of every CUDA block. A container that is decoded only once never gets them: the first decode
+    builds its table inside the kernel and this returns None; the second builds the kept copy. Must not be first reached
+    during a stream capture."""
+    layout = buffers.layout
+    device = buffers.luts.device
+    cached = getattr(layout, "_dfloat11_decode_tables", None)
+    if cached is not None and cached.device == device:
+        return cached
+    seen = getattr(layout, "_dfloat11_decodes", 0)
+    layout._dfloat11_decodes = seen + 1
+    if seen == 0:
+        return None
+    lib = _native.load()
+    luts = buffers.luts.contiguous()
+    nbytes = lib.ep_dfloat11_decode_tables_bytes(int(luts.shape[0]))
+    if nbytes < 0:
+        _native.check(int(nbytes), "dfloat11 decode tables")
+    tables = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    with torch.cuda.device(device):
+        status = lib.ep_dfloat11_build_decode_tables(_native.ptr(luts), int(luts.shape[0]), _native.ptr(tables), nbytes,
+                                                     _native.stream_handle(device))
+    _native.check(status, "dfloat11 decode tables")
+    layout._dfloat11_decode_tables = tables
+    return tables
+
+
 def decode(buffers: DFloat11Buffers, *, error: torch.Tensor | None = None) -> torch.Tensor:
     """Decode to a flat bf16 tensor on the buffers' device (one launch, no host sync after the first call)."""
     sign_mantissa = buffers.sign_mantissa
@@ -31,12 +60,13 @@ def decode(buffers: DFloat11Buffers, *, error: torch.Tensor | None = None) -> to
     if buffers.luts.ndim != 2 or buffers.luts.shape[1] != 256 or buffers.luts.shape[0] < 2:
         raise ValueError(f"dfloat11 luts must be [levels + 1, 256], got {tuple(buffers.luts.shape)}")
     out = torch.empty(n, dtype=torch.bfloat16, device=sign_mantissa.device)
+    tables = decode_tables(buffers)
     with torch.cuda.device(sign_mantissa.device):
         status = _native.load().ep_dfloat11_decode(
             _native.ptr(buffers.luts.contiguous()), int(buffers.luts.shape[0]), _native.ptr(buffers.encoded_exponent),
             buffers.encoded_exponent.numel(), _native.ptr(sign_mantissa), _native.ptr(buffers.output_positions),
-            _native.ptr(buffers.thread_meta), _native.ptr(out), n, bpt, tpb, widest, _native.ptr(error),
-            _native.stream_handle(sign_mantissa.device))
+            _native.ptr(buffers.thread_meta), _native.ptr(out), n, bpt, tpb, widest, _native.ptr(tables),
+            0 if tables is None else tables.numel(), _native.ptr(error), _native.stream_handle(sign_mantissa.device))
     _native.check(status, "dfloat11 decode")
     return out
 

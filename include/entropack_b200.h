@@ -301,7 +301,18 @@ int ep_lattice_encode(const int16_t* fields_dev, const uint8_t* cosets_dev, int6
 int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const uint8_t* encoded_dev, int64_t n_bytes,
                        const uint8_t* sign_mantissa_dev, const uint32_t* output_positions_dev, const uint16_t* thread_meta_dev,
                        void* output_dev, int64_t n_elements, int bytes_per_thread, int threads_per_block, int max_block_elems,
-                       int* error_dev, ep_stream_t stream);
+                       const void* decode_tables_dev, int64_t decode_tables_bytes, int* error_dev, ep_stream_t stream);
+
+/* A container's decode tables, built once and kept by the caller for every later decode of that container: the
+ * level tables fused with the length row and an 11-bit multi-symbol table (up to four codewords per look-up). The
+ * reference rebuilds nothing per decode either -- its kernel reads luts as stored (dfloat11.cu:314-522); this is the
+ * form that kernel's look-ups take here. ep_dfloat11_decode_tables_bytes gives the size, ep_dfloat11_build_decode_tables
+ * fills a 16-byte aligned device buffer of that size from luts (one small launch); passed to ep_dfloat11_decode as
+ * decode_tables_dev it replaces the table build at the head of every CUDA block by a copy. With a null
+ * decode_tables_dev the decode builds a 10-bit table itself. */
+int64_t ep_dfloat11_decode_tables_bytes(int num_luts);
+int ep_dfloat11_build_decode_tables(const uint8_t* luts_dev, int num_luts, void* tables_dev, int64_t tables_bytes,
+                                    ep_stream_t stream);
 
 /* 256-bin histogram of the exponent byte (u64, cleared by the call). Stands in for exponent_counter,
  * entropack/schemes/dfloat11/cuda.py:104-122. */

@@ -23,6 +23,22 @@ def _gpu_decode(buffers: dict) -> np.ndarray:
     return out.view(torch.int16).cpu().numpy().view(np.uint16)
 
 
+@pytest.mark.parametrize("name", golden_names("dfloat11_"))
+def test_kept_decode_tables_decode_like_tables_built_in_the_kernel(name):
+    """First decode of a container: 10-bit multi-symbol table built by every CUDA block; second: builds the 11-bit tables
+    that are kept on the container; later ones copy those in. All give the source bits."""
+    from entropack_b200.schemes.dfloat11 import b200
+
+    record = load_golden(f"dfloat11_{name}")
+    device_buffers = _to_device(buffers_of(record))
+    for call in range(3):
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = b200.decode(device_buffers, error=error)
+        assert int(error.item()) == 0
+        assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), record["input_bits"]), f"decode {call + 1} differs"
+        assert (getattr(device_buffers.layout, "_dfloat11_decode_tables", None) is not None) == (call >= 1)
+
+
 def _gpu_encode(bits: np.ndarray, bytes_per_thread=16, threads_per_block=128) -> dict:
     from entropack_b200.schemes.dfloat11 import b200
 
