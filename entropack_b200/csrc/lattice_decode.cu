@@ -253,8 +253,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
     for (uint32_t at = threadIdx.x * 4u; at < words; at += kDecodeThreads * 4u) {
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(shared_base + at * 4u), "l"(p.slot_tables + at) : "memory");
     }
-    ring_commit();
-    ring_wait_all();
+    ring_commit();     // waited for below, together with the first tile's ring chunks
   } else if (TABLES != kTablesGlobal) {
     // The 17 slot tables are built by the whole block, one work item per (table, run of 32 symbols): first the
     // frequency total of every run, then, from the totals before it, each run's first slot; inside a run every thread
@@ -369,7 +368,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       }
     }
   }
-  __syncthreads();
+  // tables built here: the build read its frequencies from the rings' space, which the first ring fetch below overwrites
+  if (MODE == kModeExport || (TABLES != kTablesGlobal && p.slot_tables == nullptr)) __syncthreads();
   if (MODE == kModeExport) {
     const uint32_t words = kTables * table_size + (TABLES == kTablesSharedWide ? kTables * table_size / 4 : 0u);
     for (uint32_t at = threadIdx.x; at < words; at += kDecodeThreads) p.export_tables[at] = shared_tables[at];
@@ -381,33 +381,56 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
   // a row holds at least a group's 32 vectors: stepping back one group crosses at most one row boundary
   const bool long_rows = p.vecs_per_row >= 32;
 
-  // tile t goes to block t mod grid: every SM gets its share even when there are fewer tiles than warp slots
-  for (int64_t tile = static_cast<int64_t>(warp) * gridDim.x + blockIdx.x; tile < p.tiles;
-       tile += static_cast<int64_t>(gridDim.x) * kDecodeWarps) {
-    const int64_t tile_begin = tile * p.tile_vectors;
-    const int count = static_cast<int>(min(static_cast<int64_t>(p.tile_vectors), p.vectors - tile_begin));
+  // State of the tile a warp is decoding, set by open_tile.
+  int64_t tile_begin = 0;
+  int count = 0;
+  uint32_t x = 0;
+  int origin = 0, cursor = 0, chunk = -1, refill_at = 0;
+  // Reads a tile's stream bounds and states and asks for the three ring chunks at the stream's end; false for a tile
+  // whose offsets are out of range (reported, skipped). `drain`: the previous tile's last prefetch may still be in
+  // flight and every thread must be past its reads of the old ring contents before the ring is refilled.
+  auto open_tile = [&](int64_t tile, bool drain) -> bool {
+    tile_begin = tile * p.tile_vectors;
+    count = static_cast<int>(min(static_cast<int64_t>(p.tile_vectors), p.vectors - tile_begin));
     // through a warp reduction, so that the cursor arithmetic and its tests are known to be warp-uniform
     const uint32_t begin = __reduce_min_sync(0xFFFFFFFFu, p.offsets[tile]);
     const uint32_t end = __reduce_min_sync(0xFFFFFFFFu, p.offsets[tile + 1]);
     if (end < begin || static_cast<int64_t>(end) > p.payload_words) {
       if (lane == 0) report(p.error, EP_STREAM_BAD_OFFSETS);
-      continue;
+      return false;
     }
-    uint32_t x = p.states[tile * kNumStates + lane];
-    const int origin = 2 * static_cast<int>(begin & (Ring::kWords - 1));
-    int cursor = origin + 2 * static_cast<int>(end - begin);
-    int chunk = end > begin ? static_cast<int>((end - 1u) >> Ring::kLog) : -1;
-    int refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(chunk) << Ring::kLog) - static_cast<int64_t>(begin));
-    // the previous tile's last prefetch may still be in flight and every thread must be past its reads
-    // of the old ring contents before the ring is refilled
-    ring_wait_all();
-    __syncwarp();
+    x = p.states[tile * kNumStates + lane];
+    origin = 2 * static_cast<int>(begin & (Ring::kWords - 1));
+    cursor = origin + 2 * static_cast<int>(end - begin);
+    chunk = end > begin ? static_cast<int>((end - 1u) >> Ring::kLog) : -1;
+    refill_at = origin + 2 * static_cast<int>((static_cast<int64_t>(chunk) << Ring::kLog) - static_cast<int64_t>(begin));
+    if (drain) {
+      ring_wait_all();
+      __syncwarp();
+    }
     Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk, lane);
     Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk - 1, lane);
     Ring::fetch_clipped(p.payload, p.payload_words, ring, chunk - 2, lane);
     ring_commit();
-    ring_wait_all();
-    __syncwarp();
+    return true;
+  };
+
+  // tile t goes to block t mod grid: every SM gets its share even when there are fewer tiles than warp slots. A warp's
+  // first tile is opened before the block meets at the barrier behind the tables: its bounds, states and ring chunks
+  // travel while the tables are still being copied in (or were being built).
+  int64_t tile = static_cast<int64_t>(warp) * gridDim.x + blockIdx.x;
+  bool first_pass = true;
+  const bool first_open = tile < p.tiles && open_tile(tile, false);
+  ring_wait_all();
+  __syncthreads();
+  for (; tile < p.tiles; tile += static_cast<int64_t>(gridDim.x) * kDecodeWarps, first_pass = false) {
+    if (first_pass) {
+      if (!first_open) continue;
+    } else {
+      if (!open_tile(tile, true)) continue;
+      ring_wait_all();
+      __syncwarp();
+    }
     Ring::fetch_interior(p.payload, ring, chunk - 3, lane);
     ring_commit();
 
