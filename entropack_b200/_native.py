@@ -14,7 +14,7 @@ EP_OK = 0
 STREAM_ERRORS = {
     1: "stream offsets are out of range", 2: "payload is truncated", 3: "payload contains unread words",
     4: "raw lane payload length is invalid", 5: "a decoded table selector is out of range (corrupt coset table)",
-    9: "a bounded wait inside a tensor-core product ran out",
+    9: "a bounded wait inside a kernel ran out (tensor-core product, peer barrier or a bulk copy of the DFloat11 decode)",
 }
 
 

@@ -8,10 +8,13 @@
 // block b. luts[k] are 256-entry byte tables (entry = symbol, or 256 - child level), the last row is the
 // code length per symbol.
 //
-// Decode: one CUDA block per format block, one thread per region. The block's bytes are staged once into
-// shared memory as big-endian words, the LUT levels are fused with the length row into 16-bit entries
-// (one shared load per level), each thread walks its codewords with a two-word register window, symbols
-// go to a shared staging array and leave as coalesced 16-byte bf16 stores merged with sign_mantissa.
+// Decode, two kernels, one thread per region in both. Block kernel (a container's first decode, and layouts the other
+// one does not take): a CUDA block serves up to four blocks of the format; their bytes are staged once into shared
+// memory as big-endian words, the LUT levels are fused with the length row into 16-bit entries (one shared load per
+// level), each thread walks its codewords with a two-word register window, symbols go to a shared staging array and
+// leave as coalesced 16-byte bf16 stores merged with sign_mantissa. Warp kernel (later decodes, with the tables an
+// earlier call built and kept): the unit of work is a run of 32 regions, a warp to each, persistent blocks, inputs by
+// bulk copies asked for ahead of their use; described in front of it below.
 //
 // Encode: two passes over the input. Pass 1 sums code lengths per chunk of 1024 elements; a scan gives
 // every chunk its bit offset; pass 2 re-reads the chunk, places every codeword with at most three
@@ -19,21 +22,28 @@
 // block metadata from the same bit positions.
 #include "ep_common.cuh"
 
+#include <algorithm>
+
 namespace ep {
 namespace {
 
 constexpr int kMaxLevels = 64;
 constexpr uint32_t kPointerFlag = 0x8000u;
 // Multi-symbol table: indexed by the next MULTI_BITS bits of the stream, a 64-bit entry holds up to four whole codewords
-// that fit in those bits: .x = their symbols, one per byte; .y = the bits consumed after one, two, three and four of
-// them in four 4-bit fields, and their number in bits 16-18 (0: the first codeword is longer than the window or than a
-// level-0 look-up, take the one-symbol path). A thread with fewer symbols left than the entry holds takes only those
-// and advances by their length, so the end of a region needs no path of its own. Exponent codes average under three
+// that fit in those bits: .x = their symbols, one per byte; .y = the bits consumed after none (zero), one, two, three
+// and four of them in five 4-bit fields, and their number in bits 24-26 (0: the first codeword is longer than the
+// window or than a level-0 look-up, take the one-symbol path). A thread with fewer symbols left than the entry holds
+// takes only those and advances by the field of that number, so neither the end of a region nor a finished thread
+// needs a path of its own. Exponent codes average under three
 // bits, so most look-ups deliver three or four symbols. The table is built inside the kernel with a 10-bit window, or
 // once per container with an 11-bit window (ep_dfloat11_build_decode_tables) and copied in by every later decode.
 constexpr int kBuiltMultiBits = 10;
 constexpr int kKeptMultiBits = 11;
 constexpr int kMaxFormatBlocks = 4;   // blocks of the format served by one CUDA block, at most
+// The warp-per-unit kernel: two blocks of up to 20 warps to an SM, the most that 48 registers a thread allow. What a
+// warp does is a chain of dependent steps, so throughput comes from the number of warps in flight.
+constexpr int kWarpKernelBlocksPerSm = 2;
+constexpr int kWarpKernelMaxWarps = 20;
 
 __device__ __forceinline__ uint32_t byte_swap(uint32_t x) { return __byte_perm(x, 0, 0x0123); }
 
@@ -61,6 +71,9 @@ struct DecodeParams {
   int groups;       // how many of them one CUDA block serves
   int* error;
   const uint32_t* kept_tables;   // fused level tables + multi-symbol table as an earlier launch exported them, or null
+  int64_t units;                 // warp kernel: runs of 32 regions in the whole stream
+  int units_per_block;           // warp kernel: runs per block of the format
+  int stage_alloc;               // warp kernel: elements a warp's shared slices hold
   uint32_t* export_tables;       // EXPORT: where the freshly built tables go
 };
 
@@ -132,15 +145,21 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     uint32_t packed = 0, lengths = 0, used = 0, found = 0;
     while (found < 4u) {
       const uint32_t rest = (static_cast<uint32_t>(v) << used) & (kMultiEntries - 1);      // bits not yet consumed, left-aligned
-      const uint32_t entry = tables[rest >> (kMultiBits - 8)];
+      uint32_t entry = tables[rest >> (kMultiBits - 8)];
+      if (entry & kPointerFlag) {
+        // a codeword of nine bits or more: what the window holds beyond the first byte, zero-extended, picks in the child
+        // level; if the codeword fits the window (checked below) the padding took no part in the choice
+        const uint32_t second = (rest & ((1u << (kMultiBits - 8)) - 1u)) << (16 - kMultiBits);
+        entry = tables[(entry & 0xFFu) * 256u + second];
+      }
       const uint32_t length = (entry >> 8) & 0x3Fu;
       if ((entry & kPointerFlag) || length == 0u || used + length > static_cast<uint32_t>(kMultiBits)) break;
       packed |= (entry & 0xFFu) << (8 * found);
       used += length;
-      lengths |= used << (4 * found);
       ++found;
+      lengths |= used << (4 * found);
     }
-    multi[v] = make_uint2(packed, lengths | (found << 16));
+    multi[v] = make_uint2(packed, lengths | (found << 24));
   }
   if (EXPORT) {
     __syncthreads();
@@ -209,9 +228,9 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     const bool active = i < count;
     const uint32_t window = __funnelshift_l(next, current, bit & 31u);
     const uint2 fast = multi[window >> (32 - kMultiBits)];
-    const uint32_t held = fast.y >> 16;                       // whole codewords in the window's first bits
+    const uint32_t held = fast.y >> 24;                       // whole codewords in the window's first bits
     uint32_t found = active ? min(held, static_cast<uint32_t>(count - i)) : 0u;
-    uint32_t advance = found ? (fast.y >> (4u * found - 4u)) & 0xFu : 0u;
+    uint32_t advance = (fast.y >> (4u * found)) & 0xFu;
     uint32_t symbols = fast.x;
     if (__any_sync(0xFFFFFFFFu, active && held == 0u)) {
       if (active && held == 0u) {
@@ -272,6 +291,444 @@ __global__ void __launch_bounds__(1024) dfloat11_decode_kernel(const DecodeParam
     const int64_t g = out_base + j;
     const uint32_t sm = p.sign_mantissa[g];
     p.out[g] = static_cast<uint16_t>(((sm & 0x80u) << 8) | (static_cast<uint32_t>(exponents[j]) << 7) | (sm & 0x7Fu));
+  }
+}
+
+// ---- decode, one warp per run of 32 regions ----------------------------------------------------------
+// Used when the container's kept tables are at hand and the stream is laid out in whole words. The unit of work is a run
+// of 32 consecutive regions of one block of the format: a warp walks them (one region per thread), stages the exponents
+// in its own slice of shared memory and writes the bf16 values out, with no barrier between warps. A block of the
+// format no longer maps to a CUDA block: where a unit's output starts follows from output_positions plus the counts of
+// the block's earlier regions, which the warp adds up itself. Two CUDA blocks per SM run until the units are used up
+// (unit = warp's number in the grid, then + warps in the grid), so the 17 KB of tables are copied in twice per SM, and
+// what a unit reads from global memory is asked for ahead of its use:
+//   * region records and positions of the unit after this one: loaded into registers before this unit's walk;
+//   * this unit's stream bytes: a bulk copy into the warp's stream slice, issued while the previous unit is written out;
+//   * this unit's sign/mantissa bytes: a bulk copy into the warp's byte slice, issued when its walk starts.
+// The bulk copies (cp.async.bulk, completion on an mbarrier per warp and kind) are issued by one thread and carried out
+// by the copy engine: a warp that asks for its bytes goes straight on, however many copies are queued already, which
+// per-thread cp.async copies did not allow once every warp of the GPU asked at the same moment.
+// A unit that decodes to more elements than the slice holds (the host sizes it from the mean, regions of all-equal
+// exponents exceed it) is walked without staging, each thread storing its own values.
+// What bounds it: the walk's shared-memory traffic (four one-byte stores per round to addresses that share banks at
+// random, the look-up) and the integer pipe, about equally; global memory is far from it.
+// Offsets into the stream, the records and the output are 32-bit here: the host sends larger containers to the block kernel.
+struct UnitHead {
+  uint32_t region;     // the unit's first region
+  uint32_t meta;       // this thread's region record (0: no region)
+  uint32_t before;     // this thread's share of the counts of the block's earlier regions, beyond the first three runs
+  uint32_t earlier0, earlier1, earlier2;   // this thread's records in the block's first three runs (zero where the unit is
+                                           // one of them): kept as loaded, so that asking for them does not wait for them
+  uint32_t first;      // output_positions[block]
+  uint32_t last;       // output_positions[block + 1]
+};
+
+struct Unit {
+  uint32_t start;      // first element of the unit in the output
+  uint32_t gap;
+  int count;           // codewords that start in this thread's region
+  int local;           // elements of the unit in front of this thread's
+  int total;           // elements of the unit
+};
+
+// Which unit a warp is at: its number, and the same split into block of the format and run inside the block, stepped
+// without a division.
+struct UnitCursor {
+  uint32_t index;
+  uint32_t block;
+  uint32_t run;
+};
+
+__device__ __forceinline__ void step(UnitCursor& at, uint32_t stride, uint32_t stride_blocks, uint32_t stride_runs, uint32_t runs_per_block) {
+  at.index += stride;
+  at.block += stride_blocks;
+  at.run += stride_runs;
+  if (at.run >= runs_per_block) {
+    at.run -= runs_per_block;
+    ++at.block;
+  }
+}
+
+__device__ __forceinline__ UnitHead load_unit_head(const DecodeParams& p, const UnitCursor& at, uint32_t lane) {
+  UnitHead head = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+  if (at.index < static_cast<uint32_t>(p.units)) {
+    const uint32_t block_region = at.block * static_cast<uint32_t>(p.threads_per_block);
+    const uint16_t* const records = p.thread_meta + (block_region + lane);
+    head.region = block_region + at.run * 32u;
+    if (at.run * 32u + lane < static_cast<uint32_t>(p.threads_per_block)) head.meta = records[at.run * 32u];
+    if (at.run > 0u) head.earlier0 = records[0];
+    if (at.run > 1u) head.earlier1 = records[32];
+    if (at.run > 2u) head.earlier2 = records[64];
+    for (uint32_t k = 3u; k < at.run; ++k) head.before += records[k * 32u] & 2047u;   // blocks of more than 128 regions
+    head.first = p.output_positions[at.block];
+    head.last = p.output_positions[at.block + 1u];
+  }
+  return head;
+}
+
+__device__ __forceinline__ Unit open_unit(const DecodeParams& p, const UnitHead& head, uint32_t lane) {
+  Unit unit;
+  unit.gap = head.meta >> 11;
+  unit.count = static_cast<int>(head.meta & 2047u);
+  uint32_t inclusive = static_cast<uint32_t>(unit.count);
+#pragma unroll
+  for (int step = 1; step < 32; step <<= 1) {
+    const uint32_t below = __shfl_up_sync(0xFFFFFFFFu, inclusive, step);
+    if (lane >= static_cast<uint32_t>(step)) inclusive += below;
+  }
+  unit.local = static_cast<int>(inclusive) - unit.count;
+  unit.total = static_cast<int>(__shfl_sync(0xFFFFFFFFu, inclusive, 31));   // at most 32 * 2047
+  const uint32_t before = __reduce_add_sync(0xFFFFFFFFu, head.before + (head.earlier0 & 2047u) + (head.earlier1 & 2047u) +
+                                                             (head.earlier2 & 2047u));   // at most 1024 * 2047
+  unit.start = head.first + before;
+  // a codeword has one bit at least: more of them than a region has bits is a corrupt record
+  const bool counts_bad = __any_sync(0xFFFFFFFFu, unit.count > 8 * p.bytes_per_thread);
+  const bool positions_bad = counts_bad || head.first > head.last || head.last > static_cast<uint32_t>(p.n_elements);
+  const bool overrun = before + static_cast<uint32_t>(unit.total) > head.last - head.first;
+  if (positions_bad || overrun) {   // only a corrupt container gets here: write nothing for this unit
+    if (lane == 0) report(p.error, positions_bad ? EP_STREAM_BAD_OFFSETS : EP_STREAM_NOT_CONSUMED);
+    unit.count = 0;
+    unit.total = 0;
+    unit.start = 0;
+  }
+  return unit;
+}
+
+// Bounded wait on a phase of an mbarrier; false when the limit ran out (a copy that never completes).
+constexpr uint32_t kCopyWaitLimit = 1u << 22;
+__device__ __forceinline__ bool copy_wait(uint32_t barrier_at, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kCopyWaitLimit; ++spin) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done)
+                 : "r"(barrier_at), "r"(parity)
+                 : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+// One bulk copy (issued by the calling thread, carried out by the copy engine while the warp goes on) of the 16-byte
+// pieces that cover [from, from + bytes) of `source`, whose base is 16-byte aligned, into a shared slice at the same
+// offset modulo 16; its completion flips the phase of the mbarrier. Pieces must lie inside the source: the caller clips.
+__device__ __forceinline__ void bulk_copy_in(const uint8_t* source, uint32_t first_piece_byte, uint32_t size, uint32_t slice,
+                                             uint32_t barrier_at) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barrier_at), "r"(size) : "memory");
+  if (size) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(slice),
+                 "l"(source + first_piece_byte), "r"(size), "r"(barrier_at)
+                 : "memory");
+  }
+}
+
+// The warp's copy of a span: thread 0 issues the bulk copy of the whole 16-byte pieces inside the source; where the
+// span's last piece crosses the source's end (the last unit of a container), the threads bring the bytes short of the
+// end in with plain loads, and what lies beyond stays as it was: a valid stream never looks at it.
+__device__ __forceinline__ void copy_in_span(const uint8_t* __restrict__ source, uint32_t limit, uint32_t from, uint32_t bytes,
+                                             uint32_t slice, uint8_t* slice_generic, uint32_t barrier_at, uint32_t lane) {
+  const uint32_t aligned = from & ~15u;
+  uint32_t size = ((from & 15u) + bytes + 15u) & ~15u;
+  if (size > limit - min(aligned, limit)) {
+    const uint32_t whole = (limit & ~15u) - min(aligned, limit & ~15u);
+    const uint32_t rest_from = aligned + whole;
+    if (rest_from + lane < limit && lane < 16u) slice_generic[whole + lane] = source[rest_from + lane];
+    size = whole;
+  }
+  if (lane == 0) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the slice was last touched through ordinary loads and stores
+    bulk_copy_in(source, aligned, size, slice, barrier_at);
+  }
+}
+
+__device__ __forceinline__ uint16_t bf16_bits(uint32_t exponent, uint32_t sign_mantissa) {
+  return static_cast<uint16_t>(((sign_mantissa & 0x80u) << 8) | (exponent << 7) | (sign_mantissa & 0x7Fu));
+}
+
+// Four bf16 values from four exponents and four sign/mantissa bytes: per value the high byte is sign | exponent >> 1
+// and the low byte exponent << 7 | mantissa, each a bitwise select under 0x80 per byte (one lop3), then interleaved.
+__device__ __forceinline__ uint2 merge_bf16x4(uint32_t exponents, uint32_t sign_mantissa) {
+  uint32_t low, high;
+  asm("lop3.b32 %0, %1, %2, 0x80808080, 0xE4;" : "=r"(low) : "r"(exponents << 7), "r"(sign_mantissa));
+  asm("lop3.b32 %0, %1, %2, 0x80808080, 0xE4;" : "=r"(high) : "r"(sign_mantissa), "r"(exponents >> 1));
+  return make_uint2(__byte_perm(low, high, 0x5140), __byte_perm(low, high, 0x7362));
+}
+
+// Walks this thread's region: `left` codewords from bit `bit` of the warp's stream slice on. STAGED: exponents go to the
+// warp's shared slice from `target` on (a shared address). Otherwise values go straight to the output from `element` on.
+// Every thread of the warp runs the same instructions: a finished thread takes zero symbols, the four byte stores are
+// predicated on the number of symbols delivered, and the one-symbol path for codewords longer than the window is
+// entered by the whole warp in rounds where some thread needs it. The stream word two ahead is read at the top of a
+// round, before the advance is known, so that the look-up is the only shared-memory read on the path from one round to
+// the next. The two halves of a round are written out in PTX to keep them at the instructions they need: the
+// compiler's version of the same statements came to twice as many.
+// The walk ends when the codewords are used up, wherever the cursor then is: `left` is at most the number of bits in a
+// region (checked when the unit is opened) and a codeword at most 32 bits, so a corrupt stream reads at most
+// 32 x bytes_per_thread bytes past its region, which the block's shared memory is padded for. Returns the final cursor.
+// HELD: regions of 16 bytes. A thread then reads its four stream words once (one 16-byte load, no bank conflicts), takes
+// the look-ahead word from its neighbour, and feeds the window from registers: the walk reads shared memory for the
+// look-ups only, and a corrupt stream cannot take it past what it holds.
+template <bool STAGED, bool HELD>
+__device__ __forceinline__ uint32_t walk_region(const DecodeParams& p, const uint16_t* tables, uint32_t multi_at, uint32_t words_at,
+                                                uint32_t bit, uint32_t left, uint32_t target, uint32_t element) {
+  uint32_t word_at = words_at + ((bit >> 5) << 2);   // shared address of the word the cursor is in
+  uint32_t current, next, third = 0u, fourth = 0u, fifth = 0u;
+  if (HELD) {
+    // bit < 32 + the region's first bit: the cursor starts in the region's first word
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(current), "=r"(next), "=r"(third), "=r"(fourth) : "r"(word_at));
+    uint32_t beyond;   // the warp's last region looks ahead into the word behind the unit's stream bytes
+    asm volatile("ld.shared.u32 %0, [%1+16];" : "=r"(beyond) : "r"(word_at));
+    fifth = __shfl_down_sync(0xFFFFFFFFu, current, 1);
+    if (lane_id() == 31u) fifth = beyond;
+    third = byte_swap(third);
+    fourth = byte_swap(fourth);
+    fifth = byte_swap(fifth);
+  } else {
+    asm volatile("ld.shared.u32 %0, [%2];\n\tld.shared.u32 %1, [%2+4];" : "=r"(current), "=r"(next) : "r"(word_at));
+  }
+  current = byte_swap(current);
+  next = byte_swap(next);
+  while (__any_sync(0xFFFFFFFFu, left != 0u)) {
+    uint32_t window, symbols, found, advance, after = 0u, slow;
+    if (!HELD) {
+      asm volatile("ld.shared.u32 %0, [%1+8];" : "=r"(after) : "r"(word_at));
+      after = byte_swap(after);
+    }
+    asm volatile(
+        "{\n\t"
+        ".reg .pred act, none;\n\t"
+        ".reg .b32 idx, fy, held, sh;\n\t"
+        "shf.l.wrap.b32 %0, %6, %7, %5;\n\t"           // the 32 bits under the cursor (the shift wraps at 32)
+        "mul.hi.u32 idx, %0, 2048;\n\t"                // window >> 21, on the multiplier: the shifter is the busier unit
+        "mad.lo.u32 idx, idx, 8, %9;\n\t"
+        "ld.shared.v2.u32 {%1, fy}, [idx];\n\t"         // up to four codewords of the next 11 bits
+        "mul.hi.u32 held, fy, 256;\n\t"                // fy >> 24
+        "min.u32 %2, held, %8;\n\t"                    // a finished thread (none left) takes none
+        "shl.b32 sh, %2, 2;\n\t"
+        "shr.u32 %3, fy, sh;\n\t"
+        "and.b32 %3, %3, 15;\n\t"                        // bits consumed by `found` codewords (field 0 is zero)
+        "setp.ne.u32 act, %8, 0;\n\t"
+        "setp.eq.and.u32 none, held, 0, act;\n\t"
+        "selp.u32 %4, 1, 0, none;\n\t"
+        "}\n"
+        : "=&r"(window), "=&r"(symbols), "=&r"(found), "=&r"(advance), "=&r"(slow)
+        : "r"(bit), "r"(next), "r"(current), "r"(left), "r"(multi_at));
+    if (__any_sync(0xFFFFFFFFu, slow)) {
+      if (slow) {
+        uint32_t entry = tables[window >> 24];
+        uint32_t peek = window;
+#pragma unroll 1
+        for (int hop = 0; hop < 3 && (entry & kPointerFlag); ++hop) {  // code longer than this level: the next byte picks in the child level
+          peek <<= 8;
+          entry = tables[(entry & 0xFFu) * 256u + (peek >> 24)];
+        }
+        symbols = entry & 0xFFu;
+        found = 1u;
+        advance = (entry >> 8) & 0x3Fu;
+      }
+    }
+    if (STAGED) {
+      asm volatile(
+          "{\n\t"
+          ".reg .pred q;\n\t"
+          ".reg .b32 b;\n\t"
+          "setp.gt.u32 q, %1, 0;\n\t"
+          "@q st.shared.u8 [%0], %2;\n\t"
+          "setp.gt.u32 q, %1, 1;\n\t"
+          "mul.hi.u32 b, %2, 16777216;\n\t"             // symbols >> 8, and so on: multiplier again
+          "@q st.shared.u8 [%0+1], b;\n\t"
+          "setp.gt.u32 q, %1, 2;\n\t"
+          "mul.hi.u32 b, %2, 65536;\n\t"
+          "@q st.shared.u8 [%0+2], b;\n\t"
+          "setp.gt.u32 q, %1, 3;\n\t"
+          "mul.hi.u32 b, %2, 256;\n\t"
+          "@q st.shared.u8 [%0+3], b;\n\t"
+          "}\n" ::"r"(target),
+          "r"(found), "r"(symbols)
+          : "memory");
+      target += found;
+    } else {
+      for (uint32_t k = 0; k < found; ++k) p.out[element + k] = bf16_bits((symbols >> (8u * k)) & 0xFFu, p.sign_mantissa[element + k]);
+      element += found;
+    }
+    if (HELD) {
+      asm volatile(
+          "{\n\t"
+          ".reg .pred cross;\n\t"
+          ".reg .b32 moved, changed;\n\t"
+          "sub.u32 %0, %0, %6;\n\t"
+          "add.u32 moved, %1, %7;\n\t"
+          "xor.b32 changed, moved, %1;\n\t"
+          "setp.gt.u32 cross, changed, 31;\n\t"          // into the next word (at most one: a codeword has 32 bits at most)
+          "mov.b32 %1, moved;\n\t"
+          "@cross mov.b32 %2, %3;\n\t"
+          "@cross mov.b32 %3, %4;\n\t"                   // the words still to come move up
+          "@cross mov.b32 %4, %5;\n\t"
+          "@cross mov.b32 %5, %8;\n\t"
+          "}\n"
+          : "+r"(left), "+r"(bit), "+r"(current), "+r"(next), "+r"(third), "+r"(fourth)
+          : "r"(found), "r"(advance), "r"(fifth));
+    } else {
+      asm volatile(
+          "{\n\t"
+          ".reg .pred cross;\n\t"
+          ".reg .b32 moved, changed;\n\t"
+          "sub.u32 %0, %0, %5;\n\t"
+          "add.u32 moved, %1, %6;\n\t"
+          "xor.b32 changed, moved, %1;\n\t"
+          "setp.gt.u32 cross, changed, 31;\n\t"
+          "mov.b32 %1, moved;\n\t"
+          "@cross mov.b32 %2, %3;\n\t"
+          "@cross mov.b32 %3, %7;\n\t"
+          "@cross add.u32 %4, %4, 4;\n\t"               // the cursor's word in shared memory
+          "}\n"
+          : "+r"(left), "+r"(bit), "+r"(current), "+r"(next), "+r"(word_at)
+          : "r"(found), "r"(advance), "r"(after));
+    }
+  }
+  return bit;
+}
+
+template <bool HELD>
+__global__ void __launch_bounds__(kWarpKernelMaxWarps * 32, kWarpKernelBlocksPerSm) dfloat11_decode_warps_kernel(const DecodeParams p) {
+  extern __shared__ __align__(16) uint32_t shared[];
+  // layout: fused tables u16[levels][256] | multi-symbol table uint2[2048] | mbarriers: tables, then two per warp |
+  //         per warp: stream bytes [32 * bytes_per_thread + 48] | exponents [stage_alloc + 32] | sign/mantissa [stage_alloc + 32] |
+  //         32 * bytes_per_thread + 64 bytes that only a walk over a corrupt stream reads
+  const int levels = p.num_luts - 1;
+  const uint32_t table_words = level_table_words(levels) + 2u * (1u << kKeptMultiBits);
+  const uint32_t shared_base = static_cast<uint32_t>(__cvta_generic_to_shared(shared));
+  const uint16_t* const tables = reinterpret_cast<const uint16_t*>(shared);
+  const uint32_t multi_at = shared_base + level_table_words(levels) * 4u;
+
+  const uint32_t lane = lane_id();
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t warps = blockDim.x >> 5;
+  const uint32_t region_bytes = static_cast<uint32_t>(p.bytes_per_thread);
+  const uint32_t stream_slice = 32u * region_bytes + 48u;
+  const uint32_t byte_slice = static_cast<uint32_t>(p.stage_alloc) + 32u;
+  const uint32_t barrier_bytes = (8u + 16u * warps + 15u) & ~15u;
+  const uint32_t tables_barrier = shared_base + table_words * 4u;
+  const uint32_t stream_barrier = tables_barrier + 8u + 16u * warp;   // flips when the warp's stream bytes are in
+  const uint32_t rest_barrier = stream_barrier + 8u;                    // flips when its sign/mantissa bytes are in
+  const uint32_t slices_offset = table_words * 4u + barrier_bytes + warp * (stream_slice + 2u * byte_slice);
+  uint8_t* const slice = reinterpret_cast<uint8_t*>(shared) + slices_offset;
+  uint8_t* const exponents = slice + stream_slice;
+  uint8_t* const sign_mantissa = slice + stream_slice + byte_slice;
+  const uint32_t words_at = shared_base + slices_offset;
+  const uint32_t exponents_at = words_at + stream_slice;
+  const uint32_t sign_mantissa_at = exponents_at + byte_slice;
+
+  // unit = warp's number in the grid (neighbouring units to neighbouring SMs), then + warps in the grid
+  const uint32_t units = static_cast<uint32_t>(p.units);
+  const uint32_t stride = gridDim.x * warps;
+  const uint32_t runs_per_block = static_cast<uint32_t>(p.units_per_block);
+  const uint32_t stride_blocks = stride / runs_per_block;
+  const uint32_t stride_runs = stride - stride_blocks * runs_per_block;
+  const uint32_t stream_bytes = static_cast<uint32_t>(p.n_bytes);
+  const uint32_t elements = static_cast<uint32_t>(p.n_elements);
+  const uint32_t stage_alloc = static_cast<uint32_t>(p.stage_alloc);
+  UnitCursor next_at;
+  next_at.index = blockIdx.x + warp * gridDim.x;
+  next_at.block = next_at.index / runs_per_block;
+  next_at.run = next_at.index - next_at.block * runs_per_block;
+  uint32_t index = next_at.index;
+  // Order of the requests: the first unit's region records (a warp waits for them first), its stream bytes (the copy
+  // needs no record), then the tables; the records of the unit after it once the first ones are in. Sign/mantissa bytes
+  // are asked for when a unit's walk starts: they are not needed before it ends. Stream bytes, sign/mantissa bytes and
+  // tables come in by bulk copies that one thread issues and the copy engine carries out, so that asking for them
+  // holds no warp up, however much is in flight already.
+  const UnitHead opening = load_unit_head(p, next_at, lane);
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(stream_barrier));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rest_barrier));
+    if (warp == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tables_barrier));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  uint32_t first_byte = opening.region * region_bytes;
+  // the stream bytes of the unit plus four bytes of look-ahead for the last region
+  if (index < units) copy_in_span(p.encoded, stream_bytes, first_byte, 32u * region_bytes + 4u, words_at, slice, stream_barrier, lane);
+  if (threadIdx.x == 0) bulk_copy_in(reinterpret_cast<const uint8_t*>(p.kept_tables), 0u, table_words * 4u, shared_base, tables_barrier);
+  Unit unit = open_unit(p, opening, lane);
+  bool staged = static_cast<uint32_t>(unit.total) <= stage_alloc;
+  step(next_at, stride, stride_blocks, stride_runs, runs_per_block);
+  UnitHead ahead = load_unit_head(p, next_at, lane);
+  __syncthreads();   // the tables' barrier is initialised for every thread to wait on; from here on the warps go their own ways
+  bool copies_arrive = copy_wait(tables_barrier, 0u);
+  uint32_t parity = 0u;   // of the phase the warp's two barriers are in (each flips once per unit)
+  bool stream_ahead = false, rest_asked = false;   // copies in flight beyond the phase `parity` of the stream barrier / on the other one
+  while (index < units && copies_arrive) {
+    stream_ahead = false;
+    const uint32_t shift = unit.start & 15u;                                      // of the unit's first element in the byte slices
+    const bool rest_staged = staged && unit.total > 0;
+    if (rest_staged) {
+      copy_in_span(p.sign_mantissa, elements, unit.start, static_cast<uint32_t>(unit.total), sign_mantissa_at, sign_mantissa, rest_barrier, lane);
+    } else if (lane == 0) {
+      bulk_copy_in(p.sign_mantissa, 0u, 0u, sign_mantissa_at, rest_barrier);   // nothing to bring in: the phase still flips
+    }
+    rest_asked = true;
+    copies_arrive = copy_wait(stream_barrier, parity);   // this unit's stream bytes
+    __syncwarp();
+    if (!copies_arrive) break;
+    const uint32_t first_bit = ((first_byte & 15u) + lane * region_bytes) * 8u;   // of this thread's region in the slice
+    uint32_t cursor;
+    if (staged) {
+      cursor = walk_region<true, HELD>(p, tables, multi_at, words_at, first_bit + unit.gap, static_cast<uint32_t>(unit.count),
+                                 exponents_at + shift + static_cast<uint32_t>(unit.local), 0u);
+    } else {
+      cursor = walk_region<false, HELD>(p, tables, multi_at, words_at, first_bit + unit.gap, static_cast<uint32_t>(unit.count), 0u,
+                                  unit.start + static_cast<uint32_t>(unit.local));
+    }
+    // a region's last codeword starts inside it and has 32 bits at most
+    if (cursor >= first_bit + region_bytes * 8u + 32u) report(p.error, EP_STREAM_NOT_CONSUMED);
+    __syncwarp();
+    // the slice of stream bytes is free: the next unit's can come in while this one is written out
+    first_byte = ahead.region * region_bytes;
+    if (next_at.index < units) {
+      copy_in_span(p.encoded, stream_bytes, first_byte, 32u * region_bytes + 4u, words_at, slice, stream_barrier, lane);
+      stream_ahead = true;
+    }
+    const Unit following = open_unit(p, ahead, lane);
+    const bool following_staged = static_cast<uint32_t>(following.total) <= stage_alloc;
+    copies_arrive = copy_wait(rest_barrier, parity);   // this unit's sign/mantissa bytes
+    __syncwarp();
+    if (!copies_arrive) break;
+    rest_asked = false;
+    if (staged) {
+      // 8 elements (16 bytes of bf16) per thread per round, on 8-element boundaries of the output
+      const uint32_t total = static_cast<uint32_t>(unit.total);
+      const uint32_t head = min(total, (8u - (unit.start & 7u)) & 7u);
+      const uint32_t groups = (total - head) >> 3;
+      uint16_t* const out = p.out + unit.start;
+      const uint8_t* const staged_exponents = exponents + shift;
+      const uint8_t* const staged_rest = sign_mantissa + shift;
+      if (lane < head) out[lane] = bf16_bits(staged_exponents[lane], staged_rest[lane]);
+      for (uint32_t j = head + lane * 8u; j < head + groups * 8u; j += 256u) {
+        const uint2 e = *reinterpret_cast<const uint2*>(staged_exponents + j);
+        const uint2 r = *reinterpret_cast<const uint2*>(staged_rest + j);
+        const uint2 lower = merge_bf16x4(e.x, r.x);
+        const uint2 upper = merge_bf16x4(e.y, r.y);
+        *reinterpret_cast<uint4*>(out + j) = make_uint4(lower.x, lower.y, upper.x, upper.y);
+      }
+      const uint32_t j = head + groups * 8u + lane;
+      if (j < total) out[j] = bf16_bits(staged_exponents[j], staged_rest[j]);
+    }
+    parity ^= 1u;
+    index = next_at.index;
+    step(next_at, stride, stride_blocks, stride_runs, runs_per_block);
+    ahead = load_unit_head(p, next_at, lane);
+    unit = following;
+    staged = following_staged;
+    __syncwarp();   // every thread is done with this unit's slices
+  }
+  if (!copies_arrive) {
+    // A copy did not complete within the limit: say so and take no further unit. What this warp still has in flight
+    // gets one more bounded wait each, so that the block does not retire under a copy into its shared memory.
+    if (lane == 0) report(p.error, EP_KERNEL_TIMEOUT);
+    copy_wait(tables_barrier, 0u);
+    copy_wait(stream_barrier, parity);
+    if (stream_ahead) copy_wait(stream_barrier, parity ^ 1u);
+    if (rest_asked) copy_wait(rest_barrier, parity);
   }
 }
 
@@ -492,6 +949,53 @@ extern "C" int ep_dfloat11_build_decode_tables(const uint8_t* luts_dev, int num_
   return check_launch("dfloat11_decode_kernel (table export)");
 }
 
+// The warp-per-unit kernel, for streams laid out in whole words behind 16-byte aligned bases. EP_ERR_UNSUPPORTED: not
+// such a stream (or slices too large for shared memory); nothing was launched.
+static int launch_decode_warps(DecodeParams p, ep_stream_t stream) {
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(p.encoded) | reinterpret_cast<uintptr_t>(p.sign_mantissa) |
+                          reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.kept_tables);
+  if ((bases & 15u) || (p.bytes_per_thread & 3) || p.bytes_per_thread > 1024) return EP_ERR_UNSUPPORTED;
+  p.units_per_block = (p.threads_per_block + 31) / 32;
+  p.units = p.blocks * p.units_per_block;
+  // the kernel keeps offsets into the stream, the records and the output in 32 bits
+  const int64_t covered = p.blocks * static_cast<int64_t>(p.threads_per_block) * p.bytes_per_thread;
+  if (p.units > 0x3FFFFFFF || covered + 64 > 0xFFFFFFFFll || p.n_elements > 0xFFFFFFFFll) return EP_ERR_UNSUPPORTED;
+  // A warp's byte slices hold an eighth more than the mean unit; a unit above that is decoded without staging.
+  const int64_t mean = (p.n_elements + p.units - 1) / p.units;
+  const int64_t widest = 32 * 8 * static_cast<int64_t>(p.bytes_per_thread);   // a codeword has one bit at least
+  p.stage_alloc = static_cast<int>((std::min(mean + mean / 8 + 48, widest) + 15) & ~int64_t(15));
+  const size_t tables = static_cast<size_t>(level_table_words(p.num_luts - 1) + 2u * (1u << kKeptMultiBits)) * 4;
+  const size_t per_warp = 32u * static_cast<size_t>(p.bytes_per_thread) + 48u + 2u * (static_cast<size_t>(p.stage_alloc) + 32u);
+  const size_t block_room = (227 * 1024) / kWarpKernelBlocksPerSm - 1024;   // the SM's shared memory, less what each block reserves
+  const size_t overrun_pad = 32u * static_cast<size_t>(p.bytes_per_thread) + 64u;   // what a walk over a corrupt stream may read past its slice
+  const auto barriers = [](int warps) { return (static_cast<size_t>(8 + 16 * warps) + 15) & ~size_t(15); };   // mbarriers: tables, two per warp
+  const size_t fixed = tables + overrun_pad + barriers(kWarpKernelMaxWarps);
+  if (fixed + 2 * per_warp > block_room) return EP_ERR_UNSUPPORTED;
+  int warps = static_cast<int>(std::min<size_t>(kWarpKernelMaxWarps, (block_room - fixed) / per_warp));
+  const int64_t slots = static_cast<int64_t>(kSmCount) * kWarpKernelBlocksPerSm;   // blocks in flight
+  if (p.units > warps * slots) {
+    // every warp takes ceil(units / warps in the grid) units one after another: of the block sizes from half the
+    // largest up, take the one that leaves the fewest of those turns empty (the larger one unless the gain is clear)
+    int best = warps;
+    double best_fill = 0.0;
+    for (int w = warps; w >= std::max(2, warps / 2); --w) {
+      const int64_t in_grid = w * slots;
+      const int64_t turns = (p.units + in_grid - 1) / in_grid;
+      const double fill = static_cast<double>(p.units) / static_cast<double>(turns * in_grid);
+      if (fill > best_fill + 0.02) { best_fill = fill; best = w; }
+    }
+    warps = best;
+  }
+  // few units: fewer warps to a block, so that the blocks still spread over the SMs
+  warps = static_cast<int>(std::min<int64_t>(warps, std::max<int64_t>(2, (p.units + slots - 1) / slots)));
+  const size_t shared = tables + barriers(warps) + warps * per_warp + overrun_pad;
+  const int64_t grid = std::min<int64_t>(slots, (p.units + warps - 1) / warps);
+  const auto kernel = p.bytes_per_thread == 16 ? dfloat11_decode_warps_kernel<true> : dfloat11_decode_warps_kernel<false>;
+  if (shared > 48 * 1024) EP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared)));
+  kernel<<<static_cast<unsigned>(grid), warps * 32, shared, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("dfloat11_decode_warps_kernel");
+}
+
 extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const uint8_t* encoded_dev, int64_t n_bytes,
                                   const uint8_t* sign_mantissa_dev, const uint32_t* output_positions_dev,
                                   const uint16_t* thread_meta_dev, void* output_dev, int64_t n_elements, int bytes_per_thread,
@@ -527,6 +1031,11 @@ extern "C" int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const u
   p.stage_elems = max_block_elems;
   p.error = error_dev;
   p.kept_tables = static_cast<const uint32_t*>(decode_tables_dev);
+  p.blocks = blocks;
+  if (kept) {
+    const int rc = launch_decode_warps(p, stream);
+    if (rc != EP_ERR_UNSUPPORTED) return rc;   // else: a layout the warp kernel does not take, the block kernel does
+  }
   const int threads = (threads_per_block + 31) / 32 * 32;
   const size_t block_words = ((block_bytes + 3) / 4 + 3) & ~size_t(1);
   const size_t stage_bytes = (static_cast<size_t>(max_block_elems) + 16 + 15) & ~size_t(15);

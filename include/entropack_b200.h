@@ -308,8 +308,13 @@ int ep_dfloat11_decode(const uint8_t* luts_dev, int num_luts, const uint8_t* enc
  * reference rebuilds nothing per decode either -- its kernel reads luts as stored (dfloat11.cu:314-522); this is the
  * form that kernel's look-ups take here. ep_dfloat11_decode_tables_bytes gives the size, ep_dfloat11_build_decode_tables
  * fills a 16-byte aligned device buffer of that size from luts (one small launch); passed to ep_dfloat11_decode as
- * decode_tables_dev it replaces the table build at the head of every CUDA block by a copy. With a null
- * decode_tables_dev the decode builds a 10-bit table itself. */
+ * decode_tables_dev it replaces the table build at the head of every CUDA block by a copy, and, where the layout
+ * allows it, selects the faster of the two decode kernels: one warp per run of 32 regions, persistent blocks, inputs
+ * brought in by bulk copies ahead of their use. That kernel takes containers whose bytes_per_thread is a multiple of 4,
+ * whose encoded / sign_mantissa / output buffers start on 16-byte boundaries and whose stream and element counts fit
+ * 32 bits; any other container is decoded by the block-per-format-block kernel with the same tables. A bulk copy that
+ * does not complete within its bounded wait ends the decode with EP_KERNEL_TIMEOUT in *error_dev. With a null
+ * decode_tables_dev the decode builds a 10-bit table itself (block kernel). */
 int64_t ep_dfloat11_decode_tables_bytes(int num_luts);
 int ep_dfloat11_build_decode_tables(const uint8_t* luts_dev, int num_luts, void* tables_dev, int64_t tables_bytes,
                                     ep_stream_t stream);

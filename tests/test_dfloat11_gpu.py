@@ -15,12 +15,19 @@ def _to_device(buffers: dict):
 
 
 def _gpu_decode(buffers: dict) -> np.ndarray:
+    """Three decodes of one container: tables built by every CUDA block (block-per-format-block kernel), then the
+    kept tables made and used, then used again (warp-per-unit kernel where the layout allows it). All must agree."""
     from entropack_b200.schemes.dfloat11 import b200
 
-    error = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = b200.decode(_to_device(buffers), error=error)
-    assert int(error.item()) == 0
-    return out.view(torch.int16).cpu().numpy().view(np.uint16)
+    device_buffers = _to_device(buffers)
+    results = []
+    for _ in range(3):
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = b200.decode(device_buffers, error=error)
+        assert int(error.item()) == 0
+        results.append(out.view(torch.int16).cpu().numpy().view(np.uint16))
+    assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
+    return results[0]
 
 
 @pytest.mark.parametrize("name", golden_names("dfloat11_"))
@@ -66,7 +73,8 @@ def test_encode_reproduces_reference_bitstreams(name):
 
 
 @pytest.mark.parametrize("n,bpt,tpb", [(1 << 20, 16, 128), (700001, 16, 128), (50000, 5, 32), (123457, 37, 96), (33, 16, 128), (1, 16, 128),
-                                      (300000, 255, 64)])
+                                      (300000, 255, 64), (400000, 8, 256), (250000, 12, 100), (600000, 64, 64), (90000, 8, 32),
+                                      (5000, 16, 1024)])
 def test_against_oracle_both_directions(oracle_module, n, bpt, tpb):
     g = torch.Generator().manual_seed(n)
     values = torch.randn(n, generator=g) * torch.exp(torch.randn(n, generator=g) * (3.0 if n % 2 else 0.3)) * 0.02
@@ -77,6 +85,22 @@ def test_against_oracle_both_directions(oracle_module, n, bpt, tpb):
         assert np.array_equal(ours[key], expected[key]), key
     assert np.array_equal(_gpu_decode(expected), bits)
     assert np.array_equal(oracle_module.dfloat11_decode(ours, use_regions=True), bits)
+
+
+def test_runs_of_equal_exponents_beside_wide_ones(oracle_module):
+    """Half the tensor zeros (one-bit codewords, 128 to a region), half values of every magnitude: the zero half's
+    runs of 32 regions decode to far more elements than the mean run, which the warp kernel's shared slices are sized
+    from, so they take its path without staging."""
+    n = 1 << 20
+    g = torch.Generator().manual_seed(11)
+    values = torch.randn(n, generator=g) * torch.exp(torch.randn(n, generator=g) * 4.0)
+    values[n // 3: n // 3 + n // 2] = 0.0
+    bits = values.to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    expected = oracle_module.dfloat11_encode(bits, 16, 128)
+    counts = expected["thread_meta"].astype(np.int64) & 2047
+    per_run = counts.reshape(-1, 32).sum(axis=1)
+    assert per_run.max() > 1.25 * per_run.mean() + 64     # the case is what it claims to be
+    assert np.array_equal(_gpu_decode(expected), bits)
 
 
 def test_full_size_round_trip_public_api():
@@ -102,13 +126,27 @@ def test_malformed_metadata_is_reported_not_faulted():
     positions = buffers["output_positions"].copy()
     positions[1] = positions[-1] + 1000
     bad["output_positions"] = positions
-    error = torch.zeros(1, dtype=torch.int32, device="cuda")
-    b200.decode(_to_device(bad), error=error)
-    torch.cuda.synchronize()
-    assert int(error.item()) != 0
+    device_bad = _to_device(bad)
+    for _ in range(3):   # both decode kernels
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        b200.decode(device_bad, error=error)
+        torch.cuda.synchronize()
+        assert int(error.item()) != 0
+    bad = dict(buffers)
+    meta = buffers["thread_meta"].copy()
+    meta[: meta.size // 2] |= 2047   # more codewords than any region can hold
+    bad["thread_meta"] = meta
+    device_bad = _to_device(bad)
+    for _ in range(3):
+        error = torch.zeros(1, dtype=torch.int32, device="cuda")
+        b200.decode(device_bad, error=error)
+        torch.cuda.synchronize()
+        assert int(error.item()) != 0
     bad = dict(buffers)
     luts = buffers["luts"].copy()
     luts[0, :] = 255  # every byte of level 0 points at a child level that may not exist
     bad["luts"] = luts
-    b200.decode(_to_device(bad))
-    torch.cuda.synchronize()
+    device_bad = _to_device(bad)
+    for _ in range(3):
+        b200.decode(device_bad)
+        torch.cuda.synchronize()
