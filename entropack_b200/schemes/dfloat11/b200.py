@@ -16,21 +16,17 @@ from .format import DFloat11Buffers, make_layout, parse_layout_cached
 _MAX_LUT_ROWS = 65
 
 
-def decode_tables(buffers: DFloat11Buffers) -> torch.Tensor | None:
-    """The container's decode tables (fused level tables + an 11-bit multi-symbol table, 17 KB), built on the device once
-    and kept on the layout tensor so that later decodes copy them into shared memory instead of rebuilding a smaller
-    table at the head of every CUDA block. A container that is decoded only once never gets them: the first decode
-    builds its table inside the kernel and this returns None; the second builds the kept copy. Must not be first reached
-    during a stream capture."""
+def decode_tables(buffers: DFloat11Buffers) -> torch.Tensor:
+    """The container's decode tables (fused level tables + an 11-bit multi-symbol table, 17 KB), built on the device by
+    one small launch at the container's first decode and kept on the layout tensor. With them the decode runs the
+    warp-per-run kernel, which copies them into shared memory; building them first and decoding with that kernel takes
+    less time than one decode by the kernel that builds its own table in every CUDA block, so even a container that is
+    decoded once gets them."""
     layout = buffers.layout
     device = buffers.luts.device
     cached = getattr(layout, "_dfloat11_decode_tables", None)
     if cached is not None and cached.device == device:
         return cached
-    seen = getattr(layout, "_dfloat11_decodes", 0)
-    layout._dfloat11_decodes = seen + 1
-    if seen == 0:
-        return None
     lib = _native.load()
     luts = buffers.luts.contiguous()
     nbytes = lib.ep_dfloat11_decode_tables_bytes(int(luts.shape[0]))
@@ -45,8 +41,10 @@ def decode_tables(buffers: DFloat11Buffers) -> torch.Tensor | None:
     return tables
 
 
-def decode(buffers: DFloat11Buffers, *, error: torch.Tensor | None = None) -> torch.Tensor:
-    """Decode to a flat bf16 tensor on the buffers' device (one launch, no host sync after the first call)."""
+def decode(buffers: DFloat11Buffers, *, error: torch.Tensor | None = None, kept_tables: bool = True) -> torch.Tensor:
+    """Decode to a flat bf16 tensor on the buffers' device (one launch, two at a container's first decode; no host sync).
+    ``kept_tables=False`` decodes without the container's kept tables, by the kernel that builds a table in every CUDA
+    block (what a caller of the C entry point gets who passes no tables)."""
     sign_mantissa = buffers.sign_mantissa
     _native.require_cuda(sign_mantissa)
     bpt, tpb, widest = parse_layout_cached(buffers.layout)
@@ -60,7 +58,7 @@ def decode(buffers: DFloat11Buffers, *, error: torch.Tensor | None = None) -> to
     if buffers.luts.ndim != 2 or buffers.luts.shape[1] != 256 or buffers.luts.shape[0] < 2:
         raise ValueError(f"dfloat11 luts must be [levels + 1, 256], got {tuple(buffers.luts.shape)}")
     out = torch.empty(n, dtype=torch.bfloat16, device=sign_mantissa.device)
-    tables = decode_tables(buffers)
+    tables = decode_tables(buffers) if kept_tables else None
     with torch.cuda.device(sign_mantissa.device):
         status = _native.load().ep_dfloat11_decode(
             _native.ptr(buffers.luts.contiguous()), int(buffers.luts.shape[0]), _native.ptr(buffers.encoded_exponent),

@@ -15,15 +15,15 @@ def _to_device(buffers: dict):
 
 
 def _gpu_decode(buffers: dict) -> np.ndarray:
-    """Three decodes of one container: tables built by every CUDA block (block-per-format-block kernel), then the
-    kept tables made and used, then used again (warp-per-unit kernel where the layout allows it). All must agree."""
+    """Three decodes of one container: by the kernel that builds its table in every CUDA block, then with the kept
+    tables made and used (warp-per-run kernel where the layout allows it), then with them found again. All must agree."""
     from entropack_b200.schemes.dfloat11 import b200
 
     device_buffers = _to_device(buffers)
     results = []
-    for _ in range(3):
+    for call in range(3):
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
-        out = b200.decode(device_buffers, error=error)
+        out = b200.decode(device_buffers, error=error, kept_tables=call > 0)
         assert int(error.item()) == 0
         results.append(out.view(torch.int16).cpu().numpy().view(np.uint16))
     assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
@@ -32,15 +32,15 @@ def _gpu_decode(buffers: dict) -> np.ndarray:
 
 @pytest.mark.parametrize("name", golden_names("dfloat11_"))
 def test_kept_decode_tables_decode_like_tables_built_in_the_kernel(name):
-    """First decode of a container: 10-bit multi-symbol table built by every CUDA block; second: builds the 11-bit tables
-    that are kept on the container; later ones copy those in. All give the source bits."""
+    """Without kept tables: a 10-bit multi-symbol table built by every CUDA block. With them: the 11-bit tables built at
+    the container's first decode, kept on it and copied in by every decode. All give the source bits."""
     from entropack_b200.schemes.dfloat11 import b200
 
     record = load_golden(f"dfloat11_{name}")
     device_buffers = _to_device(buffers_of(record))
-    for call in range(3):
+    for call, kept in enumerate((False, True, True, False)):
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
-        out = b200.decode(device_buffers, error=error)
+        out = b200.decode(device_buffers, error=error, kept_tables=kept)
         assert int(error.item()) == 0
         assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), record["input_bits"]), f"decode {call + 1} differs"
         assert (getattr(device_buffers.layout, "_dfloat11_decode_tables", None) is not None) == (call >= 1)
@@ -127,9 +127,9 @@ def test_malformed_metadata_is_reported_not_faulted():
     positions[1] = positions[-1] + 1000
     bad["output_positions"] = positions
     device_bad = _to_device(bad)
-    for _ in range(3):   # both decode kernels
+    for call in range(3):   # both decode kernels
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
-        b200.decode(device_bad, error=error)
+        b200.decode(device_bad, error=error, kept_tables=call > 0)
         torch.cuda.synchronize()
         assert int(error.item()) != 0
     bad = dict(buffers)
@@ -137,9 +137,9 @@ def test_malformed_metadata_is_reported_not_faulted():
     meta[: meta.size // 2] |= 2047   # more codewords than any region can hold
     bad["thread_meta"] = meta
     device_bad = _to_device(bad)
-    for _ in range(3):
+    for call in range(3):
         error = torch.zeros(1, dtype=torch.int32, device="cuda")
-        b200.decode(device_bad, error=error)
+        b200.decode(device_bad, error=error, kept_tables=call > 0)
         torch.cuda.synchronize()
         assert int(error.item()) != 0
     bad = dict(buffers)
@@ -147,6 +147,6 @@ def test_malformed_metadata_is_reported_not_faulted():
     luts[0, :] = 255  # every byte of level 0 points at a child level that may not exist
     bad["luts"] = luts
     device_bad = _to_device(bad)
-    for _ in range(3):
-        b200.decode(device_bad)
+    for call in range(3):
+        b200.decode(device_bad, kept_tables=call > 0)
         torch.cuda.synchronize()
