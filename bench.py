@@ -13,7 +13,8 @@ containers. Bytes per step = container bytes (header excluded) read once + dense
              (one region per step, a 512 MB L2 flush between steps outside the timed regions).
   e2e        the same decode through the public API starting from pinned HOST blobs: host->device
              copy of each blob, decode, device->host copy of each dense result, all inside the timed
-             region.
+             region. `to_device_only_per_gpu_GBps_rank0` beside it: the same call leaving the results on
+             the device (a checkpoint load), one byte read back.
   roofline   per-launch CUDA-event timing of the decode kernel (the only kernel in the step):
              algorithmic bytes / average launch time against the measured HBM copy bandwidth.
   cpu_baseline / --impl reference
@@ -453,6 +454,21 @@ def run_b200(args) -> None:
     clocks = sampler.stop() if rank == 0 else None
     assert torch.equal(host_outputs[0], launches[0][4].view(torch.uint8).reshape(-1).cpu())
 
+    # For context, what loading a checkpoint costs: the same call without host outputs leaves the dense tensors on the
+    # device (what a model wants), and the step reads one byte of the last one back. Not the headline: the reference arm
+    # decodes into host memory, so the number compared with it keeps the full download.
+    def load_step():
+        dense = ep.decompress_many(host_blobs, config, device=device)
+        return int(dense[-1].view(torch.uint8).reshape(-1)[-1].item())
+
+    load_step()
+    barrier()
+    load_begin = time.perf_counter()
+    for _ in range(e2e_steps):
+        load_step()
+    barrier()
+    load_seconds = time.perf_counter() - load_begin
+
     if distributed:
         timed_keys = ("seconds", "decode_seconds", "forward_seconds", "mixed_seconds")
         times = torch.tensor([total_ms, e2e_seconds] + [model[key] for key in timed_keys], dtype=torch.float64, device=device)
@@ -492,7 +508,8 @@ def run_b200(args) -> None:
         "e2e": {"value": world * bytes_per_step * e2e_steps / e2e_seconds / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
                 "per_gpu_GBps": bytes_per_step * e2e_steps / e2e_seconds / 1e9,
-                "host_cpus_near_gpu": None if bound_cpus is None else len(bound_cpus)},
+                "host_cpus_near_gpu": None if bound_cpus is None else len(bound_cpus),
+                "to_device_only_per_gpu_GBps_rank0": bytes_per_step * e2e_steps / load_seconds / 1e9},
         "others": others,
         "sharded_linear": sharded,
         "model_encode": {"workload": "synthetic DiT, 276 linears (hidden 3840, mlp 10240), bf16 N(0,0.02^2), 4 bpp, layers sharded "
@@ -748,6 +765,11 @@ def measure_others(ep, device, flush, reps: int) -> dict:
             dense.weight.copy_((torch.randn(out_features, in_features, generator=generator, device=device) * 0.02).to(torch.bfloat16))
         layer = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0))
         decoded = layer.dequantize()
+        # the same layer with the low-latency preset: half-length tiles halve the serial decode chain (reference-decodable)
+        preset = ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig.low_latency(target_bpp=4.0))
+        norm = dense.weight.float().norm()
+        rel_l2 = float((decoded.float() - dense.weight.float()).norm() / norm)
+        preset_rel_l2 = float((preset.dequantize().float() - dense.weight.float()).norm() / norm)
         for tokens in (1, 16, 256, 4096):
             x = torch.randn(tokens, in_features, generator=generator, device=device).to(torch.bfloat16)
             reference = torch.nn.functional.linear(x.float(), decoded.float())
@@ -757,7 +779,9 @@ def measure_others(ep, device, flush, reps: int) -> dict:
                 "compressed_forward_us": timed(lambda: layer(x)) * 1e3,
                 "library_gemm_us": timed(lambda: linear_forward(x, decoded)) * 1e3,
                 "cublas_dense_us": timed(lambda: torch.nn.functional.linear(x, dense.weight)) * 1e3,
-                "max_rel_err": error, "bits": layer.compressed_bits,
+                "max_rel_err": error, "bits": layer.compressed_bits, "rel_l2": rel_l2,
+                "low_latency_forward_us": timed(lambda: preset(x)) * 1e3, "low_latency_bits": preset.compressed_bits,
+                "low_latency_rel_l2": preset_rel_l2,
             }
             if tokens == 4096:
                 entry["library_gemm_tflops"] = 2.0 * tokens * out_features * in_features / entry["library_gemm_us"] / 1e6

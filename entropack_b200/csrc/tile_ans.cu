@@ -379,13 +379,31 @@ tile_ans_decode_kernel(const DecodeParams p) {
     // The merge phase below reads this block's raw bytes (512 per raw lane) right after the chain phase; asking L2 for
     // them now takes the DRAM part of that latency off the warp's serial path. Four threads per raw lane, one 128-byte
     // line each (plus one for a stream that straddles a fifth line).
-    if (NLANES > 1 && raw_mask != 0u) {
+    if (NLANES > 1 && raw_mask != 0u && !(NLANES == 2 && RAW_MASK == 1)) {
 #pragma unroll
       for (int b = 0; b < NLANES; ++b) {
         if (((raw_mask >> b) & 1u) && lane < 5u) {
           const uint8_t* line = payload_bytes + 2 * static_cast<int64_t>(raw_begin[b]) + block_lo + static_cast<int>(lane) * 128;
           if (line < payload_bytes + 2 * p.payload_words) asm volatile("prefetch.global.L2 [%0];" ::"l"(line));
         }
+      }
+    }
+    // fp16 / bf16 (low byte raw, high byte coded): the block's raw words are asked for here, into registers, and are
+    // there when the chain phase is over; no prefetch, no wait in the merge phase.
+    constexpr bool kRawAhead = NLANES == 2 && RAW_MASK == 1;
+    const bool lean = full && wide && !(raw_near_end && block_hi == count);
+    uint32_t ahead[2][3] = {{0u, 0u, 0u}, {0u, 0u, 0u}};
+    bool odd_start = false;   // the raw stream starts on an odd 16-bit word: eight bytes then straddle three payload words
+    if (kRawAhead && lean) {
+      const uint32_t first = raw_begin[0];
+      odd_start = first & 1u;
+      const uint32_t* const source =
+          reinterpret_cast<const uint32_t*>(p.payload) + ((first >> 1) + (static_cast<uint32_t>(block_lo) >> 2) + lane * 2u);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        ahead[half][0] = __ldg(source + 64 * half);
+        ahead[half][1] = __ldg(source + 64 * half + 1);
+        if (odd_start) ahead[half][2] = __ldg(source + 64 * half + 2);
       }
     }
     // ---- chain phase: groups of 32 symbols, back to front; only the tile's last group can be partial
@@ -402,7 +420,56 @@ tile_ans_decode_kernel(const DecodeParams p) {
     }
     __syncwarp();
     // ---- merge phase: raw bytes + staged symbols -> whole elements
-    if (full && wide && !(raw_near_end && block_hi == count)) {
+    if (kRawAhead && lean) {
+      // a thread makes 8 elements from two of the words it asked for (funnelled out of three where the raw stream starts
+      // on an odd 16-bit word) and 8 staged symbols, twice per block
+      const uint32_t staged = (coded[NLANES - 1].stage - lane) + lane * 8u;
+      uint4* const target = reinterpret_cast<uint4*>(out + block_lo) + lane;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const uint32_t low = odd_start ? __funnelshift_r(ahead[half][0], ahead[half][1], 16) : ahead[half][0];
+        const uint32_t high = odd_start ? __funnelshift_r(ahead[half][1], ahead[half][2], 16) : ahead[half][1];
+        const uint2 symbols = *reinterpret_cast<const uint2*>(shared_bytes + staged + 256 * half);
+        target[32 * half] = make_uint4(__byte_perm(low, symbols.x, 0x5140), __byte_perm(low, symbols.x, 0x7362),
+                                       __byte_perm(high, symbols.y, 0x5140), __byte_perm(high, symbols.y, 0x7362));
+      }
+    } else if (lean && NLANES == 4 && RAW_MASK == 7) {
+      // fp32 with three raw bytes and the top byte coded, written out for the least arithmetic: a thread makes 4 elements
+      // from two payload words per raw lane (funnelled by 16 bits where that lane's stream starts on an odd 16-bit word)
+      // and 4 staged symbols, four times per block, the loads of two rounds in flight together; every address is one
+      // 32-bit index plus literal offsets.
+      const uint32_t word = (static_cast<uint32_t>(block_lo) >> 2) + lane;
+      const uint32_t* const payload32 = reinterpret_cast<const uint32_t*>(p.payload);
+      const uint32_t staged = ((coded[NLANES - 1].stage - lane) >> 2) + lane;   // in 32-bit words
+      uint4* const target = reinterpret_cast<uint4*>(out + block_lo) + lane;
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {
+        uint32_t raw[2][3];
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+          const uint32_t first = raw_begin[b];
+          const uint32_t* const source = payload32 + ((first >> 1) + word + 64u * pair);
+          if (first & 1u) {
+            const uint32_t a = __ldg(source), a1 = __ldg(source + 1), c = __ldg(source + 32), c1 = __ldg(source + 33);
+            raw[0][b] = __funnelshift_r(a, a1, 16);
+            raw[1][b] = __funnelshift_r(c, c1, 16);
+          } else {
+            raw[0][b] = __ldg(source);
+            raw[1][b] = __ldg(source + 32);
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t symbols = shared_tables[staged + 32 * (2 * pair + k)];
+          const uint32_t ab_low = __byte_perm(raw[k][0], raw[k][1], 0x5140);
+          const uint32_t ab_high = __byte_perm(raw[k][0], raw[k][1], 0x7362);
+          const uint32_t cd_low = __byte_perm(raw[k][2], symbols, 0x5140);
+          const uint32_t cd_high = __byte_perm(raw[k][2], symbols, 0x7362);
+          target[32 * (2 * pair + k)] = make_uint4(__byte_perm(ab_low, cd_low, 0x5410), __byte_perm(ab_low, cd_low, 0x7632),
+                                                   __byte_perm(ab_high, cd_high, 0x5410), __byte_perm(ab_high, cd_high, 0x7632));
+        }
+      }
+    } else if (lean) {
       // Every thread gathers kGroup consecutive bytes of each lane (one vector read of the staging block, or
       // aligned 32-bit loads of the raw stream, shifted by 16 bits where the stream starts on an odd word),
       // transposes them into kGroup whole elements and stores 16 bytes.
