@@ -628,7 +628,7 @@ __global__ void __launch_bounds__(kByteWarps * 32, kByteBlocksPerSm) tile_ans_de
   ring_commit();
 
   const auto upkeep = [&]() {
-    if (cursor <= refill_at) {
+    if (__any_sync(0xFFFFFFFFu, cursor <= refill_at)) {   // the same in every thread; the vote tells the compiler so
       refill_at -= 2 * Ring::kChunk;
       chunk -= 1;
       ring_wait_all();
