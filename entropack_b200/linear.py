@@ -65,6 +65,23 @@ def check_kernel_errors(device: torch.device | None = None) -> None:
             _native.raise_stream_error(code, f"a product on {where}")
 
 
+def prepare_decode_plans(module: torch.nn.Module) -> int:
+    """Builds the per-container decode plans (kept decode tables) of every compressed layer under ``module`` whose
+    container is on a CUDA device, and returns how many were built.
+
+    A layer otherwise gets its plan along the way (the lossy scheme at a container's second decode), with an allocation
+    and an extra launch in the middle of an early forward pass. Calling this once after a model is loaded and moved to
+    its device makes the first pass as fast as the later ones and leaves no allocation for a pass that is being
+    captured into a CUDA graph. The reference builds its plan per container at the first decode
+    (entropack/schemes/lattice_rans/cuda.py:697-741) and has no call for a whole model."""
+    built = 0
+    for layer in module.modules():
+        container = getattr(layer, "weight", None)
+        if isinstance(layer, CompressedLinear) and isinstance(container, CompressedTensor) and container.device.type == "cuda":
+            built += bool(container.scheme.prepare_decode_plan(container.buffers, shape=tuple(container.shape)))
+    return built
+
+
 def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                    error: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T + bias`` in bf16 through ``ep_linear_forward`` (CUDA-core kernel for up to 16 tokens,

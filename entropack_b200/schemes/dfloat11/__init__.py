@@ -32,6 +32,15 @@ class DFloat11Scheme(Scheme):
 
         parse_layout_cached(buffers["layout"])
 
+    def prepare_decode_plan(self, buffers: dict, *, shape: tuple[int, ...]) -> bool:
+        from . import b200
+
+        packed = packed_buffers(buffers, DFloat11Buffers)
+        if packed.layout.device.type != "cuda" or getattr(packed.layout, "_dfloat11_decode_tables", None) is not None:
+            return False
+        b200.decode_tables(packed)
+        return True
+
     def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: DFloat11Config,
                error: torch.Tensor | None = None) -> torch.Tensor:
         buffers = packed_buffers(packed, DFloat11Buffers)

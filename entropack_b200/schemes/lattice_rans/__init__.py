@@ -47,6 +47,12 @@ class LatticeRANSScheme(Scheme):
         cached_parse(buffers["layout"], parse_layout, "_lattice_rans_layout")
         max_alphabet(packed_buffers(buffers, LatticeBuffers))
 
+    def prepare_decode_plan(self, buffers: dict, *, shape: tuple[int, ...]) -> bool:
+        from . import b200
+
+        packed = packed_buffers(buffers, LatticeBuffers)
+        return packed.layout.device.type == "cuda" and b200.prepare_plan(packed, shape=tuple(shape))
+
     def decode(self, packed: dict, *, shape: tuple[int, ...], dtype: torch.dtype, config: EntroPackLossyConfig,
                error: torch.Tensor | None = None) -> torch.Tensor:
         buffers = packed_buffers(packed, LatticeBuffers)

@@ -28,19 +28,21 @@ def max_alphabet(buffers: LatticeBuffers) -> int:
     return cached
 
 
-def slot_tables(buffers: LatticeBuffers, prob_bits: int, alphabet: int, device: torch.device) -> torch.Tensor | None:
+def slot_tables(buffers: LatticeBuffers, prob_bits: int, alphabet: int, device: torch.device, *, build_now: bool = False) -> torch.Tensor | None:
     """The container's decode plan: its 17 slot tables, built on the device once and kept on the layout tensor (as the
     reference keeps its plan, entropack/schemes/lattice_rans/cuda.py:697-741) so that later decodes copy them into
     shared memory instead of rebuilding them from the stored frequencies at the head of every launch. A container
     that is decoded only once never gets one: the first decode builds its tables inside the kernel and this returns
-    None; the second builds the kept copy (139 KB at prob_bits 11). Must not be first reached during a stream capture."""
+    None; the second builds the kept copy (139 KB at prob_bits 11), and so does a call with ``build_now`` (what
+    ``prepare_plan`` makes for every layer of a model before its first pass). Must not be first reached during a stream
+    capture."""
     layout = buffers.layout
     cached = getattr(layout, "_lattice_rans_slot_tables", None)
     if cached is not None and cached.device == device:
         return cached
     seen = getattr(layout, "_lattice_rans_decodes", 0)
     layout._lattice_rans_decodes = seen + 1
-    if seen == 0:
+    if seen == 0 and not build_now:
         return None
     lib = _native.load()
     nbytes = lib.ep_lattice_slot_tables_bytes(prob_bits, alphabet)
@@ -54,6 +56,20 @@ def slot_tables(buffers: LatticeBuffers, prob_bits: int, alphabet: int, device: 
     _native.check(status, "lattice_rans slot tables")
     layout._lattice_rans_slot_tables = tables
     return tables
+
+
+def prepare_plan(buffers: LatticeBuffers, *, shape) -> bool:
+    """Builds the container's kept slot tables now (see ``slot_tables``). False when they were there already or the
+    container's tables are of the kind that stays in global memory and is rebuilt per call."""
+    _native.require_cuda(buffers.payload)
+    if getattr(buffers.layout, "_lattice_rans_slot_tables", None) is not None:
+        return False
+    info = decode_geometry(buffers._asdict(), shape)
+    _check_lengths(buffers, info)
+    alphabet = max_alphabet(buffers)
+    if _native.load().ep_lattice_slot_tables_bytes(info["prob_bits"], alphabet) <= 0:
+        return False
+    return slot_tables(buffers, info["prob_bits"], alphabet, buffers.payload.device, build_now=True) is not None
 
 
 def _tables_or_scratch(buffers: LatticeBuffers, prob_bits: int, alphabet: int, device: torch.device, what: str):

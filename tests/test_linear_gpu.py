@@ -31,6 +31,39 @@ def test_compressed_linear_forward_matches_dense_on_decoded_weight(tokens):
     assert float((weight.float() - dense.weight.float()).norm() / dense.weight.float().norm()) < 0.09
 
 
+def test_decode_plans_of_a_model_are_built_up_front():
+    """``prepare_decode_plans`` gives every compressed layer of a module its kept decode tables before the first pass;
+    a pass with them gives what a pass of freshly compressed layers gives, which build their tables on the way."""
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(8)
+
+    def make():
+        layers = []
+        for index, (out_features, in_features, config) in enumerate((
+                (512, 1024, ep.EntroPackLossyConfig(target_bpp=4.0)), (768, 512, ep.EntroPackLossyConfig(target_bpp=6.0)),
+                (256, 768, ep.DFloat11Config()), (512, 256, ep.TileANSConfig()))):
+            dense = torch.nn.Linear(in_features, out_features, bias=index % 2 == 0, device="cuda", dtype=torch.bfloat16)
+            with torch.no_grad():
+                dense.weight.copy_((torch.randn(out_features, in_features, generator=torch.Generator(device="cuda").manual_seed(index),
+                                                device="cuda") * 0.02).to(torch.bfloat16))
+                if dense.bias is not None:
+                    dense.bias.zero_()
+            layers.append(ep.CompressedLinear.from_linear(dense, config=config))
+        return torch.nn.Sequential(*layers)
+
+    prepared, plain = make(), make()
+    assert ep.prepare_decode_plans(prepared) == 3          # two lossy containers and the DFloat11 one; Tile-ANS keeps no plan
+    assert ep.prepare_decode_plans(prepared) == 0          # nothing left to build
+    for layer in list(prepared)[:2]:
+        assert getattr(layer.weight.buffers["layout"], "_lattice_rans_slot_tables", None) is not None
+    assert getattr(prepared[2].weight.buffers["layout"], "_dfloat11_decode_tables", None) is not None
+    for tokens in (2, 300):
+        x = torch.randn(tokens, 1024, generator=g, device="cuda").to(torch.bfloat16)
+        assert torch.equal(prepared(x), plain(x))
+    ep.check_kernel_errors()
+
+
 def test_lossless_default_config_round_trips_exactly():
     import entropack_b200 as ep
 
