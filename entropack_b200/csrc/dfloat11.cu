@@ -498,10 +498,10 @@ __device__ __forceinline__ uint32_t walk_region(const DecodeParams& p, const uin
         ".reg .pred act, none;\n\t"
         ".reg .b32 idx, fy, held, sh;\n\t"
         "shf.l.wrap.b32 %0, %6, %7, %5;\n\t"           // the 32 bits under the cursor (the shift wraps at 32)
-        "mul.hi.u32 idx, %0, 2048;\n\t"                // window >> 21, on the multiplier: the shifter is the busier unit
+        "shr.u32 idx, %0, 21;\n\t"
         "mad.lo.u32 idx, idx, 8, %9;\n\t"
         "ld.shared.v2.u32 {%1, fy}, [idx];\n\t"         // up to four codewords of the next 11 bits
-        "mul.hi.u32 held, fy, 256;\n\t"                // fy >> 24
+        "shr.u32 held, fy, 24;\n\t"
         "min.u32 %2, held, %8;\n\t"                    // a finished thread (none left) takes none
         "shl.b32 sh, %2, 2;\n\t"
         "shr.u32 %3, fy, sh;\n\t"
@@ -534,13 +534,13 @@ __device__ __forceinline__ uint32_t walk_region(const DecodeParams& p, const uin
           "setp.gt.u32 q, %1, 0;\n\t"
           "@q st.shared.u8 [%0], %2;\n\t"
           "setp.gt.u32 q, %1, 1;\n\t"
-          "mul.hi.u32 b, %2, 16777216;\n\t"             // symbols >> 8, and so on: multiplier again
+          "shr.u32 b, %2, 8;\n\t"
           "@q st.shared.u8 [%0+1], b;\n\t"
           "setp.gt.u32 q, %1, 2;\n\t"
-          "mul.hi.u32 b, %2, 65536;\n\t"
+          "shr.u32 b, %2, 16;\n\t"
           "@q st.shared.u8 [%0+2], b;\n\t"
           "setp.gt.u32 q, %1, 3;\n\t"
-          "mul.hi.u32 b, %2, 256;\n\t"
+          "shr.u32 b, %2, 24;\n\t"
           "@q st.shared.u8 [%0+3], b;\n\t"
           "}\n" ::"r"(target),
           "r"(found), "r"(symbols)
