@@ -15,6 +15,7 @@
 #include <type_traits>
 
 #include "ep_common.cuh"
+#include <cstdlib>
 #include "rans_ring.cuh"
 
 namespace ep {
@@ -950,6 +951,11 @@ int launch_staged_shape(const DecodeParams& p, size_t table_bytes, cudaStream_t 
     if (fits_sm(big, kByteBlocksPerSm)) return launch_staged<NLANES, RAW_MASK, 8, kByteWarps>(p, big, stream);
     const size_t wide = staged_shared_bytes<8>(table_bytes, lanes, kWarps);
     if (fits_sm(wide, kDecodeBlocksPerSm)) return launch_staged<NLANES, RAW_MASK, 8, kWarps>(p, wide, stream);
+  }
+  if (NLANES == 4 && RAW_MASK == 7) {
+    // fp32 with its top byte coded: 14-warp blocks as well (a table staged for 14 tiles, four copies an SM), 128-word chunks
+    const size_t tall = staged_shared_bytes<7>(table_bytes, lanes, kByteWarps);
+    if (fits_sm(tall, kByteBlocksPerSm)) return launch_staged<NLANES, RAW_MASK, 7, kByteWarps>(p, tall, stream);
   }
   return launch_staged<NLANES, RAW_MASK, 7, kWarps>(p, staged_shared_bytes<7>(table_bytes, lanes, kWarps), stream);
 }
