@@ -51,7 +51,7 @@ METRIC = "decode GB/s/GPU (HBM frac)"
 # kind (`ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum --clock-control none -k regex:tile_ans_decode
 # -s 1 -c 1 python bench.py --only tile_ans_decode --kind <kind> --reps 2`). A capture, not a live measurement: it is
 # dated, and goes stale when the decode kernel's memory behaviour changes.
-DRAM_TRAFFIC = {"captured": "2026-11-25", "bytes": {"fp8_e4m3": 86.55e6, "int8": 85.29e6, "fp16": 220.24e6, "fp32": 468.45e6}}
+DRAM_TRAFFIC = {"captured": "2026-11-25", "bytes": {"fp8_e4m3": 86.55e6, "int8": 85.29e6, "fp16": 220.24e6, "fp32": 468.38e6}}
 DRAM_TRAFFIC_BYTES = float(sum(DRAM_TRAFFIC["bytes"].values()))
 
 

@@ -473,7 +473,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       return symbol;
     };
     auto upkeep = [&]() {
-      while (cursor <= refill_at) {    // at most once where the stream is intact
+      // at most once where the stream is intact; the test is the same in every thread, and the vote tells the compiler so
+      while (__any_sync(0xFFFFFFFFu, cursor <= refill_at)) {
         refill_at -= 2 * Ring::kChunk;
         chunk -= 1;
         ring_wait_all();
@@ -529,6 +530,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
         // upkeep every kStepsPerUpkeep steps at most: after fields 3 and 7 (five and four steps), or 1, 4 and 7
         if (Ring::kStepsPerUpkeep >= 8 ? (field == 3 || field == 7) : (field == 1 || field == 4 || field == 7)) upkeep();
       }
+      // voted here, where every thread of the warp still is (a partial group's idle threads skip what follows): one
+      // branch for the warp below, whose other side is for no real tensor
+      const bool tame = __all_sync(0xFFFFFFFFu, scale < 1.0e33f);
       if (valid) {
         const int4 low = *reinterpret_cast<const int4*>(&field_min[coset][0]);
         const int4 high = *reinterpret_cast<const int4*>(&field_min[coset][4]);
@@ -567,7 +571,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
           }
         } else if (MODE == kModeStoreBf16) {
           // |z + c/2| < 2^15.5, so the product can only leave the bf16 range when the scale is astronomically large
-          if (scale < 1.0e33f) {
+          if (tame) {
             uint4 packed;
             const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
             const __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
