@@ -229,3 +229,22 @@ def test_streamed_pieces_cover_every_unit_once_and_ramp_up():
     # units larger than a piece: one granule at a time
     big = SimpleNamespace(units=20, unit_output_bytes=1 << 20, granule=8)
     assert _piece_runs(big, 1 << 20, 1 << 10) == [(0, 8), (8, 8), (16, 4)]
+
+
+def test_reference_arm_of_the_bench_prints_its_line_without_a_gpu():
+    """`bench.py --impl reference` times the CPU oracle on the host cores and needs no GPU: one JSON line with the
+    headline metric's name and unit, the CPU baseline's description and an end-to-end entry without transfers."""
+    import json
+    import subprocess
+    import sys
+
+    done = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                          capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert done.returncode == 0, done.stderr[-2000:]
+    line = json.loads(done.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "GB/s" and line["higher_is_better"] is True
+    assert line["metric"].startswith("decode GB/s") and line["config"]["workload"] == "c2_tile_ans_decode"
+    assert line["value"] > 0 and line["n_gpus"] == 1 and line["steps"] == 1
+    baseline = line["cpu_baseline"]
+    assert baseline["kind"] == "port" and baseline["cores"] >= 1 and baseline["value"] == line["value"] and baseline["sample"]
+    assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
