@@ -74,7 +74,7 @@ def test_encode_reproduces_reference_bitstreams(name):
 
 @pytest.mark.parametrize("n,bpt,tpb", [(1 << 20, 16, 128), (700001, 16, 128), (50000, 5, 32), (123457, 37, 96), (33, 16, 128), (1, 16, 128),
                                       (300000, 255, 64), (400000, 8, 256), (250000, 12, 100), (600000, 64, 64), (90000, 8, 32),
-                                      (5000, 16, 1024)])
+                                      (5000, 16, 1024), (60000, 8, 20), (60000, 16, 48), (3000000, 16, 128)])
 def test_against_oracle_both_directions(oracle_module, n, bpt, tpb):
     g = torch.Generator().manual_seed(n)
     values = torch.randn(n, generator=g) * torch.exp(torch.randn(n, generator=g) * (3.0 if n % 2 else 0.3)) * 0.02
