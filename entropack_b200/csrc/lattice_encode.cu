@@ -208,40 +208,74 @@ __device__ __forceinline__ void bin_layout(const int* minmax, int* offset, int* 
   offset[kTables] = cursor;
 }
 
+// Counts go to shared-memory bins first and are folded into the global ones at the end. Where all the tables' bins fit
+// the shared array they are all there; where they do not (alphabets of a thousand symbols and more: fine scales on
+// heavy-tailed rows), every field table keeps a window of `shared_capacity / 16` bins around the value 0, where
+// nearly all of its symbols fall, and only what lies outside takes a global atomic.
 __global__ void __launch_bounds__(kThreads) histogram_kernel(const int16_t* __restrict__ fields, const uint8_t* __restrict__ cosets,
                                                              int64_t vectors, const int* __restrict__ minmax, int* __restrict__ bins,
                                                              int bins_capacity, int shared_capacity, int* __restrict__ bins_used) {
   extern __shared__ int shared_bins[];
   __shared__ int offset[kTables + 1];
   __shared__ int sym_min[kTables];
+  __shared__ int window_min[kTables];    // windowed mode: the value of a table's first shared bin
   if (threadIdx.x == 0) bin_layout(minmax, offset, sym_min);
   __syncthreads();
   const int total = offset[kTables];
   if (blockIdx.x == 0 && threadIdx.x == 0) bins_used[0] = total;
   if (total > bins_capacity) return;
   const bool staged = total <= shared_capacity;
-  if (staged) {
-    for (int t = threadIdx.x; t < total; t += kThreads) shared_bins[t] = 0;
-    __syncthreads();
+  const int window = (shared_capacity - 2) / 16;   // bins per field table in windowed mode (the coset's two come first)
+  if (!staged && threadIdx.x < kTables) {
+    const int t = threadIdx.x;
+    // centred on 0, moved inside the table's own range where that starts above or ends below
+    const int bins_here = offset[t + 1] - offset[t];
+    const int first = max(sym_min[t], min(-window / 2, sym_min[t] + bins_here - window));
+    window_min[t] = t == 0 ? 0 : first;
   }
+  const int staged_bins = staged ? total : 2 + 16 * window;
+  for (int t = threadIdx.x; t < staged_bins; t += kThreads) shared_bins[t] = 0;
+  __syncthreads();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; v < vectors; v += stride) {
     const int c = cosets[v];
     const uint4 raw = *reinterpret_cast<const uint4*>(fields + v * 8);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    if (staged) atomicAdd(&shared_bins[c], 1); else atomicAdd(&bins[c], 1);
+    atomicAdd(&shared_bins[c], 1);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int value = static_cast<int16_t>((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu);
       const int table = 1 + j * 2 + c;
-      const int bin = offset[table] + (value - sym_min[table]);
-      if (staged) atomicAdd(&shared_bins[bin], 1); else atomicAdd(&bins[bin], 1);
+      if (staged) {
+        atomicAdd(&shared_bins[offset[table] + (value - sym_min[table])], 1);
+      } else {
+        const int in_window = value - window_min[table];
+        if (static_cast<unsigned>(in_window) < static_cast<unsigned>(window)) {
+          atomicAdd(&shared_bins[2 + (table - 1) * window + in_window], 1);
+        } else {
+          atomicAdd(&bins[offset[table] + (value - sym_min[table])], 1);
+        }
+      }
     }
   }
+  __syncthreads();
   if (staged) {
-    __syncthreads();
     for (int t = threadIdx.x; t < total; t += kThreads) {
       if (shared_bins[t]) atomicAdd(&bins[t], shared_bins[t]);
+    }
+  } else {
+    for (int t = threadIdx.x; t < staged_bins; t += kThreads) {
+      const int count = shared_bins[t];
+      if (!count) continue;
+      if (t < 2) {
+        atomicAdd(&bins[t], count);
+      } else {
+        const int table = 1 + (t - 2) / window;
+        const int value = window_min[table] + (t - 2) % window;
+        const int bin = value - sym_min[table];
+        // a window may reach past a narrow table's range: nothing was counted there
+        if (bin >= 0 && bin < offset[table + 1] - offset[table]) atomicAdd(&bins[offset[table] + bin], count);
+      }
     }
   }
 }
