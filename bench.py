@@ -426,7 +426,7 @@ def run_b200(args) -> None:
     # whole-model encode: this rank's share of the synthetic 276-linear DiT at 4 bpp (layers sharded, no collectives)
     model = measure_model_encode(ep, device, rank, world) if not args.headline_only else {
         "seconds": 0.0, "layers": 0, "bpp": 0.0, "decode_seconds": 0.0, "forward_seconds": 0.0, "forward_graph_seconds": None,
-        "plans": 0, "plans_seconds": 0.0,
+        "plans": 0, "plans_seconds": 0.0, "forward_ahead_seconds": 0.0, "forward_ahead_graph_seconds": None,
         "mixed_seconds": 0.0, "mixed_bpp": 0.0}
 
     # the package's one collective: the output all-gather of a column-sharded layer (every rank takes part)
@@ -518,6 +518,8 @@ def run_b200(args) -> None:
                          "mean_bpp_rank0": model["bpp"], "decode_all_seconds": model["decode_seconds"],
                          "decode_plans_built_rank0": model["plans"], "decode_plans_seconds_rank0": model["plans_seconds"],
                          "forward_4096_tokens_seconds": model["forward_seconds"],
+                         "forward_4096_tokens_decode_ahead_seconds_rank0": model["forward_ahead_seconds"],
+                         "forward_4096_tokens_decode_ahead_cuda_graph_seconds_rank0": model["forward_ahead_graph_seconds"],
                          "forward_4096_tokens_cuda_graph_seconds_rank0": model["forward_graph_seconds"], "mixed_2p3_bpp_encode_seconds": model["mixed_seconds"],
                          "mixed_mean_bpp_rank0": model["mixed_bpp"]},
         "gpu_launches": len(launches) * args.steps,
@@ -671,6 +673,19 @@ def measure_model_encode(ep, device, rank: int, world: int) -> dict:
         torch.cuda.synchronize(device)
     forward_seconds = time.perf_counter() - begin
 
+    # the same pass with every layer's weight decoded ahead where that pays (two small layers in a row)
+    with torch.no_grad(), ep.DecodeAhead(layers) as ahead:
+        for layer in layers[:12]:
+            layer(tokens[layer.in_features])
+        ahead.drain()
+        torch.cuda.synchronize(device)
+        begin = time.perf_counter()
+        for layer in layers:
+            layer(tokens[layer.in_features])
+        ahead.drain()
+        torch.cuda.synchronize(device)
+        ahead_seconds = time.perf_counter() - begin
+
     # the same pass replayed from a CUDA graph: one submission for all the layers' kernels, no host work between them
     graph_seconds = None
     try:
@@ -691,6 +706,31 @@ def measure_model_encode(ep, device, rank: int, world: int) -> dict:
         del graph
     except Exception as error:      # capture is an optimisation of the host side only; report why it was not available
         graph_seconds = f"unavailable: {type(error).__name__}: {error}"[:200]
+
+    # and the decode-ahead pass from a graph: the two streams' kernels become branches of the graph, with no host in between
+    ahead_graph_seconds = None
+    try:
+        capture_stream = torch.cuda.Stream(device)
+        capture_stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(capture_stream), torch.no_grad(), ep.DecodeAhead(layers, cyclic=False) as ahead:
+            for layer in layers[:12]:
+                layer(tokens[layer.in_features])
+            ahead.drain()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=capture_stream):
+                for layer in layers:
+                    layer(tokens[layer.in_features])
+                ahead.drain()
+        torch.cuda.current_stream(device).wait_stream(capture_stream)
+        graph.replay()
+        torch.cuda.synchronize(device)
+        begin = time.perf_counter()
+        graph.replay()
+        torch.cuda.synchronize(device)
+        ahead_graph_seconds = time.perf_counter() - begin
+        del graph
+    except Exception as error:
+        ahead_graph_seconds = f"unavailable: {type(error).__name__}: {error}"[:200]
     del layers, tokens
 
     mixed_seconds, mixed_stored = 0.0, 0
@@ -703,7 +743,8 @@ def measure_model_encode(ep, device, rank: int, world: int) -> dict:
         mixed_seconds += time.perf_counter() - begin
         mixed_stored += container.storage_nbytes()
     return {"seconds": seconds, "layers": len(mine), "bpp": stored * 8 / max(1, elements), "decode_seconds": decode_seconds,
-            "plans": plans, "plans_seconds": plans_seconds,
+            "plans": plans, "plans_seconds": plans_seconds, "forward_ahead_seconds": ahead_seconds,
+            "forward_ahead_graph_seconds": ahead_graph_seconds,
             "forward_seconds": forward_seconds, "forward_graph_seconds": graph_seconds, "mixed_seconds": mixed_seconds, "mixed_bpp": mixed_stored * 8 / max(1, elements)}
 
 
@@ -797,6 +838,35 @@ def measure_others(ep, device, flush, reps: int) -> dict:
                 entry["library_gemm_tflops"] = 2.0 * tokens * out_features * in_features / entry["library_gemm_us"] / 1e6
                 entry["cublas_tflops"] = 2.0 * tokens * out_features * in_features / entry["cublas_dense_us"] / 1e6
             results[f"linear_{in_features}x{out_features}_M{tokens}"] = entry
+
+    # Decode-ahead: four different 3840 x 3840 layers called in a ring at 4096 tokens, each decoding its weight on every
+    # call; plain (decode, then product) against DecodeAhead (the next layer's weight decoded on a second stream on 52
+    # SMs while the current product runs on 96). Per-layer time over 16 calls inside one pair of events.
+    ring = []
+    for _ in range(4):
+        dense = torch.nn.Linear(3840, 3840, bias=False, device=device, dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_((torch.randn(3840, 3840, generator=generator, device=device) * 0.02).to(torch.bfloat16))
+        ring.append(ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0)))
+    ep.prepare_decode_plans(torch.nn.ModuleList(ring))
+    x = torch.randn(4096, 3840, generator=generator, device=device).to(torch.bfloat16)
+
+    def ring_pass(calls=16):
+        h = None
+        for index in range(calls):
+            h = ring[index % 4](x)
+        return h
+
+    plain_out = ring_pass(4)
+    plain_us = timed(ring_pass) * 1e3 / 16
+    with ep.DecodeAhead(ring) as ahead:
+        ahead_out = ring_pass(4)
+        ahead_us = timed(ring_pass) * 1e3 / 16
+        found_ready = ahead.decoded_ahead
+    results["linear_ring_4x3840x3840_M4096"] = {
+        "forward_us_per_layer": plain_us, "decode_ahead_forward_us_per_layer": ahead_us, "weights_found_decoded": found_ready,
+        "same_output": bool(torch.equal(plain_out, ahead_out))}
+    del ring, x
 
     # FP8 layer (codes lattice-coded at 5 bpp): activation quantisation + scaled fp8 product on the library's
     # tcgen05 kernel, against torch._scaled_mm on the same codes

@@ -6,6 +6,7 @@ compute runs in hand-written CUDA kernels reached through a C ABI (``include/ent
 there is no CPU or eager execution path.
 """
 from .compression import CompressedTensor, CompressionFallbackWarning, compress, decompress, decompress_many
+from .decode_ahead import DecodeAhead
 from .linear import CompressedFP8Linear, CompressedINT8Linear, CompressedLinear, check_kernel_errors, prepare_decode_plans
 from .registry import DispatchError
 from .schemes import CompressionConfig, DFloat11Config, EntroPackLossyConfig, LatticeRANSConfig, RawConfig, TileANSConfig
@@ -13,7 +14,7 @@ from .schemes import CompressionConfig, DFloat11Config, EntroPackLossyConfig, La
 __version__ = "0.1.0"
 
 __all__ = [
-    "CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DFloat11Config", "DispatchError", "EntroPackLossyConfig",
+    "CompressedFP8Linear", "CompressedINT8Linear", "CompressedLinear", "CompressedTensor", "CompressionConfig", "CompressionFallbackWarning", "DFloat11Config", "DecodeAhead", "DispatchError", "EntroPackLossyConfig",
     "LatticeRANSConfig", "RawConfig", "TileANSConfig",
     "__version__", "check_kernel_errors", "compress", "decompress", "decompress_many", "prepare_decode_plans",
 ]

@@ -29,6 +29,7 @@ _i64, _i32, _f64, _f32, _ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_double, ct
 #: name -> argument types; every function returns int status unless listed in _RESTYPES
 _PROTOTYPES = {
     "ep_abi_version": [],
+    "ep_set_sm_limits": [_i32, _i32],
     "ep_tile_ans_decode": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i32, _i32, _ptr, _ptr],
     "ep_tile_ans_decode_tiles": [_ptr, _i64, _ptr, _ptr, _ptr, _ptr, _ptr, _i64, _i64, _i32, _i32, _i64, _i64, _ptr, _ptr],
     "ep_tile_ans_histogram": [_ptr, _i64, _i32, _ptr, _ptr],

@@ -12,6 +12,11 @@ constexpr int kNumStates = 32;            // interleaved rANS states per tile ==
 constexpr uint32_t kStateMin = 1u << 15;  // renormalisation threshold, 16-bit words
 constexpr int kSmCount = 148;             // B200
 
+// How many SMs the calling thread's next launches of the lossy decode / the tensor-core product may fill
+// (ep_set_sm_limits); kSmCount when no limit is set.
+int decode_sm_limit();
+int product_sm_limit();
+
 // Records the first CUDA failure text for ep_last_cuda_error() and maps it to EP_ERR_CUDA.
 int record_cuda_error(cudaError_t error, const char* where);
 

@@ -297,7 +297,24 @@ extern "C" const char* ep_status_string(int status) {
   }
 }
 
-extern "C" int ep_abi_version(void) { return 2; }
+namespace ep {
+namespace {
+constexpr int kAllSms = 148;          // B200 (ep_common.cuh's kSmCount; this file is plain C++)
+thread_local int g_decode_sms = 0;    // 0: no limit
+thread_local int g_product_sms = 0;
+}  // namespace
+int decode_sm_limit() { return g_decode_sms > 0 && g_decode_sms < kAllSms ? g_decode_sms : kAllSms; }
+int product_sm_limit() { return g_product_sms > 0 && g_product_sms < kAllSms ? g_product_sms : kAllSms; }
+}  // namespace ep
+
+extern "C" int ep_set_sm_limits(int decode_sms, int product_sms) {
+  if (decode_sms < 0 || product_sms < 0) return EP_ERR_INVALID_ARGUMENT;
+  ep::g_decode_sms = decode_sms;
+  ep::g_product_sms = product_sms;
+  return EP_OK;
+}
+
+extern "C" int ep_abi_version(void) { return 3; }
 
 extern "C" const char* ep_last_cuda_error(void) { return ep::g_last_cuda_error.c_str(); }
 

@@ -764,8 +764,9 @@ int launch_lattice_decode(const uint16_t* payload_dev, int64_t payload_words, co
   p.product_out = product_out;
   p.tokens = tokens;
   p.rows = static_cast<int>(rows);
-  // one persistent block per SM; with fewer tiles than SMs, one block per tile
-  const unsigned blocks = static_cast<unsigned>(p.tiles < kSmCount ? p.tiles : kSmCount);
+  // one persistent block per SM (of the SMs this thread's launches may fill); with fewer tiles than that, one block per tile
+  const int sms = decode_sm_limit();
+  const unsigned blocks = static_cast<unsigned>(p.tiles < sms ? p.tiles : sms);
   // one ring per warp, plus one ring's worth of slack for aligning the first to its size
   const size_t ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * WordRing<8>::kBytes;
   const size_t narrow_ring_bytes = static_cast<size_t>(kDecodeWarps + 1) * WordRing<7>::kBytes;

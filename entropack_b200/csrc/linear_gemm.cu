@@ -17,6 +17,7 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstdlib>
 #include <mutex>
 
@@ -969,7 +970,7 @@ int launch_tcgen05(const void* x_dev, const void* weight_dev, const GemmParams& 
   EP_CUDA_CHECK(cudaFuncSetAttribute(linear_tcgen05_kernel<TILE_N, A_ROWS, OPERAND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Shape::kSharedBytes));
   const int64_t tiles = static_cast<int64_t>((p.n + TILE_N - 1) / TILE_N) * ((p.m + kTileM - 1) / kTileM);
-  const int64_t resident = static_cast<int64_t>(kSmCount) * Shape::kBlocksPerSm;
+  const int64_t resident = static_cast<int64_t>(product_sm_limit()) * Shape::kBlocksPerSm;
   const unsigned grid = static_cast<unsigned>(tiles < resident ? tiles : resident);
   linear_tcgen05_kernel<TILE_N, A_ROWS, OPERAND><<<grid, kGemmThreads, Shape::kSharedBytes, s>>>(map_x, map_w, p);
   return EP_OK;
@@ -1054,7 +1055,8 @@ int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams
   int tile_n = 32;
   bool two_blocks = false;
   int64_t best = -1;
-  const int pairs = p.m > kTileM ? resident_pairs<OPERAND>() : 0;
+  const int sms = product_sm_limit();
+  const int pairs = p.m > kTileM ? std::min(resident_pairs<OPERAND>(), sms / 2) : 0;
   if (pairs >= 32) {
     const int64_t row_pairs = (p.m + kPairTileM - 1) / kPairTileM;
     for (int candidate = kPairTileN; candidate >= 64; candidate -= 32) {
@@ -1072,7 +1074,7 @@ int launch_best_tile(const void* x_dev, const void* weight_dev, const GemmParams
     const bool narrow = candidate <= 64;
     const int box_a = narrow ? a_rows : 128;
     const int64_t blocks = row_tiles * ((p.n + candidate - 1) / candidate);
-    const int64_t resident = static_cast<int64_t>(kSmCount) * (box_a < 128 ? 3 : 1);
+    const int64_t resident = static_cast<int64_t>(sms) * (box_a < 128 ? 3 : 1);
     const int64_t cost = ((blocks + resident - 1) / resident) * 2 * (box_a + candidate);
     if (best < 0 || cost < best) {
       best = cost;

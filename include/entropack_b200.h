@@ -50,6 +50,13 @@ const char* ep_status_string(int status);
 int ep_abi_version(void);
 /* Last CUDA runtime error text seen by this library on the calling thread (for EP_ERR_CUDA). */
 const char* ep_last_cuda_error(void);
+/* How many SMs the calling thread's next launches of ep_lattice_decode (decode_sms) and of the tensor-core products
+ * ep_linear_forward / _fp8 / _int8 (product_sms) may fill; 0 lifts a limit. Both kernels are persistent, one block (or
+ * block pair) to an SM, and each needs most of an SM's shared memory, so two of them share the GPU only side by side:
+ * a caller that decodes the next layer's weight on a second stream while the current layer's product runs gives the
+ * decode 52 SMs and the product 96 (what entropack_b200.linear.DecodeAhead does). No reference counterpart: the
+ * reference decodes and multiplies one after the other (entropack/linear/linear.py:163-165). */
+int ep_set_sm_limits(int decode_sms, int product_sms);
 
 /* ---------------------------------------------------------------------------------------------
  * Tile-ANS (lossless, byte-lane rANS).  Buffer schema: entropack/schemes/tile_ans/format.py:58-64.

@@ -64,6 +64,66 @@ def test_decode_plans_of_a_model_are_built_up_front():
     ep.check_kernel_errors()
 
 
+def test_decode_ahead_gives_the_layers_own_outputs():
+    """With ``DecodeAhead`` a layer's weight is decoded on a second stream while the layer before it multiplies (on a
+    share of the SMs each); outputs are bit for bit those of the plain layers, in order, out of order, with layers in
+    the list that it does not handle, and from a CUDA graph captured after a first pass."""
+    import entropack_b200 as ep
+
+    def make(out_features, in_features, config, bias, seed):
+        dense = torch.nn.Linear(in_features, out_features, bias=bias, device="cuda", dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_((torch.randn(out_features, in_features, generator=torch.Generator(device="cuda").manual_seed(seed),
+                                            device="cuda") * 0.02).to(torch.bfloat16))
+        return ep.CompressedLinear.from_linear(dense, config=config)
+
+    lossy = ep.EntroPackLossyConfig(target_bpp=4.0)
+    layers = [make(1024, 1024, lossy, True, 0), make(1536, 1024, lossy, False, 1), make(1024, 1536, lossy, True, 2),
+              make(1024, 1024, ep.DFloat11Config(), False, 3), make(1024, 1024, ep.EntroPackLossyConfig.low_latency(4.0), True, 4)]
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(300, 1024, generator=g, device="cuda").to(torch.bfloat16)
+
+    def run(order=range(len(layers))):
+        outputs, h = [], x
+        for index in order:
+            h = layers[index](h)
+            outputs.append(h)
+        return outputs
+
+    with torch.no_grad():
+        expected = run()
+        with ep.DecodeAhead(layers) as ahead:
+            for _ in range(3):
+                for got, want in zip(run(), expected):
+                    assert torch.equal(got, want)
+            assert ahead.decoded_ahead >= 6         # layers 1 and 2 of every pass, and layer 0 of the later ones
+            # out of order: a layer whose weight was not the one decoded ahead decodes it itself
+            h = layers[2](expected[1])
+            assert torch.equal(h, expected[2])
+            h = layers[0](x)
+            assert torch.equal(h, expected[0])
+            # a captured pass
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                run()
+                ahead.drain()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    captured = run()
+                    ahead.drain()
+            torch.cuda.current_stream().wait_stream(stream)
+            for _ in range(2):
+                graph.replay()
+                torch.cuda.synchronize()
+                for got, want in zip(captured, expected):
+                    assert torch.equal(got, want)
+        assert all(getattr(layer, "_decode_ahead", None) is None for layer in layers)
+        for got, want in zip(run(), expected):
+            assert torch.equal(got, want)
+    ep.check_kernel_errors()
+
+
 def test_lossless_default_config_round_trips_exactly():
     import entropack_b200 as ep
 
