@@ -842,31 +842,32 @@ def measure_others(ep, device, flush, reps: int) -> dict:
     # Decode-ahead: four different 3840 x 3840 layers called in a ring at 4096 tokens, each decoding its weight on every
     # call; plain (decode, then product) against DecodeAhead (the next layer's weight decoded on a second stream on 52
     # SMs while the current product runs on 96). Per-layer time over 16 calls inside one pair of events.
-    ring = []
-    for _ in range(4):
-        dense = torch.nn.Linear(3840, 3840, bias=False, device=device, dtype=torch.bfloat16)
-        with torch.no_grad():
-            dense.weight.copy_((torch.randn(3840, 3840, generator=generator, device=device) * 0.02).to(torch.bfloat16))
-        ring.append(ep.CompressedLinear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=4.0)))
-    ep.prepare_decode_plans(torch.nn.ModuleList(ring))
     x = torch.randn(4096, 3840, generator=generator, device=device).to(torch.bfloat16)
+    for name, layer_cls, bpp in (("linear_ring_4x3840x3840_M4096", ep.CompressedLinear, 4.0),):
+        ring = []
+        for _ in range(4):
+            dense = torch.nn.Linear(3840, 3840, bias=False, device=device, dtype=torch.bfloat16)
+            with torch.no_grad():
+                dense.weight.copy_((torch.randn(3840, 3840, generator=generator, device=device) * 0.02).to(torch.bfloat16))
+            ring.append(layer_cls.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=bpp)))
+        ep.prepare_decode_plans(torch.nn.ModuleList(ring))
 
-    def ring_pass(calls=16):
-        h = None
-        for index in range(calls):
-            h = ring[index % 4](x)
-        return h
+        def ring_pass(calls=16):
+            h = None
+            for index in range(calls):
+                h = ring[index % 4](x)
+            return h
 
-    plain_out = ring_pass(4)
-    plain_us = timed(ring_pass) * 1e3 / 16
-    with ep.DecodeAhead(ring) as ahead:
-        ahead_out = ring_pass(4)
-        ahead_us = timed(ring_pass) * 1e3 / 16
-        found_ready = ahead.decoded_ahead
-    results["linear_ring_4x3840x3840_M4096"] = {
-        "forward_us_per_layer": plain_us, "decode_ahead_forward_us_per_layer": ahead_us, "weights_found_decoded": found_ready,
-        "same_output": bool(torch.equal(plain_out, ahead_out))}
-    del ring, x
+        plain_out = ring_pass(4)
+        plain_us = timed(ring_pass) * 1e3 / 16
+        with ep.DecodeAhead(ring) as ahead:
+            ahead_out = ring_pass(4)
+            ahead_us = timed(ring_pass) * 1e3 / 16
+            found_ready = ahead.decoded_ahead
+        results[name] = {"forward_us_per_layer": plain_us, "decode_ahead_forward_us_per_layer": ahead_us,
+                         "weights_found_decoded": found_ready, "same_output": bool(torch.equal(plain_out, ahead_out))}
+        del ring
+    del x
 
     # FP8 layer (codes lattice-coded at 5 bpp): activation quantisation + scaled fp8 product on the library's
     # tcgen05 kernel, against torch._scaled_mm on the same codes

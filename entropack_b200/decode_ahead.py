@@ -6,9 +6,12 @@ serial rANS chains that no number of SMs makes shorter than about 60 us, the pro
 the integer pipes. Within one layer there is nothing to overlap (every tile's chain ends at the same moment, so no band
 of the weight is ready early). Across layers there is: with the order of the layers known, the weight of the layer
 that runs next is decoded on a second stream, on 52 of the 148 SMs, while the current product runs on the other 96
-(``ep_set_sm_limits``). For two 3840 x 3840 layers at 4096 tokens that is 108 us a layer instead of 135 us (product
-100 us on 96 SMs, decode 66 us on 52, both hidden behind each other). It pays only between two layers that are small
-enough for their tiles to decode side by side on the decode's share; larger layers run as before.
+(``ep_set_sm_limits``). For two 3840 x 3840 layers at 4096 tokens that is 105-108 us a layer instead of 135 us (product
+100 us on 96 SMs, decode 66 us on 52, both hidden behind each other). It pays only where the next layer's tiles all
+decode side by side on that share (at most 1248 tiles: 20 million weights in 16384-symbol tiles, 9 million in the
+8192-symbol tiles of the FP8 layers' default -- four 3840 x 3840 FP8 layers at 5 bpp in a ring measured 122 us a layer
+with a two-round decode ahead against 105 us without) and the current product is not a long one; other layers run as
+before.
 
 The reference decodes and multiplies one after the other (entropack/linear/linear.py:163-165) and has nothing like it.
 """
@@ -25,16 +28,33 @@ DECODE_SMS = 52            # SMs the decode ahead may fill while a product runs
 PRODUCT_SMS = 96           # SMs the product keeps meanwhile
 DECODE_WARPS_PER_SM = 24   # tiles the lossy decode kernel holds per SM
 MIN_TOKENS = 129           # below this the product is not the two-block tensor-core kernel and is over before a decode is
+MAX_PRODUCT_WEIGHTS = 20 << 20   # a longer product loses more on 96 SMs than hiding a decode behind it gains
+
+
+class _Plan:
+    """What is known about a registered layer's weight: looked up once per container."""
+
+    __slots__ = ("container", "rows", "cols", "dtype", "nbytes", "rounds", "packed")
+
+    def __init__(self, container):
+        self.container = container
+        self.rows = self.cols = self.nbytes = self.rounds = 0
+        self.dtype = None
+        self.packed = None
 
 
 class DecodeAhead:
-    """Registers ``layers`` (``CompressedLinear`` modules in the order a forward pass calls them) for decode-ahead.
+    """Registers ``layers`` (compressed linear modules in the order a forward pass calls them) for decode-ahead.
 
     While it is active, a registered layer whose successor is eligible launches its product on ``PRODUCT_SMS`` SMs and
     then, on a second stream, the decode of the successor's weight on ``DECODE_SMS`` SMs into one of two buffers that
     the layers share; the successor's forward finds its weight decoded. A layer called out of order simply decodes
     its own weight as usual. Results are bit for bit what the layers give without it. ``cyclic`` (default) makes the
     last layer's successor the first, for passes that repeat. Use as a context manager or call ``close()``.
+
+    Handled: ``CompressedLinear`` with a lossy-coded bf16 weight, ``CompressedFP8Linear`` / ``CompressedINT8Linear`` with
+    lossy-coded codes; from 129 tokens up; successors of at most 1248 tiles. Other layers in the list run as they always
+    do.
 
     Not for training (it is skipped under autograd). To capture a pass into a CUDA graph: run one pass first (the second
     stream and the buffers are made at the first use), call ``drain()``, capture, and call ``drain()`` again before the
@@ -47,10 +67,10 @@ class DecodeAhead:
         self._position = {id(layer): index for index, layer in enumerate(self.layers)}
         if len(self._position) != len(self.layers):
             raise ValueError("a layer may be registered once in the order given")
-        self._buffers: list[torch.Tensor] | None = None
+        self._buffers: list[torch.Tensor] | None = None                  # two byte buffers
         self._side: torch.cuda.Stream | None = None
         self._pending: tuple[int, int, torch.cuda.Event] | None = None   # (layer position, buffer, decode finished)
-        self._known: dict[int, tuple] = {}                                # per layer: (container, geometry, packed buffers)
+        self._plans: dict[int, _Plan] = {}
         self._latest = 1                                                  # buffer used last
         self.decoded_ahead = 0                                            # how many forwards found their weight ready
         for layer in self.layers:
@@ -79,37 +99,43 @@ class DecodeAhead:
         self.close()
 
     # ------------------------------------------------------------------------------------------------------------
-    def _geometry(self, layer) -> tuple[int, int, int] | None:
-        """(rows, columns, tiles) of a layer whose weight this scheme can decode ahead, else None. Looked up once per
-        container: a layer keeps its answer until its weight is replaced."""
+    def _plan(self, layer) -> _Plan:
         container = getattr(layer, "weight", None)
-        known = self._known.get(id(layer))
-        if known is not None and known[0] is container:
-            return known[1]
-        from .linear import CompressedLinear
+        plan = self._plans.get(id(layer))
+        if plan is not None and plan.container is container:
+            return plan
+        from .linear import CompressedLinear, QuantizedLinear
         from .schemes.base import packed_buffers
         from .schemes.lattice_rans.format import LatticeBuffers, decode_geometry
 
-        geometry, packed = None, None
-        if (type(layer) is CompressedLinear and isinstance(container, CompressedTensor) and container.compress_method == "lattice_rans"
-                and container.encoded_dtype == torch.bfloat16 and container.dtype == torch.bfloat16 and container.device.type == "cuda"
-                and layer.in_features % 8 == 0):
+        plan = _Plan(container)
+        if type(layer) is CompressedLinear:
+            dtype = torch.bfloat16 if (isinstance(container, CompressedTensor) and container.dtype == torch.bfloat16
+                                       and container.encoded_dtype == torch.bfloat16) else None
+        elif isinstance(layer, QuantizedLinear):
+            dtype = layer.code_dtype
+        else:
+            dtype = None
+        if (dtype is not None and isinstance(container, CompressedTensor) and container.compress_method == "lattice_rans"
+                and container.device.type == "cuda" and layer.in_features % 8 == 0):
             info = decode_geometry(container.buffers, tuple(container.shape))
             if info["cols"] == layer.in_features and info["rows"] == layer.out_features:
-                geometry = (info["rows"], info["cols"], info["total_tiles"])
-                packed = packed_buffers(container.buffers, LatticeBuffers)
-        self._known[id(layer)] = (container, geometry, packed)
-        return geometry
+                plan.rows, plan.cols, plan.dtype = info["rows"], info["cols"], dtype
+                plan.nbytes = plan.rows * plan.cols * torch.empty((), dtype=dtype).element_size()
+                # tiles the decode's share of the GPU does not hold at once wait for a second round of rANS chains
+                plan.rounds = -(-info["total_tiles"] // (DECODE_SMS * DECODE_WARPS_PER_SM))
+                plan.packed = packed_buffers(container.buffers, LatticeBuffers)
+        self._plans[id(layer)] = plan
+        return plan
 
-    def _small(self, geometry) -> bool:
-        return geometry is not None and geometry[2] <= DECODE_SMS * DECODE_WARPS_PER_SM
+    def _view(self, plan: _Plan, slot: int) -> torch.Tensor:
+        return self._buffers[slot][: plan.nbytes].view(plan.dtype).view(plan.rows, plan.cols)
 
-    def _decode(self, layer, geometry, buffer: torch.Tensor) -> torch.Tensor:
+    def _decode(self, plan: _Plan, slot: int) -> torch.Tensor:
         from .schemes.lattice_rans import b200
 
-        rows, cols, _ = geometry
-        out = buffer[: rows * cols].view(rows, cols)
-        b200.decode(self._known[id(layer)][2], shape=(rows, cols), dtype=torch.bfloat16, out=out)
+        out = self._view(plan, slot)
+        b200.decode(plan.packed, shape=(plan.rows, plan.cols), dtype=plan.dtype, out=out)
         return out
 
     def _ensure(self, device: torch.device) -> None:
@@ -117,31 +143,31 @@ class DecodeAhead:
             return
         largest = 0
         for layer in self.layers:
-            geometry = self._geometry(layer)
-            if geometry is not None and layer.weight.device == device:
-                largest = max(largest, geometry[0] * geometry[1])
-        self._buffers = [torch.empty(max(1, largest), dtype=torch.bfloat16, device=device) for _ in range(2)]
+            plan = self._plan(layer)
+            if plan.dtype is not None and layer.weight.device == device:
+                largest = max(largest, plan.nbytes)
+        self._buffers = [torch.empty(max(16, largest), dtype=torch.uint8, device=device) for _ in range(2)]
         self._side = torch.cuda.Stream(device)
         self._pending = None
 
     def forward(self, layer, x: torch.Tensor) -> torch.Tensor | None:
         """The layer's output, or None when this call is not one for decode-ahead (the layer then runs as usual)."""
-        from .linear import _native_gemm_applies, linear_forward
+        from .linear import CompressedLinear, _native_gemm_applies, linear_forward
 
-        geometry = self._geometry(layer)
-        if (geometry is None or not x.is_cuda or x.dtype != torch.bfloat16 or x.device != layer.weight.device
-                or (torch.is_grad_enabled() and x.requires_grad) or x.numel() == 0):
+        plan = self._plan(layer)
+        if (plan.dtype is None or not x.is_cuda or x.device != layer.weight.device or x.numel() == 0
+                or (torch.is_grad_enabled() and x.requires_grad)):
             return None
         tokens = x.numel() // x.shape[-1]
         if tokens < MIN_TOKENS:
             return None
         device = x.device
         self._ensure(device)
-        if geometry[0] * geometry[1] > self._buffers[0].numel():
+        if plan.nbytes > self._buffers[0].numel():
             return None
-        rows, cols, _ = geometry
-        bias = layer._bias_on(device)
-        if not _native_gemm_applies(x, self._buffers[0][: rows * cols].view(rows, cols), bias):
+        plain = type(layer) is CompressedLinear
+        bias = layer._bias_on(device) if plain else None
+        if plain and not _native_gemm_applies(x, self._view(plan, 0), bias):
             return None
         main = torch.cuda.current_stream(device)
         position = self._position[id(layer)]
@@ -150,48 +176,49 @@ class DecodeAhead:
         if pending is not None and pending[0] == position:
             slot = pending[1]
             main.wait_event(pending[2])
-            weight = self._buffers[slot][: rows * cols].view(rows, cols)
+            weight = self._view(plan, slot)
             self.decoded_ahead += 1
         else:
             if pending is not None:
                 main.wait_event(pending[2])    # a decode for a layer that did not come next: let it finish, drop it
             slot = 1 - self._latest
-            weight = self._decode(layer, geometry, self._buffers[slot])
+            weight = self._decode(plan, slot)
         self._latest = slot
 
-        follower = None
+        follower_plan = None
         if position + 1 < len(self.layers) or self.cyclic:
             follower_position = (position + 1) % len(self.layers)
             follower = self.layers[follower_position]
-            follower_geometry = self._geometry(follower)
-            if not (self._small(geometry) and self._small(follower_geometry) and follower.weight.device == device
-                    and follower_geometry[0] * follower_geometry[1] <= self._buffers[0].numel()):
-                follower = None
+            candidate = self._plan(follower)
+            if (candidate.dtype is not None and follower.weight.device == device and candidate.nbytes <= self._buffers[0].numel()
+                    and candidate.rounds == 1 and plan.rows * plan.cols <= MAX_PRODUCT_WEIGHTS):
+                follower_plan = candidate
+
+        def product():
+            return linear_forward(x, weight, bias) if plain else layer._forward8(x, codes=weight)
 
         lib = _native.load()
         before_product = torch.cuda.Event()
         before_product.record(main)
-        if follower is None:
-            out = linear_forward(x, weight, bias)
-        else:
-            with torch.cuda.device(device):
-                _native.check(lib.ep_set_sm_limits(0, PRODUCT_SMS), "sm limits")
-                try:
-                    out = linear_forward(x, weight, bias)
-                finally:
-                    lib.ep_set_sm_limits(0, 0)
-        if follower is not None:
-            # The decode ahead writes the other buffer, which the product before this one read last: it may start once
-            # the calling stream has reached the point just before this product (the event was recorded there).
-            side = self._side
-            side.wait_event(before_product)
-            with torch.cuda.stream(side), torch.cuda.device(device):
-                _native.check(lib.ep_set_sm_limits(DECODE_SMS, 0), "sm limits")
-                try:
-                    self._decode(follower, follower_geometry, self._buffers[1 - slot])
-                finally:
-                    lib.ep_set_sm_limits(0, 0)
-                done = torch.cuda.Event()
-                done.record(side)
-            self._pending = (follower_position, 1 - slot, done)
+        if follower_plan is None:
+            return product()
+        with torch.cuda.device(device):
+            _native.check(lib.ep_set_sm_limits(0, PRODUCT_SMS), "sm limits")
+            try:
+                out = product()
+            finally:
+                lib.ep_set_sm_limits(0, 0)
+        # The decode ahead writes the other buffer, which the product before this one read last: it may start once the
+        # calling stream has reached the point just before this product (the event was recorded there).
+        side = self._side
+        side.wait_event(before_product)
+        with torch.cuda.stream(side), torch.cuda.device(device):
+            _native.check(lib.ep_set_sm_limits(DECODE_SMS, 0), "sm limits")
+            try:
+                self._decode(follower_plan, 1 - slot)
+            finally:
+                lib.ep_set_sm_limits(0, 0)
+            done = torch.cuda.Event()
+            done.record(side)
+        self._pending = (follower_position, 1 - slot, done)
         return out

@@ -417,12 +417,21 @@ class QuantizedLinear(CompressedLinear):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         self._require_8bit_gemm(x.device)
-        return _W8A8Function.apply(x, self) if x.requires_grad else self._forward8(x)
+        if x.requires_grad:
+            return _W8A8Function.apply(x, self)
+        ahead = getattr(self, "_decode_ahead", None)
+        if ahead is not None:
+            pipelined = ahead.forward(self, x)
+            if pipelined is not None:
+                return pipelined
+        return self._forward8(x)
 
-    def _forward8(self, x: torch.Tensor) -> torch.Tensor:
+    def _forward8(self, x: torch.Tensor, codes: torch.Tensor | None = None) -> torch.Tensor:
+        """``codes``: the weight codes where the caller has decoded them already (decode-ahead)."""
         flat = self._prepare_activation(x.reshape(-1, x.shape[-1]))
         activation, scale = self._quantize_activations(flat.detach())
-        codes = self.codes(x.device)
+        if codes is None:
+            codes = self.codes(x.device)
         weight_scale = self._scale(codes.device)
         tokens = activation.shape[0]
         rows = max(tokens, self.min_tokens)

@@ -77,9 +77,17 @@ def test_decode_ahead_gives_the_layers_own_outputs():
                                             device="cuda") * 0.02).to(torch.bfloat16))
         return ep.CompressedLinear.from_linear(dense, config=config)
 
+    def make8(cls, seed):
+        dense = torch.nn.Linear(1024, 1024, bias=seed % 2 == 0, device="cuda", dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_((torch.randn(1024, 1024, generator=torch.Generator(device="cuda").manual_seed(seed), device="cuda")
+                                * 0.02).to(torch.bfloat16))
+        return cls.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=5.0))
+
     lossy = ep.EntroPackLossyConfig(target_bpp=4.0)
     layers = [make(1024, 1024, lossy, True, 0), make(1536, 1024, lossy, False, 1), make(1024, 1536, lossy, True, 2),
-              make(1024, 1024, ep.DFloat11Config(), False, 3), make(1024, 1024, ep.EntroPackLossyConfig.low_latency(4.0), True, 4)]
+              make(1024, 1024, ep.DFloat11Config(), False, 3), make(1024, 1024, ep.EntroPackLossyConfig.low_latency(4.0), True, 4),
+              make8(ep.CompressedFP8Linear, 5), make8(ep.CompressedINT8Linear, 6), make8(ep.CompressedFP8Linear, 7)]
     g = torch.Generator(device="cuda").manual_seed(9)
     x = torch.randn(300, 1024, generator=g, device="cuda").to(torch.bfloat16)
 
@@ -96,7 +104,7 @@ def test_decode_ahead_gives_the_layers_own_outputs():
             for _ in range(3):
                 for got, want in zip(run(), expected):
                     assert torch.equal(got, want)
-            assert ahead.decoded_ahead >= 6         # layers 1 and 2 of every pass, and layer 0 of the later ones
+            assert ahead.decoded_ahead >= 15        # every pass: layers 1, 2, 5, 6 and 7; the later ones: layer 0 as well
             # out of order: a layer whose weight was not the one decoded ahead decodes it itself
             h = layers[2](expected[1])
             assert torch.equal(h, expected[2])
