@@ -866,6 +866,24 @@ def measure_others(ep, device, flush, reps: int) -> dict:
             found_ready = ahead.decoded_ahead
         results[name] = {"forward_us_per_layer": plain_us, "decode_ahead_forward_us_per_layer": ahead_us,
                          "weights_found_decoded": found_ready, "same_output": bool(torch.equal(plain_out, ahead_out))}
+        # one token through the same ring: plain = the fused decode-and-multiply kernel; decode-ahead = the next layer's
+        # weight decoded to memory while the streaming product of the current one runs on the same SMs
+        one = x[:1].contiguous()
+
+        def ring_pass_one(calls=16):
+            h = None
+            for index in range(calls):
+                h = ring[index % 4](one)
+            return h
+
+        plain_one = ring_pass_one(4)
+        plain_one_us = timed(ring_pass_one) * 1e3 / 16
+        with ep.DecodeAhead(ring):
+            ahead_one = ring_pass_one(4)
+            ahead_one_us = timed(ring_pass_one) * 1e3 / 16
+        results[name.replace("M4096", "M1")] = {
+            "forward_us_per_layer": plain_one_us, "decode_ahead_forward_us_per_layer": ahead_one_us,
+            "max_rel_difference": float((plain_one.float() - ahead_one.float()).abs().max() / plain_one.float().abs().max())}
         del ring
     del x
 

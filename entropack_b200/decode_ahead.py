@@ -27,18 +27,20 @@ from .compression import CompressedTensor
 DECODE_SMS = 52            # SMs the decode ahead may fill while a product runs
 PRODUCT_SMS = 96           # SMs the product keeps meanwhile
 DECODE_WARPS_PER_SM = 24   # tiles the lossy decode kernel holds per SM
-MIN_TOKENS = 129           # below this the product is not the two-block tensor-core kernel and is over before a decode is
+MIN_TOKENS = 129           # from here on the product is the two-block tensor-core kernel that shares the GPU by SMs
+FEW_TOKENS = 16            # up to here it is the streaming kernel, whose small blocks fit on an SM beside a decode block
+ALL_SMS = 148
 MAX_PRODUCT_WEIGHTS = 20 << 20   # a longer product loses more on 96 SMs than hiding a decode behind it gains
 
 
 class _Plan:
     """What is known about a registered layer's weight: looked up once per container."""
 
-    __slots__ = ("container", "rows", "cols", "dtype", "nbytes", "rounds", "packed")
+    __slots__ = ("container", "rows", "cols", "dtype", "nbytes", "tiles", "packed")
 
     def __init__(self, container):
         self.container = container
-        self.rows = self.cols = self.nbytes = self.rounds = 0
+        self.rows = self.cols = self.nbytes = self.tiles = 0
         self.dtype = None
         self.packed = None
 
@@ -52,9 +54,10 @@ class DecodeAhead:
     its own weight as usual. Results are bit for bit what the layers give without it. ``cyclic`` (default) makes the
     last layer's successor the first, for passes that repeat. Use as a context manager or call ``close()``.
 
-    Handled: ``CompressedLinear`` with a lossy-coded bf16 weight, ``CompressedFP8Linear`` / ``CompressedINT8Linear`` with
-    lossy-coded codes; from 129 tokens up; successors of at most 1248 tiles. Other layers in the list run as they always
-    do.
+    Handled: ``CompressedLinear`` with a lossy-coded bf16 weight (up to 16 tokens, where the product's small blocks run
+    beside the decode's on every SM, and from 129 tokens up, where the two share the GPU by SMs and the successor may have
+    at most 1248 tiles), ``CompressedFP8Linear`` / ``CompressedINT8Linear`` with lossy-coded codes (from 129 tokens up).
+    Other layers in the list, and other token counts, run as they always do.
 
     Not for training (it is skipped under autograd). To capture a pass into a CUDA graph: run one pass first (the second
     stream and the buffers are made at the first use), call ``drain()``, capture, and call ``drain()`` again before the
@@ -122,8 +125,7 @@ class DecodeAhead:
             if info["cols"] == layer.in_features and info["rows"] == layer.out_features:
                 plan.rows, plan.cols, plan.dtype = info["rows"], info["cols"], dtype
                 plan.nbytes = plan.rows * plan.cols * torch.empty((), dtype=dtype).element_size()
-                # tiles the decode's share of the GPU does not hold at once wait for a second round of rANS chains
-                plan.rounds = -(-info["total_tiles"] // (DECODE_SMS * DECODE_WARPS_PER_SM))
+                plan.tiles = info["total_tiles"]
                 plan.packed = packed_buffers(container.buffers, LatticeBuffers)
         self._plans[id(layer)] = plan
         return plan
@@ -159,13 +161,17 @@ class DecodeAhead:
                 or (torch.is_grad_enabled() and x.requires_grad)):
             return None
         tokens = x.numel() // x.shape[-1]
-        if tokens < MIN_TOKENS:
+        plain = type(layer) is CompressedLinear
+        # A few tokens: the product is the streaming kernel, whose blocks run on the same SMs as a decode's (and the weight
+        # is decoded to memory instead of being multiplied inside the fused kernel); many: the GPU is shared by SMs.
+        # In between the product's blocks need an SM's shared memory to themselves and would only queue behind a decode.
+        few = plain and tokens <= FEW_TOKENS
+        if not few and tokens < MIN_TOKENS:
             return None
         device = x.device
         self._ensure(device)
         if plan.nbytes > self._buffers[0].numel():
             return None
-        plain = type(layer) is CompressedLinear
         bias = layer._bias_on(device) if plain else None
         if plain and not _native_gemm_applies(x, self._view(plan, 0), bias):
             return None
@@ -190,9 +196,16 @@ class DecodeAhead:
             follower_position = (position + 1) % len(self.layers)
             follower = self.layers[follower_position]
             candidate = self._plan(follower)
-            if (candidate.dtype is not None and follower.weight.device == device and candidate.nbytes <= self._buffers[0].numel()
-                    and candidate.rounds == 1 and plan.rows * plan.cols <= MAX_PRODUCT_WEIGHTS):
-                follower_plan = candidate
+            # the successor's tiles have to decode side by side (a second round of rANS chains doubles the decode): on the
+            # whole GPU beside a streaming product, on the decode's share beside a tensor-core one, which moreover must
+            # not be so long that running it on 96 SMs costs more than the hidden decode saves
+            if candidate.dtype is not None and follower.weight.device == device and candidate.nbytes <= self._buffers[0].numel():
+                if few:
+                    eligible = candidate.tiles <= ALL_SMS * DECODE_WARPS_PER_SM
+                else:
+                    eligible = candidate.tiles <= DECODE_SMS * DECODE_WARPS_PER_SM and plan.rows * plan.cols <= MAX_PRODUCT_WEIGHTS
+                if eligible:
+                    follower_plan = candidate
 
         def product():
             return linear_forward(x, weight, bias) if plain else layer._forward8(x, codes=weight)
@@ -203,7 +216,7 @@ class DecodeAhead:
         if follower_plan is None:
             return product()
         with torch.cuda.device(device):
-            _native.check(lib.ep_set_sm_limits(0, PRODUCT_SMS), "sm limits")
+            _native.check(lib.ep_set_sm_limits(0, 0 if few else PRODUCT_SMS), "sm limits")
             try:
                 out = product()
             finally:
@@ -213,7 +226,7 @@ class DecodeAhead:
         side = self._side
         side.wait_event(before_product)
         with torch.cuda.stream(side), torch.cuda.device(device):
-            _native.check(lib.ep_set_sm_limits(DECODE_SMS, 0), "sm limits")
+            _native.check(lib.ep_set_sm_limits(0 if few else DECODE_SMS, 0), "sm limits")
             try:
                 self._decode(follower_plan, 1 - slot)
             finally:

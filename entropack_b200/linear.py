@@ -227,14 +227,14 @@ class CompressedLinear(torch.nn.Linear):
         return None if self.bias is None else self.bias.to(device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        fused = self._fused_forward(x)
-        if fused is not None:
-            return fused
         ahead = getattr(self, "_decode_ahead", None)
         if ahead is not None:
             pipelined = ahead.forward(self, x)
             if pipelined is not None:
                 return pipelined
+        fused = self._fused_forward(x)
+        if fused is not None:
+            return fused
         weight = self.dequantize(x.device)
         bias = self._bias_on(x.device)
         if _native_gemm_applies(x, weight, bias):

@@ -100,11 +100,23 @@ def test_decode_ahead_gives_the_layers_own_outputs():
 
     with torch.no_grad():
         expected = run()
+        expected_few = {}
+        for tokens in (8, 2):
+            h = x[:tokens]
+            for index in range(3):
+                h = layers[index](h)
+            expected_few[tokens] = h
         with ep.DecodeAhead(layers) as ahead:
             for _ in range(3):
                 for got, want in zip(run(), expected):
                     assert torch.equal(got, want)
             assert ahead.decoded_ahead >= 15        # every pass: layers 1, 2, 5, 6 and 7; the later ones: layer 0 as well
+            # a few tokens: the product's blocks share the SMs with the next layer's decode; eight tokens take the same
+            # kernels with and without (bit-equal), two would take the fused kernel without (equal to rounding)
+            h8, h2 = x[:8], x[:2]
+            for index in range(3):
+                h8, h2 = layers[index](h8), layers[index](h2)
+            assert torch.equal(h8, expected_few[8]) and _relative(h2, expected_few[2]) < 1e-2
             # out of order: a layer whose weight was not the one decoded ahead decodes it itself
             h = layers[2](expected[1])
             assert torch.equal(h, expected[2])
