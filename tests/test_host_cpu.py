@@ -248,3 +248,26 @@ def test_reference_arm_of_the_bench_prints_its_line_without_a_gpu():
     baseline = line["cpu_baseline"]
     assert baseline["kind"] == "port" and baseline["cores"] >= 1 and baseline["value"] == line["value"] and baseline["sample"]
     assert line["e2e"] == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
+
+def test_decode_ahead_registration_rules():
+    """A layer is registered once and with one DecodeAhead at a time; closing unhooks every layer (no GPU involved:
+    modules that it does not handle are carried in the list and run as they always do)."""
+    import entropack_b200 as ep
+
+    first, second = torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)
+    with pytest.raises(ValueError):
+        ep.DecodeAhead([first, first])
+    assert getattr(first, "_decode_ahead", None) is None       # a refused list leaves no hook behind
+    ahead = ep.DecodeAhead([first, second])
+    assert first._decode_ahead is ahead and second._decode_ahead is ahead
+    with pytest.raises(ValueError):
+        ep.DecodeAhead([second])
+    ahead.drain()          # nothing pending, nothing allocated: a no-op
+    ahead.close()
+    assert first._decode_ahead is None and second._decode_ahead is None
+    with ep.DecodeAhead([second, first]) as again:
+        assert second._decode_ahead is again
+    assert second._decode_ahead is None
+    x = torch.randn(3, 8)
+    assert torch.equal(first(x), torch.nn.functional.linear(x, first.weight, first.bias))
