@@ -10,7 +10,7 @@ that runs next is decoded on a second stream, on 52 of the 148 SMs, while the cu
 100 us on 96 SMs, decode 66 us on 52, both hidden behind each other). It pays only where the next layer's tiles all
 decode side by side on that share (at most 1248 tiles: 20 million weights in 16384-symbol tiles, 9 million in the
 8192-symbol tiles of the FP8 layers' default -- four 3840 x 3840 FP8 layers at 5 bpp in a ring measured 122 us a layer
-with a two-round decode ahead against 105 us without) and the current product is not a long one; other layers run as
+with a decode ahead that takes its tiles in two turns against 105 us without) and the current product is not a long one; other layers run as
 before.
 
 The reference decodes and multiplies one after the other (entropack/linear/linear.py:163-165) and has nothing like it.
@@ -196,7 +196,7 @@ class DecodeAhead:
             follower_position = (position + 1) % len(self.layers)
             follower = self.layers[follower_position]
             candidate = self._plan(follower)
-            # the successor's tiles have to decode side by side (a second round of rANS chains doubles the decode): on the
+            # the successor's tiles have to decode side by side (tiles that wait for a second turn double the decode): on the
             # whole GPU beside a streaming product, on the decode's share beside a tensor-core one, which moreover must
             # not be so long that running it on 96 SMs costs more than the hidden decode saves
             if candidate.dtype is not None and follower.weight.device == device and candidate.nbytes <= self._buffers[0].numel():
