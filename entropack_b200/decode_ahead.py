@@ -10,8 +10,8 @@ that runs next is decoded on a second stream, on 52 of the 148 SMs, while the cu
 100 us on 96 SMs, decode 66 us on 52, both hidden behind each other). It pays only where the next layer's tiles all
 decode side by side on that share (at most 1248 tiles: 20 million weights in 16384-symbol tiles, 9 million in the
 8192-symbol tiles of the FP8 layers' default -- four 3840 x 3840 FP8 layers at 5 bpp in a ring measured 122 us a layer
-with a decode ahead that takes its tiles in two turns against 105 us without) and the current product is not a long one; other layers run as
-before.
+with a decode ahead that takes its tiles in two turns against 105 us without). Beside a long product (a 10240-wide
+layer at 4096 tokens) the decode ahead gets 28 SMs and the product 120; other layers run as before.
 
 The reference decodes and multiplies one after the other (entropack/linear/linear.py:163-165) and has nothing like it.
 """
@@ -26,6 +26,13 @@ from .compression import CompressedTensor
 
 DECODE_SMS = 52            # SMs the decode ahead may fill while a product runs
 PRODUCT_SMS = 96           # SMs the product keeps meanwhile
+# beside a long product (of a layer past MAX_PRODUCT_WEIGHTS at thousands of tokens) the decode gets fewer SMs and takes
+# its tiles in two turns, still well inside the product's time: measured at 4096 tokens with a 3840 x 3840 weight
+# decoded ahead, 3840 -> 10240: 246 us together against 261 us in turn; 10240 -> 3840: 240 against 280; 3840 -> 11520: 265
+# against 287
+SLIM_DECODE_SMS = 28
+WIDE_PRODUCT_SMS = 120
+LONG_PRODUCT_WORK = 9e10   # tokens x weights from which a product outlasts a two-turn decode on SLIM_DECODE_SMS
 DECODE_WARPS_PER_SM = 24   # tiles the lossy decode kernel holds per SM
 MIN_TOKENS = 129           # from here on the product is the two-block tensor-core kernel that shares the GPU by SMs
 FEW_TOKENS = 16            # up to here it is the streaming kernel, whose small blocks fit on an SM beside a decode block
@@ -192,6 +199,7 @@ class DecodeAhead:
         self._latest = slot
 
         follower_plan = None
+        decode_sms, product_sms = (0, 0) if few else (DECODE_SMS, PRODUCT_SMS)
         if position + 1 < len(self.layers) or self.cyclic:
             follower_position = (position + 1) % len(self.layers)
             follower = self.layers[follower_position]
@@ -202,8 +210,13 @@ class DecodeAhead:
             if candidate.dtype is not None and follower.weight.device == device and candidate.nbytes <= self._buffers[0].numel():
                 if few:
                     eligible = candidate.tiles <= ALL_SMS * DECODE_WARPS_PER_SM
+                elif candidate.tiles > DECODE_SMS * DECODE_WARPS_PER_SM:
+                    eligible = False
+                elif plan.rows * plan.cols <= MAX_PRODUCT_WEIGHTS:
+                    eligible = True
                 else:
-                    eligible = candidate.tiles <= DECODE_SMS * DECODE_WARPS_PER_SM and plan.rows * plan.cols <= MAX_PRODUCT_WEIGHTS
+                    eligible = float(tokens) * plan.rows * plan.cols >= LONG_PRODUCT_WORK
+                    decode_sms, product_sms = SLIM_DECODE_SMS, WIDE_PRODUCT_SMS
                 if eligible:
                     follower_plan = candidate
 
@@ -216,7 +229,7 @@ class DecodeAhead:
         if follower_plan is None:
             return product()
         with torch.cuda.device(device):
-            _native.check(lib.ep_set_sm_limits(0, 0 if few else PRODUCT_SMS), "sm limits")
+            _native.check(lib.ep_set_sm_limits(0, product_sms), "sm limits")
             try:
                 out = product()
             finally:
@@ -226,7 +239,7 @@ class DecodeAhead:
         side = self._side
         side.wait_event(before_product)
         with torch.cuda.stream(side), torch.cuda.device(device):
-            _native.check(lib.ep_set_sm_limits(0 if few else DECODE_SMS, 0), "sm limits")
+            _native.check(lib.ep_set_sm_limits(decode_sms, 0), "sm limits")
             try:
                 self._decode(follower_plan, 1 - slot)
             finally:
