@@ -179,6 +179,68 @@ __global__ void __launch_bounds__(256) quantize_rows_8bit_kernel(const T* __rest
   }
 }
 
+// The same, for rows of at most 256 * HELD 16-byte pieces (4096 bf16 values at HELD = 2): a thread keeps its pieces in
+// registers between the maximum and the conversion, so the row is read once, and every thread derives the scale from
+// the eight warp maxima itself, so the block meets at one barrier. FP8 codes are converted two at a time.
+template <typename T, bool INT8, int HELD>
+__global__ void __launch_bounds__(256) quantize_rows_held_kernel(const T* __restrict__ x, int64_t cols, uint8_t* __restrict__ codes,
+                                                                 float* __restrict__ scales) {
+  constexpr int kVector = 16 / sizeof(T);
+  __shared__ float partial[8];
+  const T* row = x + static_cast<int64_t>(blockIdx.x) * cols;
+  uint4 held[HELD];
+  float largest = 0.0f;
+#pragma unroll
+  for (int h = 0; h < HELD; ++h) {
+    const int64_t c = static_cast<int64_t>(h * 256 + static_cast<int>(threadIdx.x)) * kVector;
+    held[h] = c < cols ? __ldcs(reinterpret_cast<const uint4*>(row + c)) : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int h = 0; h < HELD; ++h) {
+    const T* values = reinterpret_cast<const T*>(&held[h]);
+#pragma unroll
+    for (int i = 0; i < kVector; ++i) largest = fmaxf(largest, fabsf(as_float(values[i])));
+  }
+#pragma unroll
+  for (int step = 16; step > 0; step >>= 1) largest = fmaxf(largest, __shfl_xor_sync(0xFFFFFFFFu, largest, step));
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = largest;
+  __syncthreads();
+  float total = partial[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) total = fmaxf(total, partial[w]);
+  const float scale = fmaxf(__fmul_rn(total, __fdiv_rn(1.0f, INT8 ? 127.0f : 448.0f)), 1.1920928955078125e-07f);
+  if (threadIdx.x == 0) scales[blockIdx.x] = scale;
+  uint8_t* out = codes + static_cast<int64_t>(blockIdx.x) * cols;
+#pragma unroll
+  for (int h = 0; h < HELD; ++h) {
+    const int64_t c = static_cast<int64_t>(h * 256 + static_cast<int>(threadIdx.x)) * kVector;
+    if (c >= cols) continue;
+    const T* values = reinterpret_cast<const T*>(&held[h]);
+    uint32_t packed[kVector / 4];
+#pragma unroll
+    for (int i = 0; i < kVector; i += 4) {
+      if (INT8) {
+        packed[i / 4] = static_cast<uint32_t>(quantize_value<true>(as_float(values[i]), scale)) |
+                        static_cast<uint32_t>(quantize_value<true>(as_float(values[i + 1]), scale)) << 8 |
+                        static_cast<uint32_t>(quantize_value<true>(as_float(values[i + 2]), scale)) << 16 |
+                        static_cast<uint32_t>(quantize_value<true>(as_float(values[i + 3]), scale)) << 24;
+      } else {
+        float scaled[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) scaled[j] = fminf(fmaxf(__fdiv_rn(as_float(values[i + j]), scale), -448.0f), 448.0f);
+        const uint32_t low = __nv_cvt_float2_to_fp8x2(make_float2(scaled[0], scaled[1]), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t high = __nv_cvt_float2_to_fp8x2(make_float2(scaled[2], scaled[3]), __NV_SATFINITE, __NV_E4M3);
+        packed[i / 4] = low | high << 16;
+      }
+    }
+    if (kVector == 8) {
+      *reinterpret_cast<uint2*>(out + c) = make_uint2(packed[0], packed[kVector / 4 - 1]);
+    } else {
+      *reinterpret_cast<uint32_t*>(out + c) = packed[0];
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // ConvRot: y = x . R per group of `group` consecutive features (entropack/linear/convrot.py:35-61)
 // ------------------------------------------------------------------------------------------------
@@ -1294,8 +1356,15 @@ int quantize_rows(const void* x_dev, int x_kind, int64_t rows, int64_t cols, voi
   const int64_t element_bytes = x_kind == 2 ? 4 : 2;
   const int64_t per_vector = 16 / element_bytes;
   const bool vector = cols % per_vector == 0 && (reinterpret_cast<uintptr_t>(x_dev) & 15u) == 0 && (reinterpret_cast<uintptr_t>(codes_dev) & 7u) == 0;
+  const int64_t pieces = vector ? cols / per_vector : 0;     // 16-byte pieces of a row; up to 1024 stay in registers
 #define EP_LAUNCH_QUANTIZE(TYPE)                                                                                                   \
-  if (vector) {                                                                                                                    \
+  if (vector && pieces <= 256) {                                                                                                   \
+    quantize_rows_held_kernel<TYPE, INT8, 1><<<blocks, 256, 0, s>>>(static_cast<const TYPE*>(x_dev), cols, codes, scales_dev);     \
+  } else if (vector && pieces <= 512) {                                                                                            \
+    quantize_rows_held_kernel<TYPE, INT8, 2><<<blocks, 256, 0, s>>>(static_cast<const TYPE*>(x_dev), cols, codes, scales_dev);     \
+  } else if (vector && pieces <= 1024) {                                                                                           \
+    quantize_rows_held_kernel<TYPE, INT8, 4><<<blocks, 256, 0, s>>>(static_cast<const TYPE*>(x_dev), cols, codes, scales_dev);     \
+  } else if (vector) {                                                                                                             \
     quantize_rows_8bit_kernel<TYPE, INT8, true><<<blocks, 256, 0, s>>>(static_cast<const TYPE*>(x_dev), cols, codes, scales_dev);  \
   } else {                                                                                                                         \
     quantize_rows_8bit_kernel<TYPE, INT8, false><<<blocks, 256, 0, s>>>(static_cast<const TYPE*>(x_dev), cols, codes, scales_dev); \
@@ -1306,7 +1375,7 @@ int quantize_rows(const void* x_dev, int x_kind, int64_t rows, int64_t cols, voi
     default: EP_LAUNCH_QUANTIZE(float) break;
   }
 #undef EP_LAUNCH_QUANTIZE
-  return check_launch("quantize_rows_8bit_kernel");
+  return check_launch("quantize_rows kernel");
 }
 }  // namespace
 

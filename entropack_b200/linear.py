@@ -108,6 +108,18 @@ def _pad_to(tensor: torch.Tensor, dim: int, size: int) -> torch.Tensor:
     return torch.cat([tensor, tensor.new_zeros(shape)], dim=dim)
 
 
+_SIDE_STREAMS: dict[int, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    """One extra stream per device for work that runs beside a layer's weight decode."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    stream = _SIDE_STREAMS.get(index)
+    if stream is None:
+        stream = _SIDE_STREAMS[index] = torch.cuda.Stream(device=index)
+    return stream
+
+
 def _round_up(value: int, multiple: int) -> int:
     return -(-value // multiple) * multiple
 
@@ -429,7 +441,19 @@ class QuantizedLinear(CompressedLinear):
     def _forward8(self, x: torch.Tensor, codes: torch.Tensor | None = None) -> torch.Tensor:
         """``codes``: the weight codes where the caller has decoded them already (decode-ahead)."""
         flat = self._prepare_activation(x.reshape(-1, x.shape[-1]))
-        activation, scale = self._quantize_activations(flat.detach())
+        beside = (codes is None and flat.is_cuda and flat.shape[0] >= self.beside_decode_tokens
+                  and not isinstance(self.config, RawConfig))
+        if beside:
+            # the activations are quantised on a second stream while the weight codes are decoded on this one: the
+            # decode is a latency-bound chain that leaves most of an SM's issue slots and all of its memory bandwidth idle
+            flat = flat.contiguous()       # a copy, if one is needed, is made before the second stream is let go
+            current, side = torch.cuda.current_stream(flat.device), _side_stream(flat.device)
+            side.wait_stream(current)
+            activation, scale = self._quantize_activations(flat.detach(), stream=side)
+            codes = self.codes(x.device)
+            current.wait_stream(side)
+        else:
+            activation, scale = self._quantize_activations(flat.detach())
         if codes is None:
             codes = self.codes(x.device)
         weight_scale = self._scale(codes.device)
@@ -449,9 +473,14 @@ class QuantizedLinear(CompressedLinear):
     quantize_entry: ClassVar[str]
     gemm_entry: ClassVar[str]
 
-    def _quantize_activations(self, tensor: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    #: from this many tokens on, a coded layer quantises its activations beside the weight decode (below it the host's
+    #: two extra event hand-overs cost more than the few microseconds the quantiser takes)
+    beside_decode_tokens: ClassVar[int] = 1024
+
+    def _quantize_activations(self, tensor: torch.Tensor, stream: "torch.cuda.Stream | None" = None) -> tuple[torch.Tensor, torch.Tensor]:
         """Weights (once, at compression time) go through the torch expression of ``_quantize_rows``; activations on a
-        GPU, every forward, through one kernel that computes the same scale and the same codes."""
+        GPU, every forward, through one kernel that computes the same scale and the same codes. ``stream``: where the
+        kernel is launched (the caller orders it against the current stream, on which the results are allocated)."""
         kind = _SOURCE_KINDS.get(tensor.dtype)
         if not tensor.is_cuda or kind is None or tensor.numel() == 0:
             return self._quantize_rows(tensor)
@@ -461,7 +490,7 @@ class QuantizedLinear(CompressedLinear):
         with torch.cuda.device(flat.device):
             status = getattr(_native.load(), self.quantize_entry)(
                 _native.ptr(flat), kind, flat.shape[0], flat.shape[1], _native.ptr(codes), _native.ptr(scale),
-                _native.stream_handle(flat.device))
+                stream.cuda_stream if stream is not None else _native.stream_handle(flat.device))
         _native.check(status, "8-bit activation quantisation")
         return codes, scale
 

@@ -27,7 +27,8 @@ def test_matches_fp32_reference(m, n, k, bias):
     assert float((out.float() - expected).abs().max() / expected.abs().max()) <= 1e-2
 
 
-@pytest.mark.parametrize("cols", [1000, 1001, 3840])       # 16-byte row reads, element-wise fallback, more than one read per thread
+# 16-byte row reads, element-wise fallback, two and four register-held reads per thread, rows too long to hold
+@pytest.mark.parametrize("cols", [1000, 1001, 3840, 8192, 10240])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_fp8_row_quantisation_matches_the_torch_expression(dtype, cols):
     """Same scale and the same e4m3 codes, bit for bit, as QuantizedLinear._quantize_rows computes with torch ops."""
@@ -81,7 +82,7 @@ def test_fp8_gemm_matches_scaled_mm(m, n, k, out_dtype, with_bias):
         assert float((out.float() - library.float()).abs().max() / expected.abs().max()) <= 1e-2
 
 
-@pytest.mark.parametrize("cols", [777, 2048])
+@pytest.mark.parametrize("cols", [777, 2048, 3840, 8192, 10240])
 def test_int8_row_quantisation_matches_the_torch_expression(cols):
     from entropack_b200 import _native
 

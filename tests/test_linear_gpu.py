@@ -178,7 +178,7 @@ def test_state_dict_round_trip_and_reference_checkpoint_loads():
     assert decoded.cpu().contiguous().view(torch.uint8).numpy().tobytes() == record["decoded_bytes"].tobytes()
 
 
-@pytest.mark.parametrize("tokens", [1, 16, 256])
+@pytest.mark.parametrize("tokens", [1, 16, 256, 2048])      # 2048: activations quantised beside the weight decode
 def test_fp8_linear_forward(tokens):
     import entropack_b200 as ep
 
