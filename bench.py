@@ -837,6 +837,21 @@ def measure_others(ep, device, flush, reps: int) -> dict:
             if tokens == 4096:
                 entry["library_gemm_tflops"] = 2.0 * tokens * out_features * in_features / entry["library_gemm_us"] / 1e6
                 entry["cublas_tflops"] = 2.0 * tokens * out_features * in_features / entry["cublas_dense_us"] / 1e6
+            if out_features == 3840:
+                # what a call costs the host (Python + launches), taken while the device is kept busy by a spin, and the
+                # wall-clock time per call of a plain loop of eager calls (the larger of host and device time)
+                torch.cuda.synchronize(device)
+                torch.cuda._sleep(200_000_000)
+                begin = time.perf_counter()
+                for _ in range(100):
+                    layer(x)
+                entry["host_us_per_call"] = (time.perf_counter() - begin) / 100 * 1e6
+                torch.cuda.synchronize(device)
+                begin = time.perf_counter()
+                for _ in range(100):
+                    layer(x)
+                torch.cuda.synchronize(device)
+                entry["eager_loop_us_per_call"] = (time.perf_counter() - begin) / 100 * 1e6
             results[f"linear_{in_features}x{out_features}_M{tokens}"] = entry
 
     # Decode-ahead: four different 3840 x 3840 layers called in a ring at 4096 tokens, each decoding its weight on every

@@ -3,6 +3,7 @@
 There is no fallback: if the library has not been built, or no CUDA device is present, every compute
 entry point raises. ``python -m entropack_b200.build`` (or ``__graft_entry__.build()``) builds it.
 """
+import contextlib
 import ctypes
 from pathlib import Path
 
@@ -142,6 +143,23 @@ def ptr(tensor: torch.Tensor | None) -> int | None:
 
 def stream_handle(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_NO_GUARD = contextlib.nullcontext()
+
+
+def on_device(index: int):
+    """Context in which ``index`` is the current CUDA device: nothing at all when it is so already."""
+    return _NO_GUARD if torch.cuda.current_device() == index else torch.cuda.device(index)
+
+
+def raw_stream(index: int) -> int:
+    """The current stream's handle on device ``index`` without building a Stream object (a few microseconds less per
+    library call, which counts for a layer that makes two of them per forward)."""
+    if _raw_stream is not None:
+        return _raw_stream(index)
+    return torch.cuda.current_stream(index).cuda_stream
 
 
 def raise_stream_error(code: int, what: str) -> None:

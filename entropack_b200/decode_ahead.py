@@ -43,13 +43,14 @@ MAX_PRODUCT_WEIGHTS = 20 << 20   # a longer product loses more on 96 SMs than hi
 class _Plan:
     """What is known about a registered layer's weight: looked up once per container."""
 
-    __slots__ = ("container", "rows", "cols", "dtype", "nbytes", "tiles", "packed")
+    __slots__ = ("container", "payload", "rows", "cols", "dtype", "nbytes", "tiles", "packed", "prepared")
 
     def __init__(self, container):
         self.container = container
+        self.payload = None
         self.rows = self.cols = self.nbytes = self.tiles = 0
         self.dtype = None
-        self.packed = None
+        self.packed = self.prepared = None
 
 
 class DecodeAhead:
@@ -112,13 +113,16 @@ class DecodeAhead:
     def _plan(self, layer) -> _Plan:
         container = getattr(layer, "weight", None)
         plan = self._plans.get(id(layer))
-        if plan is not None and plan.container is container:
+        # module.to() swaps a container's contents in place: the payload tensor tells a moved container from the same one
+        payload = container.buffers.get("payload") if isinstance(container, CompressedTensor) else None
+        if plan is not None and plan.container is container and plan.payload is payload:
             return plan
         from .linear import CompressedLinear, QuantizedLinear
         from .schemes.base import packed_buffers
         from .schemes.lattice_rans.format import LatticeBuffers, decode_geometry
 
         plan = _Plan(container)
+        plan.payload = payload
         if type(layer) is CompressedLinear:
             dtype = torch.bfloat16 if (isinstance(container, CompressedTensor) and container.dtype == torch.bfloat16
                                        and container.encoded_dtype == torch.bfloat16) else None
@@ -144,6 +148,10 @@ class DecodeAhead:
         from .schemes.lattice_rans import b200
 
         out = self._view(plan, slot)
+        if plan.prepared is None:          # there is none before the container's slot tables are kept
+            plan.prepared = b200.prepared_decode(plan.packed, shape=(plan.rows, plan.cols), dtype=plan.dtype)
+        if plan.prepared is not None:
+            return plan.prepared(out=out)
         b200.decode(plan.packed, shape=(plan.rows, plan.cols), dtype=plan.dtype, out=out)
         return out
 

@@ -91,10 +91,11 @@ def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | N
     if error is None:
         error = kernel_error_word(x.device)
     out = torch.empty((flat.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
-    with torch.cuda.device(x.device):
+    index = x.device.index
+    with _native.on_device(index):
         status = _native.load().ep_linear_forward(
             _native.ptr(flat), _native.ptr(weight), _native.ptr(bias.contiguous() if bias is not None else None), _native.ptr(out),
-            flat.shape[0], weight.shape[0], flat.shape[1], _native.ptr(error), _native.stream_handle(x.device))
+            flat.shape[0], weight.shape[0], flat.shape[1], _native.ptr(error), _native.raw_stream(index))
     _native.check(status, "linear forward")
     return out.reshape(*x.shape[:-1], weight.shape[0])
 
@@ -235,6 +236,45 @@ class CompressedLinear(torch.nn.Linear):
         """The dense weight, decoded on ``device`` (default: where the blob lives)."""
         return decompress(self._container().to(device=device), self._decode_config)
 
+    def _decoded_for_product(self, device: torch.device, dtype: torch.dtype) -> torch.Tensor:
+        """What ``decompress`` gives for the container as ``dtype`` on ``device``, for the forward pass: from the third
+        call on through a prepared decode (``schemes/lattice_rans/b200.py``), which skips the per-call validation, lane
+        look-up and layout parsing of the general path -- they cost more host time than the decode takes on the device.
+        The prepared decode is dropped as soon as the layer's container, its storage, its device or its config object
+        is another one."""
+        held = self.__dict__.get("_prepared")
+        container = self.weight
+        if held is not None:
+            config, prepared = held
+            if (prepared is not None and config is self.config and prepared.dtype == dtype and isinstance(container, CompressedTensor)
+                    and prepared.valid_for(container.buffers, device)):
+                return prepared()
+            del self.__dict__["_prepared"]
+        dense = decompress(self._container().to(device=device, dtype=dtype), self._decode_config)
+        prepared = self._prepare_decode(device, dtype, dense)
+        if prepared is not None:
+            self.__dict__["_prepared"] = (self.config, prepared)
+        return dense
+
+    def _prepare_decode(self, device: torch.device, dtype: torch.dtype, dense: torch.Tensor):
+        container = self.weight
+        if (container.compress_method != "lattice_rans" or container.device != device or device.type != "cuda"
+                or container.encoded_dtype != dtype or tuple(dense.shape) != tuple(container.shape) or not dense.is_contiguous()):
+            return None
+        from .schemes.base import packed_buffers
+        from .schemes.lattice_rans import b200
+        from .schemes.lattice_rans.format import LatticeBuffers
+
+        config = self._decode_config
+        packed = packed_buffers(container.buffers, LatticeBuffers)
+        lane, run_on = container.scheme.lane_for(packed.layout, config.execution_backend, gate_dtype=False)
+        if lane is not b200 or run_on != device:
+            return None
+        prepared = b200.prepared_decode(packed, shape=tuple(container.shape), dtype=dtype)
+        if prepared is None or (prepared.rows, prepared.cols) != tuple(container.shape):
+            return None
+        return prepared
+
     def _bias_on(self, device: torch.device) -> torch.Tensor | None:
         return None if self.bias is None else self.bias.to(device)
 
@@ -247,7 +287,7 @@ class CompressedLinear(torch.nn.Linear):
         fused = self._fused_forward(x)
         if fused is not None:
             return fused
-        weight = self.dequantize(x.device)
+        weight = self._decoded_for_product(x.device, self.weight.dtype)
         bias = self._bias_on(x.device)
         if _native_gemm_applies(x, weight, bias):
             return linear_forward(x, weight, bias)
@@ -450,12 +490,12 @@ class QuantizedLinear(CompressedLinear):
             current, side = torch.cuda.current_stream(flat.device), _side_stream(flat.device)
             side.wait_stream(current)
             activation, scale = self._quantize_activations(flat.detach(), stream=side)
-            codes = self.codes(x.device)
+            codes = self._decoded_for_product(x.device, self.code_dtype)
             current.wait_stream(side)
         else:
             activation, scale = self._quantize_activations(flat.detach())
         if codes is None:
-            codes = self.codes(x.device)
+            codes = self._decoded_for_product(x.device, self.code_dtype)
         weight_scale = self._scale(codes.device)
         tokens = activation.shape[0]
         rows = max(tokens, self.min_tokens)

@@ -127,6 +127,59 @@ def decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype, threads_per_bl
     return snap_to_container(out, dtype) if via_float else out
 
 
+class PreparedDecode:
+    """One container's decode with the host's share done once: the geometry parsed, the lengths checked, the kept slot
+    tables found, the sixteen pointers and sizes of the library call laid out. A call then allocates the output, reads
+    the current stream and makes the library call, nothing else -- a layer that decodes its weight at every forward
+    otherwise spends more time in Python than a 3840 x 3840 decode takes on the device. ``prepared_decode`` makes one
+    only once the container's tables are kept; the object holds the buffers (and so keeps them alive) and is good for
+    as long as the caller still holds the same ``payload`` tensor (``valid_for``)."""
+
+    __slots__ = ("buffers", "tables", "rows", "cols", "dtype", "index", "_head", "_tail")
+
+    def __init__(self, buffers: LatticeBuffers, tables: torch.Tensor, info: dict, dtype: torch.dtype, alphabet: int):
+        self.buffers, self.tables, self.dtype = buffers, tables, dtype
+        self.rows, self.cols = info["rows"], info["cols"]
+        self.index = buffers.payload.device.index
+        ptr = _native.ptr
+        self._head = (ptr(buffers.payload), buffers.payload.numel(), ptr(buffers.offsets), ptr(buffers.states), ptr(buffers.stream_meta),
+                      ptr(buffers.freq_tables), buffers.freq_tables.numel(), ptr(buffers.scales))
+        self._tail = (STORE_KINDS[dtype], self.rows, self.cols, info["prob_bits"], info["tile_elements"], alphabet, ptr(tables),
+                      tables.numel(), 1)
+
+    def __reduce__(self):
+        # a copied or unpickled layer makes its own (the pointers above belong to this container's storage)
+        return (type(None), ())
+
+    def valid_for(self, buffers: dict, device: torch.device) -> bool:
+        return buffers.get("payload") is self.buffers.payload and device.type == "cuda" and device.index == self.index
+
+    def __call__(self, out: torch.Tensor | None = None, error: torch.Tensor | None = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty((self.rows, self.cols), dtype=self.dtype, device=self.buffers.payload.device)
+        error_at = None if error is None else error.data_ptr()
+        with _native.on_device(self.index):
+            status = _native.load().ep_lattice_decode(*self._head, out.data_ptr(), *self._tail, error_at, _native.raw_stream(self.index))
+        if status:
+            _native.check(status, "lattice_rans decode")
+        return out
+
+
+def prepared_decode(buffers: LatticeBuffers, *, shape, dtype: torch.dtype) -> PreparedDecode | None:
+    """A ``PreparedDecode`` for a container on a CUDA device whose slot tables are kept already (from its second decode
+    on, or after ``prepare_plan``) and whose dtype the kernel stores directly; None otherwise."""
+    if buffers.payload.device.type != "cuda" or dtype in _VIA_FLOAT32 or dtype not in STORE_KINDS:
+        return None
+    tables = getattr(buffers.layout, "_lattice_rans_slot_tables", None)
+    if tables is None or tables.device != buffers.payload.device:
+        return None
+    if not all(getattr(buffers, name).is_contiguous() for name in LatticeBuffers._fields):
+        return None
+    info = decode_geometry(buffers._asdict(), shape)
+    _check_lengths(buffers, info)
+    return PreparedDecode(buffers, tables, info, dtype, max_alphabet(buffers))
+
+
 MAX_FUSED_TOKENS = 4
 
 

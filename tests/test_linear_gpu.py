@@ -2,6 +2,7 @@
 import numpy as np
 import pytest
 import torch
+import torch.nn.functional as F
 
 from conftest import buffers_of, load_golden
 
@@ -277,3 +278,42 @@ def test_fused_small_batch_forward_matches_product_with_decoded_weight(tokens, f
                         bias=None, error=error)
     assert int(error.item()) == 0
     assert layer._fused_forward(torch.zeros(5, features, device="cuda", dtype=torch.bfloat16)) is None
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8"])
+def test_prepared_decode_follows_the_layers_container(kind):
+    """From a container's third decode on, a layer's forward decodes through a prepared call (pointers and sizes kept
+    from the general path). It must give the same bytes, and must be dropped when the layer gets another weight, is
+    copied, or has its state loaded."""
+    import copy
+
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(31)
+    cls = ep.CompressedLinear if kind == "bf16" else ep.CompressedFP8Linear
+    config = ep.EntroPackLossyConfig(target_bpp=4.0 if kind == "bf16" else 5.0)
+
+    def dense_layer():
+        dense = torch.nn.Linear(1024, 768, bias=True, device="cuda", dtype=torch.bfloat16)
+        with torch.no_grad():
+            dense.weight.copy_((torch.randn(768, 1024, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
+        return dense
+
+    first, second = dense_layer(), dense_layer()
+    layer = cls.from_linear(first, config=config)
+    x = torch.randn(48, 1024, generator=g, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        outputs = [layer(x) for _ in range(4)]
+        assert layer.__dict__.get("_prepared") is not None          # the last calls went through it
+        assert all(torch.equal(outputs[0], later) for later in outputs[1:])
+        assert _relative(outputs[0], first(x)) < 0.08
+        state = copy.deepcopy(layer.state_dict())
+        twin = copy.deepcopy(layer)
+        assert torch.equal(twin(x), outputs[0])
+        layer.compress_weight(second.weight.data)
+        replaced = [layer(x) for _ in range(4)]
+        assert all(torch.equal(replaced[0], later) for later in replaced[1:])
+        assert not torch.equal(replaced[0], outputs[0]) and _relative(replaced[0], F.linear(x, second.weight, first.bias)) < 0.08
+        layer.load_state_dict(state)
+        assert all(torch.equal(layer(x), outputs[0]) for _ in range(4))
+        assert torch.equal(twin(x), outputs[0])
