@@ -523,10 +523,18 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       seen_cosets |= coset;
       coset = min(coset, 1u);      // a corrupt coset table must not steer the look-ups past the 17 tables
       const uint32_t coset_at = coset << prob_bits;
-      uint32_t symbol[8];
+      // each value is reconstructed right behind the step that decoded it, in the shadow of the next step's chain
+      // (table read, vote, ring read), instead of all eight after the last step
+      const int4 low = *reinterpret_cast<const int4*>(&field_min[coset][0]);
+      const int4 high = *reinterpret_cast<const int4*>(&field_min[coset][4]);
+      const int lows[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
+      const float half = coset ? 0.5f : 0.0f;
+      int value[8];
+      float v[8];
 #pragma unroll
       for (int field = 0; field < 8; ++field) {
-        symbol[field] = step((1 + 2 * field) * table_size, coset_at, valid);
+        value[field] = static_cast<int>(step((1 + 2 * field) * table_size, coset_at, valid)) + lows[field];
+        if (field < 7) v[field] = __fmul_rn(__fadd_rn(static_cast<float>(value[field]), half), scale);
         // upkeep every kStepsPerUpkeep steps at most: after fields 3 and 7 (five and four steps), or 1, 4 and 7
         if (Ring::kStepsPerUpkeep >= 8 ? (field == 3 || field == 7) : (field == 1 || field == 4 || field == 7)) upkeep();
       }
@@ -534,19 +542,11 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       // branch for the warp below, whose other side is for no real tensor
       const bool tame = __all_sync(0xFFFFFFFFu, scale < 1.0e33f);
       if (valid) {
-        const int4 low = *reinterpret_cast<const int4*>(&field_min[coset][0]);
-        const int4 high = *reinterpret_cast<const int4*>(&field_min[coset][4]);
-        int value[8] = {static_cast<int>(symbol[0]) + low.x,  static_cast<int>(symbol[1]) + low.y,  static_cast<int>(symbol[2]) + low.z,
-                        static_cast<int>(symbol[3]) + low.w,  static_cast<int>(symbol[4]) + high.x, static_cast<int>(symbol[5]) + high.y,
-                        static_cast<int>(symbol[6]) + high.z, static_cast<int>(symbol[7]) + high.w};
         // z7 = 2 m + (z0 + ... + z6 mod 2); the parity of a sum is the exclusive-or of the low bits
         const int parity = (value[0] ^ value[1] ^ value[2]) ^ (value[3] ^ value[4] ^ value[5]) ^ value[6];
         value[7] = 2 * value[7] + (parity & 1);
         const int64_t vector = tile_begin + offset + lane;
-        const float half = coset ? 0.5f : 0.0f;
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __fmul_rn(__fadd_rn(static_cast<float>(value[j]), half), scale);
+        v[7] = __fmul_rn(__fadd_rn(static_cast<float>(value[7]), half), scale);
         if (MODE == kModeProduct) {
           if (row != running_row) {
             flush_products();
