@@ -38,10 +38,14 @@ namespace {
 // m16n8k16 tensor-core instructions. The instruction's k index is only a summation index, so "thread t
 // holds k = 8t .. 8t+7" is as good as the canonical fragment order as long as A and B agree. The eight
 // partial tiles meet in shared memory at the end. Nothing is staged, every load of a thread is independent
-// of the others, and the loop is unrolled so that a dozen 16-byte loads per thread are in flight.
+// of the others, and the loop is unrolled so that half a dozen 16-byte loads per thread are in flight.
 constexpr int kStreamThreads = 256;
 constexpr int kStreamWarps = kStreamThreads / 32;
 constexpr int kStreamMaxM = 16;
+// Four blocks to an SM hold a 3840-feature layer's 480 blocks in one wave and leave the compiler 64 registers: told so, it
+// keeps more loads in flight than with the 40 it takes unprompted (16.4 -> 14.3 us at 3840 x 3840); eight-fold
+// unrolling at 80 or more registers runs in two waves and takes 22 us or more.
+constexpr int kStreamBlocksPerSm = 4;
 
 __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -50,7 +54,7 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
 
 // MTILES 16-row tiles of activations (M <= 16 * MTILES)
 template <int MTILES>
-__global__ void __launch_bounds__(kStreamThreads) linear_stream_kernel(const __nv_bfloat16* __restrict__ x,
+__global__ void __launch_bounds__(kStreamThreads, kStreamBlocksPerSm) linear_stream_kernel(const __nv_bfloat16* __restrict__ x,
                                                                        const __nv_bfloat16* __restrict__ w,
                                                                        const __nv_bfloat16* __restrict__ bias,
                                                                        __nv_bfloat16* __restrict__ y, int m, int n, int k) {
@@ -67,7 +71,7 @@ __global__ void __launch_bounds__(kStreamThreads) linear_stream_kernel(const __n
   for (int t = 0; t < MTILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
 
   const int slices = (k + 31) / 32;
-#pragma unroll 4
+#pragma unroll 2
   for (int slice = warp; slice < slices; slice += kStreamWarps) {
     const int at = slice * 32 + quad * 8;                 // first k of this thread's 16 bytes
     const bool inside = at < k;                           // k is a multiple of 8: a 16-byte piece is in or out as a whole
