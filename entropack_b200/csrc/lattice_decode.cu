@@ -72,6 +72,7 @@ struct LatticeDecodeParams {
 constexpr int kModeStore = 0;       // any container dtype (store_kind)
 constexpr int kModeStoreBf16 = 1;   // bf16, one 16-byte store
 constexpr int kModeProduct = 2;     // nothing is stored: the vector is multiplied into up to kMaxTokens dot products
+constexpr int kModeStoreCodes = 4;  // e4m3 or int8 codes (the 8-bit layers' weights), one 8-byte store
 constexpr int kModeExport = 3;      // no decoding: the block builds the slot tables and writes them to global memory
 constexpr int kMaxTokens = 4;    // instantiated for 1, 2 and 4 tokens: every token costs its instructions whether used or not
 
@@ -583,6 +584,28 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
           } else {
             store_vector(p.output, vector, v, EP_STORE_BF16);
           }
+        } else if (MODE == kModeStoreCodes) {
+          // finite values (see `tame`): the saturating conversions give what clamping first and converting then gives
+          if (tame) {
+            uint2 packed;
+            if (p.store_kind == EP_STORE_F8_E4M3) {
+              const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t b = __nv_cvt_float2_to_fp8x2(make_float2(v[2], v[3]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t c = __nv_cvt_float2_to_fp8x2(make_float2(v[4], v[5]), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t d = __nv_cvt_float2_to_fp8x2(make_float2(v[6], v[7]), __NV_SATFINITE, __NV_E4M3);
+              packed = make_uint2(a | (b << 16), c | (d << 16));
+            } else {
+              // round to nearest even and saturate to [-128, 127] in one conversion each, low bytes gathered pairwise
+              uint32_t code[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(code[j]) : "f"(v[j]));
+              packed.x = __byte_perm(__byte_perm(code[0], code[1], 0x0040), __byte_perm(code[2], code[3], 0x0040), 0x5410);
+              packed.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
+            }
+            *reinterpret_cast<uint2*>(static_cast<char*>(p.output) + vector * 8) = packed;
+          } else {
+            store_vector(p.output, vector, v, p.store_kind);
+          }
         } else {
           store_vector(p.output, vector, v, p.store_kind);
         }
@@ -710,6 +733,7 @@ int launch_for_mode(Launch&& launch, size_t shared, bool product, int tokens, in
                        : launch(lattice_decode_kernel<TABLES, kModeProduct, 4, PB>, shared);
   }
   if (store_kind == EP_STORE_BF16) return launch(lattice_decode_kernel<TABLES, kModeStoreBf16, 0, PB>, shared);
+  if (store_kind == EP_STORE_F8_E4M3 || store_kind == EP_STORE_I8) return launch(lattice_decode_kernel<TABLES, kModeStoreCodes, 0, PB>, shared);
   return launch(lattice_decode_kernel<TABLES, kModeStore, 0, PB>, shared);
 }
 

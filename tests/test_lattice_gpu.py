@@ -83,6 +83,21 @@ def test_every_container_cast_matches_oracle(oracle_module, dtype):
         assert bool((expected.cpu().double() if dtype.is_floating_point else expected.cpu().to(torch.float64)).max() >= float(top) * 0.999)
 
 
+@pytest.mark.parametrize("scale", [1.0, 0.25, 0.0])
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float8_e4m3fn, torch.bfloat16], ids=lambda d: str(d).removeprefix("torch."))
+def test_code_stores_round_ties_like_the_oracle(oracle_module, dtype, scale):
+    """Row scales of exactly 1 and 1/4 put the half-integer lattice points (coset 1) on rounding ties of the integer
+    and e4m3 grids; the one-instruction saturating conversions of the 8-bit code stores must break them to even as
+    the reference's rint-then-clamp does. A zero scale decodes to zeros."""
+    record = load_golden("lattice_bf16_6p0_outliers")
+    buffers = buffers_of(record)
+    buffers["scales"] = np.full_like(buffers["scales"], np.float32(scale))
+    shape = tuple(int(v) for v in record["shape"])
+    expected = oracle_module.lattice_decode(buffers, shape, dtype)
+    decoded = _gpu_decode(buffers, shape, dtype)
+    assert _bytes(decoded) == _bytes(expected)
+
+
 @pytest.mark.parametrize("name", golden_names("lattice_"))
 def test_encode_matches_oracle_bit_for_bit(oracle_module, name):
     """Same input -> the GPU encoder and the CPU oracle produce identical containers (every buffer)."""
