@@ -89,6 +89,14 @@ __device__ __forceinline__ uint32_t bf16_bits(float v) {
   return static_cast<uint32_t>(__bfloat16_as_ushort(h));
 }
 
+// Two values as a pair of bf16, the first in the low half: round to nearest even, anything beyond the largest finite
+// bf16 (infinities included) becomes that value with its sign.
+__device__ __forceinline__ uint32_t bf16x2_saturating(float low, float high) {
+  uint32_t pair;
+  asm("cvt.rn.satfinite.bf16x2.f32 %0, %1, %2;" : "=r"(pair) : "f"(high), "f"(low));
+  return pair;
+}
+
 // Writes the eight reconstructed values of vector `vector` as `kind` elements.
 __device__ __forceinline__ void store_vector(void* output, int64_t vector, const float* v, int kind) {
   char* const base = static_cast<char*>(output);
@@ -539,9 +547,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
         // upkeep every kStepsPerUpkeep steps at most: after fields 3 and 7 (five and four steps), or 1, 4 and 7
         if (Ring::kStepsPerUpkeep >= 8 ? (field == 3 || field == 7) : (field == 1 || field == 4 || field == 7)) upkeep();
       }
-      // voted here, where every thread of the warp still is (a partial group's idle threads skip what follows): one
-      // branch for the warp below, whose other side is for no real tensor
-      const bool tame = __all_sync(0xFFFFFFFFu, scale < 1.0e33f);
       if (valid) {
         // z7 = 2 m + (z0 + ... + z6 mod 2); the parity of a sum is the exclusive-or of the low bits
         const int parity = (value[0] ^ value[1] ^ value[2]) ^ (value[3] ^ value[4] ^ value[5]) ^ value[6];
@@ -571,22 +576,17 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
             }
           }
         } else if (MODE == kModeStoreBf16) {
-          // |z + c/2| < 2^15.5, so the product can only leave the bf16 range when the scale is astronomically large
-          if (tame) {
-            uint4 packed;
-            const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
-            const __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
-            packed.x = *reinterpret_cast<const uint32_t*>(&a);
-            packed.y = *reinterpret_cast<const uint32_t*>(&b);
-            packed.z = *reinterpret_cast<const uint32_t*>(&c);
-            packed.w = *reinterpret_cast<const uint32_t*>(&d);
-            *reinterpret_cast<uint4*>(static_cast<char*>(p.output) + vector * 16) = packed;
-          } else {
-            store_vector(p.output, vector, v, EP_STORE_BF16);
-          }
+          // the container cast clamps to the largest finite bf16 before it rounds; the saturating conversion does both
+          // (and keeps a NaN a NaN, as the reference's clamp does), so no value needs a second look
+          uint4 packed;
+          packed.x = bf16x2_saturating(v[0], v[1]);
+          packed.y = bf16x2_saturating(v[2], v[3]);
+          packed.z = bf16x2_saturating(v[4], v[5]);
+          packed.w = bf16x2_saturating(v[6], v[7]);
+          *reinterpret_cast<uint4*>(static_cast<char*>(p.output) + vector * 16) = packed;
         } else if (MODE == kModeStoreCodes) {
-          // finite values (see `tame`): the saturating conversions give what clamping first and converting then gives
-          if (tame) {
+          // the saturating conversions give what clamping first and converting then gives
+          {
             uint2 packed;
             if (p.store_kind == EP_STORE_F8_E4M3) {
               const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(v[0], v[1]), __NV_SATFINITE, __NV_E4M3);
@@ -603,8 +603,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
               packed.y = __byte_perm(__byte_perm(code[4], code[5], 0x0040), __byte_perm(code[6], code[7], 0x0040), 0x5410);
             }
             *reinterpret_cast<uint2*>(static_cast<char*>(p.output) + vector * 8) = packed;
-          } else {
-            store_vector(p.output, vector, v, p.store_kind);
           }
         } else {
           store_vector(p.output, vector, v, p.store_kind);
