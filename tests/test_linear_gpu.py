@@ -317,3 +317,31 @@ def test_prepared_decode_follows_the_layers_container(kind):
         layer.load_state_dict(state)
         assert all(torch.equal(layer(x), outputs[0]) for _ in range(4))
         assert torch.equal(twin(x), outputs[0])
+
+
+def test_fp8_layer_with_activations_quantised_beside_the_decode_captures_into_a_graph():
+    """From 1024 tokens on the 8-bit layers quantise their activations on a second stream while the weight codes are
+    decoded. Captured into a CUDA graph the second stream must fork from and join the capturing one: the replay gives
+    the eager call's bytes."""
+    import entropack_b200 as ep
+
+    g = torch.Generator(device="cuda").manual_seed(17)
+    dense = torch.nn.Linear(1024, 768, bias=True, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        dense.weight.copy_((torch.randn(768, 1024, generator=g, device="cuda") * 0.02).to(torch.bfloat16))
+    layer = ep.CompressedFP8Linear.from_linear(dense, config=ep.EntroPackLossyConfig(target_bpp=5.0))
+    x = torch.randn(1536, 1024, generator=g, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        eager = [layer(x) for _ in range(3)][-1]          # the container's decode plan and prepared decode exist now
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                captured = layer(x)
+        torch.cuda.current_stream().wait_stream(stream)
+        captured.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+    assert torch.equal(captured, eager)
+    ep.check_kernel_errors()
