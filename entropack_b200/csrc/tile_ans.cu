@@ -15,7 +15,6 @@
 #include <type_traits>
 
 #include "ep_common.cuh"
-#include <cstdlib>
 #include "rans_ring.cuh"
 
 namespace ep {
