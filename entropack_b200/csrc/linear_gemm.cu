@@ -18,7 +18,6 @@
 #include <cuda_fp8.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 #include "ep_common.cuh"
