@@ -482,8 +482,9 @@ __global__ void __launch_bounds__(kDecodeThreads, 1) lattice_decode_kernel(const
       return symbol;
     };
     auto upkeep = [&]() {
-      // at most once where the stream is intact; the test is the same in every thread, and the vote tells the compiler so
-      while (__any_sync(0xFFFFFFFFu, cursor <= refill_at)) {
+      // needed at most once where the stream is intact (a corrupt one reads stale ring words, inside the ring, and is
+      // reported at the tile's end); the test is the same in every thread, and the vote tells the compiler so
+      if (__any_sync(0xFFFFFFFFu, cursor <= refill_at)) {
         refill_at -= 2 * Ring::kChunk;
         chunk -= 1;
         ring_wait_all();
