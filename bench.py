@@ -228,7 +228,7 @@ def run_only(args) -> None:
                 cols, args.inner, None, _native.stream_handle(device)), "8-bit linear forward"))
         report.update(operand=args.operand, inner=args.inner, us=times)
     elif args.only == "layer_forward":
-        # CompressedLinear.forward (decode + product, or the fused kernel up to 4 tokens): rows = tokens, cols = out features
+        # CompressedLinear.forward (decode + product, or the fused kernel for one token on a large layer): rows = tokens, cols = out features
         dense = torch.nn.Linear(args.inner, cols, bias=False, device=device, dtype=torch.bfloat16)
         with torch.no_grad():
             dense.weight.copy_(make_case("bf16", cols, args.inner, device))
@@ -890,8 +890,8 @@ def measure_others(ep, device, flush, reps: int) -> dict:
             found_ready = ahead.decoded_ahead
         results[name] = {"forward_us_per_layer": plain_us, "decode_ahead_forward_us_per_layer": ahead_us,
                          "weights_found_decoded": found_ready, "same_output": bool(torch.equal(plain_out, ahead_out))}
-        # one token through the same ring: plain = the fused decode-and-multiply kernel; decode-ahead = the next layer's
-        # weight decoded to memory while the streaming product of the current one runs on the same SMs
+        # one token through the same ring: plain = decode, then the streaming product; decode-ahead = the next layer's
+        # weight decoded while the streaming product of the current one runs on the same SMs
         one = x[:1].contiguous()
 
         def ring_pass_one(calls=16):

@@ -137,6 +137,14 @@ class CompressedLinear(torch.nn.Linear):
 
     state_buffer_names: ClassVar[tuple[str, ...]] = ()
     state_buffer_dtypes: ClassVar[dict[str, torch.dtype]] = {}
+    #: When ``forward`` multiplies inside the decode kernel (``_fused_forward``: no dense weight is ever written) instead
+    #: of decoding and then multiplying: up to this many tokens and from this many weights on. The fused kernel's steps
+    #: carry the product's instructions, so it only wins where the dense weight it avoids would leave L2 on its way to
+    #: the product -- measured at 4 bpp: 87 against 91 us for one token on 3840 -> 10240 and 83 against 89 us on
+    #: 10240 -> 3840, but 69 against 62 us on 3840 x 3840 and 83 against 65 us there at four tokens. A caller that wants
+    #: the weight never materialised sets ``fused_max_tokens = 4`` and ``fused_min_weights = 0`` on the layer or the class.
+    fused_max_tokens: ClassVar[int] = 1
+    fused_min_weights: ClassVar[int] = 32 << 20
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, config=None,
                  device: str | torch.device | None = None, dtype: torch.dtype = torch.bfloat16):
@@ -284,9 +292,11 @@ class CompressedLinear(torch.nn.Linear):
             pipelined = ahead.forward(self, x)
             if pipelined is not None:
                 return pipelined
-        fused = self._fused_forward(x)
-        if fused is not None:
-            return fused
+        if (x.shape[-1] and x.numel() // x.shape[-1] <= self.fused_max_tokens
+                and self.in_features * self.out_features >= self.fused_min_weights):
+            fused = self._fused_forward(x)
+            if fused is not None:
+                return fused
         weight = self._decoded_for_product(x.device, self.weight.dtype)
         bias = self._bias_on(x.device)
         if _native_gemm_applies(x, weight, bias):
@@ -295,7 +305,8 @@ class CompressedLinear(torch.nn.Linear):
 
     def _fused_forward(self, x: torch.Tensor) -> torch.Tensor | None:
         """At decode-time batch sizes (up to 4 tokens) a lossy-coded bf16 weight is multiplied while it is being
-        decoded, without ever being written out; None when that path does not apply."""
+        decoded, without ever being written out; None when that path does not apply. ``forward`` takes it where it is
+        the faster one (``fused_max_tokens``, ``fused_min_weights``)."""
         container = self.weight
         if (type(self) is not CompressedLinear or not isinstance(container, CompressedTensor) or container.compress_method != "lattice_rans"
                 or container.encoded_dtype != torch.bfloat16 or container.dtype != torch.bfloat16 or x.dtype != torch.bfloat16

@@ -113,7 +113,7 @@ def test_decode_ahead_gives_the_layers_own_outputs():
                     assert torch.equal(got, want)
             assert ahead.decoded_ahead >= 15        # every pass: layers 1, 2, 5, 6 and 7; the later ones: layer 0 as well
             # a few tokens: the product's blocks share the SMs with the next layer's decode; eight tokens take the same
-            # kernels with and without (bit-equal), two would take the fused kernel without (equal to rounding)
+            # kernels with and without (bit-equal), and so do two (layers of this size no longer take the fused kernel)
             h8, h2 = x[:8], x[:2]
             for index in range(3):
                 h8, h2 = layers[index](h8), layers[index](h2)
@@ -267,10 +267,13 @@ def test_fused_small_batch_forward_matches_product_with_decoded_weight(tokens, f
     x = x[:1] if tokens % 2 else x        # [1, tokens, K] or [2, tokens / 2, K]: leading dimensions are flattened
     weight = layer.dequantize()
     expected = torch.nn.functional.linear(x.float(), weight.float(), None if not bias else dense.bias.float())
-    assert layer._fused_forward(x) is not None
-    out = layer(x)
-    assert out.shape == expected.shape and out.dtype == torch.bfloat16
-    assert float((out.float() - expected).abs().max() / expected.abs().max()) <= 2.0 ** -7
+    # the kernel itself, then the layer's own choice (a layer this small decodes and multiplies in turn), then the layer
+    # told to multiply while it decodes whatever its size
+    for out in (layer._fused_forward(x), layer(x)):
+        assert out is not None and out.shape == expected.shape and out.dtype == torch.bfloat16
+        assert float((out.float() - expected).abs().max() / expected.abs().max()) <= 2.0 ** -7
+    layer.fused_max_tokens, layer.fused_min_weights = 4, 0
+    assert torch.equal(layer(x), layer._fused_forward(x))
     # the error word stays clear and five tokens take the two-kernel path
     error = torch.zeros(1, dtype=torch.int32, device="cuda")
     lane = layer.weight.scheme.lane()
