@@ -271,3 +271,25 @@ def test_decode_ahead_registration_rules():
     assert second._decode_ahead is None
     x = torch.randn(3, 8)
     assert torch.equal(first(x), torch.nn.functional.linear(x, first.weight, first.bias))
+
+
+def test_forward_asks_for_the_fused_kernel_only_where_it_pays(monkeypatch):
+    """The layer multiplies inside the decode kernel for one token on a large layer, and decodes and multiplies in turn
+    otherwise; the two thresholds are plain attributes a caller may change. (The kernels themselves need a GPU: here
+    the decode is replaced by a dense weight and the fused kernel by a recorder.)"""
+    import entropack_b200 as ep
+
+    layer = ep.CompressedLinear(64, 48, bias=False, config=ep.EntroPackLossyConfig(target_bpp=4.0), device="cpu")
+    dense = torch.randn(48, 64).to(torch.bfloat16)
+    asked = []
+    monkeypatch.setattr(layer, "_decoded_for_product", lambda device, dtype: dense)
+    monkeypatch.setattr(layer, "_fused_forward", lambda x: asked.append(tuple(x.shape)) or None)
+    one, four = torch.randn(1, 64).to(torch.bfloat16), torch.randn(2, 2, 64).to(torch.bfloat16)
+    assert (type(layer).fused_max_tokens, type(layer).fused_min_weights) == (1, 32 << 20)
+    assert torch.equal(layer(one), torch.nn.functional.linear(one, dense)) and asked == []      # a small layer: never
+    layer.fused_min_weights = 64 * 48
+    layer(one), layer(four)
+    assert asked == [(1, 64)]                                                                    # large enough: one token only
+    layer.fused_max_tokens = 4
+    layer(four)
+    assert asked == [(1, 64), (2, 2, 64)]
