@@ -87,11 +87,13 @@ def test_every_container_cast_matches_oracle(oracle_module, dtype):
 
 @pytest.mark.parametrize("scale", [1.0, 0.25, 0.0])
 @pytest.mark.parametrize("dtype", [torch.int8, torch.float8_e4m3fn, torch.bfloat16], ids=lambda d: str(d).removeprefix("torch."))
-def test_code_stores_round_ties_like_the_oracle(oracle_module, dtype, scale):
+@pytest.mark.parametrize("name", ["lattice_bf16_6p0_outliers", "lattice_bf16_9p0_pb12", "lattice_bf16_10p5_wide"])
+def test_code_stores_round_ties_like_the_oracle(oracle_module, name, dtype, scale):
     """Row scales of exactly 1 and 1/4 put the half-integer lattice points (coset 1) on rounding ties of the integer
     and e4m3 grids; the one-instruction saturating conversions of the 8-bit code stores must break them to even as
-    the reference's rint-then-clamp does. A zero scale decodes to zeros."""
-    record = load_golden("lattice_bf16_6p0_outliers")
+    the reference's rint-then-clamp does. A zero scale decodes to zeros. Three bitstreams: tables in shared memory,
+    and the two kinds of 12-bit tables that stay in global memory (alphabets of 51 and of 613 symbols)."""
+    record = load_golden(name)
     buffers = buffers_of(record)
     buffers["scales"] = np.full_like(buffers["scales"], np.float32(scale))
     shape = tuple(int(v) for v in record["shape"])
