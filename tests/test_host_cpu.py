@@ -293,3 +293,20 @@ def test_forward_asks_for_the_fused_kernel_only_where_it_pays(monkeypatch):
     layer.fused_max_tokens = 4
     layer(four)
     assert asked == [(1, 64), (2, 2, 64)]
+
+
+def test_transfer_order_keeps_both_directions_busy():
+    """Containers that upload faster than they download go first, smallest upload first; the rest follow, largest
+    download first (Johnson's rule for upload -> download); without a download the given order stands."""
+    from types import SimpleNamespace
+
+    from entropack_b200.compression.pipeline import _transfer_order
+
+    def container(upload_bytes, elements, element_size):
+        return SimpleNamespace(entropack_quant_state=torch.empty(upload_bytes, dtype=torch.uint8),
+                               numel=lambda: elements, element_size=lambda: element_size)
+
+    # uploads / downloads in bytes: 0: 60/64, 1: 30/32, 2: 200/128 (uploads more than it downloads), 3: 300/256, 4: 10/64
+    items = [container(60, 64, 1), container(30, 16, 2), container(200, 32, 4), container(300, 128, 2), container(10, 64, 1)]
+    assert _transfer_order(items, with_download=True) == [4, 1, 0, 3, 2]
+    assert _transfer_order(items, with_download=False) == [0, 1, 2, 3, 4]
