@@ -51,56 +51,65 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// MTILES 16-row tiles of activations (M <= 16 * MTILES)
-template <int MTILES>
-__global__ void __launch_bounds__(kStreamThreads, kStreamBlocksPerSm) linear_stream_kernel(const __nv_bfloat16* __restrict__ x,
-                                                                       const __nv_bfloat16* __restrict__ w,
-                                                                       const __nv_bfloat16* __restrict__ bias,
-                                                                       __nv_bfloat16* __restrict__ y, int m, int n, int k) {
-  __shared__ float partial[kStreamWarps][MTILES][4][32];
+// GROUPS sets of eight output features per block: a warp multiplies the activation fragments it has loaded with
+// GROUPS weight fragments, so a wide layer (10240 features: 1280 sets) still runs as one wave of blocks -- 427 blocks of
+// three sets instead of 1280 of one, which would take more than two -- and reads the activations a third as often.
+template <int GROUPS>
+__global__ void __launch_bounds__(kStreamThreads, GROUPS == 1 ? kStreamBlocksPerSm : kStreamBlocksPerSm - 1)
+linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
+                     __nv_bfloat16* __restrict__ y, int m, int n, int k) {
+  __shared__ float partial[kStreamWarps][GROUPS][4][32];
   const uint32_t lane = lane_id();
   const int warp = threadIdx.x >> 5;
-  const int group = lane >> 2;      // feature within the block's eight / activation row within a tile
+  const int group = lane >> 2;      // feature within a set of eight / activation row
   const int quad = lane & 3;        // which 8 of the slice's 32 k
-  const int feature = blockIdx.x * 8 + group;
+  const int first = blockIdx.x * 8 * GROUPS;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  const uint4* w_row = reinterpret_cast<const uint4*>(w + static_cast<int64_t>(min(feature, n - 1)) * k);
-  float acc[MTILES][4];
+  const uint4* w_row[GROUPS];
+  bool real[GROUPS];
+  float acc[GROUPS][4];
 #pragma unroll
-  for (int t = 0; t < MTILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+  for (int g = 0; g < GROUPS; ++g) {
+    const int feature = first + 8 * g + group;
+    real[g] = feature < n;
+    w_row[g] = reinterpret_cast<const uint4*>(w + static_cast<int64_t>(min(feature, n - 1)) * k);
+    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+  }
+  const int upper = group, lower = group + 8;
 
   const int slices = (k + 31) / 32;
 #pragma unroll 2
   for (int slice = warp; slice < slices; slice += kStreamWarps) {
     const int at = slice * 32 + quad * 8;                 // first k of this thread's 16 bytes
     const bool inside = at < k;                           // k is a multiple of 8: a 16-byte piece is in or out as a whole
-    const uint4 b = inside && feature < n ? __ldg(w_row + (at >> 3)) : zero;
+    uint4 b[GROUPS];
 #pragma unroll
-    for (int t = 0; t < MTILES; ++t) {
-      const int upper = t * 16 + group, lower = upper + 8;
-      const uint4 au = inside && upper < m ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(upper) * k + at)) : zero;
-      const uint4 al = inside && lower < m ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(lower) * k + at)) : zero;
-      mma_m16n8k16(acc[t], au.x, al.x, au.y, al.y, b.x, b.y);
-      mma_m16n8k16(acc[t], au.z, al.z, au.w, al.w, b.z, b.w);
+    for (int g = 0; g < GROUPS; ++g) b[g] = inside && real[g] ? __ldg(w_row[g] + (at >> 3)) : zero;
+    const uint4 au = inside && upper < m ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(upper) * k + at)) : zero;
+    const uint4 al = inside && lower < m ? __ldg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(lower) * k + at)) : zero;
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+      mma_m16n8k16(acc[g], au.x, al.x, au.y, al.y, b[g].x, b[g].y);
+      mma_m16n8k16(acc[g], au.z, al.z, au.w, al.w, b[g].z, b[g].w);
     }
   }
 #pragma unroll
-  for (int t = 0; t < MTILES; ++t) {
+  for (int g = 0; g < GROUPS; ++g) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) partial[warp][t][j][lane] = acc[t][j];
+    for (int j = 0; j < 4; ++j) partial[warp][g][j][lane] = acc[g][j];
   }
   __syncthreads();
   // accumulator fragment: c0, c1 = (row group, columns 2 quad, 2 quad + 1), c2, c3 = the same columns of row group + 8
-  for (int item = threadIdx.x; item < MTILES * 4 * 32; item += kStreamThreads) {
-    const int t = item / 128, j = (item >> 5) & 3, holder = item & 31;
+  for (int item = threadIdx.x; item < GROUPS * 4 * 32; item += kStreamThreads) {
+    const int g = item / 128, j = (item >> 5) & 3, holder = item & 31;
     float total = 0.0f;
 #pragma unroll
-    for (int v = 0; v < kStreamWarps; ++v) total += partial[v][t][j][holder];
-    const int row = t * 16 + (holder >> 2) + (j >= 2 ? 8 : 0);
-    const int column = blockIdx.x * 8 + (holder & 3) * 2 + (j & 1);
+    for (int v = 0; v < kStreamWarps; ++v) total += partial[v][g][j][holder];
+    const int row = (holder >> 2) + (j >= 2 ? 8 : 0);
+    const int column = first + 8 * g + (holder & 3) * 2 + (j & 1);
     if (row < m && column < n) {
-      const float b = bias ? __bfloat162float(bias[column]) : 0.0f;
-      y[static_cast<int64_t>(row) * n + column] = __float2bfloat16_rn(total + b);
+      const float bias_value = bias ? __bfloat162float(bias[column]) : 0.0f;
+      y[static_cast<int64_t>(row) * n + column] = __float2bfloat16_rn(total + bias_value);
     }
   }
 }
@@ -1018,10 +1027,21 @@ bool make_tile_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k, 
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MTILES>
+// Sets of eight features per block: as few as keep the whole layer in one wave of resident blocks (four blocks an SM
+// with one set, three with more), four at most.
 int launch_stream(const __nv_bfloat16* x, const __nv_bfloat16* w, const __nv_bfloat16* bias, __nv_bfloat16* y, int m, int n, int k,
                   cudaStream_t s) {
-  linear_stream_kernel<MTILES><<<(n + 7) / 8, kStreamThreads, 0, s>>>(x, w, bias, y, m, n, k);
+  const int sets = (n + 7) / 8;
+  const auto blocks = [sets](int per_block) { return static_cast<unsigned>((sets + per_block - 1) / per_block); };
+  if (sets <= kStreamBlocksPerSm * kSmCount) {
+    linear_stream_kernel<1><<<blocks(1), kStreamThreads, 0, s>>>(x, w, bias, y, m, n, k);
+  } else if (blocks(2) <= static_cast<unsigned>((kStreamBlocksPerSm - 1) * kSmCount)) {
+    linear_stream_kernel<2><<<blocks(2), kStreamThreads, 0, s>>>(x, w, bias, y, m, n, k);
+  } else if (blocks(3) <= static_cast<unsigned>((kStreamBlocksPerSm - 1) * kSmCount)) {
+    linear_stream_kernel<3><<<blocks(3), kStreamThreads, 0, s>>>(x, w, bias, y, m, n, k);
+  } else {
+    linear_stream_kernel<4><<<blocks(4), kStreamThreads, 0, s>>>(x, w, bias, y, m, n, k);
+  }
   return check_launch("linear_stream_kernel");
 }
 
@@ -1205,7 +1225,7 @@ extern "C" int ep_linear_forward(const void* x_dev, const void* weight_dev, cons
   const auto* bias = static_cast<const __nv_bfloat16*>(bias_dev);
   auto* y = static_cast<__nv_bfloat16*>(y_dev);
   const int mi = static_cast<int>(m), ni = static_cast<int>(n), ki = static_cast<int>(k);
-  if (m <= kStreamMaxM) return launch_stream<1>(x, w, bias, y, mi, ni, ki, s);
+  if (m <= kStreamMaxM) return launch_stream(x, w, bias, y, mi, ni, ki, s);
   GemmParams p = {};
   p.bias = bias;
   p.y = y;

@@ -7,7 +7,8 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("m,n,k,bias", [
     (1, 512, 1024, True), (4, 384, 3840, False), (16, 1000, 264, True),          # few tokens: the streaming kernel,
-    (16, 3840, 3840, True), (3, 1001, 1000, False), (9, 3840, 10240, True),       # with ragged features and a ragged last slice
+    (16, 3840, 3840, True), (3, 1001, 1000, False), (9, 3840, 10240, True),       # with ragged features and a ragged last slice,
+    (16, 5000, 512, True), (16, 10240, 3840, False), (3, 10250, 264, True), (5, 11520, 264, False),   # 2, 3, 3 and 4 feature sets a block
     (17, 128, 64, False), (128, 128, 128, True), (256, 384, 1024, True),         # tensor-core kernel
     (300, 1000, 264, True), (130, 136, 3840, False), (1024, 3840, 3840, True),
     (4096, 3840, 3840, True), (1500, 10000, 1088, True), (2100, 4600, 1152, False),   # two-block tiles, whole and ragged
