@@ -84,7 +84,7 @@ def prepare_decode_plans(module: torch.nn.Module) -> int:
 
 def linear_forward(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                    error: torch.Tensor | None = None) -> torch.Tensor:
-    """``x @ weight.T + bias`` in bf16 through ``ep_linear_forward`` (CUDA-core kernel for up to 16 tokens,
+    """``x @ weight.T + bias`` in bf16 through ``ep_linear_forward`` (streaming mma.sync kernel for up to 16 tokens,
     tcgen05 tensor-core kernel above). ``error`` defaults to the device's shared error word (``check_kernel_errors``)."""
     flat = x.reshape(-1, x.shape[-1]).contiguous()
     weight = weight.contiguous()

@@ -1,4 +1,4 @@
-"""The library's bf16 GEMM (CUDA-core kernel for small M, tcgen05/TMEM kernel above) against an fp32 torch reference."""
+"""The library's bf16 GEMM (streaming mma.sync kernel for up to 16 rows, tcgen05/TMEM kernel above) against an fp32 torch reference."""
 import pytest
 import torch
 
