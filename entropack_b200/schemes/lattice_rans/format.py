@@ -74,8 +74,8 @@ class EntroPackLossyConfig(CompressionConfig):
 
         It pays while all of a layer's tiles still decode side by side: a B200 holds 3552 of them at once (24 warps on each
         of 148 SMs), that is layers of up to about 29 million weights at 8192 symbols a tile. Measured at 4 bpp, one token:
-        3840 x 3840 (14.7 M weights) 75 -> 51 us per forward; 3840 -> 10240 (39.3 M weights, 4800 half-length tiles, two
-        rounds) 91 -> 95 us, so larger layers keep the default."""
+        3840 x 3840 (14.7 M weights) 62 -> 46 us per forward; 3840 -> 10240 (39.3 M weights, 4800 half-length tiles, two
+        rounds) 87 -> 91 us, so larger layers keep the default."""
         fields.setdefault("tile_elements", cls.LOW_LATENCY_TILE_ELEMENTS)
         return cls(target_bpp=target_bpp, **fields)
 

@@ -310,3 +310,16 @@ def test_transfer_order_keeps_both_directions_busy():
     items = [container(60, 64, 1), container(30, 16, 2), container(200, 32, 4), container(300, 128, 2), container(10, 64, 1)]
     assert _transfer_order(items, with_download=True) == [4, 1, 0, 3, 2]
     assert _transfer_order(items, with_download=False) == [0, 1, 2, 3, 4]
+
+
+def test_low_latency_preset_is_an_ordinary_tile_setting():
+    """The preset only shortens the tiles (8192 symbols: 910 vectors, 257 chain steps instead of 513); every other field
+    keeps its default or the caller's value, and the tile rule for plain configs is the reference's."""
+    import entropack_b200 as ep
+    from entropack_b200.schemes.lattice_rans.format import recommended_tile_elements
+
+    preset, plain = ep.EntroPackLossyConfig.low_latency(4.0), ep.EntroPackLossyConfig(target_bpp=4.0)
+    assert preset.tile_elements == 8192 and preset.target_bpp == 4.0
+    assert {k: v for k, v in vars(preset).items() if k != "tile_elements"} == {k: v for k, v in vars(plain).items() if k != "tile_elements"}
+    assert ep.EntroPackLossyConfig.low_latency(3.5, tile_elements=4096, row_rdo_iterations=2).tile_elements == 4096
+    assert [recommended_tile_elements(b) for b in (1.5, 2.0, 2.3, 4.0, 4.5, 7.0, 7.5)] == [32768, 32768, 16384, 16384, 8192, 8192, 4096]
